@@ -1,0 +1,229 @@
+/*
+ * xabe_moe.h -- C ABI of the sm_100a MoE FFN kernel set (libxabe_moe_sm100.so).
+ *
+ * The reference project has no FFI layer on this path: xabe-engine calls Rust
+ * methods of `xabe_cuda::kernels::moe::MoeKernels` and of
+ * `xabe_engine::block::moe::MoeBlock`.  Each entry point below mirrors one of
+ * those methods one to one (cited by file:line, paths relative to the
+ * reference project root), so that a thin `extern "C"` shim in xabe-cuda can
+ * replace their bodies.
+ *
+ * Conventions
+ *  - Every pointer named `dev_*`, every `const float*`/`float*` argument of a
+ *    launch call and every buffer in `xabe_moe_buffer_view` is DEVICE memory
+ *    on the handle's device.  The caller owns weights, inputs and outputs;
+ *    the handle owns only scratch allocated once by xabe_moe_create.
+ *  - `stream` is a `cudaStream_t` passed as `void*`.  Launch calls only
+ *    enqueue: no synchronisation, no allocation, no host read-back, and every
+ *    grid is a function of the geometry alone.  The live token count lives in
+ *    a device scalar (crates/xabe-cuda/src/kernels/moe.rs:34-41).
+ *  - Quantized tensors stay in GGUF FILE layout: 210-byte Q6_K superblocks and
+ *    34-byte Q8_0 blocks, not re-strided (the reference pads Q6_K to 224 B in
+ *    `to_device_layout`, moe.rs:410-444; this library reads the raw bytes).
+ *    `dev_bytes` must be 16-byte aligned.
+ *  - Every call returns an `xabe_status`; on failure a thread-local message
+ *    is available from xabe_moe_last_error().  Shapes and formats are
+ *    validated before anything is launched (moe.rs:6729-6746).  Nothing
+ *    throws across the boundary.
+ *  - One handle per host thread (the reference takes `&mut self`).
+ *  - There is no CPU fallback: without a CUDA device every entry point that
+ *    needs one returns XABE_ERR_DRIVER.
+ */
+#ifndef XABE_MOE_H
+#define XABE_MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* MoeError / MoeBlockError variants (moe.rs:4602-4637, crates/xabe-engine/src/block/moe.rs:493-547) */
+typedef enum xabe_status {
+    XABE_OK = 0,
+    XABE_ERR_UNSUPPORTED_GEOMETRY = 1,   /* MoeError::UnsupportedGeometry */
+    XABE_ERR_RAGGED_WEIGHTS = 2,         /* MoeError::RaggedWeights */
+    XABE_ERR_WRONG_ELEMENT_COUNT = 3,    /* MoeError::WrongElementCount */
+    XABE_ERR_TOO_MANY_TOKENS = 4,        /* MoeError::TooManyTokens / MoeBlockError::TooManyTokens */
+    XABE_ERR_SHARED_ONLY_BUFFERS = 5,    /* MoeError::SharedOnlyBuffers */
+    XABE_ERR_DRIVER = 6,                 /* MoeError::Driver */
+    XABE_ERR_BUFFER_LENGTH = 7,          /* MoeBlockError::BufferLength */
+    XABE_ERR_UNSUPPORTED_EXPERT_TYPE = 8,/* MoeBlockError::UnsupportedExpertType */
+    XABE_ERR_UNSUPPORTED_DENSE_TYPE = 9, /* MoeBlockError::UnsupportedDenseType */
+    XABE_ERR_INVALID_ARGUMENT = 10,      /* null pointer, misaligned tensor */
+    XABE_ERR_DEVICE_STATUS = 11          /* a kernel recorded a bounded-wait timeout */
+} xabe_status;
+
+/* ExpertQuant::code (moe.rs:319-327) */
+#define XABE_QUANT_Q6_K 0
+#define XABE_QUANT_Q8_0 1
+
+/* BufferScope (moe.rs:4682-4694) */
+#define XABE_SCOPE_ROUTED 0
+#define XABE_SCOPE_SHARED_ONLY 1
+
+/* MoeGeometry (moe.rs:4523-4540) */
+typedef struct xabe_moe_geometry {
+    uint32_t num_experts;
+    uint32_t experts_per_token;
+    uint32_t hidden;
+    uint32_t intermediate;
+    uint32_t block_size;
+    uint32_t max_tokens;
+} xabe_moe_geometry;
+
+/* QuantTensor (moe.rs:448-464) */
+typedef struct xabe_quant_tensor {
+    const void* dev_bytes;
+    size_t n_bytes;
+    int32_t quant;
+} xabe_quant_tensor;
+
+/* MoeLayerWeights (crates/xabe-engine/src/block/moe.rs:634-658) */
+typedef struct xabe_moe_layer_weights {
+    const float* post_norm;          /* [hidden] */
+    const float* router;             /* [num_experts][hidden], expert row contiguous */
+    const float* router_bias;        /* [num_experts] added to the logits, or NULL.  Not in the reference
+                                        (Qwen3.6 has none); carries the benchmark's Zipf routing skew. */
+    xabe_quant_tensor gate_exps;     /* [num_experts][intermediate][hidden] */
+    xabe_quant_tensor up_exps;       /* [num_experts][intermediate][hidden] */
+    xabe_quant_tensor down_exps;     /* [num_experts][hidden][intermediate] */
+    const float* shared_gate_inp;    /* [hidden] */
+    xabe_quant_tensor shared_gate;   /* [intermediate][hidden] */
+    xabe_quant_tensor shared_up;     /* [intermediate][hidden] */
+    xabe_quant_tensor shared_down;   /* [hidden][intermediate] */
+} xabe_moe_layer_weights;
+
+/* MoeBuffers accessors (moe.rs:4713-4864) and the MoeBlock intermediates
+ * (crates/xabe-engine/src/block/moe.rs:1022-1060). */
+typedef struct xabe_moe_buffer_view {
+    const int32_t* valid_tokens;        /* device scalar */
+    const int32_t* topk_ids;            /* [max_tokens][k] */
+    const float* topk_weights;          /* [max_tokens][k] */
+    const int32_t* sorted_token_ids;    /* [sorted_capacity] */
+    const int32_t* expert_ids;          /* [expert_block_capacity] */
+    const int32_t* num_tokens_post_pad; /* device scalar */
+    const float* partial;               /* [max_tokens*k][hidden], weighted contributions */
+    const float* normed;                /* [max_tokens][hidden]  attn_post_norm */
+    const float* logits;                /* [max_tokens][num_experts] */
+    const float* routed;                /* [max_tokens][hidden]  ffn_moe_out */
+    const float* shexp;                 /* [max_tokens][hidden]  shared expert, ungated */
+    const float* gate;                  /* [max_tokens]          sigmoid gate */
+    uint64_t sorted_capacity;           /* MoeGeometry::sorted_capacity, moe.rs:4575-4584 */
+    uint64_t expert_block_capacity;     /* moe.rs:4587-4589 */
+} xabe_moe_buffer_view;
+
+typedef struct xabe_moe xabe_moe;
+
+/* Thread-local text of the last failure on this thread ("" if none). */
+const char* xabe_moe_last_error(void);
+
+/* ABI revision of this header. */
+int xabe_moe_abi_version(void);
+
+/* MoeGeometry::{sorted_capacity, expert_block_capacity} (moe.rs:4575-4589). Pure host. */
+uint64_t xabe_moe_sorted_capacity(const xabe_moe_geometry* g);
+uint64_t xabe_moe_expert_block_capacity(const xabe_moe_geometry* g);
+
+/* MoeKernels::new + MoeKernels::buffers + MoeBlock::new (moe.rs:5038-5111,
+ * 5362-5403; block/moe.rs:948-977).  Validates the geometry exactly as the
+ * reference does, then allocates every scratch buffer once.  `scope` is
+ * XABE_SCOPE_ROUTED or XABE_SCOPE_SHARED_ONLY (dense FFN: no routing tables).
+ * `eps` is the RMSNorm epsilon (block/moe.rs:179). */
+int xabe_moe_create(const xabe_moe_geometry* geometry, int device, int scope, float eps,
+                    xabe_moe** out);
+void xabe_moe_destroy(xabe_moe* m);
+
+/* MoeKernels::set_valid_tokens (moe.rs:5473-5491): publishes the live token
+ * count into the device scalar; a no-op when unchanged.  Call it before a
+ * stream capture, as MoeBlock::publish_tokens does (block/moe.rs:1074-1089). */
+int xabe_moe_set_valid_tokens(xabe_moe* m, void* stream, int tokens);
+
+/* LayerOpsKernels::rms_norm as the block calls it (layer_ops.rs:777,
+ * block/moe.rs:1121-1129): normed = x * (1/sqrt(mean(x^2)+eps)) * weight for
+ * the live rows.  Result lands in the handle's `normed` buffer (and a
+ * half-precision copy the expert kernels read). */
+int xabe_moe_rms_norm(xabe_moe* m, void* stream, const float* x, const float* weight);
+
+/* moe_block_router_logits (block/moe.rs:301-382): logits[t][e] =
+ * dot(router[e], normed[t]), summed in the order that kernel pins, so logits
+ * are bit-identical at every batch width.  Reads the handle's `normed`.
+ * `bias` ([num_experts], may be NULL) is added to each logit afterwards. */
+int xabe_moe_router_logits(xabe_moe* m, void* stream, const float* router, const float* bias);
+
+/* MoeKernels::route_and_dispatch (moe.rs:5498-5558): softmax over all experts,
+ * top-k (probability desc, index asc), renormalise over the selected k, then
+ * the block-aligned dispatch tables of moe_align_block_size.  `logits` is
+ * [max_tokens][num_experts]; pass NULL to use the handle's own logits. */
+int xabe_moe_route_and_dispatch(xabe_moe* m, void* stream, const float* logits);
+
+/* MoeKernels::grouped_forward_partial (moe.rs:5727-6188): routed experts over
+ * the current dispatch tables; leaves weight * expert_mlp in `partial`.
+ * `hidden_states` NULL = the handle's `normed`. */
+int xabe_moe_grouped_forward_partial(xabe_moe* m, void* stream, xabe_quant_tensor gate,
+                                     xabe_quant_tensor up, xabe_quant_tensor down,
+                                     const float* hidden_states);
+
+/* MoeKernels::grouped_forward (moe.rs:6345-6375): the above plus the
+ * ascending-k sum of moe_reduce (moe.rs:4049-4065) into `out`
+ * [max_tokens][hidden]. */
+int xabe_moe_grouped_forward(xabe_moe* m, void* stream, xabe_quant_tensor gate,
+                             xabe_quant_tensor up, xabe_quant_tensor down,
+                             const float* hidden_states, float* out);
+
+/* MoeKernels::shared_expert (moe.rs:6488-6727): expert_mlp of one expert for
+ * every live token, ungated.  `out` NULL = the handle's `shexp`. Also the
+ * dense FFN of the 27B sibling (block/dense_ffn.rs:9-16). */
+int xabe_moe_shared_expert(xabe_moe* m, void* stream, xabe_quant_tensor gate,
+                           xabe_quant_tensor up, xabe_quant_tensor down,
+                           const float* hidden_states, float* out);
+
+/* MoeBlock::forward (block/moe.rs:1091-1329): the whole block.  `residual`,
+ * `ffn_out`, `l_out` are [max_tokens][hidden] f32 device buffers whose element
+ * counts are checked like check_len (block/moe.rs:1107-1110).  Rows at and
+ * beyond `tokens` are never written. */
+int xabe_moe_block_forward(xabe_moe* m, void* stream, const xabe_moe_layer_weights* w,
+                           const float* residual, size_t residual_len, int tokens,
+                           float* ffn_out, size_t ffn_out_len, float* l_out, size_t l_out_len);
+
+/* The same call for a caller that holds HOST buffers: copies `tokens` rows of
+ * `host_residual` to the device, runs the block and copies `ffn_out`/`l_out`
+ * rows back, all on `stream`; returns after enqueueing (synchronise the
+ * stream before reading).  Host buffers should be pinned.  Either output may
+ * be NULL.  (The reference reaches this through `Forward`, which uploads the
+ * step's inputs itself: crates/xabe-engine/src/forward.rs:3534-3585.) */
+int xabe_moe_block_forward_host(xabe_moe* m, void* stream, const xabe_moe_layer_weights* w,
+                                const float* host_residual, int tokens, float* host_ffn_out,
+                                float* host_l_out);
+
+/* DenseFfnBlock::forward (block/dense_ffn.rs:1047): l_out = mlp(rmsnorm(x)) + x.
+ * The handle must have been created with geometry.hidden/intermediate of the
+ * dense model; XABE_SCOPE_SHARED_ONLY is enough. */
+int xabe_dense_ffn_block_forward(xabe_moe* m, void* stream, const float* post_norm,
+                                 xabe_quant_tensor gate, xabe_quant_tensor up,
+                                 xabe_quant_tensor down, const float* residual,
+                                 size_t residual_len, int tokens, float* ffn_out,
+                                 size_t ffn_out_len, float* l_out, size_t l_out_len);
+
+/* MoeBlock::buffers and the intermediate accessors (block/moe.rs:1022-1060). */
+int xabe_moe_buffers(xabe_moe* m, xabe_moe_buffer_view* out);
+
+/* MoeKernels::set_exact_decode_regime (moe.rs:5450): pin the routed experts to
+ * the decode-shaped kernels whatever the token width, so a row's floats land
+ * exactly where plain decode's would. */
+int xabe_moe_set_exact_decode_regime(xabe_moe* m, int on);
+
+/* Reads (and clears) the device status word the kernels' bounded waits write:
+ * 0 when every wait completed.  Synchronises `stream`. */
+int xabe_moe_device_status(xabe_moe* m, void* stream, int* status_out);
+
+/* Standalone dequantisation (crates/xabe-cuda/src/kernels/dequant.rs, gated
+ * bit-identical by crates/xabe-engine/tests/dequant_differential.rs:1-18):
+ * `out` receives n_bytes / block_bytes * block_elements floats. */
+int xabe_dequantize(void* stream, xabe_quant_tensor t, float* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* XABE_MOE_H */

@@ -1,0 +1,394 @@
+// Everything in the MoE block that is not an expert matrix product:
+// RMSNorm, router logits, softmax top-k routing, the block-aligned dispatch
+// tables, the gate-and-combine epilogue, and standalone dequantisation.
+//
+// RMSNorm, the router logits and the shared-gate dot product reproduce, sum
+// for sum, the reduction order of the reference's device kernels, because
+// their results pick experts: a last-bit change in a logit can run a
+// different expert (crates/xabe-engine/src/block/moe.rs:250-269).
+#pragma once
+
+#include "common.cuh"
+
+namespace xabe {
+
+// ---------------------------------------------------------------------------
+// RMSNorm.  Order of crates/xabe-cuda/src/kernels/layer_ops.rs:129-150 with
+// the block width of layer_ops.rs:1219-1221 (the launcher passes it): thread
+// tid sums x[j]^2 for j = tid, tid+blockDim, ... with fused multiply-add,
+// then block_reduce_sum; 1/sqrtf (not rsqrtf); x * inv_rms * w in that order.
+// Also writes a half-precision copy, the B operand of the expert kernels.
+// grid: (max_tokens); rows at and beyond *valid_tokens are skipped.
+// ---------------------------------------------------------------------------
+__global__ void k_rms_norm(const float* __restrict__ x, const float* __restrict__ weight,
+                           float* __restrict__ out, __half* __restrict__ out_h,
+                           const int* __restrict__ valid_tokens, int width, float eps) {
+    __shared__ float scratch[32];
+    int row = blockIdx.x;
+    if (row >= *valid_tokens) return;
+    size_t base = (size_t)row * width;
+    float partial = 0.0f;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+        float v = x[base + j];
+        partial = fmaf(v, v, partial);
+    }
+    float sum_sq = block_reduce_sum_pinned(partial, scratch);
+    float inv_rms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum_sq, (float)width), eps)));
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+        float y = __fmul_rn(__fmul_rn(x[base + j], inv_rms), weight[j]);
+        out[base + j] = y;
+        if (out_h) out_h[base + j] = __float2half_rn(y);
+    }
+}
+
+__global__ void k_set_scalar(int* dst, int value) { *dst = value; }
+
+// fp32 rows -> half rows (for callers that hand hidden states straight to the
+// expert entry points).
+__global__ void k_rows_to_half(const float* __restrict__ x, __half* __restrict__ out,
+                               const int* __restrict__ valid_tokens, int width) {
+    int row = blockIdx.x;
+    if (row >= *valid_tokens) return;
+    size_t base = (size_t)row * width;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) out[base + j] = __float2half_rn(x[base + j]);
+}
+
+// ---------------------------------------------------------------------------
+// Router logits.  The value-level order of moe_block_router_logits
+// (crates/xabe-engine/src/block/moe.rs:301-382): 256 lanes; lane v sums
+// w[e][j] * x[t][j] for j = v, v+256, ... ascending with fused multiply-add;
+// shuffle-down tree inside each group of 32 consecutive lanes; the eight
+// group totals added in ascending order starting from +0.  Here one real warp
+// carries all 256 lanes of one expert (lane l holds lanes l, l+32, ...), so
+// the weight row is read once, fully coalesced, and the result is
+// bit-identical for every token-tile width TT.
+// grid: (ceil(E / 4), ceil(max_tokens / TT)), block 128 (one expert per warp).
+// ---------------------------------------------------------------------------
+template <int TT>
+__global__ void __launch_bounds__(128) k_router_logits(const float* __restrict__ w,
+                                                        const float* __restrict__ x,
+                                                        const int* __restrict__ valid_tokens,
+                                                        int hidden, int num_experts,
+                                                        const float* __restrict__ bias,
+                                                        float* __restrict__ logits) {
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int e = blockIdx.x * 4 + warp;
+    int t0 = blockIdx.y * TT;
+    int live = *valid_tokens;
+    if (e >= num_experts || t0 >= live) return;
+    float acc[8][TT];
+#pragma unroll
+    for (int g = 0; g < 8; ++g)
+#pragma unroll
+        for (int u = 0; u < TT; ++u) acc[g][u] = 0.0f;
+    const float* wrow = w + (size_t)e * hidden;
+    const float* xr[TT];
+#pragma unroll
+    for (int u = 0; u < TT; ++u) {
+        int t = t0 + u < live ? t0 + u : live - 1;
+        xr[u] = x + (size_t)t * hidden;
+    }
+    for (int jc = 0; jc < hidden; jc += 256) {
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+            int j = jc + g * 32 + lane;
+            if (j < hidden) {
+                float wj = __ldg(wrow + j);
+#pragma unroll
+                for (int u = 0; u < TT; ++u) acc[g][u] = fmaf(wj, xr[u][j], acc[g][u]);
+            }
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < TT; ++u) {
+        float total = 0.0f;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+            float v = acc[g][u];
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) v += __shfl_down_sync(0xffffffffu, v, off);
+            total += v;  // only lane 0's value is the tree's root
+        }
+        if (lane == 0 && t0 + u < live)
+            logits[(size_t)(t0 + u) * num_experts + e] = bias ? __fadd_rn(total, bias[e]) : total;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Routing: stable softmax over all experts, k selection passes by
+// (probability desc, index asc), renormalise over the selected k in selection
+// order (crates/xabe-kernels/src/moe/router.rs:32-76).  One warp per token.
+// The softmax denominator keeps the reference device kernel's tree
+// (crates/xabe-cuda/src/kernels/moe.rs:1883-1917): 256 lanes, lane v adds
+// exp[v], exp[v+256], ...; halving steps 128..1.  Lane l of the warp holds
+// experts l, l+32, ..., so steps 128/64/32 are in-register and 16..1 are
+// shuffle-downs.  num_experts <= 512.
+// grid: (ceil(max_tokens / 8)), block 256.
+// ---------------------------------------------------------------------------
+constexpr int kRouteLaneExperts = 16;
+
+__device__ __forceinline__ void route_one_token(const float* __restrict__ row, int num_experts, int top_k,
+                                                int lane, int* __restrict__ ids_out,
+                                                float* __restrict__ w_out) {
+    float lg[kRouteLaneExperts];
+    float mx = row[0];
+#pragma unroll
+    for (int i = 0; i < kRouteLaneExperts; ++i) {
+        int e = lane + 32 * i;
+        lg[i] = e < num_experts ? row[e] : 0.0f;
+        if (e < num_experts) mx = fmaxf(mx, lg[i]);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    float p[kRouteLaneExperts];
+#pragma unroll
+    for (int i = 0; i < kRouteLaneExperts; ++i) {
+        int e = lane + 32 * i;
+        p[i] = e < num_experts ? expf(lg[i] - mx) : 0.0f;
+    }
+    // lane v of 256: v = lane + 32*i (i < 8) holds p[i] + p[i + 8]
+    float v8[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v8[i] = p[i] + p[i + 8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v8[i] += v8[i + 4];  // step 128
+    v8[0] += v8[2];                                  // step 64
+    v8[1] += v8[3];
+    float s = v8[0] + v8[1];                         // step 32
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) s += __shfl_down_sync(0xffffffffu, s, off);
+    float sum_exp = __shfl_sync(0xffffffffu, s, 0);
+#pragma unroll
+    for (int i = 0; i < kRouteLaneExperts; ++i) {
+        int e = lane + 32 * i;
+        p[i] = e < num_experts ? __fdiv_rn(p[i], sum_exp) : -1.0f;
+    }
+    float sel_sum = 0.0f;
+    float sel[16];
+    for (int j = 0; j < top_k; ++j) {
+        float bv = -1.0f;
+        int bi = -1;
+#pragma unroll
+        for (int i = 0; i < kRouteLaneExperts; ++i) {
+            int e = lane + 32 * i;
+            if (p[i] > bv || (p[i] == bv && p[i] >= 0.0f && (bi < 0 || e < bi))) { bv = p[i]; bi = e; }
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            float cv = __shfl_xor_sync(0xffffffffu, bv, off);
+            int ci = __shfl_xor_sync(0xffffffffu, bi, off);
+            if (cv > bv || (cv == bv && ci >= 0 && (bi < 0 || ci < bi))) { bv = cv; bi = ci; }
+        }
+#pragma unroll
+        for (int i = 0; i < kRouteLaneExperts; ++i)
+            if (bi >= 0 && lane + 32 * i == bi) p[i] = -1.0f;
+        if (lane == 0) ids_out[j] = bi;
+        if (j < 16) sel[j] = bv;
+        sel_sum += bv;  // selection order, as router.rs:62
+    }
+    if (lane == 0) {
+        for (int j = 0; j < top_k; ++j)
+            w_out[j] = sel_sum > 0.0f ? __fdiv_rn(sel[j], sel_sum) : __fdiv_rn(1.0f, (float)top_k);
+    }
+}
+
+__global__ void __launch_bounds__(256) k_route(const float* __restrict__ logits,
+                                               const int* __restrict__ valid_tokens, int num_experts,
+                                               int top_k, int* __restrict__ topk_ids,
+                                               float* __restrict__ topk_weights) {
+    int lane = threadIdx.x & 31;
+    int token = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (token >= *valid_tokens) return;
+    route_one_token(logits + (size_t)token * num_experts, num_experts, top_k, lane,
+                    topk_ids + (size_t)token * top_k, topk_weights + (size_t)token * top_k);
+}
+
+// ---------------------------------------------------------------------------
+// Dispatch tables (crates/xabe-kernels/src/moe/dispatch.rs:60-131).  Three
+// passes over fixed-size chunks of the flat (token, k) list, no float and no
+// order-dependent atomics: (1) per-chunk expert histograms + sentinel fill of
+// the whole capacity, (2) one block turns them into padded exclusive offsets,
+// expert_ids and num_tokens_post_pad, (3) each chunk places its pairs in
+// ascending flat order with warp match ranks.  The sentinel is
+// valid_tokens * top_k (dispatch.rs:24-26), inactive blocks are -1.
+// ---------------------------------------------------------------------------
+constexpr int kAlignChunk = 1024;  // flat pairs per chunk (one warp each)
+
+__global__ void __launch_bounds__(32) k_align_count(const int* __restrict__ topk_ids,
+                                                    const int* __restrict__ valid_tokens, int top_k,
+                                                    int num_experts, int n_chunks, int sorted_capacity,
+                                                    int block_capacity, int* __restrict__ chunk_hist,
+                                                    int* __restrict__ sorted_token_ids,
+                                                    int* __restrict__ expert_ids) {
+    extern __shared__ int hist[];
+    int c = blockIdx.x, lane = threadIdx.x;
+    int numel = *valid_tokens * top_k;
+    for (int e = lane; e < num_experts; e += 32) hist[e] = 0;
+    __syncwarp();
+    int begin = c * kAlignChunk;
+    for (int i = begin + lane; i < begin + kAlignChunk && i < numel; i += 32) atomicAdd(&hist[topk_ids[i]], 1);
+    __syncwarp();
+    for (int e = lane; e < num_experts; e += 32) chunk_hist[(size_t)c * num_experts + e] = hist[e];
+    // sentinel / inactive fill over this chunk's share of the capacity
+    int per = (sorted_capacity + n_chunks - 1) / n_chunks;
+    for (int i = c * per + lane; i < (c + 1) * per && i < sorted_capacity; i += 32) sorted_token_ids[i] = numel;
+    int perb = (block_capacity + n_chunks - 1) / n_chunks;
+    for (int i = c * perb + lane; i < (c + 1) * perb && i < block_capacity; i += 32) expert_ids[i] = -1;
+}
+
+// One block, one thread per expert (num_experts <= 1024).
+__global__ void k_align_scan(int num_experts, int n_chunks, int block_size, int* __restrict__ chunk_hist,
+                             int* __restrict__ expert_offsets, int* __restrict__ expert_ids,
+                             int* __restrict__ num_tokens_post_pad) {
+    extern __shared__ int padded[];  // [num_experts + 1]
+    int e = threadIdx.x;
+    int total = 0;
+    if (e < num_experts) {
+        for (int c = 0; c < n_chunks; ++c) {
+            int h = chunk_hist[(size_t)c * num_experts + e];
+            chunk_hist[(size_t)c * num_experts + e] = total;  // exclusive prefix over chunks
+            total += h;
+        }
+        padded[e] = (total + block_size - 1) / block_size * block_size;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int i = 0; i < num_experts; ++i) {
+            int p = padded[i];
+            padded[i] = run;
+            run += p;
+        }
+        padded[num_experts] = run;
+        *num_tokens_post_pad = run;
+    }
+    __syncthreads();
+    if (e < num_experts) {
+        int start = padded[e], end = padded[e + 1];
+        expert_offsets[e] = start;
+        if (e == 0) expert_offsets[num_experts] = padded[num_experts];
+        for (int b = start / block_size; b < end / block_size; ++b) expert_ids[b] = e;
+        for (int c = 0; c < n_chunks; ++c) chunk_hist[(size_t)c * num_experts + e] += start;
+    }
+}
+
+__global__ void __launch_bounds__(32) k_align_scatter(const int* __restrict__ topk_ids,
+                                                      const int* __restrict__ valid_tokens, int top_k,
+                                                      int num_experts, const int* __restrict__ chunk_hist,
+                                                      int* __restrict__ sorted_token_ids) {
+    extern __shared__ int cursor[];
+    int c = blockIdx.x, lane = threadIdx.x;
+    int numel = *valid_tokens * top_k;
+    int begin = c * kAlignChunk;
+    if (begin >= numel) return;
+    for (int e = lane; e < num_experts; e += 32) cursor[e] = chunk_hist[(size_t)c * num_experts + e];
+    __syncwarp();
+    for (int i0 = begin; i0 < begin + kAlignChunk && i0 < numel; i0 += 32) {
+        int i = i0 + lane;
+        bool on = i < numel;
+        unsigned active = __ballot_sync(0xffffffffu, on);
+        if (on) {
+            int e = topk_ids[i];
+            unsigned same = __match_any_sync(active, e);
+            int rank = __popc(same & ((1u << lane) - 1u));
+            int pos = cursor[e] + rank;
+            sorted_token_ids[pos] = i;
+            __syncwarp(active);
+            if (rank == 0) cursor[e] += __popc(same);
+        }
+        __syncwarp();
+    }
+}
+
+// ---------------------------------------------------------------------------
+// moe_reduce (crates/xabe-cuda/src/kernels/moe.rs:4049-4065):
+// out[t][h] = sum over ascending k of partial[t*K + k][h].
+// grid: (max_tokens, ceil(hidden / 256)), block 256.
+// ---------------------------------------------------------------------------
+__global__ void k_reduce(const float* __restrict__ partial, const int* __restrict__ valid_tokens, int top_k,
+                         int hidden, float* __restrict__ out) {
+    int t = blockIdx.x;
+    if (t >= *valid_tokens) return;
+    int j = blockIdx.y * blockDim.x + threadIdx.x;
+    if (j >= hidden) return;
+    size_t pbase = (size_t)t * top_k * hidden;
+    float r = 0.0f;
+    for (int k = 0; k < top_k; ++k) r += partial[pbase + (size_t)k * hidden + j];
+    out[(size_t)t * hidden + j] = r;
+}
+
+// ---------------------------------------------------------------------------
+// moe_block_gate_and_combine (crates/xabe-engine/src/block/moe.rs:424-483):
+// g = 1 / (1 + expf(-dot(w_gate, normed[t]))) with the dot product on 256
+// lanes at stride 256 and block_reduce_sum; routed = ascending-k sum of
+// partial; ffn_out = routed + shexp * g (routed on the left); l_out =
+// ffn_out + residual (the pre-norm input).
+// grid: (max_tokens, ceil(hidden / 256)), block 256.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) k_gate_and_combine(
+    const float* __restrict__ w, const float* __restrict__ normed, const float* __restrict__ partial,
+    const float* __restrict__ shexp, const float* __restrict__ residual, const int* __restrict__ valid_tokens,
+    int top_k, int hidden, float* __restrict__ gate, float* __restrict__ routed, float* __restrict__ ffn_out,
+    float* __restrict__ l_out) {
+    __shared__ float scratch[32];
+    int t = blockIdx.x;
+    if (t >= *valid_tokens) return;
+    size_t base = (size_t)t * hidden;
+    const float* xs = normed + base;
+    float s = 0.0f;
+    for (int j = threadIdx.x; j < hidden; j += 256) s = fmaf(w[j], xs[j], s);
+    s = block_reduce_sum_pinned(s, scratch);
+    float g = __fdiv_rn(1.0f, 1.0f + expf(-s));
+    if (threadIdx.x == 0 && blockIdx.y == 0) gate[t] = g;
+    int j = blockIdx.y * blockDim.x + threadIdx.x;
+    if (j >= hidden) return;
+    size_t pbase = (size_t)t * top_k * hidden;
+    float r = 0.0f;
+    for (int k = 0; k < top_k; ++k) r += partial[pbase + (size_t)k * hidden + j];
+    float v = fmaf(shexp[base + j], g, r);
+    routed[base + j] = r;
+    ffn_out[base + j] = v;
+    l_out[base + j] = v + residual[base + j];
+}
+
+// Dense FFN epilogue (crates/xabe-engine/src/block/dense_ffn.rs:234-251):
+// l_out = ffn_out + residual for the live rows.
+__global__ void k_add_residual(const float* __restrict__ ffn, const float* __restrict__ residual,
+                               const int* __restrict__ valid_tokens, int hidden, float* __restrict__ l_out) {
+    int t = blockIdx.x;
+    if (t >= *valid_tokens) return;
+    size_t base = (size_t)t * hidden;
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) l_out[base + j] = ffn[base + j] + residual[base + j];
+}
+
+// ---------------------------------------------------------------------------
+// Standalone dequantisation, bit-identical to the scalar reference because
+// reconstruction is multiplications only: Q6_K (d * sc) * q
+// (crates/xabe-kernels/src/quant.rs:171-202), Q8_0 q * d (quant.rs:62-69).
+// One thread per element.
+// ---------------------------------------------------------------------------
+__global__ void k_dequant_q6k(const uint8_t* __restrict__ bytes, size_t n_elems, float* __restrict__ out) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_elems) return;
+    const uint8_t* blk = bytes + (i >> 8) * kQ6KBlockBytes;
+    int r = (int)(i & 255);
+    int half = r >> 7, grp = (r & 127) >> 5, l = r & 31;
+    uint8_t qb = blk[half * 64 + (grp & 1) * 32 + l];
+    int nib = grp < 2 ? (qb & 0xF) : (qb >> 4);
+    int hi = (blk[128 + half * 32 + l] >> (2 * grp)) & 3;
+    int q = (nib | (hi << 4)) - 32;
+    int sc = (int)(int8_t)blk[192 + half * 8 + 2 * grp + (l >> 4)];
+    float d = __half2float(__ushort_as_half((unsigned short)(blk[208] | (blk[209] << 8))));
+    out[i] = __fmul_rn(__fmul_rn(d, (float)sc), (float)q);
+}
+
+__global__ void k_dequant_q8_0(const uint8_t* __restrict__ bytes, size_t n_elems, float* __restrict__ out) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_elems) return;
+    const uint8_t* blk = bytes + (i >> 5) * kQ8BlockBytes;
+    float d = __half2float(__ushort_as_half((unsigned short)(blk[0] | (blk[1] << 8))));
+    int q = (int)(int8_t)blk[2 + (i & 31)];
+    out[i] = __fmul_rn((float)q, d);
+}
+
+}  // namespace xabe

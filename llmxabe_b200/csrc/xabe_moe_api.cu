@@ -1,0 +1,649 @@
+// C ABI of the sm_100a MoE FFN kernel set.  See include/xabe_moe.h for the
+// contract and for the reference method each entry point mirrors.
+#include "../../include/xabe_moe.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+
+#include "common.cuh"
+#include "expert_kernels.cuh"
+#include "glue_kernels.cuh"
+
+using namespace xabe;
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    return code;
+}
+
+#define CUDA_TRY(expr)                                                                         \
+    do {                                                                                       \
+        cudaError_t e__ = (expr);                                                              \
+        if (e__ != cudaSuccess)                                                                \
+            return fail(XABE_ERR_DRIVER, "CUDA driver error: %s (%s)", cudaGetErrorString(e__), #expr); \
+    } while (0)
+
+uint64_t sorted_capacity_of(const xabe_moe_geometry& g) {
+    // MoeGeometry::sorted_capacity, crates/xabe-cuda/src/kernels/moe.rs:4575-4584
+    uint64_t numel = (uint64_t)g.max_tokens * g.experts_per_token;
+    uint64_t active = g.num_experts < numel ? g.num_experts : numel;
+    uint64_t bound = numel + active * (g.block_size - 1);
+    return (bound + g.block_size - 1) / g.block_size * g.block_size;
+}
+
+size_t block_bytes_of(int quant) { return quant == XABE_QUANT_Q6_K ? 210 : 34; }
+size_t block_elems_of(int quant) { return quant == XABE_QUANT_Q6_K ? 256 : 32; }
+
+int nb_cap_for(int block_size) {
+    int nb = (block_size + 7) / 8;
+    return nb <= 1 ? 1 : nb <= 2 ? 2 : nb <= 4 ? 4 : 8;
+}
+
+}  // namespace
+
+struct xabe_moe {
+    xabe_moe_geometry g{};
+    int device = 0;
+    int scope = XABE_SCOPE_ROUTED;
+    float eps = 1e-6f;
+    bool exact_decode = false;
+    uint64_t sorted_capacity = 0, block_capacity = 0;
+    int n_chunks = 0;
+    int published_tokens = -1;
+    int* h_status = nullptr;  // pinned
+    // device scratch
+    int* valid_tokens = nullptr;
+    int* status = nullptr;
+    int* topk_ids = nullptr;
+    float* topk_weights = nullptr;
+    int* sorted_token_ids = nullptr;
+    int* expert_ids = nullptr;
+    int* num_tokens_post_pad = nullptr;
+    int* chunk_hist = nullptr;
+    int* expert_offsets = nullptr;
+    float* normed = nullptr;
+    __half* normed_h = nullptr;
+    float* logits = nullptr;
+    __half* inter_routed = nullptr;
+    __half* inter_shared = nullptr;
+    float* partial = nullptr;
+    float* routed = nullptr;
+    float* shexp = nullptr;
+    float* gate = nullptr;
+    float* stage_in = nullptr;
+    float* stage_ffn = nullptr;
+    float* stage_out = nullptr;
+    int smem_gateup = 0, smem_down = 0;
+};
+
+namespace {
+
+template <typename T>
+cudaError_t dev_alloc(T** p, size_t n) {
+    cudaError_t e = cudaMalloc((void**)p, (n ? n : 1) * sizeof(T));
+    if (e == cudaSuccess) e = cudaMemset(*p, 0, (n ? n : 1) * sizeof(T));
+    return e;
+}
+
+// check_stack, crates/xabe-cuda/src/kernels/moe.rs:6729-6746
+int check_stack(const char* which, const xabe_quant_tensor& t, size_t expected) {
+    if (t.quant != XABE_QUANT_Q6_K && t.quant != XABE_QUANT_Q8_0)
+        return fail(XABE_ERR_UNSUPPORTED_EXPERT_TYPE,
+                    "expert stack `%s` has quant tag %d, which the grouped GEMM cannot unpack (it handles "
+                    "Q6_K and Q8_0)", which, t.quant);
+    if (!t.dev_bytes) return fail(XABE_ERR_INVALID_ARGUMENT, "%s: null device pointer", which);
+    if (((uintptr_t)t.dev_bytes & 15) != 0)
+        return fail(XABE_ERR_INVALID_ARGUMENT, "%s: device pointer must be 16-byte aligned", which);
+    size_t bb = block_bytes_of(t.quant);
+    if (t.n_bytes % bb != 0)
+        return fail(XABE_ERR_RAGGED_WEIGHTS, "%s: %zu bytes is not a whole number of %zu B blocks", which,
+                    t.n_bytes, bb);
+    size_t found = t.n_bytes / bb * block_elems_of(t.quant);
+    if (found != expected)
+        return fail(XABE_ERR_WRONG_ELEMENT_COUNT,
+                    "%s: expected %zu elements for this geometry, stack holds %zu", which, expected, found);
+    return XABE_OK;
+}
+
+size_t gateup_smem(int k, int quant, int block_size) {
+    uint32_t row_bytes = k / 256 * span_bytes_of(quant);
+    size_t tiles = 2 * (size_t)staged_capacity(8u * row_bytes);
+    size_t red = (size_t)2048 * nb_cap_for(block_size);
+    return tiles > red ? tiles : red;
+}
+size_t down_smem(int k, int quant) {
+    uint32_t row_bytes = k / 256 * span_bytes_of(quant);
+    return staged_capacity(64u * row_bytes);
+}
+
+template <int QR, int QS>
+int launch_gateup(xabe_moe* m, cudaStream_t st, const ExpertLaunch& L, int y_blocks, size_t smem) {
+    auto kern = k_expert_gateup<QR, QS>;
+    CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid(L.rows / 8, y_blocks);
+    kern<<<grid, kExpertThreads, smem, st>>>(L);
+    CUDA_TRY(cudaGetLastError());
+    return XABE_OK;
+}
+template <int QR, int QS>
+int launch_down(xabe_moe* m, cudaStream_t st, const ExpertLaunch& L, int y_blocks, size_t smem) {
+    auto kern = k_expert_down<QR, QS>;
+    CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid(L.rows / 64, y_blocks);
+    kern<<<grid, kExpertThreads, smem, st>>>(L);
+    CUDA_TRY(cudaGetLastError());
+    return XABE_OK;
+}
+
+#define DISPATCH_QQ(fn, qr, qs, ...)                                                   \
+    ((qr) == XABE_QUANT_Q6_K                                                           \
+         ? ((qs) == XABE_QUANT_Q6_K ? fn<QUANT_Q6K, QUANT_Q6K>(__VA_ARGS__)           \
+                                    : fn<QUANT_Q6K, QUANT_Q8_0>(__VA_ARGS__))         \
+         : ((qs) == XABE_QUANT_Q6_K ? fn<QUANT_Q8_0, QUANT_Q6K>(__VA_ARGS__)          \
+                                    : fn<QUANT_Q8_0, QUANT_Q8_0>(__VA_ARGS__)))
+
+struct MlpWeights {
+    bool present = false;
+    xabe_quant_tensor gate{}, up{}, down{};
+};
+
+// Both projections of the routed experts and/or the shared expert, each in one
+// launch.  `routed`/`shared` say which halves ride the launch.
+int run_experts(xabe_moe* m, cudaStream_t st, const MlpWeights& routed, const MlpWeights& shared,
+                float* shexp_out) {
+    const auto& g = m->g;
+    if (!routed.present && !shared.present) return XABE_OK;
+    if (routed.present && routed.gate.quant != routed.up.quant)
+        return fail(XABE_ERR_UNSUPPORTED_EXPERT_TYPE,
+                    "routed gate and up stacks must share one format (found tags %d and %d)",
+                    routed.gate.quant, routed.up.quant);
+    if (shared.present && shared.gate.quant != shared.up.quant)
+        return fail(XABE_ERR_UNSUPPORTED_EXPERT_TYPE,
+                    "shared gate and up matrices must share one format (found tags %d and %d)",
+                    shared.gate.quant, shared.up.quant);
+    int shared_tiles = shared.present ? (int)((g.max_tokens + g.block_size - 1) / g.block_size) : 0;
+    int routed_blocks = routed.present ? (int)m->block_capacity : 0;
+    ExpertLaunch L{};
+    L.routed_blocks = routed_blocks;
+    L.block_size = (int)g.block_size;
+    L.top_k = (int)g.experts_per_token;
+    L.max_tokens = (int)g.max_tokens;
+    L.sorted_token_ids = m->sorted_token_ids;
+    L.expert_ids = m->expert_ids;
+    L.valid_tokens = m->valid_tokens;
+    L.topk_weights = m->topk_weights;
+    L.status = m->status;
+    int qr = routed.present ? routed.gate.quant : shared.gate.quant;
+    int qs = shared.present ? shared.gate.quant : qr;
+    // gate/up + SwiGLU
+    L.r_a = routed.present ? (const uint8_t*)routed.gate.dev_bytes : nullptr;
+    L.r_b = routed.present ? (const uint8_t*)routed.up.dev_bytes : nullptr;
+    L.s_a = shared.present ? (const uint8_t*)shared.gate.dev_bytes : nullptr;
+    L.s_b = shared.present ? (const uint8_t*)shared.up.dev_bytes : nullptr;
+    L.rows = (int)g.intermediate;
+    L.k = (int)g.hidden;
+    L.x_routed = m->normed_h;
+    L.x_shared = m->normed_h;
+    L.inter_routed = m->inter_routed;
+    L.inter_shared = m->inter_shared;
+    size_t smem = gateup_smem(L.k, qr, L.block_size);
+    size_t smem_s = gateup_smem(L.k, qs, L.block_size);
+    if (smem_s > smem) smem = smem_s;
+    if (smem > 220 * 1024)
+        return fail(XABE_ERR_UNSUPPORTED_GEOMETRY, "gate/up row tile of %zu bytes does not fit shared memory", smem);
+    int rc = DISPATCH_QQ(launch_gateup, qr, qs, m, st, L, routed_blocks + shared_tiles, smem);
+    if (rc) return rc;
+    // down
+    qr = routed.present ? routed.down.quant : shared.down.quant;
+    qs = shared.present ? shared.down.quant : qr;
+    L.r_a = routed.present ? (const uint8_t*)routed.down.dev_bytes : nullptr;
+    L.r_b = nullptr;
+    L.s_a = shared.present ? (const uint8_t*)shared.down.dev_bytes : nullptr;
+    L.s_b = nullptr;
+    L.rows = (int)g.hidden;
+    L.k = (int)g.intermediate;
+    L.x_routed = m->inter_routed;
+    L.x_shared = m->inter_shared;
+    L.partial = m->partial;
+    L.shexp = shexp_out;
+    smem = down_smem(L.k, qr);
+    smem_s = down_smem(L.k, qs);
+    if (smem_s > smem) smem = smem_s;
+    if (smem > 220 * 1024)
+        return fail(XABE_ERR_UNSUPPORTED_GEOMETRY, "down row tile of %zu bytes does not fit shared memory", smem);
+    return DISPATCH_QQ(launch_down, qr, qs, m, st, L, routed_blocks + shared_tiles, smem);
+}
+
+int check_routed(xabe_moe* m, const char* entry) {
+    if (m->scope != XABE_SCOPE_ROUTED)
+        return fail(XABE_ERR_SHARED_ONLY_BUFFERS,
+                    "`%s` needs the routed dispatch tables, but these buffers were allocated for the "
+                    "shared-expert path only", entry);
+    return XABE_OK;
+}
+
+int rows_to_half(xabe_moe* m, cudaStream_t st, const float* hidden_states) {
+    k_rows_to_half<<<m->g.max_tokens, 256, 0, st>>>(hidden_states, m->normed_h, m->valid_tokens, (int)m->g.hidden);
+    CUDA_TRY(cudaGetLastError());
+    return XABE_OK;
+}
+
+int launch_rms_norm(xabe_moe* m, cudaStream_t st, const float* x, const float* weight) {
+    // block_for_width, crates/xabe-cuda/src/kernels/layer_ops.rs:1219-1221
+    int block = ((int)m->g.hidden + 31) / 32 * 32;
+    if (block > 1024) block = 1024;
+    if (block < 32) block = 32;
+    k_rms_norm<<<m->g.max_tokens, block, 0, st>>>(x, weight, m->normed, m->normed_h, m->valid_tokens,
+                                                 (int)m->g.hidden, m->eps);
+    CUDA_TRY(cudaGetLastError());
+    return XABE_OK;
+}
+
+int launch_router(xabe_moe* m, cudaStream_t st, const float* router, const float* bias) {
+    const auto& g = m->g;
+    dim3 block(128);
+    if (g.max_tokens == 1) {
+        dim3 grid((g.num_experts + 3) / 4, 1);
+        k_router_logits<1><<<grid, block, 0, st>>>(router, m->normed, m->valid_tokens, (int)g.hidden,
+                                                   (int)g.num_experts, bias, m->logits);
+    } else if (g.max_tokens <= 4) {
+        dim3 grid((g.num_experts + 3) / 4, 1);
+        k_router_logits<4><<<grid, block, 0, st>>>(router, m->normed, m->valid_tokens, (int)g.hidden,
+                                                   (int)g.num_experts, bias, m->logits);
+    } else {
+        dim3 grid((g.num_experts + 3) / 4, (g.max_tokens + 7) / 8);
+        k_router_logits<8><<<grid, block, 0, st>>>(router, m->normed, m->valid_tokens, (int)g.hidden,
+                                                   (int)g.num_experts, bias, m->logits);
+    }
+    CUDA_TRY(cudaGetLastError());
+    return XABE_OK;
+}
+
+int launch_route_and_dispatch(xabe_moe* m, cudaStream_t st, const float* logits) {
+    const auto& g = m->g;
+    k_route<<<(g.max_tokens + 7) / 8, 256, 0, st>>>(logits, m->valid_tokens, (int)g.num_experts,
+                                                   (int)g.experts_per_token, m->topk_ids, m->topk_weights);
+    CUDA_TRY(cudaGetLastError());
+    size_t hist_bytes = (size_t)(g.num_experts + 1) * sizeof(int);
+    k_align_count<<<m->n_chunks, 32, hist_bytes, st>>>(m->topk_ids, m->valid_tokens, (int)g.experts_per_token,
+                                                      (int)g.num_experts, m->n_chunks, (int)m->sorted_capacity,
+                                                      (int)m->block_capacity, m->chunk_hist,
+                                                      m->sorted_token_ids, m->expert_ids);
+    CUDA_TRY(cudaGetLastError());
+    int threads = ((int)g.num_experts + 31) / 32 * 32;
+    k_align_scan<<<1, threads, hist_bytes, st>>>((int)g.num_experts, m->n_chunks, (int)g.block_size,
+                                                 m->chunk_hist, m->expert_offsets, m->expert_ids,
+                                                 m->num_tokens_post_pad);
+    CUDA_TRY(cudaGetLastError());
+    k_align_scatter<<<m->n_chunks, 32, hist_bytes, st>>>(m->topk_ids, m->valid_tokens,
+                                                        (int)g.experts_per_token, (int)g.num_experts,
+                                                        m->chunk_hist, m->sorted_token_ids);
+    CUDA_TRY(cudaGetLastError());
+    return XABE_OK;
+}
+
+int check_mlp(xabe_moe* m, const char* prefix, const xabe_quant_tensor& gate, const xabe_quant_tensor& up,
+              const xabe_quant_tensor& down, size_t matrices) {
+    size_t n = matrices * (size_t)m->g.intermediate * m->g.hidden;
+    char name[64];
+    int rc;
+    snprintf(name, sizeof(name), "%s gate", prefix);
+    if ((rc = check_stack(name, gate, n))) return rc;
+    snprintf(name, sizeof(name), "%s up", prefix);
+    if ((rc = check_stack(name, up, n))) return rc;
+    snprintf(name, sizeof(name), "%s down", prefix);
+    if ((rc = check_stack(name, down, n))) return rc;
+    return XABE_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* xabe_moe_last_error(void) { return g_last_error.c_str(); }
+int xabe_moe_abi_version(void) { return 1; }
+
+uint64_t xabe_moe_sorted_capacity(const xabe_moe_geometry* g) { return g ? sorted_capacity_of(*g) : 0; }
+uint64_t xabe_moe_expert_block_capacity(const xabe_moe_geometry* g) {
+    return g && g->block_size ? sorted_capacity_of(*g) / g->block_size : 0;
+}
+
+int xabe_moe_create(const xabe_moe_geometry* geometry, int device, int scope, float eps, xabe_moe** out) {
+    if (!geometry || !out) return fail(XABE_ERR_INVALID_ARGUMENT, "null geometry or output pointer");
+    *out = nullptr;
+    const xabe_moe_geometry g = *geometry;
+    auto bad = [&](const char* reason) {
+        return fail(XABE_ERR_UNSUPPORTED_GEOMETRY,
+                    "unsupported MoE geometry {experts %u, top_k %u, hidden %u, intermediate %u, block %u, "
+                    "max_tokens %u}: %s",
+                    g.num_experts, g.experts_per_token, g.hidden, g.intermediate, g.block_size, g.max_tokens,
+                    reason);
+    };
+    // MoeKernels::new, crates/xabe-cuda/src/kernels/moe.rs:5043-5111
+    if (g.block_size == 0) return bad("block_size must be non-zero");
+    if (scope == XABE_SCOPE_ROUTED) {
+        if (g.experts_per_token == 0) return bad("experts_per_token must be non-zero");
+        if (g.experts_per_token > g.num_experts) return bad("experts_per_token must not exceed num_experts");
+        if (g.num_experts > 512) return bad("num_experts exceeds the 512 the routing warp holds");
+        if (g.experts_per_token > 16) return bad("experts_per_token exceeds 16");
+    } else if (scope != XABE_SCOPE_SHARED_ONLY) {
+        return fail(XABE_ERR_INVALID_ARGUMENT, "unknown buffer scope %d", scope);
+    }
+    if (g.max_tokens == 0) return bad("max_tokens must be non-zero");
+    if (g.hidden == 0 || g.intermediate == 0) return bad("hidden and intermediate must be non-zero");
+    if (g.hidden % 256 != 0) return bad("hidden must be a multiple of the 256-element superblock");
+    if (g.intermediate % 256 != 0) return bad("intermediate must be a multiple of the 256-element superblock");
+    if (g.block_size > 8 * kMaxNB) return bad("block_size exceeds the slots the tensor-core tile stages");
+    if (g.max_tokens > 65535) return bad("max_tokens exceeds the 65535 grid limit");
+    uint64_t cap = scope == XABE_SCOPE_ROUTED ? sorted_capacity_of(g) : 0;
+    uint64_t shared_tiles = (g.max_tokens + g.block_size - 1) / g.block_size;
+    if (cap / g.block_size + shared_tiles > 65535)
+        return bad("dispatch-block capacity exceeds the 65535 grid.y limit");
+
+    int n_dev = 0;
+    CUDA_TRY(cudaGetDeviceCount(&n_dev));
+    if (device < 0 || device >= n_dev) return fail(XABE_ERR_DRIVER, "CUDA driver error: no device %d", device);
+    CUDA_TRY(cudaSetDevice(device));
+    cudaDeviceProp prop{};
+    CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+    if (prop.major < 10)
+        return fail(XABE_ERR_DRIVER, "device %d is sm_%d%d; this library is built for sm_100a only", device,
+                    prop.major, prop.minor);
+
+    xabe_moe* m = new (std::nothrow) xabe_moe();
+    if (!m) return fail(XABE_ERR_DRIVER, "out of host memory");
+    m->g = g;
+    m->device = device;
+    m->scope = scope;
+    m->eps = eps;
+    m->sorted_capacity = cap;
+    m->block_capacity = cap / g.block_size;
+    uint64_t pairs = (uint64_t)g.max_tokens * (scope == XABE_SCOPE_ROUTED ? g.experts_per_token : 0);
+    m->n_chunks = (int)((pairs + kAlignChunk - 1) / kAlignChunk);
+    if (m->n_chunks < 1) m->n_chunks = 1;
+    size_t T = g.max_tokens, H = g.hidden, I = g.intermediate, E = g.num_experts, K = g.experts_per_token;
+    cudaError_t e = cudaSuccess;
+    auto A = [&](cudaError_t r) { if (e == cudaSuccess) e = r; };
+    A(cudaHostAlloc((void**)&m->h_status, sizeof(int), cudaHostAllocDefault));
+    A(dev_alloc(&m->valid_tokens, 1));
+    A(dev_alloc(&m->status, 1));
+    A(dev_alloc(&m->normed, T * H));
+    A(dev_alloc(&m->normed_h, T * H));
+    A(dev_alloc(&m->inter_shared, T * I));
+    A(dev_alloc(&m->shexp, T * H));
+    A(dev_alloc(&m->stage_in, T * H));
+    A(dev_alloc(&m->stage_ffn, T * H));
+    A(dev_alloc(&m->stage_out, T * H));
+    if (scope == XABE_SCOPE_ROUTED) {
+        A(dev_alloc(&m->topk_ids, T * K));
+        A(dev_alloc(&m->topk_weights, T * K));
+        A(dev_alloc(&m->sorted_token_ids, (size_t)cap));
+        A(dev_alloc(&m->expert_ids, (size_t)m->block_capacity));
+        A(dev_alloc(&m->num_tokens_post_pad, 1));
+        A(dev_alloc(&m->chunk_hist, (size_t)m->n_chunks * E));
+        A(dev_alloc(&m->expert_offsets, E + 1));
+        A(dev_alloc(&m->logits, T * E));
+        A(dev_alloc(&m->inter_routed, (size_t)cap * I));
+        A(dev_alloc(&m->partial, T * K * H));
+        A(dev_alloc(&m->routed, T * H));
+        A(dev_alloc(&m->gate, T));
+    }
+    if (e != cudaSuccess) {
+        xabe_moe_destroy(m);
+        return fail(XABE_ERR_DRIVER, "CUDA driver error: %s (allocating MoE buffers)", cudaGetErrorString(e));
+    }
+    *out = m;
+    return XABE_OK;
+}
+
+void xabe_moe_destroy(xabe_moe* m) {
+    if (!m) return;
+    cudaSetDevice(m->device);
+    void* dev[] = {m->valid_tokens, m->status, m->topk_ids, m->topk_weights, m->sorted_token_ids, m->expert_ids,
+                   m->num_tokens_post_pad, m->chunk_hist, m->expert_offsets, m->normed, m->normed_h, m->logits,
+                   m->inter_routed, m->inter_shared, m->partial, m->routed, m->shexp, m->gate, m->stage_in,
+                   m->stage_ffn, m->stage_out};
+    for (void* p : dev)
+        if (p) cudaFree(p);
+    if (m->h_status) cudaFreeHost(m->h_status);
+    delete m;
+}
+
+int xabe_moe_set_valid_tokens(xabe_moe* m, void* stream, int tokens) {
+    if (!m) return fail(XABE_ERR_INVALID_ARGUMENT, "null handle");
+    if (tokens < 0 || (uint32_t)tokens > m->g.max_tokens)
+        return fail(XABE_ERR_TOO_MANY_TOKENS, "%d tokens exceeds the %u the buffers were sized for", tokens,
+                    m->g.max_tokens);
+    if (tokens == m->published_tokens) return XABE_OK;  // moe.rs:5480-5483
+    // The value travels as a kernel argument, so no host memory is read later
+    // and nothing has to be synchronised.
+    k_set_scalar<<<1, 1, 0, (cudaStream_t)stream>>>(m->valid_tokens, tokens);
+    CUDA_TRY(cudaGetLastError());
+    m->published_tokens = tokens;
+    return XABE_OK;
+}
+
+int xabe_moe_rms_norm(xabe_moe* m, void* stream, const float* x, const float* weight) {
+    if (!m || !x || !weight) return fail(XABE_ERR_INVALID_ARGUMENT, "null argument to rms_norm");
+    return launch_rms_norm(m, (cudaStream_t)stream, x, weight);
+}
+
+int xabe_moe_router_logits(xabe_moe* m, void* stream, const float* router, const float* bias) {
+    if (!m || !router) return fail(XABE_ERR_INVALID_ARGUMENT, "null argument to router_logits");
+    int rc = check_routed(m, "router_logits");
+    if (rc) return rc;
+    return launch_router(m, (cudaStream_t)stream, router, bias);
+}
+
+int xabe_moe_route_and_dispatch(xabe_moe* m, void* stream, const float* logits) {
+    if (!m) return fail(XABE_ERR_INVALID_ARGUMENT, "null handle");
+    int rc = check_routed(m, "route_and_dispatch");
+    if (rc) return rc;
+    return launch_route_and_dispatch(m, (cudaStream_t)stream, logits ? logits : m->logits);
+}
+
+int xabe_moe_grouped_forward_partial(xabe_moe* m, void* stream, xabe_quant_tensor gate, xabe_quant_tensor up,
+                                     xabe_quant_tensor down, const float* hidden_states) {
+    if (!m) return fail(XABE_ERR_INVALID_ARGUMENT, "null handle");
+    int rc = check_routed(m, "grouped_forward");
+    if (rc) return rc;
+    if ((rc = check_mlp(m, "routed", gate, up, down, m->g.num_experts))) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (hidden_states && (rc = rows_to_half(m, st, hidden_states))) return rc;
+    MlpWeights r;
+    r.present = true;
+    r.gate = gate;
+    r.up = up;
+    r.down = down;
+    return run_experts(m, st, r, MlpWeights{}, nullptr);
+}
+
+int xabe_moe_grouped_forward(xabe_moe* m, void* stream, xabe_quant_tensor gate, xabe_quant_tensor up,
+                             xabe_quant_tensor down, const float* hidden_states, float* out) {
+    if (!out) return fail(XABE_ERR_INVALID_ARGUMENT, "null output");
+    int rc = xabe_moe_grouped_forward_partial(m, stream, gate, up, down, hidden_states);
+    if (rc) return rc;
+    dim3 grid(m->g.max_tokens, (m->g.hidden + 255) / 256);
+    k_reduce<<<grid, 256, 0, (cudaStream_t)stream>>>(m->partial, m->valid_tokens, (int)m->g.experts_per_token,
+                                                     (int)m->g.hidden, out);
+    CUDA_TRY(cudaGetLastError());
+    return XABE_OK;
+}
+
+int xabe_moe_shared_expert(xabe_moe* m, void* stream, xabe_quant_tensor gate, xabe_quant_tensor up,
+                           xabe_quant_tensor down, const float* hidden_states, float* out) {
+    if (!m) return fail(XABE_ERR_INVALID_ARGUMENT, "null handle");
+    int rc;
+    if ((rc = check_mlp(m, "shared", gate, up, down, 1))) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (hidden_states && (rc = rows_to_half(m, st, hidden_states))) return rc;
+    MlpWeights s;
+    s.present = true;
+    s.gate = gate;
+    s.up = up;
+    s.down = down;
+    return run_experts(m, st, MlpWeights{}, s, out ? out : m->shexp);
+}
+
+int xabe_moe_block_forward(xabe_moe* m, void* stream, const xabe_moe_layer_weights* w, const float* residual,
+                           size_t residual_len, int tokens, float* ffn_out, size_t ffn_out_len, float* l_out,
+                           size_t l_out_len) {
+    if (!m || !w || !residual || !ffn_out || !l_out)
+        return fail(XABE_ERR_INVALID_ARGUMENT, "null argument to block_forward");
+    int rc = check_routed(m, "block_forward");
+    if (rc) return rc;
+    const auto& g = m->g;
+    // block/moe.rs:1100-1110
+    if (tokens < 0 || (uint32_t)tokens > g.max_tokens)
+        return fail(XABE_ERR_TOO_MANY_TOKENS, "%d tokens exceeds the %u this block was sized for", tokens,
+                    g.max_tokens);
+    size_t n = (size_t)g.max_tokens * g.hidden;
+    if (residual_len != n)
+        return fail(XABE_ERR_BUFFER_LENGTH, "residual must hold %zu floats, holds %zu", n, residual_len);
+    if (ffn_out_len != n)
+        return fail(XABE_ERR_BUFFER_LENGTH, "ffn_out must hold %zu floats, holds %zu", n, ffn_out_len);
+    if (l_out_len != n) return fail(XABE_ERR_BUFFER_LENGTH, "l_out must hold %zu floats, holds %zu", n, l_out_len);
+    if (!w->post_norm || !w->router || !w->shared_gate_inp)
+        return fail(XABE_ERR_INVALID_ARGUMENT, "null dense weight in layer weights");
+    if ((rc = check_mlp(m, "routed", w->gate_exps, w->up_exps, w->down_exps, g.num_experts))) return rc;
+    if ((rc = check_mlp(m, "shared", w->shared_gate, w->shared_up, w->shared_down, 1))) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    if ((rc = xabe_moe_set_valid_tokens(m, stream, tokens))) return rc;
+    if ((rc = launch_rms_norm(m, st, residual, w->post_norm))) return rc;
+    if ((rc = launch_router(m, st, w->router, w->router_bias))) return rc;
+    if ((rc = launch_route_and_dispatch(m, st, m->logits))) return rc;
+    MlpWeights r, s;
+    r.present = s.present = true;
+    r.gate = w->gate_exps;
+    r.up = w->up_exps;
+    r.down = w->down_exps;
+    s.gate = w->shared_gate;
+    s.up = w->shared_up;
+    s.down = w->shared_down;
+    if ((rc = run_experts(m, st, r, s, m->shexp))) return rc;
+    dim3 grid(g.max_tokens, (g.hidden + 255) / 256);
+    k_gate_and_combine<<<grid, 256, 0, st>>>(w->shared_gate_inp, m->normed, m->partial, m->shexp, residual,
+                                             m->valid_tokens, (int)g.experts_per_token, (int)g.hidden, m->gate,
+                                             m->routed, ffn_out, l_out);
+    CUDA_TRY(cudaGetLastError());
+    return XABE_OK;
+}
+
+int xabe_moe_block_forward_host(xabe_moe* m, void* stream, const xabe_moe_layer_weights* w,
+                                const float* host_residual, int tokens, float* host_ffn_out, float* host_l_out) {
+    if (!m || !host_residual) return fail(XABE_ERR_INVALID_ARGUMENT, "null argument to block_forward_host");
+    if (tokens < 0 || (uint32_t)tokens > m->g.max_tokens)
+        return fail(XABE_ERR_TOO_MANY_TOKENS, "%d tokens exceeds the %u this block was sized for", tokens,
+                    m->g.max_tokens);
+    cudaStream_t st = (cudaStream_t)stream;
+    size_t bytes = (size_t)tokens * m->g.hidden * sizeof(float);
+    size_t n = (size_t)m->g.max_tokens * m->g.hidden;
+    if (bytes) CUDA_TRY(cudaMemcpyAsync(m->stage_in, host_residual, bytes, cudaMemcpyHostToDevice, st));
+    int rc = xabe_moe_block_forward(m, stream, w, m->stage_in, n, tokens, m->stage_ffn, n, m->stage_out, n);
+    if (rc) return rc;
+    if (bytes && host_ffn_out)
+        CUDA_TRY(cudaMemcpyAsync(host_ffn_out, m->stage_ffn, bytes, cudaMemcpyDeviceToHost, st));
+    if (bytes && host_l_out)
+        CUDA_TRY(cudaMemcpyAsync(host_l_out, m->stage_out, bytes, cudaMemcpyDeviceToHost, st));
+    return XABE_OK;
+}
+
+int xabe_dense_ffn_block_forward(xabe_moe* m, void* stream, const float* post_norm, xabe_quant_tensor gate,
+                                 xabe_quant_tensor up, xabe_quant_tensor down, const float* residual,
+                                 size_t residual_len, int tokens, float* ffn_out, size_t ffn_out_len,
+                                 float* l_out, size_t l_out_len) {
+    if (!m || !post_norm || !residual || !ffn_out || !l_out)
+        return fail(XABE_ERR_INVALID_ARGUMENT, "null argument to dense_ffn_block_forward");
+    const auto& g = m->g;
+    if (tokens < 0 || (uint32_t)tokens > g.max_tokens)
+        return fail(XABE_ERR_TOO_MANY_TOKENS, "%d tokens exceeds the %u this block was sized for", tokens,
+                    g.max_tokens);
+    size_t n = (size_t)g.max_tokens * g.hidden;
+    if (residual_len != n || ffn_out_len != n || l_out_len != n)
+        return fail(XABE_ERR_BUFFER_LENGTH, "dense block buffers must hold %zu floats", n);
+    int rc;
+    if ((rc = check_mlp(m, "dense", gate, up, down, 1))) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    if ((rc = xabe_moe_set_valid_tokens(m, stream, tokens))) return rc;
+    if ((rc = launch_rms_norm(m, st, residual, post_norm))) return rc;
+    MlpWeights s;
+    s.present = true;
+    s.gate = gate;
+    s.up = up;
+    s.down = down;
+    if ((rc = run_experts(m, st, MlpWeights{}, s, ffn_out))) return rc;
+    k_add_residual<<<g.max_tokens, 256, 0, st>>>(ffn_out, residual, m->valid_tokens, (int)g.hidden, l_out);
+    CUDA_TRY(cudaGetLastError());
+    return XABE_OK;
+}
+
+int xabe_moe_buffers(xabe_moe* m, xabe_moe_buffer_view* out) {
+    if (!m || !out) return fail(XABE_ERR_INVALID_ARGUMENT, "null argument to buffers");
+    out->valid_tokens = m->valid_tokens;
+    out->topk_ids = m->topk_ids;
+    out->topk_weights = m->topk_weights;
+    out->sorted_token_ids = m->sorted_token_ids;
+    out->expert_ids = m->expert_ids;
+    out->num_tokens_post_pad = m->num_tokens_post_pad;
+    out->partial = m->partial;
+    out->normed = m->normed;
+    out->logits = m->logits;
+    out->routed = m->routed;
+    out->shexp = m->shexp;
+    out->gate = m->gate;
+    out->sorted_capacity = m->sorted_capacity;
+    out->expert_block_capacity = m->block_capacity;
+    return XABE_OK;
+}
+
+int xabe_moe_set_exact_decode_regime(xabe_moe* m, int on) {
+    if (!m) return fail(XABE_ERR_INVALID_ARGUMENT, "null handle");
+    m->exact_decode = on != 0;
+    return XABE_OK;
+}
+
+int xabe_moe_device_status(xabe_moe* m, void* stream, int* status_out) {
+    if (!m || !status_out) return fail(XABE_ERR_INVALID_ARGUMENT, "null argument to device_status");
+    cudaStream_t st = (cudaStream_t)stream;
+    CUDA_TRY(cudaMemcpyAsync(m->h_status, m->status, sizeof(int), cudaMemcpyDeviceToHost, st));
+    CUDA_TRY(cudaMemsetAsync(m->status, 0, sizeof(int), st));
+    CUDA_TRY(cudaStreamSynchronize(st));
+    *status_out = *m->h_status;
+    if (*status_out != 0)
+        return fail(XABE_ERR_DEVICE_STATUS, "a kernel's bounded wait ran out (device status %d)", *status_out);
+    return XABE_OK;
+}
+
+int xabe_dequantize(void* stream, xabe_quant_tensor t, float* out) {
+    if (!out) return fail(XABE_ERR_INVALID_ARGUMENT, "null output");
+    if (t.quant != XABE_QUANT_Q6_K && t.quant != XABE_QUANT_Q8_0)
+        return fail(XABE_ERR_UNSUPPORTED_EXPERT_TYPE, "quant tag %d is neither Q6_K nor Q8_0", t.quant);
+    if (!t.dev_bytes) return fail(XABE_ERR_INVALID_ARGUMENT, "null device pointer");
+    size_t bb = block_bytes_of(t.quant);
+    if (t.n_bytes % bb != 0)
+        return fail(XABE_ERR_RAGGED_WEIGHTS, "dequantize: %zu bytes is not a whole number of %zu B blocks",
+                    t.n_bytes, bb);
+    size_t n = t.n_bytes / bb * block_elems_of(t.quant);
+    if (n == 0) return XABE_OK;
+    unsigned blocks = (unsigned)((n + 255) / 256);
+    if (t.quant == XABE_QUANT_Q6_K)
+        k_dequant_q6k<<<blocks, 256, 0, (cudaStream_t)stream>>>((const uint8_t*)t.dev_bytes, n, out);
+    else
+        k_dequant_q8_0<<<blocks, 256, 0, (cudaStream_t)stream>>>((const uint8_t*)t.dev_bytes, n, out);
+    CUDA_TRY(cudaGetLastError());
+    return XABE_OK;
+}
+
+}  // extern "C"

@@ -620,6 +620,8 @@ int xo_moe_block_forward(const xo_moe_layer* L, const float* residual, size_t to
             xo_rms_norm(x, L->post_norm, L->eps, H, nrm);
             xo_gemv(L->router, E, H, nrm, logits + (size_t)t * E);
         }
+        if (L->router_bias)
+            for (size_t e = 0; e < E; ++e) logits[(size_t)t * E + e] = logits[(size_t)t * E + e] + L->router_bias[e];
         xo_route_token(logits + (size_t)t * E, E, K, ids + (size_t)t * K, wts + (size_t)t * K);
     }
     int rc = xo_routed_forward_q(L, normed, tokens, ids, wts, threads, routed);

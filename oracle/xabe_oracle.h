@@ -117,6 +117,7 @@ typedef struct {
     uint32_t num_experts, top_k, hidden, inter;
     const float* post_norm;      /* [hidden] */
     const float* router;         /* [num_experts][hidden] */
+    const float* router_bias;    /* [num_experts] added to the logits, or NULL (benchmark Zipf skew) */
     const uint8_t* gate_exps; int gate_quant;   /* [E][inter][hidden] file layout */
     const uint8_t* up_exps;   int up_quant;
     const uint8_t* down_exps; int down_quant;   /* [E][hidden][inter] */

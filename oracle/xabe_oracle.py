@@ -61,6 +61,7 @@ class _Cmp(C.Structure):
 class _Layer(C.Structure):
     _fields_ = [("num_experts", C.c_uint32), ("top_k", C.c_uint32), ("hidden", C.c_uint32),
                 ("inter", C.c_uint32), ("post_norm", C.c_void_p), ("router", C.c_void_p),
+                ("router_bias", C.c_void_p),
                 ("gate_exps", C.c_void_p), ("gate_quant", C.c_int),
                 ("up_exps", C.c_void_p), ("up_quant", C.c_int),
                 ("down_exps", C.c_void_p), ("down_quant", C.c_int),
@@ -338,13 +339,16 @@ class Layer:
     def __init__(self, *, num_experts, top_k, hidden, inter, post_norm, router,
                  gate_exps, gate_quant, up_exps, up_quant, down_exps, down_quant,
                  shared_gate_inp, shared_gate, shared_gate_quant, shared_up, shared_up_quant,
-                 shared_down, shared_down_quant, eps=1e-6):
+                 shared_down, shared_down_quant, eps=1e-6, router_bias=None):
         self.keep = dict(post_norm=_f32(post_norm), router=_f32(router),
                          gate_exps=_u8(gate_exps), up_exps=_u8(up_exps), down_exps=_u8(down_exps),
                          shared_gate_inp=_f32(shared_gate_inp), shared_gate=_u8(shared_gate),
                          shared_up=_u8(shared_up), shared_down=_u8(shared_down))
         k = self.keep
+        if router_bias is not None:
+            k["router_bias"] = _f32(router_bias)
         self.c = _Layer(num_experts, top_k, hidden, inter, _p(k["post_norm"]), _p(k["router"]),
+                        _p(k["router_bias"]) if router_bias is not None else None,
                         _p(k["gate_exps"]), gate_quant, _p(k["up_exps"]), up_quant,
                         _p(k["down_exps"]), down_quant, _p(k["shared_gate_inp"]),
                         _p(k["shared_gate"]), shared_gate_quant, _p(k["shared_up"]),
