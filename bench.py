@@ -1,0 +1,315 @@
+"""Benchmark of the per-layer MoE FFN block.
+
+    python bench.py --gpus N --steps K --warmup W [--workload decode64] [--impl reference]
+
+A step is one pass of the block over one batch of synthetic tokens through one
+layer's weights.  Layers rotate every step over `--layers` resident layers so
+that weights come from HBM, not from L2.  `value` is tokens per second per
+layer over all ranks (inputs resident); `e2e` is the same through the
+host-buffer entry point, copies included.  At N > 1 every rank is a replica
+with its own layers and its own batch (weak scaling, no data-path collective),
+the reference's own multi-GPU model.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "moe_layer_tokens_per_s"
+UNIT = "tokens/s/layer"
+
+# name -> (tokens, bucket width, zipf skew).  Geometry 256 experts / top-8 / 2048 / 512, Q6_K everywhere.
+WORKLOADS = {
+    "decode1": (1, 16, False),      # BASELINE config 0
+    "decode3": (3, 16, True),       # BASELINE config 1, three sequences
+    "decode64": (64, 16, True),     # BASELINE config 1, 64 tokens  (default)
+    "prefill2048": (2048, 32, True),  # BASELINE config 2
+}
+
+Q6K_EXPERT_BYTES = 3 * (512 * 2048 // 256) * 210   # 2,580,480
+ROUTER_BYTES = 256 * 2048 * 4
+VEC_BYTES = 2 * 2048 * 4                           # post-norm weight + shared-gate vector
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return float(p["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+    return 6650.0, "fallback (no MEASURED_PEAKS.json)"
+
+
+def layer_algorithmic_bytes(distinct: int, tokens: int) -> int:
+    """Weights of the experts actually routed + shared expert + router + vectors + x in, ffn_out, l_out."""
+    return distinct * Q6K_EXPERT_BYTES + Q6K_EXPERT_BYTES + ROUTER_BYTES + VEC_BYTES + tokens * 3 * 2048 * 4
+
+
+def gateup_algorithmic_bytes(distinct: int, tokens: int) -> int:
+    """What the gate/up launch must move: gate and up of the routed experts and of the shared one,
+    the f16 activations in, the f16 intermediates out."""
+    per = 2 * (512 * 2048 // 256) * 210
+    return (distinct + 1) * per + tokens * 2048 * 2 + tokens * 9 * 512 * 2
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def host_layer_from_device(w):
+    """The oracle's view of a device layer (bytes copied back to the host)."""
+    from oracle import xabe_oracle as oracle
+    n = lambda t: t.detach().cpu().numpy()
+    return oracle.Layer(num_experts=256, top_k=8, hidden=2048, inter=512, post_norm=n(w.post_norm),
+                        router=n(w.router), router_bias=None if w.router_bias is None else n(w.router_bias),
+                        gate_exps=n(w.gate_exps.bytes), gate_quant=int(w.gate_exps.quant),
+                        up_exps=n(w.up_exps.bytes), up_quant=int(w.up_exps.quant),
+                        down_exps=n(w.down_exps.bytes), down_quant=int(w.down_exps.quant),
+                        shared_gate_inp=n(w.shared_gate_inp), shared_gate=n(w.shared_gate.bytes),
+                        shared_gate_quant=int(w.shared_gate.quant), shared_up=n(w.shared_up.bytes),
+                        shared_up_quant=int(w.shared_up.quant), shared_down=n(w.shared_down.bytes),
+                        shared_down_quant=int(w.shared_down.quant))
+
+
+def time_cpu_oracle(layer, x, steps: int, warmup: int, budget_s: float):
+    """Times the CPU oracle (every host thread) on a bounded sample of the batch.  Returns
+    (tokens/s, sample tokens, steps timed, threads)."""
+    from oracle import xabe_oracle as oracle
+    threads = oracle.max_threads()
+    sample = x.shape[0]
+    t0 = time.perf_counter()
+    oracle.moe_block_forward(layer, x[:sample], dev_order=False, threads=threads)
+    once = time.perf_counter() - t0
+    # shrink the per-step sample until warmup + steps fit the budget
+    while sample > 1 and once * (steps + warmup) > budget_s:
+        sample = max(1, sample // 2)
+        t0 = time.perf_counter()
+        oracle.moe_block_forward(layer, x[:sample], dev_order=False, threads=threads)
+        once = time.perf_counter() - t0
+    for _ in range(max(0, warmup - 1)):
+        oracle.moe_block_forward(layer, x[:sample], dev_order=False, threads=threads)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        oracle.moe_block_forward(layer, x[:sample], dev_order=False, threads=threads)
+    dt = time.perf_counter() - t0
+    return sample * steps / dt, sample, steps, threads, dt / steps * 1e3
+
+
+def run_reference(args) -> dict:
+    """`--impl reference`: the CPU oracle (the port of the reference's scalar path) on the host cores."""
+    tokens, block_size, zipf = WORKLOADS[args.workload]
+    from llmxabe_b200 import synth
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from helpers import oracle_layer
+    from oracle import xabe_oracle as oracle
+    L = synth.moe_layer(seed=0, layer=0, zipf=zipf)
+    layer = oracle_layer(oracle, L)
+    x = synth.activations(tokens, 2048, seed=0, layer=900)
+    tps, sample, steps, threads, ms = time_cpu_oracle(layer, x, args.steps, args.warmup, budget_s=150.0)
+    return {
+        "impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "tokens": tokens, "experts": 256, "top_k": 8, "hidden": 2048,
+                   "intermediate": 512, "quant": "Q6_K"},
+        "cpu_baseline": {"value": tps, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": f"{sample} of {tokens} tokens per step, one layer, OpenMP over tokens/experts"},
+        "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+
+
+def run_ours(args) -> dict:
+    import torch
+    import torch.distributed as dist
+
+    from llmxabe_b200 import synth
+    from llmxabe_b200.moe import MoeBlock, MoeGeometry
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the MoE path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    tokens, block_size, zipf = WORKLOADS[args.workload]
+    H = 2048
+    g = MoeGeometry.qwen3_6(block_size, tokens)
+    block = MoeBlock(g)
+    layers = [synth.moe_layer_on_device(seed=rank, layer=i, zipf=zipf) for i in range(args.layers)]
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(4242 + rank)
+    xs = [torch.randn(tokens, H, device="cuda", generator=gen) for _ in range(args.layers)]
+    ffn = torch.empty(tokens, H, device="cuda")
+    lout = torch.empty(tokens, H, device="cuda")
+    hx = [x.cpu().pin_memory() for x in xs]
+    hout = torch.empty(tokens, H).pin_memory()
+    stream = torch.cuda.current_stream()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step(i):
+        block.forward(layers[i % args.layers], xs[i % args.layers], tokens, ffn, lout)
+
+    def step_host(i):
+        block.forward_host(layers[i % args.layers], hx[i % args.layers], tokens, None, hout)
+        stream.synchronize()  # the caller reads the result every step
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(steps):
+            fn(i)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        barrier()
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    # warm-up: at least W steps and at least 0.3 s, so clocks are up (the reference warms by duration,
+    # crates/xabe-engine/src/bin/bench_dense_ffn.rs:57-65)
+    t0 = time.perf_counter()
+    i = 0
+    while i < max(args.warmup, 3) or time.perf_counter() - t0 < 0.3:
+        step(i)
+        i += 1
+    torch.cuda.synchronize()
+    # distinct experts each resident layer's batch routes (the "unique" denominator of the byte count)
+    distinct = []
+    for li in range(args.layers):
+        step(li)
+        torch.cuda.synchronize()
+        distinct.append(int(torch.unique(block.buffers().topk_ids[:tokens]).numel()))
+    d_mean = sum(distinct) / len(distinct)
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ms = timed(step, args.steps)
+    clocks = sampler.stop()
+    # the same region again with per-stage CUDA events, for the dominant kernel's duration
+    block.moe.stage_profile(True)
+    timed(step, min(args.steps, 256))
+    stage_ms, calls = block.moe.stage_times()
+    block.moe.stage_profile(False)
+    for i in range(3):
+        step_host(i)
+    ms_e2e = timed(step_host, args.steps)
+    status = block.moe.device_status()
+
+    peak, peak_src = measured_peaks()
+    gateup_ms = stage_ms["gate_up"] / max(calls, 1)
+    gu_bytes = gateup_algorithmic_bytes(d_mean, tokens)
+    achieved = gu_bytes / (gateup_ms * 1e-3) / 1e9 if gateup_ms > 0 else 0.0
+    layer_bytes = layer_algorithmic_bytes(d_mean, tokens)
+    out = {
+        "metric": METRIC, "value": world * tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16 activations x exact Q6_K codes, fp32 scales+accumulate",
+        "data": "synthetic",
+        "config": {"workload": args.workload, "tokens_per_rank": tokens, "experts": 256, "top_k": 8,
+                   "hidden": 2048, "intermediate": 512, "quant": "Q6_K", "bucket": block_size,
+                   "resident_layers": args.layers, "distinct_experts_mean": d_mean,
+                   "l2": f"layers rotate every step; each touches {layer_bytes / 1e6:.0f} MB of weights "
+                         f"(> 126 MB L2) out of {args.layers} resident layers",
+                   "parallelism": f"replicas x{world}"},
+        "e2e": {"value": world * tokens / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": tokens * H * 4, "d2h_bytes_per_step": tokens * H * 4},
+        "gpu_launches": 9 * args.steps,
+        "clocks": clocks,
+        "roofline": {"bound": "hbm", "kernel": "k_expert_gateup", "achieved": achieved, "peak": peak,
+                     "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                     "algorithmic_bytes_per_launch": gu_bytes, "ms_per_launch": gateup_ms},
+        "layer_roofline": {"algorithmic_bytes": layer_bytes, "achieved_gbs": layer_bytes / (ms * 1e-3) / 1e9,
+                           "frac": layer_bytes / (ms * 1e-3) / 1e9 / peak},
+        "stage_ms": {k: v / max(calls, 1) for k, v in stage_ms.items()},
+        "device_status": status,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu:
+        layer = host_layer_from_device(layers[0])
+        tps, sample, steps, threads, cms = time_cpu_oracle(layer, xs[0].cpu().numpy(), 3, 1, budget_s=30.0)
+        out["cpu_baseline"] = {"value": tps, "unit": UNIT, "cores": threads, "kind": "port",
+                               "sample": f"{sample} of {tokens} tokens x {steps} passes over layer 0 "
+                                         f"({cms:.0f} ms per pass)"}
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return out if rank == 0 else {}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="decode64", choices=sorted(WORKLOADS))
+    ap.add_argument("--layers", type=int, default=4, help="distinct resident layers the steps rotate over")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the timed CPU baseline")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        if int(os.environ.get("RANK", "0")) != 0:
+            return
+        print(json.dumps(run_reference(args)), flush=True)
+        return
+    out = run_ours(args)
+    if out:
+        print(json.dumps(out), flush=True)
+
+
+if __name__ == "__main__":
+    main()

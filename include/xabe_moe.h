@@ -218,6 +218,16 @@ int xabe_moe_set_exact_decode_regime(xabe_moe* m, int on);
  * 0 when every wait completed.  Synchronises `stream`. */
 int xabe_moe_device_status(xabe_moe* m, void* stream, int* status_out);
 
+/* StageProfile (crates/xabe-engine/src/forward.rs:783-855): CUDA-event spans
+ * around the stages of xabe_moe_block_forward, pre-allocated, off by default.
+ * Stages: 0 rms_norm, 1 router logits, 2 route + dispatch, 3 gate/up + SwiGLU
+ * (routed and shared), 4 down, 5 gate-and-combine.  xabe_moe_stage_times
+ * synchronises `stream`, returns the summed milliseconds per stage over the
+ * calls recorded since the last read (at most 256) and resets the record. */
+#define XABE_STAGE_COUNT 6
+int xabe_moe_stage_profile(xabe_moe* m, int on);
+int xabe_moe_stage_times(xabe_moe* m, void* stream, float* ms_sum, int* calls);
+
 /* Standalone dequantisation (crates/xabe-cuda/src/kernels/dequant.rs, gated
  * bit-identical by crates/xabe-engine/tests/dequant_differential.rs:1-18):
  * `out` receives n_bytes / block_bytes * block_elements floats. */

@@ -56,6 +56,8 @@ SYMBOLS = {
     "xabe_moe_buffers": (_i, [_vp, C.POINTER(BufferViewC)]),
     "xabe_moe_set_exact_decode_regime": (_i, [_vp, _i]),
     "xabe_moe_device_status": (_i, [_vp, _vp, C.POINTER(_i)]),
+    "xabe_moe_stage_profile": (_i, [_vp, _i]),
+    "xabe_moe_stage_times": (_i, [_vp, _vp, C.POINTER(C.c_float), C.POINTER(_i)]),
     "xabe_dequantize": (_i, [_vp, QuantTensorC, _vp]),
 }
 

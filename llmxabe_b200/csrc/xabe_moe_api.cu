@@ -85,10 +85,20 @@ struct xabe_moe {
     float* stage_in = nullptr;
     float* stage_ffn = nullptr;
     float* stage_out = nullptr;
-    int smem_gateup = 0, smem_down = 0;
+    // stage profile: CUDA-event spans around each stage of block_forward
+    bool prof_on = false;
+    int prof_calls = 0;
+    cudaEvent_t* prof_events = nullptr;  // [kProfCalls][XABE_STAGE_COUNT + 1]
 };
 
 namespace {
+
+constexpr int kProfCalls = 256;
+
+inline void prof_mark(xabe_moe* m, cudaStream_t st, int idx) {
+    if (m->prof_on && m->prof_calls < kProfCalls)
+        cudaEventRecord(m->prof_events[m->prof_calls * (XABE_STAGE_COUNT + 1) + idx], st);
+}
 
 template <typename T>
 cudaError_t dev_alloc(T** p, size_t n) {
@@ -162,7 +172,7 @@ struct MlpWeights {
 // Both projections of the routed experts and/or the shared expert, each in one
 // launch.  `routed`/`shared` say which halves ride the launch.
 int run_experts(xabe_moe* m, cudaStream_t st, const MlpWeights& routed, const MlpWeights& shared,
-                float* shexp_out) {
+                float* shexp_out, int mark_between = -1) {
     const auto& g = m->g;
     if (!routed.present && !shared.present) return XABE_OK;
     if (routed.present && routed.gate.quant != routed.up.quant)
@@ -205,6 +215,7 @@ int run_experts(xabe_moe* m, cudaStream_t st, const MlpWeights& routed, const Ml
         return fail(XABE_ERR_UNSUPPORTED_GEOMETRY, "gate/up row tile of %zu bytes does not fit shared memory", smem);
     int rc = DISPATCH_QQ(launch_gateup, qr, qs, m, st, L, routed_blocks + shared_tiles, smem);
     if (rc) return rc;
+    if (mark_between >= 0) prof_mark(m, st, mark_between);
     // down
     qr = routed.present ? routed.down.quant : shared.down.quant;
     qs = shared.present ? shared.down.quant : qr;
@@ -418,6 +429,10 @@ void xabe_moe_destroy(xabe_moe* m) {
     for (void* p : dev)
         if (p) cudaFree(p);
     if (m->h_status) cudaFreeHost(m->h_status);
+    if (m->prof_events) {
+        for (int i = 0; i < kProfCalls * (XABE_STAGE_COUNT + 1); ++i) cudaEventDestroy(m->prof_events[i]);
+        delete[] m->prof_events;
+    }
     delete m;
 }
 
@@ -521,9 +536,13 @@ int xabe_moe_block_forward(xabe_moe* m, void* stream, const xabe_moe_layer_weigh
     if ((rc = check_mlp(m, "shared", w->shared_gate, w->shared_up, w->shared_down, 1))) return rc;
     cudaStream_t st = (cudaStream_t)stream;
     if ((rc = xabe_moe_set_valid_tokens(m, stream, tokens))) return rc;
+    prof_mark(m, st, 0);
     if ((rc = launch_rms_norm(m, st, residual, w->post_norm))) return rc;
+    prof_mark(m, st, 1);
     if ((rc = launch_router(m, st, w->router, w->router_bias))) return rc;
+    prof_mark(m, st, 2);
     if ((rc = launch_route_and_dispatch(m, st, m->logits))) return rc;
+    prof_mark(m, st, 3);
     MlpWeights r, s;
     r.present = s.present = true;
     r.gate = w->gate_exps;
@@ -532,12 +551,15 @@ int xabe_moe_block_forward(xabe_moe* m, void* stream, const xabe_moe_layer_weigh
     s.gate = w->shared_gate;
     s.up = w->shared_up;
     s.down = w->shared_down;
-    if ((rc = run_experts(m, st, r, s, m->shexp))) return rc;
+    if ((rc = run_experts(m, st, r, s, m->shexp, 4))) return rc;
+    prof_mark(m, st, 5);
     dim3 grid(g.max_tokens, (g.hidden + 255) / 256);
     k_gate_and_combine<<<grid, 256, 0, st>>>(w->shared_gate_inp, m->normed, m->partial, m->shexp, residual,
                                              m->valid_tokens, (int)g.experts_per_token, (int)g.hidden, m->gate,
                                              m->routed, ffn_out, l_out);
     CUDA_TRY(cudaGetLastError());
+    prof_mark(m, st, 6);
+    if (m->prof_on && m->prof_calls < kProfCalls) m->prof_calls++;
     return XABE_OK;
 }
 
@@ -623,6 +645,35 @@ int xabe_moe_device_status(xabe_moe* m, void* stream, int* status_out) {
     *status_out = *m->h_status;
     if (*status_out != 0)
         return fail(XABE_ERR_DEVICE_STATUS, "a kernel's bounded wait ran out (device status %d)", *status_out);
+    return XABE_OK;
+}
+
+int xabe_moe_stage_profile(xabe_moe* m, int on) {
+    if (!m) return fail(XABE_ERR_INVALID_ARGUMENT, "null handle");
+    if (on && !m->prof_events) {
+        int n = kProfCalls * (XABE_STAGE_COUNT + 1);
+        m->prof_events = new (std::nothrow) cudaEvent_t[n];
+        if (!m->prof_events) return fail(XABE_ERR_DRIVER, "out of host memory");
+        for (int i = 0; i < n; ++i) CUDA_TRY(cudaEventCreate(&m->prof_events[i]));
+    }
+    m->prof_on = on != 0;
+    m->prof_calls = 0;
+    return XABE_OK;
+}
+
+int xabe_moe_stage_times(xabe_moe* m, void* stream, float* ms_sum, int* calls) {
+    if (!m || !ms_sum || !calls) return fail(XABE_ERR_INVALID_ARGUMENT, "null argument to stage_times");
+    CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
+    for (int s = 0; s < XABE_STAGE_COUNT; ++s) ms_sum[s] = 0.0f;
+    for (int c = 0; c < m->prof_calls; ++c)
+        for (int s = 0; s < XABE_STAGE_COUNT; ++s) {
+            float ms = 0.0f;
+            cudaEvent_t* e = m->prof_events + c * (XABE_STAGE_COUNT + 1);
+            CUDA_TRY(cudaEventElapsedTime(&ms, e[s], e[s + 1]));
+            ms_sum[s] += ms;
+        }
+    *calls = m->prof_calls;
+    m->prof_calls = 0;
     return XABE_OK;
 }
 

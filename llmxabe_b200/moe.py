@@ -178,6 +178,19 @@ class MoeKernels:
         _check(_lib.lib().xabe_moe_device_status(self._h, _stream_ptr(stream), C.byref(st)))
         return st.value
 
+    STAGES = ("rms_norm", "router_logits", "route_dispatch", "gate_up", "down", "combine")
+
+    def stage_profile(self, on: bool) -> None:
+        """StageProfile of the reference (crates/xabe-engine/src/forward.rs:783-855)."""
+        _check(_lib.lib().xabe_moe_stage_profile(self._h, int(on)))
+
+    def stage_times(self, stream=None) -> tuple[dict, int]:
+        """Summed milliseconds per stage and the number of block calls they cover."""
+        ms = (C.c_float * len(self.STAGES))()
+        calls = C.c_int(0)
+        _check(_lib.lib().xabe_moe_stage_times(self._h, _stream_ptr(stream), ms, C.byref(calls)))
+        return dict(zip(self.STAGES, [float(v) for v in ms])), calls.value
+
     # -- MoeBuffers accessors as torch views over the handle's scratch
     def buffers(self) -> "MoeBuffers":
         v = _lib.BufferViewC()

@@ -131,3 +131,52 @@ def dense_layer(*, seed: int = 0, layer: int = 0, hidden: int = 5120, inter: int
     n = hidden * inter
     return (np.ones(hidden, dtype=np.float32), quant_bytes(quant, n, seed, layer, _T_SGATE),
             quant_bytes(quant, n, seed, layer, _T_SUP), quant_bytes(quant, n, seed, layer, _T_SDOWN))
+
+
+# ---------------------------------------------------------------------------
+# The same distributions generated ON the device (torch), for benchmark layers
+# that are only ever checked through size-independent properties: a 667 MB
+# layer takes milliseconds instead of ten seconds of host time.  Not
+# bit-identical to the numpy generator above.
+# ---------------------------------------------------------------------------
+def _device_quant_bytes(torch, quant: int, n_elements: int, gen, device):
+    if quant == Q6K:
+        nsb = n_elements // 256
+        out = torch.empty((nsb, 210), dtype=torch.uint8, device=device)
+        out[:, :192] = torch.randint(0, 256, (nsb, 192), dtype=torch.uint8, device=device, generator=gen)
+        out[:, 192:208] = torch.randint(-32, 32, (nsb, 16), dtype=torch.int8, device=device,
+                                        generator=gen).view(torch.uint8)
+        d = (torch.randn(nsb, device=device, generator=gen).abs() * 2e-4).to(torch.float16)
+        out[:, 208:210] = d.view(torch.uint8).view(nsb, 2)
+        return out.view(-1)
+    nb = n_elements // 32
+    out = torch.empty((nb, 34), dtype=torch.uint8, device=device)
+    d = (torch.randn(nb, device=device, generator=gen).abs() * (2e-4 * Q8_0_SCALE_MATCH)).to(torch.float16)
+    out[:, 0:2] = d.view(torch.uint8).view(nb, 2)
+    out[:, 2:34] = torch.randint(-128, 128, (nb, 32), dtype=torch.int8, device=device,
+                                 generator=gen).view(torch.uint8)
+    return out.view(-1)
+
+
+def moe_layer_on_device(*, seed: int = 0, layer: int = 0, num_experts: int = 256, top_k: int = 8,
+                        hidden: int = 2048, inter: int = 512, routed_quant: int = Q6K,
+                        down_quant: int | None = None, shared_quant: int = Q6K, zipf: bool = False,
+                        device="cuda"):
+    """A `MoeLayerWeights` whose tensors are generated on `device` (see the note above)."""
+    import torch
+    from .moe import MoeLayerWeights
+    down_quant = routed_quant if down_quant is None else down_quant
+    gen = torch.Generator(device=device)
+    gen.manual_seed((seed * 1000003 + layer) & 0x7FFFFFFF)
+    n = num_experts * inter * hidden
+    q = lambda quant, count: _device_quant_bytes(torch, quant, count, gen, device)
+    bias = torch.from_numpy(zipf_bias(num_experts, seed, layer)) if zipf else None
+    return MoeLayerWeights(
+        layer=layer, post_norm=torch.ones(hidden, device=device),
+        router=torch.randn(num_experts, hidden, device=device, generator=gen) * 0.02, router_bias=bias,
+        gate_exps=q(routed_quant, n), gate_quant=routed_quant, up_exps=q(routed_quant, n),
+        up_quant=routed_quant, down_exps=q(down_quant, n), down_quant=down_quant,
+        shared_gate_inp=torch.randn(hidden, device=device, generator=gen) * 0.02,
+        shared_gate=q(shared_quant, inter * hidden), shared_gate_quant=shared_quant,
+        shared_up=q(shared_quant, inter * hidden), shared_up_quant=shared_quant,
+        shared_down=q(shared_quant, inter * hidden), shared_down_quant=shared_quant, device=device)
