@@ -60,9 +60,12 @@ __global__ void k_rows_to_half(const float* __restrict__ x, __half* __restrict__
 // shuffle-down tree inside each group of 32 consecutive lanes; the eight
 // group totals added in ascending order starting from +0.  Here one real warp
 // carries all 256 lanes of one expert (lane l holds lanes l, l+32, ...), so
-// the weight row is read once, fully coalesced, and the result is
-// bit-identical for every token-tile width TT.
-// grid: (ceil(E / 4), ceil(max_tokens / TT)), block 128 (one expert per warp).
+// the result is bit-identical for every token-tile width TT.
+// The four expert rows of a CTA (contiguous in the router tensor) arrive in
+// shared memory through ONE bulk TMA copy: every byte of the row is in flight
+// at once instead of one dependent DRAM round trip per loop iteration.
+// grid: (ceil(E / 4), ceil(max_tokens / (TT * tiles_per_cta))), block 128.
+// dynamic shared memory: 4 * hidden * 4 bytes.
 // ---------------------------------------------------------------------------
 template <int TT>
 __global__ void __launch_bounds__(128) k_router_logits(const float* __restrict__ w,
@@ -70,47 +73,71 @@ __global__ void __launch_bounds__(128) k_router_logits(const float* __restrict__
                                                         const int* __restrict__ valid_tokens,
                                                         int hidden, int num_experts,
                                                         const float* __restrict__ bias,
-                                                        float* __restrict__ logits) {
+                                                        float* __restrict__ logits, int tiles_per_cta,
+                                                        int* __restrict__ status) {
+    extern __shared__ __align__(128) float w_rows[];
+    __shared__ __align__(8) uint64_t bar;
     int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    int e = blockIdx.x * 4 + warp;
-    int t0 = blockIdx.y * TT;
+    int e0 = blockIdx.x * 4;
+    int e = e0 + warp;
+    int t_first = blockIdx.y * TT * tiles_per_cta;
     int live = *valid_tokens;
-    if (e >= num_experts || t0 >= live) return;
-    float acc[8][TT];
-#pragma unroll
-    for (int g = 0; g < 8; ++g)
-#pragma unroll
-        for (int u = 0; u < TT; ++u) acc[g][u] = 0.0f;
-    const float* wrow = w + (size_t)e * hidden;
-    const float* xr[TT];
-#pragma unroll
-    for (int u = 0; u < TT; ++u) {
-        int t = t0 + u < live ? t0 + u : live - 1;
-        xr[u] = x + (size_t)t * hidden;
+    if (t_first >= live) return;
+    if (threadIdx.x == 0) {
+        int rows = min(4, num_experts - e0);
+        uint32_t bytes = (uint32_t)rows * hidden * 4u;
+        mbar_init(&bar, 1);
+        fence_mbar_init();
+        mbar_expect_tx(&bar, bytes);
+        tma_bulk_g2s(w_rows, w + (size_t)e0 * hidden, bytes, &bar);
     }
-    for (int jc = 0; jc < hidden; jc += 256) {
+    __syncthreads();
+    if (!__syncthreads_and(mbar_wait_bounded(&bar, 0, status))) return;
+    if (e >= num_experts) return;
+    const float* wrow = w_rows + (size_t)warp * hidden;
+    for (int tile = 0; tile < tiles_per_cta; ++tile) {
+        int t0 = t_first + tile * TT;
+        if (t0 >= live) break;
+        float acc[8][TT];
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-            int j = jc + g * 32 + lane;
-            if (j < hidden) {
-                float wj = __ldg(wrow + j);
+        for (int g = 0; g < 8; ++g)
 #pragma unroll
-                for (int u = 0; u < TT; ++u) acc[g][u] = fmaf(wj, xr[u][j], acc[g][u]);
+            for (int u = 0; u < TT; ++u) acc[g][u] = 0.0f;
+        const float* xr[TT];
+#pragma unroll
+        for (int u = 0; u < TT; ++u) {
+            int t = t0 + u < live ? t0 + u : live - 1;
+            xr[u] = x + (size_t)t * hidden;
+        }
+        // hidden is a multiple of 256 (checked when the handle is created).  Loads are
+        // issued in batches of eight before the multiply-adds that consume them, so a
+        // warp keeps eight cache lines in flight instead of stalling on each one.
+        for (int jc = 0; jc < hidden; jc += 256) {
+            float wv[8];
+#pragma unroll
+            for (int g = 0; g < 8; ++g) wv[g] = wrow[jc + g * 32 + lane];
+#pragma unroll
+            for (int u = 0; u < TT; ++u) {
+                float xv[8];
+#pragma unroll
+                for (int g = 0; g < 8; ++g) xv[g] = __ldg(xr[u] + jc + g * 32 + lane);
+#pragma unroll
+                for (int g = 0; g < 8; ++g) acc[g][u] = fmaf(wv[g], xv[g], acc[g][u]);
             }
         }
-    }
 #pragma unroll
-    for (int u = 0; u < TT; ++u) {
-        float total = 0.0f;
+        for (int u = 0; u < TT; ++u) {
+            float total = 0.0f;
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-            float v = acc[g][u];
+            for (int g = 0; g < 8; ++g) {
+                float v = acc[g][u];
 #pragma unroll
-            for (int off = 16; off > 0; off >>= 1) v += __shfl_down_sync(0xffffffffu, v, off);
-            total += v;  // only lane 0's value is the tree's root
+                for (int off = 16; off > 0; off >>= 1) v += __shfl_down_sync(0xffffffffu, v, off);
+                total += v;  // only lane 0's value is the tree's root
+            }
+            if (lane == 0 && t0 + u < live)
+                logits[(size_t)(t0 + u) * num_experts + e] = bias ? __fadd_rn(total, bias[e]) : total;
         }
-        if (lane == 0 && t0 + u < live)
-            logits[(size_t)(t0 + u) * num_experts + e] = bias ? __fadd_rn(total, bias[e]) : total;
     }
 }
 
@@ -125,8 +152,7 @@ __global__ void __launch_bounds__(128) k_router_logits(const float* __restrict__
 // shuffle-downs.  num_experts <= 512.
 // grid: (ceil(max_tokens / 8)), block 256.
 // ---------------------------------------------------------------------------
-constexpr int kRouteLaneExperts = 16;
-
+template <int kRouteLaneExperts>
 __device__ __forceinline__ void route_one_token(const float* __restrict__ row, int num_experts, int top_k,
                                                 int lane, int* __restrict__ ids_out,
                                                 float* __restrict__ w_out) {
@@ -149,7 +175,7 @@ __device__ __forceinline__ void route_one_token(const float* __restrict__ row, i
     // lane v of 256: v = lane + 32*i (i < 8) holds p[i] + p[i + 8]
     float v8[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) v8[i] = p[i] + p[i + 8];
+    for (int i = 0; i < 8; ++i) v8[i] = kRouteLaneExperts > 8 ? p[i] + p[(i + 8) % kRouteLaneExperts] : p[i];
 #pragma unroll
     for (int i = 0; i < 4; ++i) v8[i] += v8[i + 4];  // step 128
     v8[0] += v8[2];                                  // step 64
@@ -199,8 +225,12 @@ __global__ void __launch_bounds__(256) k_route(const float* __restrict__ logits,
     int lane = threadIdx.x & 31;
     int token = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (token >= *valid_tokens) return;
-    route_one_token(logits + (size_t)token * num_experts, num_experts, top_k, lane,
-                    topk_ids + (size_t)token * top_k, topk_weights + (size_t)token * top_k);
+    if (num_experts <= 256)
+        route_one_token<8>(logits + (size_t)token * num_experts, num_experts, top_k, lane,
+                           topk_ids + (size_t)token * top_k, topk_weights + (size_t)token * top_k);
+    else
+        route_one_token<16>(logits + (size_t)token * num_experts, num_experts, top_k, lane,
+                            topk_ids + (size_t)token * top_k, topk_weights + (size_t)token * top_k);
 }
 
 // ---------------------------------------------------------------------------
@@ -238,8 +268,8 @@ __global__ void __launch_bounds__(32) k_align_count(const int* __restrict__ topk
 
 // One block, one thread per expert (num_experts <= 1024).
 __global__ void k_align_scan(int num_experts, int n_chunks, int block_size, int* __restrict__ chunk_hist,
-                             int* __restrict__ expert_offsets, int* __restrict__ expert_ids,
-                             int* __restrict__ num_tokens_post_pad) {
+                             int* __restrict__ expert_offsets, int* __restrict__ expert_counts,
+                             int* __restrict__ expert_ids, int* __restrict__ num_tokens_post_pad) {
     extern __shared__ int padded[];  // [num_experts + 1]
     int e = threadIdx.x;
     int total = 0;
@@ -250,6 +280,7 @@ __global__ void k_align_scan(int num_experts, int n_chunks, int block_size, int*
             total += h;
         }
         padded[e] = (total + block_size - 1) / block_size * block_size;
+        expert_counts[e] = total;
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -297,6 +328,223 @@ __global__ void __launch_bounds__(32) k_align_scatter(const int* __restrict__ to
             if (rank == 0) cursor[e] += __popc(same);
         }
         __syncwarp();
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Column groups: the unit of work of the streaming expert kernels.  The live
+// slots of an expert are contiguous in sorted_token_ids (from its padded
+// offset), so they are cut into groups of up to 8 consecutive slots = the 8
+// token columns of one n8 tensor-core tile.  One item is 20 ints (80 bytes,
+// 16-byte aligned): expert, first slot, columns, pad, 8 flat (token, k) ids,
+// 8 routing weights (float bits).
+// ---------------------------------------------------------------------------
+constexpr int kWorkItemInts = 20;
+
+__device__ __forceinline__ void emit_expert_groups(int e, int count, int start, int base,
+                                                   const int* __restrict__ sorted_token_ids,
+                                                   const float* __restrict__ topk_weights,
+                                                   int* __restrict__ work_items) {
+    int groups = (count + 7) >> 3;
+    for (int i = 0; i < groups; ++i) {
+        int* it = work_items + (size_t)(base + i) * kWorkItemInts;
+        int first = start + 8 * i;
+        int ncols = min(8, count - 8 * i);
+        it[0] = e;
+        it[1] = first;
+        it[2] = ncols;
+        it[3] = 0;
+        for (int c = 0; c < 8; ++c) {
+            int flat = c < ncols ? sorted_token_ids[first + c] : 0;
+            it[4 + c] = flat;
+            it[12 + c] = c < ncols ? __float_as_int(topk_weights[flat]) : 0;
+        }
+    }
+}
+
+// General path, after k_align_scatter.  One block, one thread per expert.
+__global__ void k_build_work(int num_experts, const int* __restrict__ expert_offsets,
+                             const int* __restrict__ expert_counts, const int* __restrict__ sorted_token_ids,
+                             const float* __restrict__ topk_weights, int* __restrict__ work_items,
+                             int* __restrict__ n_work) {
+    extern __shared__ int base_s[];  // [num_experts + 1]
+    int e = threadIdx.x;
+    if (e < num_experts) base_s[e] = (expert_counts[e] + 7) >> 3;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int i = 0; i < num_experts; ++i) {
+            int g = base_s[i];
+            base_s[i] = run;
+            run += g;
+        }
+        *n_work = run;
+    }
+    __syncthreads();
+    if (e < num_experts)
+        emit_expert_groups(e, expert_counts[e], expert_offsets[e], base_s[e], sorted_token_ids, topk_weights,
+                           work_items);
+}
+
+// ---------------------------------------------------------------------------
+// Decode widths (at most 2048 flat pairs): routing, the dispatch tables and
+// the column groups in ONE single-CTA launch instead of five.  Same results
+// as the general path: warps route tokens; per-warp chunks of the flat list
+// are histogrammed, offset and scattered in ascending flat order.
+// block 256 (8 warps); dynamic shared memory: (3 * 2048 + 11 * E + 2) ints.
+// `logits` NULL = the routing was done by k_route already.
+// ---------------------------------------------------------------------------
+constexpr int kSmallPairs = 2048;
+
+__global__ void __launch_bounds__(256) k_route_dispatch_small(
+    const float* __restrict__ logits, const int* __restrict__ valid_tokens, int num_experts, int top_k,
+    int block_size, int sorted_capacity, int block_capacity, int* __restrict__ topk_ids,
+    float* __restrict__ topk_weights, int* __restrict__ sorted_token_ids, int* __restrict__ expert_ids,
+    int* __restrict__ num_tokens_post_pad, int* __restrict__ expert_offsets, int* __restrict__ expert_counts,
+    int* __restrict__ work_items, int* __restrict__ n_work) {
+    extern __shared__ int sm[];
+    int* ids_s = sm;                          // [kSmallPairs]
+    int* hist = ids_s + kSmallPairs;          // [8][E] per-warp chunk histograms -> cursors
+    int* start_s = hist + 8 * num_experts;    // [E + 1] padded exclusive offsets
+    int* count_s = start_s + num_experts + 1; // [E] live counts
+    int* cstart_s = count_s + num_experts;    // [E] unpadded exclusive offsets
+    int* sorted_s = cstart_s + num_experts;   // [kSmallPairs] live flat ids in dispatch order
+    float* wts_s = (float*)(sorted_s + kSmallPairs);  // [kSmallPairs] routing weights by flat id
+    int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int live = *valid_tokens;
+    int numel = live * top_k;
+    if (logits) {  // at most one token per warp is routed here; wider steps route in k_route first
+        for (int t = warp; t < live; t += 8) {
+            if (num_experts <= 256)
+                route_one_token<8>(logits + (size_t)t * num_experts, num_experts, top_k, lane,
+                                   topk_ids + (size_t)t * top_k, topk_weights + (size_t)t * top_k);
+            else
+                route_one_token<16>(logits + (size_t)t * num_experts, num_experts, top_k, lane,
+                                    topk_ids + (size_t)t * top_k, topk_weights + (size_t)t * top_k);
+        }
+    }
+    for (int i = tid; i < 8 * num_experts; i += 256) hist[i] = 0;
+    for (int i = tid; i < sorted_capacity; i += 256) sorted_token_ids[i] = numel;
+    for (int i = tid; i < block_capacity; i += 256) expert_ids[i] = -1;
+    __syncthreads();  // ids are in global memory, written by this block
+    for (int i = tid; i < numel; i += 256) {
+        ids_s[i] = topk_ids[i];
+        wts_s[i] = topk_weights[i];
+    }
+    __syncthreads();
+    // warp w owns flat pairs [w * chunk, (w + 1) * chunk), chunk a multiple of 32
+    int chunk = ((numel + 7) / 8 + 31) / 32 * 32;
+    int begin = warp * chunk, end = min(numel, begin + chunk);
+    for (int i = begin + lane; i < end; i += 32) atomicAdd(&hist[warp * num_experts + ids_s[i]], 1);
+    __syncthreads();
+    for (int e = tid; e < num_experts; e += 256) {
+        int total = 0;
+        for (int w = 0; w < 8; ++w) {
+            int h = hist[w * num_experts + e];
+            hist[w * num_experts + e] = total;
+            total += h;
+        }
+        count_s[e] = total;
+        start_s[e] = (total + block_size - 1) / block_size * block_size;
+    }
+    __syncthreads();
+    if (warp == 0) {  // exclusive scan of the padded counts: each lane owns a contiguous run of experts
+        int per = (num_experts + 31) / 32;
+        int lo = lane * per, hi = min(num_experts, lo + per);
+        int sum = 0, csum = 0;
+        for (int e = lo; e < hi; ++e) {
+            sum += start_s[e];
+            csum += count_s[e];
+        }
+        int incl = sum, cincl = csum;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            int v = __shfl_up_sync(0xffffffffu, incl, off);
+            int cv = __shfl_up_sync(0xffffffffu, cincl, off);
+            if (lane >= off) {
+                incl += v;
+                cincl += cv;
+            }
+        }
+        int run = incl - sum, crun = cincl - csum;
+        for (int e = lo; e < hi; ++e) {
+            int p = start_s[e];
+            start_s[e] = run;
+            run += p;
+            cstart_s[e] = crun;
+            crun += count_s[e];
+        }
+        if (lane == 31) {
+            start_s[num_experts] = incl;
+            *num_tokens_post_pad = incl;
+        }
+    }
+    __syncthreads();
+    for (int e = tid; e < num_experts; e += 256) {
+        int s0 = start_s[e], s1 = start_s[e + 1];
+        expert_offsets[e] = s0;
+        expert_counts[e] = count_s[e];
+        for (int b = s0 / block_size; b < s1 / block_size; ++b) expert_ids[b] = e;
+        for (int w = 0; w < 8; ++w) hist[w * num_experts + e] += s0;
+    }
+    if (tid == 0) expert_offsets[num_experts] = start_s[num_experts];
+    __syncthreads();
+    int* cursor = hist + warp * num_experts;
+    for (int i0 = begin; i0 < end; i0 += 32) {
+        int i = i0 + lane;
+        bool on = i < end;
+        unsigned active = __ballot_sync(0xffffffffu, on);
+        if (on) {
+            int e = ids_s[i];
+            unsigned same = __match_any_sync(active, e);
+            int rank = __popc(same & ((1u << lane) - 1u));
+            int pos = cursor[e] + rank;
+            sorted_token_ids[pos] = i;
+            sorted_s[cstart_s[e] + (pos - start_s[e])] = i;
+            __syncwarp(active);
+            if (rank == 0) cursor[e] += __popc(same);
+        }
+        __syncwarp();
+    }
+    __syncthreads();
+    // column groups: reuse hist[0..E) as the group base
+    for (int e = tid; e < num_experts; e += 256) hist[e] = (count_s[e] + 7) >> 3;
+    __syncthreads();
+    if (warp == 0) {
+        int per = (num_experts + 31) / 32;
+        int lo = lane * per, hi = min(num_experts, lo + per);
+        int sum = 0;
+        for (int e = lo; e < hi; ++e) sum += hist[e];
+        int incl = sum;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            int v = __shfl_up_sync(0xffffffffu, incl, off);
+            if (lane >= off) incl += v;
+        }
+        int run = incl - sum;
+        for (int e = lo; e < hi; ++e) {
+            int gcount = hist[e];
+            hist[e] = run;
+            run += gcount;
+        }
+        if (lane == 31) *n_work = incl;
+    }
+    __syncthreads();
+    for (int e = tid; e < num_experts; e += 256) {
+        int count = count_s[e], groups = (count + 7) >> 3;
+        for (int i = 0; i < groups; ++i) {
+            int* it = work_items + (size_t)(hist[e] + i) * kWorkItemInts;
+            int ncols = min(8, count - 8 * i);
+            it[0] = e;
+            it[1] = start_s[e] + 8 * i;
+            it[2] = ncols;
+            it[3] = 0;
+            for (int c = 0; c < 8; ++c) {
+                int flat = c < ncols ? sorted_s[cstart_s[e] + 8 * i + c] : 0;
+                it[4 + c] = flat;
+                it[12 + c] = c < ncols ? __float_as_int(wts_s[flat]) : 0;
+            }
+        }
     }
 }
 

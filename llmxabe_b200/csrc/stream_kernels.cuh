@@ -1,0 +1,491 @@
+// Streaming expert projections: persistent CTAs, one per SM, that keep a ring
+// of TMA-filled weight tiles in flight while sixteen consumer warps unpack and
+// multiply.  This is the tuned path for the decode-shaped geometry (a
+// contraction of at most 8 superblocks for gate/up and 2 for down); other
+// shapes use the one-tile-per-CTA kernels of expert_kernels.cuh.
+//
+// Unit of work: (column group, run of row tiles).  A column group is up to 8
+// token columns of one expert (or of the shared expert): the n8 dimension of
+// the tensor-core tile.  For one unit the producer warp copies the group's f16
+// activation rows and its descriptor into shared memory once, then streams the
+// unit's weight tiles through the ring; each consumer warp loads its B
+// fragments from the activation rows into registers once per unit, so the
+// inner loop touches nothing but the weight tile.
+//
+// Arithmetic (same contract as expert_kernels.cuh): exact integer codes as the
+// f16 A operand, one k16 step per scale group, fp32 scale applied to the
+// step's fp32 result, fp32 accumulation.  gate/up: the eight consumer warps of
+// a group split the contraction by superblock and their partial tiles are
+// added in ascending warp order.  A token's value never depends on the other
+// columns of its group, on the group's position in the list, or on which CTA
+// or ring stage carried it.
+//
+// Every wait is bounded: on a timeout the warp records STATUS_TMA_TIMEOUT,
+// raises the CTA's abort flag (which every other wait polls) and returns.
+#pragma once
+
+#include "common.cuh"
+#include "glue_kernels.cuh"
+
+namespace xabe {
+
+constexpr int kStreamGroups = 2;
+constexpr int kStreamGroupWarps = 8;
+constexpr int kStreamConsumerWarps = kStreamGroups * kStreamGroupWarps;
+constexpr int kStreamThreads = 32 * (1 + kStreamConsumerWarps);  // warp 0 is the producer
+constexpr int kStreamMaxStages = 4;
+constexpr int kXRowPadBytes = 32;  // makes the B-fragment reads bank-conflict free
+
+constexpr int MODE_GATEUP = 0;
+constexpr int MODE_DOWN = 1;
+
+struct StreamLaunch {
+    const uint8_t* r_a;  // routed gate (or down) stack
+    const uint8_t* r_b;  // routed up stack
+    const uint8_t* s_a;  // shared gate (or down)
+    const uint8_t* s_b;  // shared up
+    int rows;            // output rows per matrix
+    int k;               // contraction length
+    int top_k;
+    int has_routed, has_shared;
+    const int* work_items;  // column groups (kWorkItemInts each)
+    const int* n_work;      // device scalar
+    const int* valid_tokens;
+    const __half* x_routed;  // gate/up: normed_h [token]; down: inter [slot]
+    const __half* x_shared;  // gate/up: normed_h [token]; down: inter_shared [token]
+    __half* inter_routed;    // gate/up out, [slot][rows]
+    __half* inter_shared;    // gate/up out, [token][rows]
+    float* partial;          // down out, [flat][rows]
+    float* shexp;            // down out, [token][rows]
+    int* status;
+    int n_stages;
+    uint32_t tile_cap;    // staged bytes reserved per tensor per stage (multiple of 16)
+    uint32_t x_stride;    // bytes between activation rows in shared memory
+};
+
+struct StreamSmem {
+    // byte offsets into dynamic shared memory, identical on host and device
+    uint32_t stages, xbuf, items, red, bars, total;
+};
+
+__host__ __device__ inline StreamSmem stream_smem_layout(int mode, int n_stages, uint32_t tile_cap,
+                                                         uint32_t x_stride) {
+    StreamSmem L;
+    uint32_t stage_bytes = (mode == MODE_GATEUP ? 2u : 1u) * tile_cap;
+    L.stages = 0;
+    L.xbuf = L.stages + (uint32_t)n_stages * stage_bytes;
+    L.items = L.xbuf + 2u * 8u * x_stride;
+    L.red = L.items + 2u * 96u;
+    L.bars = L.red + (mode == MODE_GATEUP ? (uint32_t)(kStreamGroups * 2 * kStreamGroupWarps * 4 * 32 * 4) : 0u);
+    L.total = L.bars + 8u * (2u * kStreamMaxStages + 4u + 4u * kStreamGroups) + 64u;
+    return L;
+}
+
+struct StreamBars {
+    uint64_t* full;      // [n_stages]  producer -> consumers (tx bytes)
+    uint64_t* empty;     // [n_stages]  8 consumer warps -> producer
+    uint64_t* xfull;     // [2]
+    uint64_t* xempty;    // [2]  16 consumer warps -> producer
+    uint64_t* redfull;   // [groups][2]  8 warps -> epilogue warp
+    uint64_t* redempty;  // [groups][2]  epilogue warp -> 8 warps
+};
+
+__device__ __forceinline__ StreamBars stream_bars(uint8_t* smem, const StreamSmem& L) {
+    StreamBars b;
+    b.full = (uint64_t*)(smem + L.bars);
+    b.empty = b.full + kStreamMaxStages;
+    b.xfull = b.empty + kStreamMaxStages;
+    b.xempty = b.xfull + 2;
+    b.redfull = b.xempty + 2;
+    b.redempty = b.redfull + 2 * kStreamGroups;
+    return b;
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Bounded wait that also gives up when another warp of the CTA already has.
+__device__ __forceinline__ bool stream_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
+    for (uint32_t it = 0; it < kWaitLimit; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 63u) == 63u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    if (status) atomicExch(status, STATUS_TMA_TIMEOUT);
+    return false;
+}
+
+// How the units of one launch are laid out; computed identically by every warp.
+struct StreamPlan {
+    int n_routed, n_groups, row_tiles, tiles_per_unit, runs, units;
+};
+
+__device__ __forceinline__ StreamPlan stream_plan(const StreamLaunch& L, int rows_per_tile) {
+    StreamPlan p;
+    int valid = *L.valid_tokens;
+    p.n_routed = L.has_routed ? *L.n_work : 0;
+    int n_shared = L.has_shared ? (valid + 7) >> 3 : 0;
+    p.n_groups = p.n_routed + n_shared;
+    p.row_tiles = L.rows / rows_per_tile;
+    long total_tiles = (long)p.n_groups * p.row_tiles;
+    // enough units that every CTA gets about four, but runs as long as that allows:
+    // the activation rows are staged once per unit
+    long g = total_tiles / (4L * gridDim.x);
+    if (g < 1) g = 1;
+    if (g > 16) g = 16;
+    if (g > p.row_tiles) g = p.row_tiles;
+    p.tiles_per_unit = (int)g;
+    p.runs = (p.row_tiles + p.tiles_per_unit - 1) / p.tiles_per_unit;
+    p.units = p.n_groups * p.runs;
+    return p;
+}
+
+
+template <bool MIS>
+__device__ __forceinline__ uint32_t ldw(const uint8_t* p) {
+    if (MIS) {  // p is 2 modulo 4
+        const uint32_t* q = (const uint32_t*)(p - 2);
+        return __byte_perm(q[0], q[1], 0x5432);
+    }
+    return *(const uint32_t*)p;
+}
+
+// One 256-element span of the contraction for fragment rows pa (g) and pb (g+8).
+// bf[step] holds this lane's B fragment of step `step` (16 steps per span).
+// Each of the four lanes that share a row pair converts the scales of the
+// steps it owns (step % 4 == t) and the others fetch them with a shuffle.
+template <int QUANT, bool MIS>
+__device__ __forceinline__ void stream_span(const uint8_t* pa, const uint8_t* pb, const uint2 (&bf)[16], int lane,
+                                            float (&acc)[4]) {
+    const uint32_t bias32 = 0x64206420u;   // half2(1056): 1024 + 32
+    const uint32_t bias128 = 0x64806480u;  // half2(1152): 1024 + 128
+    const int t = lane & 3;
+    const int quad = lane & ~3;
+    float own_a[4], own_b[4];
+    if (QUANT == QUANT_Q6K) {
+        float da = f16_at(pa + 208), db = f16_at(pb + 208);
+#pragma unroll
+        for (int hc = 0; hc < 4; ++hc) {
+            // step = hc*4 + j with j == t: scale index half*8 + 2*j + c  (quant.rs:183,195-198)
+            int si = 192 + (hc >> 1) * 8 + 2 * t + (hc & 1);
+            own_a[hc] = da * (float)(int)(int8_t)pa[si];
+            own_b[hc] = db * (float)(int)(int8_t)pb[si];
+        }
+#pragma unroll
+        for (int hc = 0; hc < 4; ++hc) {
+            const int half = hc >> 1, c = hc & 1;
+            const int off = half * 64 + 16 * c + 4 * t;
+            const int offh = 128 + half * 32 + 16 * c + 4 * t;
+            uint32_t a_ql0 = ldw<MIS>(pa + off), a_ql1 = ldw<MIS>(pa + off + 32), a_qh = ldw<MIS>(pa + offh);
+            uint32_t b_ql0 = ldw<MIS>(pb + off), b_ql1 = ldw<MIS>(pb + off + 32), b_qh = ldw<MIS>(pb + offh);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float dsa = __shfl_sync(0xffffffffu, own_a[hc], quad | j);
+                float dsb = __shfl_sync(0xffffffffu, own_b[hc], quad | j);
+                uint32_t ra = q6k_codes(j, a_ql0, a_ql1, a_qh);
+                uint32_t rb = q6k_codes(j, b_ql0, b_ql1, b_qh);
+                uint32_t a[4];
+                a[0] = bytes01_to_h2(ra, bias32);
+                a[1] = bytes01_to_h2(rb, bias32);
+                a[2] = bytes23_to_h2(ra, bias32);
+                a[3] = bytes23_to_h2(rb, bias32);
+                float d[4];
+                mma_f16_16816(d, a, bf[hc * 4 + j].x, bf[hc * 4 + j].y);
+                acc[0] = fmaf(dsa, d[0], acc[0]);
+                acc[1] = fmaf(dsa, d[1], acc[1]);
+                acc[2] = fmaf(dsb, d[2], acc[2]);
+                acc[3] = fmaf(dsb, d[3], acc[3]);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {  // step = 4*i + t  ->  block (4*i + t) / 2
+            int blk = (4 * i + t) >> 1;
+            own_a[i] = f16_at(pa + blk * kQ8BlockBytes);
+            own_b[i] = f16_at(pb + blk * kQ8BlockBytes);
+        }
+#pragma unroll
+        for (int step = 0; step < 16; ++step) {
+            const int blk = step >> 1, c = step & 1;
+            float dsa = __shfl_sync(0xffffffffu, own_a[step >> 2], quad | (step & 3));
+            float dsb = __shfl_sync(0xffffffffu, own_b[step >> 2], quad | (step & 3));
+            // block bases are 34*blk: word alignment alternates with the block index
+            const uint8_t* qa = pa + blk * kQ8BlockBytes + 2 + 16 * c + 4 * t;
+            const uint8_t* qb = pb + blk * kQ8BlockBytes + 2 + 16 * c + 4 * t;
+            uint32_t wa = ((blk & 1) ? ldw<MIS>(qa) : ldw<!MIS>(qa)) ^ 0x80808080u;
+            uint32_t wb = ((blk & 1) ? ldw<MIS>(qb) : ldw<!MIS>(qb)) ^ 0x80808080u;
+            uint32_t a[4];
+            a[0] = bytes01_to_h2(wa, bias128);
+            a[1] = bytes01_to_h2(wb, bias128);
+            a[2] = bytes23_to_h2(wa, bias128);
+            a[3] = bytes23_to_h2(wb, bias128);
+            float d[4];
+            mma_f16_16816(d, a, bf[step].x, bf[step].y);
+            acc[0] = fmaf(dsa, d[0], acc[0]);
+            acc[1] = fmaf(dsa, d[1], acc[1]);
+            acc[2] = fmaf(dsb, d[2], acc[2]);
+            acc[3] = fmaf(dsb, d[3], acc[3]);
+        }
+    }
+}
+
+// Element offset (within a span) of this lane's four activations for `step`.
+template <int QUANT>
+__device__ __forceinline__ int step_k_offset(int step, int t) {
+    if (QUANT == QUANT_Q6K) {
+        int hc = step >> 2, j = step & 3;
+        return (hc >> 1) * 128 + j * 32 + 16 * (hc & 1) + 4 * t;
+    }
+    return (step >> 1) * 32 + 16 * (step & 1) + 4 * t;
+}
+
+template <int QUANT>
+__device__ __forceinline__ void load_bfrags(const uint8_t* xrow, int span, int t, uint2 (&bf)[16]) {
+#pragma unroll
+    for (int step = 0; step < 16; ++step)
+        bf[step] = *(const uint2*)(xrow + 2 * (span * 256 + step_k_offset<QUANT>(step, t)));
+}
+
+// The host only selects these kernels when every row pitch is a multiple of 4
+// bytes, so all lanes of a warp (and both fragment rows) share one alignment.
+template <int QUANT>
+__device__ __forceinline__ void span_dispatch(const uint8_t* pa, const uint8_t* pb, const uint2 (&bf)[16], int lane,
+                                              float (&acc)[4]) {
+    if ((uintptr_t)pa & 2) stream_span<QUANT, true>(pa, pb, bf, lane, acc);
+    else stream_span<QUANT, false>(pa, pb, bf, lane, acc);
+}
+
+// ---------------------------------------------------------------------------
+// The kernel.  MODE_GATEUP: tile = 8 gate rows + the same 8 up rows (fragment
+// rows 0-7 / 8-15), eight warps split the spans, SwiGLU epilogue, f16 out.
+// MODE_DOWN: tile = 128 rows, one m16 tile per warp over the whole contraction
+// (at most two spans), weight * value (routed) or value (shared) out, fp32.
+// grid: number of SMs; block: kStreamThreads.
+// ---------------------------------------------------------------------------
+template <int MODE, int QR, int QS>
+__global__ void __launch_bounds__(kStreamThreads, 1) k_expert_stream(StreamLaunch L) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ int abort_flag;
+    constexpr int ROWS_PER_TILE = MODE == MODE_GATEUP ? 8 : 128;
+    constexpr int NSP = MODE == MODE_GATEUP ? 1 : 2;  // spans a consumer warp owns
+    const StreamSmem lay = stream_smem_layout(MODE, L.n_stages, L.tile_cap, L.x_stride);
+    const StreamBars bars = stream_bars(smem, lay);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int S = L.n_stages;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int i = 0; i < S; ++i) {
+            mbar_init(&bars.full[i], 1);
+            mbar_init(&bars.empty[i], kStreamGroupWarps);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bars.xfull[i], 1);
+            mbar_init(&bars.xempty[i], kStreamConsumerWarps);
+        }
+        for (int i = 0; i < 2 * kStreamGroups; ++i) {
+            mbar_init(&bars.redfull[i], kStreamGroupWarps);
+            mbar_init(&bars.redempty[i], 1);
+        }
+        fence_mbar_init();
+    }
+    __syncthreads();
+    const StreamPlan plan = stream_plan(L, ROWS_PER_TILE);
+    const int n_spans = L.k / kSpanElems;
+    const uint32_t stage_bytes = (MODE == MODE_GATEUP ? 2u : 1u) * L.tile_cap;
+    volatile int* abortp = &abort_flag;
+
+    if (warp == 0) {
+        // ------------------------------ producer ------------------------------
+        if (lane != 0) return;
+        uint32_t it = 0, ux = 0;
+        for (int u = blockIdx.x; u < plan.units; u += gridDim.x, ++ux) {
+            const int cg = u / plan.runs, run = u % plan.runs;
+            const bool shared = cg >= plan.n_routed;
+            const int quant = shared ? QS : QR;
+            const int row_bytes = n_spans * span_bytes_of(quant);
+            const int xb = ux & 1;
+            int* desc = (int*)(smem + lay.items + xb * 96);  // [0..3] written here, [4..] item copy
+            if (ux >= 2 && !stream_wait(&bars.xempty[xb], ((ux >> 1) - 1) & 1, abortp, L.status)) return;
+            int expert, first, ncols;
+            const int* item = nullptr;
+            if (!shared) {
+                item = L.work_items + (size_t)cg * kWorkItemInts;
+                expert = item[0];
+                first = item[1];
+                ncols = item[2];
+            } else {
+                expert = -1;
+                first = (cg - plan.n_routed) * 8;
+                ncols = min(8, *L.valid_tokens - first);
+            }
+            desc[0] = expert;
+            desc[1] = first;
+            desc[2] = ncols;
+            const uint32_t xrow_bytes = (uint32_t)L.k * 2u;
+            mbar_expect_tx(&bars.xfull[xb], ncols * xrow_bytes + (shared ? 0u : 64u));
+            uint8_t* xdst = smem + lay.xbuf + (uint32_t)xb * 8u * L.x_stride;
+            for (int c = 0; c < ncols; ++c) {
+                size_t src_row;
+                if (MODE == MODE_GATEUP) src_row = shared ? (size_t)(first + c) : (size_t)(item[4 + c] / L.top_k);
+                else src_row = (size_t)(first + c);  // slot (routed) or token (shared)
+                const __half* src = (shared ? L.x_shared : L.x_routed) + src_row * L.k;
+                tma_bulk_g2s(xdst + c * L.x_stride, src, xrow_bytes, &bars.xfull[xb]);
+            }
+            if (!shared) tma_bulk_g2s(desc + 4, item + 4, 64u, &bars.xfull[xb]);  // flat ids + weights
+            const uint8_t* wa = shared ? L.s_a : L.r_a;
+            const uint8_t* wb = shared ? L.s_b : L.r_b;
+            const size_t row0 = (shared ? 0 : (size_t)expert * L.rows);
+            const int t_begin = run * plan.tiles_per_unit;
+            const int t_end = min(plan.row_tiles, t_begin + plan.tiles_per_unit);
+            for (int tile = t_begin; tile < t_end; ++tile, ++it) {
+                const int st = it % S;
+                const uint32_t use = it / S;
+                if (use >= 1 && !stream_wait(&bars.empty[st], (use - 1) & 1, abortp, L.status)) return;
+                const size_t start = (row0 + (size_t)tile * ROWS_PER_TILE) * row_bytes;
+                const uint32_t tile_bytes = (uint32_t)ROWS_PER_TILE * row_bytes;
+                const size_t a0 = start & ~(size_t)15, a1 = (start + tile_bytes + 15) & ~(size_t)15;
+                const uint32_t nbytes = (uint32_t)(a1 - a0);
+                uint8_t* dst = smem + lay.stages + (uint32_t)st * stage_bytes;
+                mbar_expect_tx(&bars.full[st], (MODE == MODE_GATEUP ? 2u : 1u) * nbytes);
+                tma_bulk_g2s(dst, wa + a0, nbytes, &bars.full[st]);
+                if (MODE == MODE_GATEUP) tma_bulk_g2s(dst + L.tile_cap, wb + a0, nbytes, &bars.full[st]);
+            }
+        }
+        return;
+    }
+
+    // -------------------------------- consumers --------------------------------
+    const int cw = warp - 1;
+    const int gi = cw / kStreamGroupWarps;  // group
+    const int w = cw % kStreamGroupWarps;   // warp within the group
+    const int g = lane >> 2, t = lane & 3;
+    float* red = (float*)(smem + lay.red);
+    uint32_t it = 0, ux = 0, gt = 0;  // ring tile counter, unit counter, this group's tile counter
+    for (int u = blockIdx.x; u < plan.units; u += gridDim.x, ++ux) {
+        const int cg = u / plan.runs, run = u % plan.runs;
+        const bool shared = cg >= plan.n_routed;
+        const int quant = shared ? QS : QR;
+        const int row_bytes = n_spans * span_bytes_of(quant);
+        const int xb = ux & 1;
+        if (!stream_wait(&bars.xfull[xb], (ux >> 1) & 1, abortp, L.status)) return;
+        const int* desc = (const int*)(smem + lay.items + xb * 96);
+        const int expert = desc[0], first = desc[1], ncols = desc[2];
+        int flat0 = 0, flat1 = 0;
+        float wgt0 = 0.f, wgt1 = 0.f;
+        if (MODE == MODE_DOWN && !shared) {
+            flat0 = desc[4 + 2 * t];
+            flat1 = desc[4 + 2 * t + 1];
+            wgt0 = __int_as_float(desc[12 + 2 * t]);
+            wgt1 = __int_as_float(desc[12 + 2 * t + 1]);
+        }
+        // B fragments of this unit: column g of the group (dead columns read stale rows
+        // and are never stored)
+        const uint8_t* xrow = smem + lay.xbuf + (uint32_t)xb * 8u * L.x_stride + g * L.x_stride;
+        uint2 bf[NSP][16];
+#pragma unroll
+        for (int sp = 0; sp < NSP; ++sp) {
+            int span = MODE == MODE_GATEUP ? w : sp;
+            if (span < n_spans) {
+                if (quant == QUANT_Q6K) load_bfrags<QUANT_Q6K>(xrow, span, t, bf[sp]);
+                else load_bfrags<QUANT_Q8_0>(xrow, span, t, bf[sp]);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars.xempty[xb]);
+        const uint32_t phase = (uint32_t)((((shared ? 0 : (size_t)expert * L.rows)) * row_bytes) & 15);
+        const int t_begin = run * plan.tiles_per_unit;
+        const int t_end = min(plan.row_tiles, t_begin + plan.tiles_per_unit);
+        for (int tile = t_begin; tile < t_end; ++tile, ++it) {
+            if ((int)(it & 1) != gi) continue;
+            const int st = it % S;
+            if (!stream_wait(&bars.full[st], (it / S) & 1, abortp, L.status)) return;
+            const uint8_t* tb = smem + lay.stages + (uint32_t)st * stage_bytes +
+                                (uint32_t)((phase + (size_t)tile * ROWS_PER_TILE * row_bytes) & 15);
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            if (MODE == MODE_GATEUP) {
+                if (w < n_spans) {
+                    const uint8_t* pa = tb + g * row_bytes + w * span_bytes_of(quant);
+                    const uint8_t* pb = pa + L.tile_cap;
+                    if (quant == QUANT_Q6K) span_dispatch<QUANT_Q6K>(pa, pb, bf[0], lane, acc);
+                    else span_dispatch<QUANT_Q8_0>(pa, pb, bf[0], lane, acc);
+                }
+            } else {
+                const uint8_t* pa = tb + (size_t)(w * 16 + g) * row_bytes;
+                const uint8_t* pb = pa + 8 * (size_t)row_bytes;
+#pragma unroll
+                for (int sp = 0; sp < NSP; ++sp) {
+                    if (sp < n_spans) {
+                        if (quant == QUANT_Q6K)
+                            span_dispatch<QUANT_Q6K>(pa + sp * 210, pb + sp * 210, bf[sp], lane, acc);
+                        else
+                            span_dispatch<QUANT_Q8_0>(pa + sp * 272, pb + sp * 272, bf[sp], lane, acc);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars.empty[st]);  // the ring stage may be refilled
+            if (MODE == MODE_GATEUP) {
+                const int buf = gt & 1;
+                float* rb = red + ((size_t)(gi * 2 + buf) * kStreamGroupWarps) * 128;
+                if (gt >= 2 && !stream_wait(&bars.redempty[gi * 2 + buf], ((gt >> 1) - 1) & 1, abortp, L.status))
+                    return;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) rb[(w * 4 + i) * 32 + lane] = acc[i];
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars.redfull[gi * 2 + buf]);
+                if (w == (int)(gt % kStreamGroupWarps)) {  // the epilogue rotates over the group's warps
+                    if (!stream_wait(&bars.redfull[gi * 2 + buf], (gt >> 1) & 1, abortp, L.status)) return;
+                    float tot[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        float s = rb[(0 * 4 + i) * 32 + lane];
+#pragma unroll
+                        for (int ww = 1; ww < kStreamGroupWarps; ++ww) s += rb[(ww * 4 + i) * 32 + lane];
+                        tot[i] = s;
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars.redempty[gi * 2 + buf]);
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        int col = 2 * t + i;
+                        if (col < ncols) {
+                            float gv = tot[i], uv = tot[2 + i];
+                            float v = __fdiv_rn(gv, 1.0f + expf(-gv)) * uv;
+                            __half* dst = (shared ? L.inter_shared : L.inter_routed) + (size_t)(first + col) * L.rows;
+                            dst[tile * 8 + g] = __float2half_rn(v);
+                        }
+                    }
+                }
+                ++gt;
+            } else {
+                const int row = tile * 128 + w * 16 + g;
+                if (shared) {
+                    if (2 * t < ncols) {
+                        float* dst = L.shexp + (size_t)(first + 2 * t) * L.rows;
+                        dst[row] = acc[0];
+                        dst[row + 8] = acc[2];
+                    }
+                    if (2 * t + 1 < ncols) {
+                        float* dst = L.shexp + (size_t)(first + 2 * t + 1) * L.rows;
+                        dst[row] = acc[1];
+                        dst[row + 8] = acc[3];
+                    }
+                } else {
+                    if (2 * t < ncols) {
+                        float* dst = L.partial + (size_t)flat0 * L.rows;
+                        dst[row] = wgt0 * acc[0];
+                        dst[row + 8] = wgt0 * acc[2];
+                    }
+                    if (2 * t + 1 < ncols) {
+                        float* dst = L.partial + (size_t)flat1 * L.rows;
+                        dst[row] = wgt1 * acc[1];
+                        dst[row + 8] = wgt1 * acc[3];
+                    }
+                }
+            }
+        }
+    }
+}
+
+}  // namespace xabe

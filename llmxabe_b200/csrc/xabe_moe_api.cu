@@ -4,6 +4,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
@@ -11,6 +12,7 @@
 #include "common.cuh"
 #include "expert_kernels.cuh"
 #include "glue_kernels.cuh"
+#include "stream_kernels.cuh"
 
 using namespace xabe;
 
@@ -73,6 +75,12 @@ struct xabe_moe {
     int* num_tokens_post_pad = nullptr;
     int* chunk_hist = nullptr;
     int* expert_offsets = nullptr;
+    int* expert_counts = nullptr;
+    int* work_items = nullptr;  // column groups, kWorkItemInts ints each
+    int* n_work = nullptr;      // device scalar: routed column groups this step
+    uint64_t work_capacity = 0;
+    int sm_count = 0;
+    bool force_tile_kernels = false;  // use the one-tile-per-CTA kernels even where the streaming ones apply
     float* normed = nullptr;
     __half* normed_h = nullptr;
     float* logits = nullptr;
@@ -164,6 +172,60 @@ int launch_down(xabe_moe* m, cudaStream_t st, const ExpertLaunch& L, int y_block
          : ((qs) == XABE_QUANT_Q6_K ? fn<QUANT_Q8_0, QUANT_Q6K>(__VA_ARGS__)          \
                                     : fn<QUANT_Q8_0, QUANT_Q8_0>(__VA_ARGS__)))
 
+// ---- streaming (persistent) expert kernels --------------------------------
+struct StreamShape {
+    bool ok = false;
+    int n_stages = 0;
+    uint32_t tile_cap = 0, x_stride = 0, smem = 0;
+};
+
+// Whether the streaming kernel serves this projection, and with what ring.
+StreamShape stream_shape(int mode, int rows, int k, int q_routed, int q_shared) {
+    StreamShape sh;
+    int n_spans = k / 256;
+    int max_spans = mode == MODE_GATEUP ? kStreamGroupWarps : 2;
+    if (n_spans > max_spans) return sh;
+    if (mode == MODE_DOWN && rows % 128 != 0) return sh;
+    if (mode == MODE_GATEUP && rows % 8 != 0) return sh;
+    uint32_t rb_max = 0;
+    for (int q : {q_routed, q_shared}) {
+        uint32_t rb = (uint32_t)n_spans * span_bytes_of(q);
+        if (rb % 4 != 0) return sh;  // a warp's rows must share one word alignment
+        if (rb > rb_max) rb_max = rb;
+    }
+    uint32_t rows_per_tile = mode == MODE_GATEUP ? 8 : 128;
+    sh.tile_cap = (staged_capacity(rows_per_tile * rb_max) + 15u) & ~15u;
+    sh.x_stride = (uint32_t)k * 2u + kXRowPadBytes;
+    for (int S = kStreamMaxStages; S >= 2; --S) {
+        StreamSmem L = stream_smem_layout(mode, S, sh.tile_cap, sh.x_stride);
+        if (L.total <= 200u * 1024u) {
+            sh.ok = true;
+            sh.n_stages = S;
+            sh.smem = L.total;
+            return sh;
+        }
+    }
+    return sh;
+}
+
+template <int MODE, int QR, int QS>
+int launch_stream_t(xabe_moe* m, cudaStream_t st, const StreamLaunch& L, uint32_t smem) {
+    auto kern = k_expert_stream<MODE, QR, QS>;
+    CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<m->sm_count, kStreamThreads, smem, st>>>(L);
+    CUDA_TRY(cudaGetLastError());
+    return XABE_OK;
+}
+
+template <int MODE>
+int launch_stream(xabe_moe* m, cudaStream_t st, const StreamLaunch& L, uint32_t smem, int qr, int qs) {
+    if (qr == XABE_QUANT_Q6_K)
+        return qs == XABE_QUANT_Q6_K ? launch_stream_t<MODE, QUANT_Q6K, QUANT_Q6K>(m, st, L, smem)
+                                     : launch_stream_t<MODE, QUANT_Q6K, QUANT_Q8_0>(m, st, L, smem);
+    return qs == XABE_QUANT_Q6_K ? launch_stream_t<MODE, QUANT_Q8_0, QUANT_Q6K>(m, st, L, smem)
+                                 : launch_stream_t<MODE, QUANT_Q8_0, QUANT_Q8_0>(m, st, L, smem);
+}
+
 struct MlpWeights {
     bool present = false;
     xabe_quant_tensor gate{}, up{}, down{};
@@ -208,6 +270,28 @@ int run_experts(xabe_moe* m, cudaStream_t st, const MlpWeights& routed, const Ml
     L.x_shared = m->normed_h;
     L.inter_routed = m->inter_routed;
     L.inter_shared = m->inter_shared;
+    StreamLaunch SL{};
+    SL.top_k = L.top_k;
+    SL.has_routed = routed.present;
+    SL.has_shared = shared.present;
+    SL.work_items = m->work_items;
+    SL.n_work = m->n_work;
+    SL.valid_tokens = m->valid_tokens;
+    SL.status = m->status;
+    SL.inter_routed = m->inter_routed;
+    SL.inter_shared = m->inter_shared;
+    SL.partial = m->partial;
+    SL.shexp = shexp_out;
+    StreamShape gu = stream_shape(MODE_GATEUP, (int)g.intermediate, (int)g.hidden, qr, qs);
+    if (gu.ok && !m->force_tile_kernels) {
+        SL.r_a = L.r_a; SL.r_b = L.r_b; SL.s_a = L.s_a; SL.s_b = L.s_b;
+        SL.rows = L.rows; SL.k = L.k;
+        SL.x_routed = m->normed_h; SL.x_shared = m->normed_h;
+        SL.n_stages = gu.n_stages; SL.tile_cap = gu.tile_cap; SL.x_stride = gu.x_stride;
+        int rcs = launch_stream<MODE_GATEUP>(m, st, SL, gu.smem, qr, qs);
+        if (rcs) return rcs;
+        if (mark_between >= 0) prof_mark(m, st, mark_between);
+    } else {
     size_t smem = gateup_smem(L.k, qr, L.block_size);
     size_t smem_s = gateup_smem(L.k, qs, L.block_size);
     if (smem_s > smem) smem = smem_s;
@@ -216,6 +300,7 @@ int run_experts(xabe_moe* m, cudaStream_t st, const MlpWeights& routed, const Ml
     int rc = DISPATCH_QQ(launch_gateup, qr, qs, m, st, L, routed_blocks + shared_tiles, smem);
     if (rc) return rc;
     if (mark_between >= 0) prof_mark(m, st, mark_between);
+    }
     // down
     qr = routed.present ? routed.down.quant : shared.down.quant;
     qs = shared.present ? shared.down.quant : qr;
@@ -229,8 +314,16 @@ int run_experts(xabe_moe* m, cudaStream_t st, const MlpWeights& routed, const Ml
     L.x_shared = m->inter_shared;
     L.partial = m->partial;
     L.shexp = shexp_out;
-    smem = down_smem(L.k, qr);
-    smem_s = down_smem(L.k, qs);
+    StreamShape dn = stream_shape(MODE_DOWN, (int)g.hidden, (int)g.intermediate, qr, qs);
+    if (dn.ok && !m->force_tile_kernels) {
+        SL.r_a = L.r_a; SL.r_b = nullptr; SL.s_a = L.s_a; SL.s_b = nullptr;
+        SL.rows = L.rows; SL.k = L.k;
+        SL.x_routed = m->inter_routed; SL.x_shared = m->inter_shared;
+        SL.n_stages = dn.n_stages; SL.tile_cap = dn.tile_cap; SL.x_stride = dn.x_stride;
+        return launch_stream<MODE_DOWN>(m, st, SL, dn.smem, qr, qs);
+    }
+    size_t smem = down_smem(L.k, qr);
+    size_t smem_s = down_smem(L.k, qs);
     if (smem_s > smem) smem = smem_s;
     if (smem > 220 * 1024)
         return fail(XABE_ERR_UNSUPPORTED_GEOMETRY, "down row tile of %zu bytes does not fit shared memory", smem);
@@ -264,30 +357,50 @@ int launch_rms_norm(xabe_moe* m, cudaStream_t st, const float* x, const float* w
 
 int launch_router(xabe_moe* m, cudaStream_t st, const float* router, const float* bias) {
     const auto& g = m->g;
+    if (((uintptr_t)router & 15) != 0)
+        return fail(XABE_ERR_INVALID_ARGUMENT, "router weights must be 16-byte aligned");
     dim3 block(128);
-    if (g.max_tokens == 1) {
-        dim3 grid((g.num_experts + 3) / 4, 1);
-        k_router_logits<1><<<grid, block, 0, st>>>(router, m->normed, m->valid_tokens, (int)g.hidden,
-                                                   (int)g.num_experts, bias, m->logits);
-    } else if (g.max_tokens <= 4) {
-        dim3 grid((g.num_experts + 3) / 4, 1);
-        k_router_logits<4><<<grid, block, 0, st>>>(router, m->normed, m->valid_tokens, (int)g.hidden,
-                                                   (int)g.num_experts, bias, m->logits);
-    } else {
-        dim3 grid((g.num_experts + 3) / 4, (g.max_tokens + 7) / 8);
-        k_router_logits<8><<<grid, block, 0, st>>>(router, m->normed, m->valid_tokens, (int)g.hidden,
-                                                   (int)g.num_experts, bias, m->logits);
-    }
-    CUDA_TRY(cudaGetLastError());
-    return XABE_OK;
+    size_t smem = (size_t)4 * g.hidden * sizeof(float);
+    if (smem > 200 * 1024) return fail(XABE_ERR_UNSUPPORTED_GEOMETRY, "router rows do not fit shared memory");
+    unsigned ex = (g.num_experts + 3) / 4;
+    auto go = [&](auto kern, int tt) -> int {
+        // wide passes share one staged copy of the rows between eight token tiles
+        int tiles_per_cta = g.max_tokens > 128 ? 8 : 1;
+        unsigned ty = (g.max_tokens + tt * tiles_per_cta - 1) / (tt * tiles_per_cta);
+        CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kern<<<dim3(ex, ty), block, smem, st>>>(router, m->normed, m->valid_tokens, (int)g.hidden,
+                                                (int)g.num_experts, bias, m->logits, tiles_per_cta, m->status);
+        CUDA_TRY(cudaGetLastError());
+        return XABE_OK;
+    };
+    if (g.max_tokens == 1) return go(k_router_logits<1>, 1);
+    if (g.max_tokens <= 4) return go(k_router_logits<4>, 4);
+    return go(k_router_logits<8>, 8);
 }
 
 int launch_route_and_dispatch(xabe_moe* m, cudaStream_t st, const float* logits) {
     const auto& g = m->g;
+    size_t hist_bytes = (size_t)(g.num_experts + 1) * sizeof(int);
+    if ((uint64_t)g.max_tokens * g.experts_per_token <= (uint64_t)kSmallPairs) {
+        // decode widths: one single-CTA launch
+        size_t smem = (size_t)(3 * kSmallPairs + 11 * g.num_experts + 2) * sizeof(int);
+        const float* fused_logits = logits;
+        if (g.max_tokens > 8) {  // more than one token per warp: route on many SMs first
+            k_route<<<(g.max_tokens + 7) / 8, 256, 0, st>>>(logits, m->valid_tokens, (int)g.num_experts,
+                                                           (int)g.experts_per_token, m->topk_ids, m->topk_weights);
+            CUDA_TRY(cudaGetLastError());
+            fused_logits = nullptr;
+        }
+        k_route_dispatch_small<<<1, 256, smem, st>>>(
+            fused_logits, m->valid_tokens, (int)g.num_experts, (int)g.experts_per_token, (int)g.block_size,
+            (int)m->sorted_capacity, (int)m->block_capacity, m->topk_ids, m->topk_weights, m->sorted_token_ids,
+            m->expert_ids, m->num_tokens_post_pad, m->expert_offsets, m->expert_counts, m->work_items, m->n_work);
+        CUDA_TRY(cudaGetLastError());
+        return XABE_OK;
+    }
     k_route<<<(g.max_tokens + 7) / 8, 256, 0, st>>>(logits, m->valid_tokens, (int)g.num_experts,
                                                    (int)g.experts_per_token, m->topk_ids, m->topk_weights);
     CUDA_TRY(cudaGetLastError());
-    size_t hist_bytes = (size_t)(g.num_experts + 1) * sizeof(int);
     k_align_count<<<m->n_chunks, 32, hist_bytes, st>>>(m->topk_ids, m->valid_tokens, (int)g.experts_per_token,
                                                       (int)g.num_experts, m->n_chunks, (int)m->sorted_capacity,
                                                       (int)m->block_capacity, m->chunk_hist,
@@ -295,12 +408,15 @@ int launch_route_and_dispatch(xabe_moe* m, cudaStream_t st, const float* logits)
     CUDA_TRY(cudaGetLastError());
     int threads = ((int)g.num_experts + 31) / 32 * 32;
     k_align_scan<<<1, threads, hist_bytes, st>>>((int)g.num_experts, m->n_chunks, (int)g.block_size,
-                                                 m->chunk_hist, m->expert_offsets, m->expert_ids,
-                                                 m->num_tokens_post_pad);
+                                                 m->chunk_hist, m->expert_offsets, m->expert_counts,
+                                                 m->expert_ids, m->num_tokens_post_pad);
     CUDA_TRY(cudaGetLastError());
     k_align_scatter<<<m->n_chunks, 32, hist_bytes, st>>>(m->topk_ids, m->valid_tokens,
                                                         (int)g.experts_per_token, (int)g.num_experts,
                                                         m->chunk_hist, m->sorted_token_ids);
+    CUDA_TRY(cudaGetLastError());
+    k_build_work<<<1, threads, hist_bytes, st>>>((int)g.num_experts, m->expert_offsets, m->expert_counts,
+                                                 m->sorted_token_ids, m->topk_weights, m->work_items, m->n_work);
     CUDA_TRY(cudaGetLastError());
     return XABE_OK;
 }
@@ -375,6 +491,9 @@ int xabe_moe_create(const xabe_moe_geometry* geometry, int device, int scope, fl
 
     xabe_moe* m = new (std::nothrow) xabe_moe();
     if (!m) return fail(XABE_ERR_DRIVER, "out of host memory");
+    m->sm_count = prop.multiProcessorCount;
+    // debugging aid: XABE_MOE_FORCE_TILE_KERNELS=1 keeps the streaming kernels out of the way
+    if (const char* e = getenv("XABE_MOE_FORCE_TILE_KERNELS")) m->force_tile_kernels = e[0] == '1';
     m->g = g;
     m->device = device;
     m->scope = scope;
@@ -405,6 +524,10 @@ int xabe_moe_create(const xabe_moe_geometry* geometry, int device, int scope, fl
         A(dev_alloc(&m->num_tokens_post_pad, 1));
         A(dev_alloc(&m->chunk_hist, (size_t)m->n_chunks * E));
         A(dev_alloc(&m->expert_offsets, E + 1));
+        A(dev_alloc(&m->expert_counts, E + 1));
+        m->work_capacity = (T * K + 7) / 8 + (E < T * K ? E : T * K) + 1;
+        A(dev_alloc(&m->work_items, (size_t)m->work_capacity * kWorkItemInts));
+        A(dev_alloc(&m->n_work, 1));
         A(dev_alloc(&m->logits, T * E));
         A(dev_alloc(&m->inter_routed, (size_t)cap * I));
         A(dev_alloc(&m->partial, T * K * H));
@@ -423,7 +546,8 @@ void xabe_moe_destroy(xabe_moe* m) {
     if (!m) return;
     cudaSetDevice(m->device);
     void* dev[] = {m->valid_tokens, m->status, m->topk_ids, m->topk_weights, m->sorted_token_ids, m->expert_ids,
-                   m->num_tokens_post_pad, m->chunk_hist, m->expert_offsets, m->normed, m->normed_h, m->logits,
+                   m->num_tokens_post_pad, m->chunk_hist, m->expert_offsets, m->expert_counts, m->work_items, m->n_work,
+                   m->normed, m->normed_h, m->logits,
                    m->inter_routed, m->inter_shared, m->partial, m->routed, m->shexp, m->gate, m->stage_in,
                    m->stage_ffn, m->stage_out};
     for (void* p : dev)
