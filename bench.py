@@ -75,7 +75,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -237,9 +237,39 @@ def run_ours(args) -> dict:
         distinct.append(int(torch.unique(block.buffers().topk_ids[:tokens]).numel()))
     d_mean = sum(distinct) / len(distinct)
 
+    # Decode steps are replayed from a CUDA graph, as the reference's decode bodies are
+    # (crates/xabe-engine/src/forward.rs:2059,3145): one graph holds one step per resident layer.
+    graph = None
+    if args.graph:
+        block.publish_tokens(tokens)
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for i in range(args.layers):
+                step(i)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(args.layers):
+                step(i)
+        torch.cuda.synchronize()
+
+    def replay(i):
+        if i % args.layers == 0:
+            graph.replay()
+
     sampler = ClockSampler(local_rank)
     sampler.start()
-    ms = timed(step, args.steps)
+    ms_eager = timed(step, args.steps)
+    if graph is not None:
+        steps_g = (args.steps + args.layers - 1) // args.layers * args.layers
+        for i in range(args.layers * 3):
+            replay(i)
+        ms = timed(replay, steps_g)
+    else:
+        ms = ms_eager
     clocks = sampler.stop()
     # the same region again with per-stage CUDA events, for the dominant kernel's duration
     block.moe.stage_profile(True)
@@ -251,6 +281,7 @@ def run_ours(args) -> dict:
     ms_e2e = timed(step_host, args.steps)
     status = block.moe.device_status()
 
+    launches_per_step = 7 if tokens * 8 <= 2048 and tokens > 8 else (6 if tokens <= 8 else 11)
     peak, peak_src = measured_peaks()
     gateup_ms = stage_ms["gate_up"] / max(calls, 1)
     gu_bytes = gateup_algorithmic_bytes(d_mean, tokens)
@@ -269,7 +300,7 @@ def run_ours(args) -> dict:
                    "parallelism": f"replicas x{world}"},
         "e2e": {"value": world * tokens / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": tokens * H * 4, "d2h_bytes_per_step": tokens * H * 4},
-        "gpu_launches": 9 * args.steps,
+        "gpu_launches": launches_per_step * args.steps, "ms_per_step_eager": ms_eager, "cuda_graph": graph is not None,
         "clocks": clocks,
         "roofline": {"bound": "hbm", "kernel": "k_expert_gateup", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
@@ -300,6 +331,7 @@ def main():
     ap.add_argument("--workload", default="decode64", choices=sorted(WORKLOADS))
     ap.add_argument("--layers", type=int, default=4, help="distinct resident layers the steps rotate over")
     ap.add_argument("--no-cpu", action="store_true", help="skip the timed CPU baseline")
+    ap.add_argument("--no-graph", dest="graph", action="store_false", help="time eager launches instead of CUDA-graph replay")
     args = ap.parse_args()
     if args.impl == "reference":
         if int(os.environ.get("RANK", "0")) != 0:

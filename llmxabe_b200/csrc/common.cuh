@@ -19,6 +19,7 @@ constexpr int QUANT_Q8_0 = 1;
 // Device status word values (read by xabe_moe_device_status).
 constexpr int STATUS_OK = 0;
 constexpr int STATUS_TMA_TIMEOUT = 1;
+constexpr int STATUS_BAD_WORK_ITEM = 2;
 
 // Iterations a wait on an mbarrier may spin before the kernel gives up,
 // records STATUS_TMA_TIMEOUT and returns.  try_wait itself blocks for a

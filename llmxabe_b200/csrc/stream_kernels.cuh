@@ -61,6 +61,10 @@ struct StreamLaunch {
     int n_stages;
     uint32_t tile_cap;    // staged bytes reserved per tensor per stage (multiple of 16)
     uint32_t x_stride;    // bytes between activation rows in shared memory
+    int num_experts;      // bounds for the producer's self-check of a column group
+    int x_rows_routed;    // rows the routed activation buffer holds
+    int max_tokens;
+    int down_row_step;    // MODE_DOWN: rows of one fragment half are this far apart (bank-conflict free reads)
 };
 
 struct StreamSmem {
@@ -137,6 +141,7 @@ __device__ __forceinline__ StreamPlan stream_plan(const StreamLaunch& L, int row
     if (g > p.row_tiles) g = p.row_tiles;
     p.tiles_per_unit = (int)g;
     p.runs = (p.row_tiles + p.tiles_per_unit - 1) / p.tiles_per_unit;
+    p.tiles_per_unit = (p.row_tiles + p.runs - 1) / p.runs;  // even runs
     p.units = p.n_groups * p.runs;
     return p;
 }
@@ -151,47 +156,59 @@ __device__ __forceinline__ uint32_t ldw(const uint8_t* p) {
     return *(const uint32_t*)p;
 }
 
-// One 256-element span of the contraction for fragment rows pa (g) and pb (g+8).
-// bf[step] holds this lane's B fragment of step `step` (16 steps per span).
-// Each of the four lanes that share a row pair converts the scales of the
-// steps it owns (step % 4 == t) and the others fetch them with a shuffle.
+// Four 4-code words (groups j = 0..3) of one (ql word 0, ql word 1, qh word)
+// triple, five-plus-six operations for all four: the high bit pairs are
+// pre-masked so that a bitwise select merges nibble and pair in one LOP3.
+__device__ __forceinline__ void q6k_codes4(uint32_t ql0, uint32_t ql1, uint32_t qh, uint32_t (&raw)[4]) {
+    const uint32_t m = 0x0F0F0F0Fu;
+    uint32_t qa = qh & 0x33333333u;         // pairs of groups 0 (bits 0-1) and 2 (bits 4-5)
+    uint32_t qb = (qh >> 2) & 0x33333333u;  // pairs of groups 1 and 3
+    raw[0] = (ql0 & m) | ((qa << 4) & ~m);
+    raw[1] = (ql1 & m) | ((qb << 4) & ~m);
+    raw[2] = ((ql0 >> 4) & m) | (qa & ~m);
+    raw[3] = ((ql1 >> 4) & m) | (qb & ~m);
+}
+
+// Half a span (128 elements, 8 k16 steps) of the contraction for fragment rows
+// pa (g) and pb (g+8); `h` picks the half.  bf[step] is this lane's B fragment
+// of step `step` of that half.  Each of the four lanes that share a row pair
+// converts the scales of the steps it owns (step % 4 == t); the others fetch
+// them with a shuffle.
 template <int QUANT, bool MIS>
-__device__ __forceinline__ void stream_span(const uint8_t* pa, const uint8_t* pb, const uint2 (&bf)[16], int lane,
+__device__ __forceinline__ void stream_half(const uint8_t* pa, const uint8_t* pb, int h, const uint2* bf, int lane,
                                             float (&acc)[4]) {
     const uint32_t bias32 = 0x64206420u;   // half2(1056): 1024 + 32
     const uint32_t bias128 = 0x64806480u;  // half2(1152): 1024 + 128
     const int t = lane & 3;
     const int quad = lane & ~3;
-    float own_a[4], own_b[4];
+    float own_a[2], own_b[2];
     if (QUANT == QUANT_Q6K) {
         float da = f16_at(pa + 208), db = f16_at(pb + 208);
 #pragma unroll
-        for (int hc = 0; hc < 4; ++hc) {
-            // step = hc*4 + j with j == t: scale index half*8 + 2*j + c  (quant.rs:183,195-198)
-            int si = 192 + (hc >> 1) * 8 + 2 * t + (hc & 1);
-            own_a[hc] = da * (float)(int)(int8_t)pa[si];
-            own_b[hc] = db * (float)(int)(int8_t)pb[si];
+        for (int c = 0; c < 2; ++c) {
+            // step = c*4 + j with j == t: scale index half*8 + 2*j + c  (quant.rs:183,195-198)
+            int si = 192 + h * 8 + 2 * t + c;
+            own_a[c] = da * (float)(int)(int8_t)pa[si];
+            own_b[c] = db * (float)(int)(int8_t)pb[si];
         }
 #pragma unroll
-        for (int hc = 0; hc < 4; ++hc) {
-            const int half = hc >> 1, c = hc & 1;
-            const int off = half * 64 + 16 * c + 4 * t;
-            const int offh = 128 + half * 32 + 16 * c + 4 * t;
-            uint32_t a_ql0 = ldw<MIS>(pa + off), a_ql1 = ldw<MIS>(pa + off + 32), a_qh = ldw<MIS>(pa + offh);
-            uint32_t b_ql0 = ldw<MIS>(pb + off), b_ql1 = ldw<MIS>(pb + off + 32), b_qh = ldw<MIS>(pb + offh);
+        for (int c = 0; c < 2; ++c) {
+            const int off = h * 64 + 16 * c + 4 * t;
+            const int offh = 128 + h * 32 + 16 * c + 4 * t;
+            uint32_t ra[4], rb[4];
+            q6k_codes4(ldw<MIS>(pa + off), ldw<MIS>(pa + off + 32), ldw<MIS>(pa + offh), ra);
+            q6k_codes4(ldw<MIS>(pb + off), ldw<MIS>(pb + off + 32), ldw<MIS>(pb + offh), rb);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                float dsa = __shfl_sync(0xffffffffu, own_a[hc], quad | j);
-                float dsb = __shfl_sync(0xffffffffu, own_b[hc], quad | j);
-                uint32_t ra = q6k_codes(j, a_ql0, a_ql1, a_qh);
-                uint32_t rb = q6k_codes(j, b_ql0, b_ql1, b_qh);
+                float dsa = __shfl_sync(0xffffffffu, own_a[c], quad | j);
+                float dsb = __shfl_sync(0xffffffffu, own_b[c], quad | j);
                 uint32_t a[4];
-                a[0] = bytes01_to_h2(ra, bias32);
-                a[1] = bytes01_to_h2(rb, bias32);
-                a[2] = bytes23_to_h2(ra, bias32);
-                a[3] = bytes23_to_h2(rb, bias32);
+                a[0] = bytes01_to_h2(ra[j], bias32);
+                a[1] = bytes01_to_h2(rb[j], bias32);
+                a[2] = bytes23_to_h2(ra[j], bias32);
+                a[3] = bytes23_to_h2(rb[j], bias32);
                 float d[4];
-                mma_f16_16816(d, a, bf[hc * 4 + j].x, bf[hc * 4 + j].y);
+                mma_f16_16816(d, a, bf[c * 4 + j].x, bf[c * 4 + j].y);
                 acc[0] = fmaf(dsa, d[0], acc[0]);
                 acc[1] = fmaf(dsa, d[1], acc[1]);
                 acc[2] = fmaf(dsb, d[2], acc[2]);
@@ -200,21 +217,21 @@ __device__ __forceinline__ void stream_span(const uint8_t* pa, const uint8_t* pb
         }
     } else {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {  // step = 4*i + t  ->  block (4*i + t) / 2
-            int blk = (4 * i + t) >> 1;
+        for (int i = 0; i < 2; ++i) {  // step = 4*i + t of this half -> block h*4 + (4*i + t) / 2
+            int blk = h * 4 + ((4 * i + t) >> 1);
             own_a[i] = f16_at(pa + blk * kQ8BlockBytes);
             own_b[i] = f16_at(pb + blk * kQ8BlockBytes);
         }
 #pragma unroll
-        for (int step = 0; step < 16; ++step) {
-            const int blk = step >> 1, c = step & 1;
+        for (int step = 0; step < 8; ++step) {
+            const int blk = h * 4 + (step >> 1), c = step & 1;
             float dsa = __shfl_sync(0xffffffffu, own_a[step >> 2], quad | (step & 3));
             float dsb = __shfl_sync(0xffffffffu, own_b[step >> 2], quad | (step & 3));
             // block bases are 34*blk: word alignment alternates with the block index
             const uint8_t* qa = pa + blk * kQ8BlockBytes + 2 + 16 * c + 4 * t;
             const uint8_t* qb = pb + blk * kQ8BlockBytes + 2 + 16 * c + 4 * t;
-            uint32_t wa = ((blk & 1) ? ldw<MIS>(qa) : ldw<!MIS>(qa)) ^ 0x80808080u;
-            uint32_t wb = ((blk & 1) ? ldw<MIS>(qb) : ldw<!MIS>(qb)) ^ 0x80808080u;
+            uint32_t wa = ((step >> 1) & 1 ? ldw<MIS>(qa) : ldw<!MIS>(qa)) ^ 0x80808080u;
+            uint32_t wb = ((step >> 1) & 1 ? ldw<MIS>(qb) : ldw<!MIS>(qb)) ^ 0x80808080u;
             uint32_t a[4];
             a[0] = bytes01_to_h2(wa, bias128);
             a[1] = bytes01_to_h2(wb, bias128);
@@ -230,30 +247,49 @@ __device__ __forceinline__ void stream_span(const uint8_t* pa, const uint8_t* pb
     }
 }
 
-// Element offset (within a span) of this lane's four activations for `step`.
+// Element offset (within a span) of this lane's four activations for step
+// `step` (0..7) of half `h`.
 template <int QUANT>
-__device__ __forceinline__ int step_k_offset(int step, int t) {
+__device__ __forceinline__ int step_k_offset(int h, int step, int t) {
     if (QUANT == QUANT_Q6K) {
-        int hc = step >> 2, j = step & 3;
-        return (hc >> 1) * 128 + j * 32 + 16 * (hc & 1) + 4 * t;
+        int c = step >> 2, j = step & 3;
+        return h * 128 + j * 32 + 16 * c + 4 * t;
     }
-    return (step >> 1) * 32 + 16 * (step & 1) + 4 * t;
+    return (h * 4 + (step >> 1)) * 32 + 16 * (step & 1) + 4 * t;
 }
 
 template <int QUANT>
-__device__ __forceinline__ void load_bfrags(const uint8_t* xrow, int span, int t, uint2 (&bf)[16]) {
+__device__ __forceinline__ void load_bfrags_half(const uint8_t* xrow, int span, int h, int t, uint2* bf) {
 #pragma unroll
-    for (int step = 0; step < 16; ++step)
-        bf[step] = *(const uint2*)(xrow + 2 * (span * 256 + step_k_offset<QUANT>(step, t)));
+    for (int step = 0; step < 8; ++step)
+        bf[step] = *(const uint2*)(xrow + 2 * (span * 256 + step_k_offset<QUANT>(h, step, t)));
 }
 
 // The host only selects these kernels when every row pitch is a multiple of 4
 // bytes, so all lanes of a warp (and both fragment rows) share one alignment.
 template <int QUANT>
-__device__ __forceinline__ void span_dispatch(const uint8_t* pa, const uint8_t* pb, const uint2 (&bf)[16], int lane,
+__device__ __forceinline__ void half_dispatch(const uint8_t* pa, const uint8_t* pb, int h, const uint2* bf, int lane,
                                               float (&acc)[4]) {
-    if ((uintptr_t)pa & 2) stream_span<QUANT, true>(pa, pb, bf, lane, acc);
-    else stream_span<QUANT, false>(pa, pb, bf, lane, acc);
+    if ((uintptr_t)pa & 2) stream_half<QUANT, true>(pa, pb, h, bf, lane, acc);
+    else stream_half<QUANT, false>(pa, pb, h, bf, lane, acc);
+}
+
+// MODE_DOWN: the tile row (0..127) that fragment row g (half 0) or g+8 (half 1)
+// of warp w reads.  With step 1 a warp owns 16 consecutive rows.  With step 4
+// the eight rows of a fragment half are four rows apart: a 420-byte row pitch
+// (two Q6_K superblocks) is 105 words, so rows four apart start 4 banks apart
+// and the eight 16-byte reads of a load cover all 32 banks exactly once.
+__device__ __forceinline__ int down_row(int w, int g, int half, int step) {
+    if (step == 4) return (w >> 1) * 32 + 4 * g + 2 * (w & 1) + half;
+    return w * 16 + g + 8 * half;
+}
+
+// Which span feeds half `h` of warp-slot `w`.  Superblocks of 210 bytes
+// alternate between word-aligned and not, so a gate/up warp takes its two
+// halves from neighbouring spans: every warp then carries one aligned and one
+// unaligned half and the eight warps of a group finish together.
+__device__ __forceinline__ int gateup_span_of(int w, int h, int n_spans) {
+    return h == 0 ? w : (w + 1) % n_spans;
 }
 
 // ---------------------------------------------------------------------------
@@ -318,6 +354,27 @@ __global__ void __launch_bounds__(kStreamThreads, 1) k_expert_stream(StreamLaunc
                 expert = -1;
                 first = (cg - plan.n_routed) * 8;
                 ncols = min(8, *L.valid_tokens - first);
+            }
+            // self-check: a column group that points outside its buffers is skipped and
+            // recorded, never dereferenced
+            bool sane = ncols >= 1 && ncols <= 8 && first >= 0;
+            if (!shared) {
+                sane = sane && expert >= 0 && expert < L.num_experts;
+                if (MODE == MODE_GATEUP) {
+                    for (int c = 0; sane && c < ncols; ++c) {
+                        int tok = item[4 + c] / L.top_k;
+                        sane = item[4 + c] >= 0 && tok < L.max_tokens;
+                    }
+                } else {
+                    sane = sane && first + ncols <= L.x_rows_routed;
+                }
+            } else {
+                sane = sane && first + ncols <= L.max_tokens;
+            }
+            if (!sane) {
+                *abortp = 1;
+                atomicExch(L.status, STATUS_BAD_WORK_ITEM);
+                return;
             }
             desc[0] = expert;
             desc[1] = first;
@@ -385,10 +442,14 @@ __global__ void __launch_bounds__(kStreamThreads, 1) k_expert_stream(StreamLaunc
         uint2 bf[NSP][16];
 #pragma unroll
         for (int sp = 0; sp < NSP; ++sp) {
-            int span = MODE == MODE_GATEUP ? w : sp;
-            if (span < n_spans) {
-                if (quant == QUANT_Q6K) load_bfrags<QUANT_Q6K>(xrow, span, t, bf[sp]);
-                else load_bfrags<QUANT_Q8_0>(xrow, span, t, bf[sp]);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                int span = MODE == MODE_GATEUP ? gateup_span_of(w, h, n_spans) : sp;
+                bool on = MODE == MODE_GATEUP ? w < n_spans : sp < n_spans;
+                if (on) {
+                    if (quant == QUANT_Q6K) load_bfrags_half<QUANT_Q6K>(xrow, span, h, t, &bf[sp][8 * h]);
+                    else load_bfrags_half<QUANT_Q8_0>(xrow, span, h, t, &bf[sp][8 * h]);
+                }
             }
         }
         __syncwarp();
@@ -397,7 +458,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) k_expert_stream(StreamLaunc
         const int t_begin = run * plan.tiles_per_unit;
         const int t_end = min(plan.row_tiles, t_begin + plan.tiles_per_unit);
         for (int tile = t_begin; tile < t_end; ++tile, ++it) {
-            if ((int)(it & 1) != gi) continue;
+            if ((int)(it % kStreamGroups) != gi) continue;
             const int st = it % S;
             if (!stream_wait(&bars.full[st], (it / S) & 1, abortp, L.status)) return;
             const uint8_t* tb = smem + lay.stages + (uint32_t)st * stage_bytes +
@@ -405,21 +466,27 @@ __global__ void __launch_bounds__(kStreamThreads, 1) k_expert_stream(StreamLaunc
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
             if (MODE == MODE_GATEUP) {
                 if (w < n_spans) {
-                    const uint8_t* pa = tb + g * row_bytes + w * span_bytes_of(quant);
-                    const uint8_t* pb = pa + L.tile_cap;
-                    if (quant == QUANT_Q6K) span_dispatch<QUANT_Q6K>(pa, pb, bf[0], lane, acc);
-                    else span_dispatch<QUANT_Q8_0>(pa, pb, bf[0], lane, acc);
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const uint8_t* pa = tb + g * row_bytes + gateup_span_of(w, h, n_spans) * span_bytes_of(quant);
+                        const uint8_t* pb = pa + L.tile_cap;
+                        if (quant == QUANT_Q6K) half_dispatch<QUANT_Q6K>(pa, pb, h, &bf[0][8 * h], lane, acc);
+                        else half_dispatch<QUANT_Q8_0>(pa, pb, h, &bf[0][8 * h], lane, acc);
+                    }
                 }
             } else {
-                const uint8_t* pa = tb + (size_t)(w * 16 + g) * row_bytes;
-                const uint8_t* pb = pa + 8 * (size_t)row_bytes;
+                const uint8_t* pa = tb + (size_t)down_row(w, g, 0, L.down_row_step) * row_bytes;
+                const uint8_t* pb = tb + (size_t)down_row(w, g, 1, L.down_row_step) * row_bytes;
 #pragma unroll
                 for (int sp = 0; sp < NSP; ++sp) {
                     if (sp < n_spans) {
-                        if (quant == QUANT_Q6K)
-                            span_dispatch<QUANT_Q6K>(pa + sp * 210, pb + sp * 210, bf[sp], lane, acc);
-                        else
-                            span_dispatch<QUANT_Q8_0>(pa + sp * 272, pb + sp * 272, bf[sp], lane, acc);
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            if (quant == QUANT_Q6K)
+                                half_dispatch<QUANT_Q6K>(pa + sp * 210, pb + sp * 210, h, &bf[sp][8 * h], lane, acc);
+                            else
+                                half_dispatch<QUANT_Q8_0>(pa + sp * 272, pb + sp * 272, h, &bf[sp][8 * h], lane, acc);
+                        }
                     }
                 }
             }
@@ -459,28 +526,29 @@ __global__ void __launch_bounds__(kStreamThreads, 1) k_expert_stream(StreamLaunc
                 }
                 ++gt;
             } else {
-                const int row = tile * 128 + w * 16 + g;
+                const int row_lo = tile * 128 + down_row(w, g, 0, L.down_row_step);
+                const int row_hi = tile * 128 + down_row(w, g, 1, L.down_row_step);
                 if (shared) {
                     if (2 * t < ncols) {
                         float* dst = L.shexp + (size_t)(first + 2 * t) * L.rows;
-                        dst[row] = acc[0];
-                        dst[row + 8] = acc[2];
+                        dst[row_lo] = acc[0];
+                        dst[row_hi] = acc[2];
                     }
                     if (2 * t + 1 < ncols) {
                         float* dst = L.shexp + (size_t)(first + 2 * t + 1) * L.rows;
-                        dst[row] = acc[1];
-                        dst[row + 8] = acc[3];
+                        dst[row_lo] = acc[1];
+                        dst[row_hi] = acc[3];
                     }
                 } else {
                     if (2 * t < ncols) {
                         float* dst = L.partial + (size_t)flat0 * L.rows;
-                        dst[row] = wgt0 * acc[0];
-                        dst[row + 8] = wgt0 * acc[2];
+                        dst[row_lo] = wgt0 * acc[0];
+                        dst[row_hi] = wgt0 * acc[2];
                     }
                     if (2 * t + 1 < ncols) {
                         float* dst = L.partial + (size_t)flat1 * L.rows;
-                        dst[row] = wgt1 * acc[1];
-                        dst[row + 8] = wgt1 * acc[3];
+                        dst[row_lo] = wgt1 * acc[1];
+                        dst[row_hi] = wgt1 * acc[3];
                     }
                 }
             }

@@ -196,9 +196,14 @@ StreamShape stream_shape(int mode, int rows, int k, int q_routed, int q_shared) 
     uint32_t rows_per_tile = mode == MODE_GATEUP ? 8 : 128;
     sh.tile_cap = (staged_capacity(rows_per_tile * rb_max) + 15u) & ~15u;
     sh.x_stride = (uint32_t)k * 2u + kXRowPadBytes;
-    for (int S = kStreamMaxStages; S >= 2; --S) {
+    int s_max = kStreamMaxStages;
+    if (const char* e = getenv("XABE_MOE_STREAM_STAGES")) {  // tuning aid
+        int v = atoi(e);
+        if (v >= 2 && v < s_max) s_max = v;
+    }
+    for (int S = s_max; S >= 2; --S) {
         StreamSmem L = stream_smem_layout(mode, S, sh.tile_cap, sh.x_stride);
-        if (L.total <= 200u * 1024u) {
+        if (L.total <= 226u * 1024u) {
             sh.ok = true;
             sh.n_stages = S;
             sh.smem = L.total;
@@ -282,6 +287,9 @@ int run_experts(xabe_moe* m, cudaStream_t st, const MlpWeights& routed, const Ml
     SL.inter_shared = m->inter_shared;
     SL.partial = m->partial;
     SL.shexp = shexp_out;
+    SL.num_experts = (int)g.num_experts;
+    SL.max_tokens = (int)g.max_tokens;
+    SL.x_rows_routed = (int)m->sorted_capacity;
     StreamShape gu = stream_shape(MODE_GATEUP, (int)g.intermediate, (int)g.hidden, qr, qs);
     if (gu.ok && !m->force_tile_kernels) {
         SL.r_a = L.r_a; SL.r_b = L.r_b; SL.s_a = L.s_a; SL.s_b = L.s_b;
@@ -320,6 +328,13 @@ int run_experts(xabe_moe* m, cudaStream_t st, const MlpWeights& routed, const Ml
         SL.rows = L.rows; SL.k = L.k;
         SL.x_routed = m->inter_routed; SL.x_shared = m->inter_shared;
         SL.n_stages = dn.n_stages; SL.tile_cap = dn.tile_cap; SL.x_stride = dn.x_stride;
+        {
+            // rows four apart land 4 banks apart when the row pitch in words is 4 * odd + 1 ... see down_row
+            uint32_t words = (uint32_t)(L.k / 256) * span_bytes_of(qr) / 4u;
+            uint32_t words_s = (uint32_t)(L.k / 256) * span_bytes_of(qs) / 4u;
+            bool four = ((words * 4u) % 32u) % 8u == 4u && ((words_s * 4u) % 32u) % 8u == 4u;
+            SL.down_row_step = four ? 4 : 1;
+        }
         return launch_stream<MODE_DOWN>(m, st, SL, dn.smem, qr, qs);
     }
     size_t smem = down_smem(L.k, qr);
