@@ -13,10 +13,14 @@
 #include "expert_kernels.cuh"
 #include "glue_kernels.cuh"
 #include "stream_kernels.cuh"
+#include "prefill_kernels.cuh"
 
 using namespace xabe;
 
 namespace {
+
+// Wide passes only take the tcgen05 prefill kernels; the launch shape comes from max_tokens.
+constexpr uint32_t kPrefillMinTokens = 512;
 
 thread_local std::string g_last_error;
 
@@ -80,6 +84,9 @@ struct xabe_moe {
     int* n_work = nullptr;      // device scalar: routed column groups this step
     uint64_t work_capacity = 0;
     int sm_count = 0;
+    int* pf_items = nullptr;    // token tiles for the tcgen05 prefill kernels
+    int* pf_n_items = nullptr;
+    uint64_t pf_capacity = 0;
     bool force_tile_kernels = false;  // use the one-tile-per-CTA kernels even where the streaming ones apply
     float* normed = nullptr;
     __half* normed_h = nullptr;
@@ -231,6 +238,33 @@ int launch_stream(xabe_moe* m, cudaStream_t st, const StreamLaunch& L, uint32_t 
                                  : launch_stream_t<MODE, QUANT_Q8_0, QUANT_Q8_0>(m, st, L, smem);
 }
 
+// ---- prefill (tcgen05) expert kernels ---------------------------------------
+// Wide passes only: the launch shape comes from max_tokens, as every other one.
+
+bool prefill_applies(const xabe_moe* m, int gateup_rows, int down_rows, int hidden, int inter) {
+    if (m->exact_decode || m->force_tile_kernels) return false;
+    if (const char* e = getenv("XABE_MOE_NO_PREFILL_KERNELS")) if (e[0] == '1') return false;
+    if (m->g.max_tokens < kPrefillMinTokens) return false;
+    return gateup_rows % 64 == 0 && down_rows % kPfTileM == 0 && hidden % kPfChunkK == 0 && inter % kPfChunkK == 0;
+}
+
+template <int MODE, int QR, int QS>
+int launch_prefill_t(cudaStream_t st, const PrefillLaunch& L, dim3 grid, size_t smem) {
+    auto kern = k_prefill_gemm<MODE, QR, QS>;
+    CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<grid, kPfThreads, smem, st>>>(L);
+    CUDA_TRY(cudaGetLastError());
+    return XABE_OK;
+}
+template <int MODE>
+int launch_prefill(cudaStream_t st, const PrefillLaunch& L, dim3 grid, size_t smem, int qr, int qs) {
+    if (qr == XABE_QUANT_Q6_K)
+        return qs == XABE_QUANT_Q6_K ? launch_prefill_t<MODE, QUANT_Q6K, QUANT_Q6K>(st, L, grid, smem)
+                                     : launch_prefill_t<MODE, QUANT_Q6K, QUANT_Q8_0>(st, L, grid, smem);
+    return qs == XABE_QUANT_Q6_K ? launch_prefill_t<MODE, QUANT_Q8_0, QUANT_Q6K>(st, L, grid, smem)
+                                 : launch_prefill_t<MODE, QUANT_Q8_0, QUANT_Q8_0>(st, L, grid, smem);
+}
+
 struct MlpWeights {
     bool present = false;
     xabe_quant_tensor gate{}, up{}, down{};
@@ -275,6 +309,42 @@ int run_experts(xabe_moe* m, cudaStream_t st, const MlpWeights& routed, const Ml
     L.x_shared = m->normed_h;
     L.inter_routed = m->inter_routed;
     L.inter_shared = m->inter_shared;
+    if (prefill_applies(m, (int)g.intermediate, (int)g.hidden, (int)g.hidden, (int)g.intermediate)) {
+        PrefillLaunch P{};
+        P.top_k = L.top_k;
+        P.has_routed = routed.present;
+        P.has_shared = shared.present;
+        P.items = m->pf_items;
+        P.n_items = m->pf_n_items;
+        P.valid_tokens = m->valid_tokens;
+        P.sorted_token_ids = m->sorted_token_ids;
+        P.topk_weights = m->topk_weights;
+        P.inter_routed = m->inter_routed;
+        P.inter_shared = m->inter_shared;
+        P.partial = m->partial;
+        P.shexp = shexp_out;
+        P.status = m->status;
+        P.max_tokens = (int)g.max_tokens;
+        P.n_stages = kPfMaxStages;
+        size_t smem_pf = (size_t)P.n_stages * kPfStageBytes + 1024;
+        unsigned ycap = (routed.present ? (unsigned)m->pf_capacity : 0u) +
+                        (shared.present ? (g.max_tokens + kPfTileN - 1) / kPfTileN : 0u);
+        P.r_a = L.r_a; P.r_b = L.r_b; P.s_a = L.s_a; P.s_b = L.s_b;
+        P.rows = (int)g.intermediate; P.k = (int)g.hidden;
+        P.x_routed = m->normed_h; P.x_shared = m->normed_h;
+        int rcp = launch_prefill<MODE_GATEUP>(st, P, dim3(g.intermediate / 64, ycap), smem_pf, qr, qs);
+        if (rcp) return rcp;
+        if (mark_between >= 0) prof_mark(m, st, mark_between);
+        int qrd = routed.present ? routed.down.quant : shared.down.quant;
+        int qsd = shared.present ? shared.down.quant : qrd;
+        P.r_a = routed.present ? (const uint8_t*)routed.down.dev_bytes : nullptr;
+        P.r_b = nullptr;
+        P.s_a = shared.present ? (const uint8_t*)shared.down.dev_bytes : nullptr;
+        P.s_b = nullptr;
+        P.rows = (int)g.hidden; P.k = (int)g.intermediate;
+        P.x_routed = m->inter_routed; P.x_shared = m->inter_shared;
+        return launch_prefill<MODE_DOWN>(st, P, dim3(g.hidden / kPfTileM, ycap), smem_pf, qrd, qsd);
+    }
     StreamLaunch SL{};
     SL.top_k = L.top_k;
     SL.has_routed = routed.present;
@@ -411,6 +481,12 @@ int launch_route_and_dispatch(xabe_moe* m, cudaStream_t st, const float* logits)
             (int)m->sorted_capacity, (int)m->block_capacity, m->topk_ids, m->topk_weights, m->sorted_token_ids,
             m->expert_ids, m->num_tokens_post_pad, m->expert_offsets, m->expert_counts, m->work_items, m->n_work);
         CUDA_TRY(cudaGetLastError());
+        if (g.max_tokens >= kPrefillMinTokens) {  // few experts, many tokens: the prefill kernels still apply
+            int threads = ((int)g.num_experts + 31) / 32 * 32;
+            k_build_prefill_items<<<1, threads, hist_bytes, st>>>((int)g.num_experts, m->expert_offsets,
+                                                                  m->expert_counts, m->pf_items, m->pf_n_items);
+            CUDA_TRY(cudaGetLastError());
+        }
         return XABE_OK;
     }
     k_route<<<(g.max_tokens + 7) / 8, 256, 0, st>>>(logits, m->valid_tokens, (int)g.num_experts,
@@ -432,6 +508,9 @@ int launch_route_and_dispatch(xabe_moe* m, cudaStream_t st, const float* logits)
     CUDA_TRY(cudaGetLastError());
     k_build_work<<<1, threads, hist_bytes, st>>>((int)g.num_experts, m->expert_offsets, m->expert_counts,
                                                  m->sorted_token_ids, m->topk_weights, m->work_items, m->n_work);
+    CUDA_TRY(cudaGetLastError());
+    k_build_prefill_items<<<1, threads, hist_bytes, st>>>((int)g.num_experts, m->expert_offsets, m->expert_counts,
+                                                          m->pf_items, m->pf_n_items);
     CUDA_TRY(cudaGetLastError());
     return XABE_OK;
 }
@@ -543,6 +622,9 @@ int xabe_moe_create(const xabe_moe_geometry* geometry, int device, int scope, fl
         m->work_capacity = (T * K + 7) / 8 + (E < T * K ? E : T * K) + 1;
         A(dev_alloc(&m->work_items, (size_t)m->work_capacity * kWorkItemInts));
         A(dev_alloc(&m->n_work, 1));
+        m->pf_capacity = (T * K + kPfTileN - 1) / kPfTileN + (E < T * K ? E : T * K) + 1;
+        A(dev_alloc(&m->pf_items, (size_t)m->pf_capacity * kPfItemInts));
+        A(dev_alloc(&m->pf_n_items, 1));
         A(dev_alloc(&m->logits, T * E));
         A(dev_alloc(&m->inter_routed, (size_t)cap * I));
         A(dev_alloc(&m->partial, T * K * H));
@@ -561,7 +643,7 @@ void xabe_moe_destroy(xabe_moe* m) {
     if (!m) return;
     cudaSetDevice(m->device);
     void* dev[] = {m->valid_tokens, m->status, m->topk_ids, m->topk_weights, m->sorted_token_ids, m->expert_ids,
-                   m->num_tokens_post_pad, m->chunk_hist, m->expert_offsets, m->expert_counts, m->work_items, m->n_work,
+                   m->num_tokens_post_pad, m->chunk_hist, m->expert_offsets, m->expert_counts, m->work_items, m->n_work, m->pf_items, m->pf_n_items,
                    m->normed, m->normed_h, m->logits,
                    m->inter_routed, m->inter_shared, m->partial, m->routed, m->shexp, m->gate, m->stage_in,
                    m->stage_ffn, m->stage_out};
