@@ -233,6 +233,29 @@ int xabe_moe_stage_times(xabe_moe* m, void* stream, float* ms_sum, int* calls);
  * `out` receives n_bytes / block_bytes * block_elements floats. */
 int xabe_dequantize(void* stream, xabe_quant_tensor t, float* out);
 
+/* Shared-expert MLP (expert_mlp of one expert for `tokens` rows, ungated) for
+ * callers that cannot allocate device memory.  It has no counterpart in the
+ * reference.  Who needs it: a worker whose device memory was all handed out at
+ * start-up and is guarded by its own arena, or code that runs where the CUDA
+ * allocator must not be entered (a latency-critical callback, a region under
+ * another allocator's lock) -- such callers cannot call xabe_moe_create, which
+ * allocates.  This call allocates nothing, on the host or on the device: its
+ * scratch (f16 activations, f16 SwiGLU intermediate, two control words) is a
+ * 327,936-byte static device array that every GPU loading the library holds
+ * until the process exits.
+ *   limits: tokens <= 64, hidden <= 2048, intermediate <= 512 (both multiples
+ *           of 256); anything larger is rejected with a status and a message.
+ *   `hidden_states` [tokens][hidden] f32 and `out` [tokens][hidden] f32 are
+ *   device buffers of the caller; weights as for xabe_moe_shared_expert.
+ *   The first call on a device looks up the array's device address; make that
+ *   first call before any stream capture.  All calls share the one array, which
+ *   keeps the previous call's contents (the call rewrites every word it later
+ *   reads): two calls whose kernels overlap on the GPU -- different streams, or
+ *   different host threads -- race on it, so keep them on one stream. */
+int xabe_shared_expert_noalloc(void* stream, xabe_quant_tensor gate, xabe_quant_tensor up,
+                               xabe_quant_tensor down, int hidden, int intermediate,
+                               const float* hidden_states, int tokens, float* out);
+
 #ifdef __cplusplus
 }
 #endif

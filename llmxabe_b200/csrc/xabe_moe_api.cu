@@ -919,3 +919,139 @@ int xabe_dequantize(void* stream, xabe_quant_tensor t, float* out) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Shared-expert MLP for callers that must not allocate.
+//
+// Some hosts of this library run where device allocation is off the table: a
+// serving worker whose memory budget was handed out at start-up and is guarded
+// by its own arena, or a caller inside a region where the CUDA allocator may
+// not be entered (a latency-critical callback, code running under a foreign
+// allocator's lock).  xabe_moe_create allocates, so such a caller cannot hold a
+// handle.  This entry point needs none: its scratch (the f16 copy of the
+// activations, the f16 SwiGLU intermediate, the live-token scalar and the
+// status word) lives in one file-scope device array that every GPU loading the
+// library carries until the process exits.
+// ---------------------------------------------------------------------------
+namespace {
+
+constexpr int kNoAllocMaxTokens = 64;
+constexpr int kNoAllocMaxHidden = 2048;
+constexpr int kNoAllocMaxInter = 512;
+constexpr size_t kNoAllocHeader = 256;  // [0] live tokens, [1] status word
+constexpr size_t kNoAllocXBytes = (size_t)kNoAllocMaxTokens * kNoAllocMaxHidden * sizeof(__half);
+constexpr size_t kNoAllocInterBytes = (size_t)kNoAllocMaxTokens * kNoAllocMaxInter * sizeof(__half);
+constexpr size_t kNoAllocBytes = kNoAllocHeader + kNoAllocXBytes + kNoAllocInterBytes;  // 327,936 B
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+constexpr int kNoAllocMaxDevices = 64;
+unsigned char* g_noalloc_ptr[kNoAllocMaxDevices] = {};  // device address of the array, per device
+
+// In host code `g_noalloc_scratch` is only a handle for the runtime, not an
+// address a kernel may use: the device address comes from the runtime, once
+// per device, with that device current.
+int noalloc_scratch_for_current_device(unsigned char** out) {
+    int dev = -1;
+    CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kNoAllocMaxDevices)
+        return fail(XABE_ERR_DRIVER, "device index %d is outside the %d this entry point tracks", dev,
+                    kNoAllocMaxDevices);
+    if (!g_noalloc_ptr[dev]) {
+        unsigned char* p = nullptr;
+        CUDA_TRY(cudaGetSymbolAddress((void**)&p, g_noalloc_scratch));
+        if (!p) return fail(XABE_ERR_DRIVER, "the runtime returned a null address for the static scratch");
+        g_noalloc_ptr[dev] = p;
+    }
+    *out = g_noalloc_ptr[dev];
+    return XABE_OK;
+}
+
+}  // namespace
+
+extern "C" int xabe_shared_expert_noalloc(void* stream, xabe_quant_tensor gate, xabe_quant_tensor up,
+                                          xabe_quant_tensor down, int hidden, int intermediate,
+                                          const float* hidden_states, int tokens, float* out) {
+    if (!hidden_states || !out) return fail(XABE_ERR_INVALID_ARGUMENT, "null activation or output pointer");
+    if (tokens < 0 || tokens > kNoAllocMaxTokens)
+        return fail(XABE_ERR_TOO_MANY_TOKENS, "%d tokens exceeds the %d the static scratch holds", tokens,
+                    kNoAllocMaxTokens);
+    if (hidden <= 0 || intermediate <= 0 || hidden % 256 != 0 || intermediate % 256 != 0 || hidden % 64 != 0)
+        return fail(XABE_ERR_UNSUPPORTED_GEOMETRY,
+                    "hidden %d / intermediate %d: both must be positive multiples of 256", hidden, intermediate);
+    if (hidden > kNoAllocMaxHidden || intermediate > kNoAllocMaxInter)
+        return fail(XABE_ERR_UNSUPPORTED_GEOMETRY,
+                    "hidden %d / intermediate %d exceed the %d / %d the static scratch holds", hidden, intermediate,
+                    kNoAllocMaxHidden, kNoAllocMaxInter);
+    size_t n = (size_t)hidden * intermediate;
+    int rc;
+    if ((rc = check_stack("shared gate", gate, n))) return rc;
+    if ((rc = check_stack("shared up", up, n))) return rc;
+    if ((rc = check_stack("shared down", down, n))) return rc;
+    if (gate.quant != up.quant)
+        return fail(XABE_ERR_UNSUPPORTED_EXPERT_TYPE, "gate and up must share one format (found tags %d and %d)",
+                    gate.quant, up.quant);
+    const int bucket = 16;
+    size_t smem_gu = gateup_smem(hidden, gate.quant, bucket);
+    size_t smem_dn = down_smem(intermediate, down.quant);
+    if (smem_gu > 48 * 1024 || smem_dn > 48 * 1024)
+        return fail(XABE_ERR_UNSUPPORTED_GEOMETRY, "row tiles of %zu / %zu bytes exceed the 48 KB this entry point uses",
+                    smem_gu, smem_dn);
+    if (tokens == 0) return XABE_OK;
+    unsigned char* base = nullptr;
+    if ((rc = noalloc_scratch_for_current_device(&base))) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    int* live = (int*)base;
+    int* status = live + 1;
+    __half* x_h = (__half*)(base + kNoAllocHeader);
+    __half* inter = (__half*)(base + kNoAllocHeader + kNoAllocXBytes);
+    // the array keeps the previous call's contents: the two words that must start clean are rewritten,
+    // the activation and intermediate rows this call reads are all rewritten by it
+    k_set_scalar<<<1, 1, 0, st>>>(live, tokens);
+    k_set_scalar<<<1, 1, 0, st>>>(status, 0);
+    k_rows_to_half<<<tokens, 256, 0, st>>>(hidden_states, x_h, live, hidden);
+    CUDA_TRY(cudaGetLastError());
+    ExpertLaunch L{};
+    L.routed_blocks = 0;
+    L.block_size = bucket;
+    L.top_k = 1;
+    L.max_tokens = kNoAllocMaxTokens;
+    L.valid_tokens = live;
+    L.status = status;
+    L.s_a = (const uint8_t*)gate.dev_bytes;
+    L.s_b = (const uint8_t*)up.dev_bytes;
+    L.rows = intermediate;
+    L.k = hidden;
+    L.x_shared = x_h;
+    L.inter_shared = inter;
+    unsigned tiles = (unsigned)((tokens + bucket - 1) / bucket);
+    // The dynamic shared-memory ceiling of a kernel is a per-function attribute that other entry points
+    // of this library also set; state it again here (an attribute write, not an allocation).
+    if (gate.quant == XABE_QUANT_Q6_K) {
+        CUDA_TRY(cudaFuncSetAttribute(k_expert_gateup<QUANT_Q6K, QUANT_Q6K>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_gu));
+        k_expert_gateup<QUANT_Q6K, QUANT_Q6K><<<dim3(intermediate / 8, tiles), kExpertThreads, smem_gu, st>>>(L);
+    } else {
+        CUDA_TRY(cudaFuncSetAttribute(k_expert_gateup<QUANT_Q8_0, QUANT_Q8_0>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_gu));
+        k_expert_gateup<QUANT_Q8_0, QUANT_Q8_0><<<dim3(intermediate / 8, tiles), kExpertThreads, smem_gu, st>>>(L);
+    }
+    CUDA_TRY(cudaGetLastError());
+    L.s_a = (const uint8_t*)down.dev_bytes;
+    L.s_b = nullptr;
+    L.rows = hidden;
+    L.k = intermediate;
+    L.x_shared = inter;
+    L.shexp = out;
+    if (down.quant == XABE_QUANT_Q6_K) {
+        CUDA_TRY(cudaFuncSetAttribute(k_expert_down<QUANT_Q6K, QUANT_Q6K>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dn));
+        k_expert_down<QUANT_Q6K, QUANT_Q6K><<<dim3(hidden / 64, tiles), kExpertThreads, smem_dn, st>>>(L);
+    } else {
+        CUDA_TRY(cudaFuncSetAttribute(k_expert_down<QUANT_Q8_0, QUANT_Q8_0>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dn));
+        k_expert_down<QUANT_Q8_0, QUANT_Q8_0><<<dim3(hidden / 64, tiles), kExpertThreads, smem_dn, st>>>(L);
+    }
+    CUDA_TRY(cudaGetLastError());
+    return XABE_OK;
+}

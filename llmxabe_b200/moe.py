@@ -245,6 +245,19 @@ def dequantize(t: QuantTensor, stream=None) -> torch.Tensor:
     return out
 
 
+def shared_expert_noalloc(gate: QuantTensor, up: QuantTensor, down: QuantTensor, hidden: int, intermediate: int,
+                          hidden_states: torch.Tensor, tokens: int, out: torch.Tensor, stream=None) -> None:
+    """Shared-expert MLP for callers that cannot allocate device memory (no handle, static scratch).
+
+    Meant for a worker whose memory was all handed out at start-up, or for code that runs where the
+    CUDA allocator must not be entered.  Limits: tokens <= 64, hidden <= 2048, intermediate <= 512.
+    Calls share one static scratch array, so keep them on one stream; make the first call on a device
+    before any stream capture.
+    """
+    _check(_lib.lib().xabe_shared_expert_noalloc(_stream_ptr(stream), gate._c(), up._c(), down._c(), hidden,
+                                                 intermediate, hidden_states.data_ptr(), tokens, out.data_ptr()))
+
+
 class MoeLayerWeights:
     """One layer's MoE weights resident on the device (block/moe.rs:634-658).
 
