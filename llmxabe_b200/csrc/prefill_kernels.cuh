@@ -173,50 +173,64 @@ __device__ __forceinline__ uint4 codes8_to_h8(uint32_t c0, uint32_t c1, uint32_t
     return o;
 }
 
-// Dequantise 32 consecutive elements [k0, k0 + 32) of one weight row (k0 a
-// multiple of 32) into four 16-byte chunks of the A tile.
+// Raw bytes of 32 consecutive weights [k0, k0 + 32) of one row (k0 a multiple
+// of 32), fetched ahead of their use so that the global-load latency of chunk
+// kc + 1 hides behind the arithmetic of chunk kc.
+struct Raw32 {
+    uint32_t lo[8];  // Q6_K: the 32 nibble bytes; Q8_0: the 32 codes
+    uint32_t hi[8];  // Q6_K: the 32 bit-pair bytes
+    float s0, s1;    // scale of elements 0-15 and 16-31, times kPfWeightScale
+};
+
 template <int QUANT>
-__device__ __forceinline__ void dequant32_to_smem(const uint8_t* row_bytes_ptr, int k0, uint8_t* a_tile, int tile_row,
-                                                  int chunk0) {
+__device__ __forceinline__ void load_raw32(const uint8_t* row_ptr, int k0, Raw32& r) {
     if (QUANT == QUANT_Q6K) {
         // element map of crates/xabe-kernels/src/quant.rs:175-198
-        const uint8_t* blk = row_bytes_ptr + (size_t)(k0 >> 8) * kQ6KBlockBytes;
-        int r = k0 & 255;
-        int half = r >> 7, j = (r & 127) >> 5;
-        uint32_t ql[8], qh[8];
-        ldg_32bytes(blk + half * 64 + (j & 1) * 32, ql);
-        ldg_32bytes(blk + 128 + half * 32, qh);
+        const uint8_t* blk = row_ptr + (size_t)(k0 >> 8) * kQ6KBlockBytes;
+        int e = k0 & 255;
+        int half = e >> 7, j = (e & 127) >> 5;
+        ldg_32bytes(blk + half * 64 + (j & 1) * 32, r.lo);
+        ldg_32bytes(blk + 128 + half * 32, r.hi);
         float d = __half2float(__ushort_as_half(__ldg((const unsigned short*)(blk + 208)))) * kPfWeightScale;
-        float s0 = d * (float)(int)(int8_t)__ldg(blk + 192 + half * 8 + 2 * j);
-        float s1 = d * (float)(int)(int8_t)__ldg(blk + 192 + half * 8 + 2 * j + 1);
-        __half2 ds[2] = {__float2half2_rn(s0), __float2half2_rn(s1)};
+        // both scales sit in one 2-byte-aligned halfword: index half*8 + 2*j (+1)
+        unsigned short sc = __ldg((const unsigned short*)(blk + 192 + half * 8 + 2 * j));
+        r.s0 = d * (float)(int)(int8_t)(sc & 0xFF);
+        r.s1 = d * (float)(int)(int8_t)(sc >> 8);
+    } else {
+        const uint8_t* blk = row_ptr + (size_t)(k0 >> 5) * kQ8BlockBytes;
+        ldg_32bytes(blk + 2, r.lo);
+        float d = __half2float(__ushort_as_half(__ldg((const unsigned short*)blk))) * kPfWeightScale;
+        r.s0 = r.s1 = d;
+    }
+}
+
+// Unpack, scale and store the 32 weights as four 16-byte chunks of the A tile.
+template <int QUANT>
+__device__ __forceinline__ void store_raw32(const Raw32& r, int k0, uint8_t* a_tile, int tile_row, int chunk0) {
+    __half2 ds[2] = {__float2half2_rn(r.s0), __float2half2_rn(r.s1)};
+    if (QUANT == QUANT_Q6K) {
+        const int j = ((k0 & 127) >> 5);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
             uint32_t raw[2];
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
-                uint32_t lo = (j < 2 ? ql[2 * c + i] : (ql[2 * c + i] >> 4)) & 0x0F0F0F0Fu;
-                uint32_t hi = ((qh[2 * c + i] >> (2 * j)) & 0x03030303u) << 4;
+                uint32_t lo = (j < 2 ? r.lo[2 * c + i] : (r.lo[2 * c + i] >> 4)) & 0x0F0F0F0Fu;
+                uint32_t hi = ((r.hi[2 * c + i] >> (2 * j)) & 0x03030303u) << 4;
                 raw[i] = lo | hi;
             }
-            // l = 8c .. 8c+7: scale group l / 16
+            // elements 8c .. 8c+7 of the group: scale group (8c) / 16
             uint4 v = codes8_to_h8(raw[0], raw[1], 0x64206420u, ds[c >> 1]);
             *(uint4*)(a_tile + swz_off(tile_row, chunk0 + c)) = v;
         }
     } else {
-        const uint8_t* blk = row_bytes_ptr + (size_t)(k0 >> 5) * kQ8BlockBytes;
-        uint32_t q[8];
-        ldg_32bytes(blk + 2, q);
-        float d = __half2float(__ushort_as_half(__ldg((const unsigned short*)blk))) * kPfWeightScale;
-        __half2 ds2 = __float2half2_rn(d);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-            uint4 v = codes8_to_h8(q[2 * c] ^ 0x80808080u, q[2 * c + 1] ^ 0x80808080u, 0x64806480u, ds2);
+            uint4 v = codes8_to_h8(r.lo[2 * c] ^ 0x80808080u, r.lo[2 * c + 1] ^ 0x80808080u, 0x64806480u, ds[0]);
             *(uint4*)(a_tile + swz_off(tile_row, chunk0 + c)) = v;
         }
     }
 }
-
 
 __device__ __forceinline__ void mbar_arrive_pf(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -359,22 +373,38 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L)
         const int src = col_src[row];
         const __half* xptr = (shared ? L.x_shared : L.x_routed) + (size_t)(src < 0 ? 0 : src) * L.k;
         bool ok = true;
+        Raw32 raw;
+        uint4 xv[4];
+        const uint4 zero4 = make_uint4(0, 0, 0, 0);
+        // software pipeline: the bytes of chunk kc + 1 are in flight while chunk kc is unpacked
+        {
+            const int k0 = part * 32;
+            if (quant == QUANT_Q6K) load_raw32<QUANT_Q6K>(wptr, k0, raw);
+            else load_raw32<QUANT_Q8_0>(wptr, k0, raw);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) xv[c] = src < 0 ? zero4 : __ldg((const uint4*)(xptr + k0) + c);
+        }
         for (int kc = 0; kc < n_chunks && ok; ++kc) {
             const int st = kc % S;
             const uint32_t use = kc / S;
+            const int k0 = kc * kPfChunkK + part * 32;
+            Raw32 cur = raw;
+            uint4 xc[4] = {xv[0], xv[1], xv[2], xv[3]};
+            if (kc + 1 < n_chunks) {
+                const int k1 = k0 + kPfChunkK;
+                if (quant == QUANT_Q6K) load_raw32<QUANT_Q6K>(wptr, k1, raw);
+                else load_raw32<QUANT_Q8_0>(wptr, k1, raw);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) xv[c] = src < 0 ? zero4 : __ldg((const uint4*)(xptr + k1) + c);
+            }
             if (use >= 1) ok = stream_wait_pf(&empty_bar[st], (use - 1) & 1, abortp, L.status);
             if (!ok) break;
             uint8_t* a_tile = stages + (size_t)st * kPfStageBytes;
             uint8_t* b_tile = a_tile + kPfTileM * kPfChunkK * 2;
-            const int k0 = kc * kPfChunkK + part * 32;
-            if (quant == QUANT_Q6K) dequant32_to_smem<QUANT_Q6K>(wptr, k0, a_tile, row, part * 4);
-            else dequant32_to_smem<QUANT_Q8_0>(wptr, k0, a_tile, row, part * 4);
-            const uint4* xs = (const uint4*)(xptr + k0);
+            if (quant == QUANT_Q6K) store_raw32<QUANT_Q6K>(cur, k0, a_tile, row, part * 4);
+            else store_raw32<QUANT_Q8_0>(cur, k0, a_tile, row, part * 4);
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint4 v = src < 0 ? make_uint4(0, 0, 0, 0) : __ldg(xs + c);
-                *(uint4*)(b_tile + swz_off(row, part * 4 + c)) = v;
-            }
+            for (int c = 0; c < 4; ++c) *(uint4*)(b_tile + swz_off(row, part * 4 + c)) = xc[c];
             fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
             __syncwarp();
             if (lane == 0) mbar_arrive_pf(&full_bar[st]);
