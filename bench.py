@@ -34,6 +34,8 @@ WORKLOADS = {
     "decode3": (3, 16, True),       # BASELINE config 1, three sequences
     "decode64": (64, 16, True),     # BASELINE config 1, 64 tokens  (default)
     "prefill2048": (2048, 32, True),  # BASELINE config 2
+    # BASELINE config 3 (expert-parallel stack, strong scaling): run_ep() below; tokens/layers from --ep-*
+    "ep_prefill_stack": (16384, 64, True),
 }
 
 Q6K_EXPERT_BYTES = 3 * (512 * 2048 // 256) * 210   # 2,580,480
@@ -322,6 +324,107 @@ def run_ours(args) -> dict:
     return out if rank == 0 else {}
 
 
+def run_ep(args) -> dict:
+    """BASELINE config 3: a stack of MoE layers (Q6_K experts, Q8_0 shared expert), `--ep-tokens` tokens,
+    experts sharded over the ranks with NCCL all-to-all dispatch/combine.  Strong scaling: the global
+    batch is fixed, each rank owns tokens/N tokens and 256/N experts of every layer."""
+    import torch
+    import torch.distributed as dist
+
+    from llmxabe_b200 import synth
+    from llmxabe_b200.ep import CudaEpBackend, EpMoeBlock
+    from llmxabe_b200.moe import MoeGeometry, QuantTensor
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    E, K, H, I = 256, 8, 2048, 512
+    tokens, n_layers = args.ep_tokens, args.ep_layers
+    per, epr = tokens // world, E // world
+    g = MoeGeometry(E, K, H, I, 64, per)
+    max_rows = tokens * K if world == 1 else min(tokens * K, int(tokens * K / world * 3) + 1024)
+    layers = []
+    for li in range(n_layers):
+        # replicated tensors share one seed on every rank; the expert stacks are this rank's own
+        front = synth.moe_layer_on_device(seed=7, layer=li, num_experts=1, top_k=1, routed_quant=synth.Q6K,
+                                          shared_quant=synth.Q8_0, zipf=False)
+        gen = torch.Generator(device="cuda")
+        gen.manual_seed(7000 + li)
+        front.router = torch.randn(E, H, device="cuda", generator=gen) * 0.02
+        front.router_bias = torch.from_numpy(synth.zipf_bias(E, 7, li)).cuda()
+        gen.manual_seed(900000 + li * 64 + rank)
+        n = epr * I * H
+        local = [QuantTensor(synth._device_quant_bytes(torch, synth.Q6K, n, gen, "cuda"), front.gate_exps.quant)
+                 for _ in range(3)]
+        layers.append((front, local))
+    backend = CudaEpBackend(g, epr, max_rows, layers[0][0], *layers[0][1])
+    blk = EpMoeBlock(backend, E, K, rank, world)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(31 + rank)
+    x0 = torch.randn(per, H, device="cuda", generator=gen)
+    bufs = [torch.empty(per, H, device="cuda") for _ in range(2)]
+    ffn = torch.empty(per, H, device="cuda")
+
+    def step(_i):
+        h = x0
+        for li, (front, local) in enumerate(layers):
+            backend.set_layer(front, *local)
+            out = bufs[li & 1]
+            blk.forward(h, per, ffn, out)
+            h = out
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 1)):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    stream = torch.cuda.current_stream()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(args.steps):
+        step(i)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    barrier()
+    clocks = sampler.stop()
+    rows = sum(blk.last_plan.recv_counts)
+    if world > 1:
+        t = torch.tensor([ms, float(rows)], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, rows = float(t[0].item()), int(t[1].item())
+    status = backend.front_k.device_status() | backend.back_k.device_status()
+    flops = 2.0 * tokens * (K + 1) * 3 * H * I * n_layers
+    out = {
+        "metric": METRIC, "value": tokens * n_layers / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f16 x f16 -> f32 (tcgen05), weights dequantised to f16",
+        "data": "synthetic",
+        "config": {"workload": "ep_prefill_stack", "tokens_global": tokens, "layers": n_layers, "experts": E,
+                   "top_k": K, "hidden": H, "intermediate": I, "quant": "Q6_K experts, Q8_0 shared",
+                   "parallelism": f"ep{world} ({epr} experts/rank), NCCL all-to-all-v dispatch + combine",
+                   "max_rows_received_by_a_rank_last_layer": rows,
+                   "l2": "every layer has its own weights; a pass streams all of them"},
+        "clocks": clocks, "device_status": status,
+        "roofline": {"bound": "tensor", "achieved": flops / (ms * 1e-3) / 1e12 / world, "unit": "TFLOP/s per GPU",
+                     "peak": 1628.8, "frac": flops / (ms * 1e-3) / 1e12 / world / 1628.8, "traffic": None},
+        "gpu_launches": None,
+    }
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return out if rank == 0 else {}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -331,6 +434,8 @@ def main():
     ap.add_argument("--workload", default="decode64", choices=sorted(WORKLOADS))
     ap.add_argument("--layers", type=int, default=4, help="distinct resident layers the steps rotate over")
     ap.add_argument("--no-cpu", action="store_true", help="skip the timed CPU baseline")
+    ap.add_argument("--ep-tokens", type=int, default=16384)
+    ap.add_argument("--ep-layers", type=int, default=40)
     ap.add_argument("--no-graph", dest="graph", action="store_false", help="time eager launches instead of CUDA-graph replay")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -338,7 +443,7 @@ def main():
             return
         print(json.dumps(run_reference(args)), flush=True)
         return
-    out = run_ours(args)
+    out = run_ep(args) if args.workload == "ep_prefill_stack" else run_ours(args)
     if out:
         print(json.dumps(out), flush=True)
 

@@ -158,6 +158,22 @@ int xabe_moe_router_logits(xabe_moe* m, void* stream, const float* router, const
  * [max_tokens][num_experts]; pass NULL to use the handle's own logits. */
 int xabe_moe_route_and_dispatch(xabe_moe* m, void* stream, const float* logits);
 
+/* MoeKernels::build_dispatch (moe.rs:5623-5714): the dispatch tables from a
+ * routing decision that already exists.  `topk_ids` [max_tokens][k] int32 and
+ * `topk_weights` [max_tokens][k] f32 are copied into the handle (either may be
+ * NULL = keep what the handle holds).  Expert parallelism uses it on the rank
+ * that owns the experts: the rows it received are "tokens" with k = 1. */
+int xabe_moe_build_dispatch(xabe_moe* m, void* stream, const int32_t* topk_ids, const float* topk_weights);
+
+/* The last launch of MoeBlock::forward on its own (moe_block_gate_and_combine,
+ * block/moe.rs:424-483, 1297-1326): routed = ascending-k sum of the handle's
+ * `partial`, gate = sigmoid(dot(shared_gate_inp, normed)), ffn_out = routed +
+ * shexp * gate, l_out = ffn_out + residual.  Expert parallelism calls it after
+ * the combine exchange has filled `partial`. */
+int xabe_moe_gate_and_combine(xabe_moe* m, void* stream, const float* shared_gate_inp, const float* residual,
+                              size_t residual_len, float* ffn_out, size_t ffn_out_len, float* l_out,
+                              size_t l_out_len);
+
 /* MoeKernels::grouped_forward_partial (moe.rs:5727-6188): routed experts over
  * the current dispatch tables; leaves weight * expert_mlp in `partial`.
  * `hidden_states` NULL = the handle's `normed`. */

@@ -46,6 +46,8 @@ SYMBOLS = {
     "xabe_moe_rms_norm": (_i, [_vp, _vp, _vp, _vp]),
     "xabe_moe_router_logits": (_i, [_vp, _vp, _vp, _vp]),
     "xabe_moe_route_and_dispatch": (_i, [_vp, _vp, _vp]),
+    "xabe_moe_build_dispatch": (_i, [_vp, _vp, _vp, _vp]),
+    "xabe_moe_gate_and_combine": (_i, [_vp, _vp, _vp, _vp, _sz, _vp, _sz, _vp, _sz]),
     "xabe_moe_grouped_forward_partial": (_i, [_vp, _vp, QuantTensorC, QuantTensorC, QuantTensorC, _vp]),
     "xabe_moe_grouped_forward": (_i, [_vp, _vp, QuantTensorC, QuantTensorC, QuantTensorC, _vp, _vp]),
     "xabe_moe_shared_expert": (_i, [_vp, _vp, QuantTensorC, QuantTensorC, QuantTensorC, _vp, _vp]),

@@ -4,15 +4,15 @@
 // One CTA computes one output tile D[128 weight rows][128 token columns] of
 // one expert (or of the shared expert).  The contraction runs in chunks of 64
 // elements through a ring of shared-memory stages:
-//   * eight producer warps read the raw GGUF bytes (Q6_K superblocks or Q8_0
+//   * sixteen producer warps (two groups on alternate stage pairs) read the raw GGUF bytes (Q6_K superblocks or Q8_0
 //     blocks) of the tile's 128 weight rows, unpack them, scale them and write
 //     f16 values into the stage's A tile in the 128-byte-swizzled K-major
 //     layout the tensor core reads; they also gather the 128 token rows of f16
 //     activations into the B tile, same layout;
 //   * one thread issues four tcgen05.mma (M128 N128 K16, f16 x f16 -> f32)
 //     per stage and commits them to the stage's "empty" barrier;
-//   * four epilogue warps read the accumulator from TMEM with tcgen05.ld and
-//     apply SwiGLU (gate/up) or the routing weight (down).
+//   * four of the producer warps then read the accumulator from TMEM with
+//     tcgen05.ld and apply SwiGLU (gate/up) or the routing weight (down).
 //
 // Numerics: weights are rounded to f16 after the fp32-exact code is multiplied
 // by the f16-rounded group scale (times 256, undone in the epilogue, which
@@ -33,8 +33,11 @@ constexpr int kPfTileM = 128;       // weight rows per tile (TMEM lanes)
 constexpr int kPfTileN = 128;       // token columns per tile
 constexpr int kPfChunkK = 64;       // contraction elements per stage (one 128-byte swizzle row of f16)
 constexpr int kPfStageBytes = 2 * kPfTileM * kPfChunkK * 2;  // A tile + B tile, 16 KB each
-constexpr int kPfProducerWarps = 8;
-constexpr int kPfThreads = 32 * (4 + 1 + kPfProducerWarps);  // 4 epilogue warps, 1 MMA warp, 8 producers
+constexpr int kPfProducerWarps = 8;   // warps that fill one stage pair
+constexpr int kPfProducerGroups = 2;  // groups working on alternate stage pairs
+// warp 4 issues the MMAs; every other warp is a producer, and warps 0-3 (one per TMEM lane quadrant)
+// also run the epilogue once the contraction is done
+constexpr int kPfThreads = 32 * (1 + kPfProducerWarps * kPfProducerGroups);
 constexpr int kPfMaxStages = 6;
 constexpr float kPfWeightScale = 256.0f;
 constexpr int kPfItemInts = 4;  // expert, first slot (or first token), columns, pad
@@ -173,61 +176,100 @@ __device__ __forceinline__ uint4 codes8_to_h8(uint32_t c0, uint32_t c1, uint32_t
     return o;
 }
 
-// Raw bytes of 32 consecutive weights [k0, k0 + 32) of one row (k0 a multiple
-// of 32), fetched ahead of their use so that the global-load latency of chunk
-// kc + 1 hides behind the arithmetic of chunk kc.
-struct Raw32 {
-    uint32_t lo[8];  // Q6_K: the 32 nibble bytes; Q8_0: the 32 codes
-    uint32_t hi[8];  // Q6_K: the 32 bit-pair bytes
-    float s0, s1;    // scale of elements 0-15 and 16-31, times kPfWeightScale
-};
-
-template <int QUANT>
-__device__ __forceinline__ void load_raw32(const uint8_t* row_ptr, int k0, Raw32& r) {
-    if (QUANT == QUANT_Q6K) {
-        // element map of crates/xabe-kernels/src/quant.rs:175-198
-        const uint8_t* blk = row_ptr + (size_t)(k0 >> 8) * kQ6KBlockBytes;
-        int e = k0 & 255;
-        int half = e >> 7, j = (e & 127) >> 5;
-        ldg_32bytes(blk + half * 64 + (j & 1) * 32, r.lo);
-        ldg_32bytes(blk + 128 + half * 32, r.hi);
-        float d = __half2float(__ushort_as_half(__ldg((const unsigned short*)(blk + 208)))) * kPfWeightScale;
-        // both scales sit in one 2-byte-aligned halfword: index half*8 + 2*j (+1)
-        unsigned short sc = __ldg((const unsigned short*)(blk + 192 + half * 8 + 2 * j));
-        r.s0 = d * (float)(int)(int8_t)(sc & 0xFF);
-        r.s1 = d * (float)(int)(int8_t)(sc >> 8);
-    } else {
-        const uint8_t* blk = row_ptr + (size_t)(k0 >> 5) * kQ8BlockBytes;
-        ldg_32bytes(blk + 2, r.lo);
-        float d = __half2float(__ushort_as_half(__ldg((const unsigned short*)blk))) * kPfWeightScale;
-        r.s0 = r.s1 = d;
-    }
-}
-
-// Unpack, scale and store the 32 weights as four 16-byte chunks of the A tile.
-template <int QUANT>
-__device__ __forceinline__ void store_raw32(const Raw32& r, int k0, uint8_t* a_tile, int tile_row, int chunk0) {
-    __half2 ds[2] = {__float2half2_rn(r.s0), __float2half2_rn(r.s1)};
-    if (QUANT == QUANT_Q6K) {
-        const int j = ((k0 & 127) >> 5);
+// Five aligned words covering the 16 (+2) bytes at the 2-byte-aligned global
+// address p, returned as the four words that start at p.
+__device__ __forceinline__ void ldg_16bytes(const uint8_t* p, uint32_t (&w)[4]) {
+    uintptr_t a = (uintptr_t)p;
+    const uint32_t* q = (const uint32_t*)(a & ~(uintptr_t)3);
+    if (a & 2) {
+        uint32_t prev = __ldg(q);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            uint32_t raw[2];
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                uint32_t lo = (j < 2 ? r.lo[2 * c + i] : (r.lo[2 * c + i] >> 4)) & 0x0F0F0F0Fu;
-                uint32_t hi = ((r.hi[2 * c + i] >> (2 * j)) & 0x03030303u) << 4;
-                raw[i] = lo | hi;
-            }
-            // elements 8c .. 8c+7 of the group: scale group (8c) / 16
-            uint4 v = codes8_to_h8(raw[0], raw[1], 0x64206420u, ds[c >> 1]);
-            *(uint4*)(a_tile + swz_off(tile_row, chunk0 + c)) = v;
+        for (int i = 0; i < 4; ++i) {
+            uint32_t next = __ldg(q + i + 1);
+            w[i] = __funnelshift_r(prev, next, 16);
+            prev = next;
         }
     } else {
 #pragma unroll
+        for (int i = 0; i < 4; ++i) w[i] = __ldg(q + i);
+    }
+}
+
+// One producer thread's share of a PAIR of contraction chunks (128 elements of
+// one weight row), fetched one pair ahead of its use.
+//   Q6_K: the pair is one half of a superblock.  The thread owns positions
+//     l in [16*part, 16*part + 16) of all four 32-element groups: 16 nibble
+//     bytes from each of the two ql runs, 16 bit-pair bytes, four scales.
+//     Every byte of the half is fetched exactly once per tile.
+//   Q8_0: the thread owns elements [64*part, 64*part + 64): two blocks.
+struct Raw128 {
+    uint32_t a[8];  // Q6_K: ql run 0 (4 words), ql run 1 (4 words); Q8_0: block 0 codes
+    uint32_t b[8];  // Q6_K: qh (4 words, rest unused);               Q8_0: block 1 codes
+    float s[4];     // Q6_K: scale of group j (for this thread's l range); Q8_0: s[0], s[1] block scales
+};
+
+template <int QUANT>
+__device__ __forceinline__ void load_raw128(const uint8_t* row_ptr, int pair, int part, Raw128& r) {
+    if (QUANT == QUANT_Q6K) {
+        // element map of crates/xabe-kernels/src/quant.rs:175-198
+        const uint8_t* blk = row_ptr + (size_t)(pair >> 1) * kQ6KBlockBytes;
+        const int half = pair & 1;
+        uint32_t w[4];
+        ldg_16bytes(blk + half * 64 + 16 * part, w);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) r.a[i] = w[i];
+        ldg_16bytes(blk + half * 64 + 32 + 16 * part, w);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) r.a[4 + i] = w[i];
+        ldg_16bytes(blk + 128 + half * 32 + 16 * part, w);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) r.b[i] = w[i];
+        float d = __half2float(__ushort_as_half(__ldg((const unsigned short*)(blk + 208)))) * kPfWeightScale;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)  // scale index half*8 + 2*j + l/16, l/16 == part
+            r.s[j] = d * (float)(int)(int8_t)__ldg(blk + 192 + half * 8 + 2 * j + part);
+    } else {
+        const uint8_t* blk = row_ptr + (size_t)(pair * 4 + part * 2) * kQ8BlockBytes;
+        ldg_32bytes(blk + 2, r.a);
+        ldg_32bytes(blk + kQ8BlockBytes + 2, r.b);
+        r.s[0] = __half2float(__ushort_as_half(__ldg((const unsigned short*)blk))) * kPfWeightScale;
+        r.s[1] = __half2float(__ushort_as_half(__ldg((const unsigned short*)(blk + kQ8BlockBytes)))) * kPfWeightScale;
+        r.s[2] = r.s[3] = 0.f;
+    }
+}
+
+// Unpack, scale and store into the A tiles of the pair's two stages.
+template <int QUANT>
+__device__ __forceinline__ void store_raw128(const Raw128& r, int part, uint8_t* a_tile0, uint8_t* a_tile1,
+                                             int tile_row) {
+    if (QUANT == QUANT_Q6K) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            // group j: nibbles of ql run (j & 1), low for j < 2 and high otherwise; bit pair j of qh
+            __half2 ds2 = __float2half2_rn(r.s[j]);
+            uint8_t* tile = (j >> 1) ? a_tile1 : a_tile0;
+            uint32_t raw[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                uint32_t q = r.a[(j & 1) * 4 + i];
+                uint32_t lo = (j < 2 ? q : (q >> 4)) & 0x0F0F0F0Fu;
+                uint32_t hi = ((r.b[i] >> (2 * j)) & 0x03030303u) << 4;
+                raw[i] = lo | hi;
+            }
+            // 16 elements at (j & 1) * 32 + 16 * part of the stage's 64: two 16-byte chunks
+            const int chunk = (j & 1) * 4 + 2 * part;
+            *(uint4*)(tile + swz_off(tile_row, chunk)) = codes8_to_h8(raw[0], raw[1], 0x64206420u, ds2);
+            *(uint4*)(tile + swz_off(tile_row, chunk + 1)) = codes8_to_h8(raw[2], raw[3], 0x64206420u, ds2);
+        }
+    } else {
+        uint8_t* tile = part ? a_tile1 : a_tile0;  // elements [64 * part, 64 * part + 64) are one whole stage row
+        __half2 d0 = __float2half2_rn(r.s[0]), d1 = __float2half2_rn(r.s[1]);
+#pragma unroll
         for (int c = 0; c < 4; ++c) {
-            uint4 v = codes8_to_h8(r.lo[2 * c] ^ 0x80808080u, r.lo[2 * c + 1] ^ 0x80808080u, 0x64806480u, ds[0]);
-            *(uint4*)(a_tile + swz_off(tile_row, chunk0 + c)) = v;
+            *(uint4*)(tile + swz_off(tile_row, c)) =
+                codes8_to_h8(r.a[2 * c] ^ 0x80808080u, r.a[2 * c + 1] ^ 0x80808080u, 0x64806480u, d0);
+            *(uint4*)(tile + swz_off(tile_row, 4 + c)) =
+                codes8_to_h8(r.b[2 * c] ^ 0x80808080u, r.b[2 * c + 1] ^ 0x80808080u, 0x64806480u, d1);
         }
     }
 }
@@ -241,6 +283,7 @@ __device__ __forceinline__ bool stream_wait_pf(uint64_t* bar, uint32_t parity, v
     for (uint32_t it = 0; it < kWaitLimit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 63u) == 63u && *abort_flag) return false;
+        if (it >= 16u) __nanosleep(it < 256u ? 32u : 256u);  // long waits back off and leave the issue slots to working warps
     }
     *abort_flag = 1;
     if (status) atomicExch(status, STATUS_TMA_TIMEOUT);
@@ -354,9 +397,11 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L)
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_s;
 
-    if (warp >= 5) {
+    const int prod_id = warp < 4 ? warp : warp - 1;        // producer warp index 0..15 (warp 4 is the MMA issuer)
+    const int pgroup = prod_id / kPfProducerWarps;        // which stage pairs: pgroup, pgroup + 2, ...
+    if (warp != 4) {
         // ------------------------------ producers ------------------------------
-        const int p = tid - 5 * 32;          // 0..255
+        const int p = (prod_id % kPfProducerWarps) * 32 + lane;  // 0..255
         const int row = p & (kPfTileM - 1);  // tile row = TMEM lane, and B token column
         const int part = p >> 7;             // which 32-element half of the 64-element chunk
         const uint8_t* wbase;
@@ -372,44 +417,44 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L)
         const uint8_t* wptr = wbase + ((shared ? 0 : (size_t)expert * L.rows) + wrow) * row_bytes;
         const int src = col_src[row];
         const __half* xptr = (shared ? L.x_shared : L.x_routed) + (size_t)(src < 0 ? 0 : src) * L.k;
+        // The contraction is walked in PAIRS of chunks (128 elements, stages 2*pr and 2*pr + 1),
+        // so that each byte of a Q6_K half-superblock is fetched once; the bytes of pair pr + 1
+        // are in flight while pair pr is unpacked.  The thread fills row `row` of the A tiles and
+        // row `row`, elements [64 * part, +64) of the pair, of the B tiles.
         bool ok = true;
-        Raw32 raw;
-        uint4 xv[4];
+        const int n_pairs = n_chunks >> 1;  // the contraction is a multiple of 256
+        Raw128 raw;
+        uint4 xv[8];
         const uint4 zero4 = make_uint4(0, 0, 0, 0);
-        // software pipeline: the bytes of chunk kc + 1 are in flight while chunk kc is unpacked
-        {
-            const int k0 = part * 32;
-            if (quant == QUANT_Q6K) load_raw32<QUANT_Q6K>(wptr, k0, raw);
-            else load_raw32<QUANT_Q8_0>(wptr, k0, raw);
+        for (int pr = pgroup; pr < n_pairs && ok; pr += kPfProducerGroups) {
+            // the other producer group and the second CTA-resident warps hide this latency
+            if (quant == QUANT_Q6K) load_raw128<QUANT_Q6K>(wptr, pr, part, raw);
+            else load_raw128<QUANT_Q8_0>(wptr, pr, part, raw);
 #pragma unroll
-            for (int c = 0; c < 4; ++c) xv[c] = src < 0 ? zero4 : __ldg((const uint4*)(xptr + k0) + c);
-        }
-        for (int kc = 0; kc < n_chunks && ok; ++kc) {
-            const int st = kc % S;
-            const uint32_t use = kc / S;
-            const int k0 = kc * kPfChunkK + part * 32;
-            Raw32 cur = raw;
-            uint4 xc[4] = {xv[0], xv[1], xv[2], xv[3]};
-            if (kc + 1 < n_chunks) {
-                const int k1 = k0 + kPfChunkK;
-                if (quant == QUANT_Q6K) load_raw32<QUANT_Q6K>(wptr, k1, raw);
-                else load_raw32<QUANT_Q8_0>(wptr, k1, raw);
-#pragma unroll
-                for (int c = 0; c < 4; ++c) xv[c] = src < 0 ? zero4 : __ldg((const uint4*)(xptr + k1) + c);
-            }
-            if (use >= 1) ok = stream_wait_pf(&empty_bar[st], (use - 1) & 1, abortp, L.status);
+            for (int c = 0; c < 8; ++c)
+                xv[c] = src < 0 ? zero4 : __ldg((const uint4*)(xptr + pr * 128 + 64 * part) + c);
+            const Raw128& cur = raw;
+            const uint4* xc = xv;
+            const int kc0 = 2 * pr, kc1 = 2 * pr + 1;
+            const int st0 = kc0 % S, st1 = kc1 % S;
+            if (kc0 / S >= 1) ok = stream_wait_pf(&empty_bar[st0], (kc0 / S - 1) & 1, abortp, L.status);
+            if (ok && kc1 / S >= 1) ok = stream_wait_pf(&empty_bar[st1], (kc1 / S - 1) & 1, abortp, L.status);
             if (!ok) break;
-            uint8_t* a_tile = stages + (size_t)st * kPfStageBytes;
-            uint8_t* b_tile = a_tile + kPfTileM * kPfChunkK * 2;
-            if (quant == QUANT_Q6K) store_raw32<QUANT_Q6K>(cur, k0, a_tile, row, part * 4);
-            else store_raw32<QUANT_Q8_0>(cur, k0, a_tile, row, part * 4);
+            uint8_t* a0 = stages + (size_t)st0 * kPfStageBytes;
+            uint8_t* a1 = stages + (size_t)st1 * kPfStageBytes;
+            if (quant == QUANT_Q6K) store_raw128<QUANT_Q6K>(cur, part, a0, a1, row);
+            else store_raw128<QUANT_Q8_0>(cur, part, a0, a1, row);
+            uint8_t* b_tile = (part ? a1 : a0) + kPfTileM * kPfChunkK * 2;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) *(uint4*)(b_tile + swz_off(row, part * 4 + c)) = xc[c];
+            for (int c = 0; c < 8; ++c) *(uint4*)(b_tile + swz_off(row, c)) = xc[c];
             fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
             __syncwarp();
-            if (lane == 0) mbar_arrive_pf(&full_bar[st]);
+            if (lane == 0) {
+                mbar_arrive_pf(&full_bar[st0]);
+                mbar_arrive_pf(&full_bar[st1]);
+            }
         }
-    } else if (warp == 4) {
+    } else {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_f16(kPfTileM, kPfTileN);
@@ -429,7 +474,8 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L)
             }
             if (ok) umma_commit(&accum_bar);
         }
-    } else {
+    }
+    if (warp < 4) {
         // ------------------------------- epilogue -------------------------------
         bool ok = stream_wait_pf(&accum_bar, 0, abortp, L.status);
         tc_fence_after();

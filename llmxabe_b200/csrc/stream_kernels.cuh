@@ -114,6 +114,7 @@ __device__ __forceinline__ bool stream_wait(uint64_t* bar, uint32_t parity, vola
     for (uint32_t it = 0; it < kWaitLimit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 63u) == 63u && *abort_flag) return false;
+        if (it >= 16u) __nanosleep(it < 256u ? 32u : 256u);  // long waits back off and leave the issue slots to working warps
     }
     *abort_flag = 1;
     if (status) atomicExch(status, STATUS_TMA_TIMEOUT);

@@ -463,6 +463,7 @@ int launch_router(xabe_moe* m, cudaStream_t st, const float* router, const float
     return go(k_router_logits<8>, 8);
 }
 
+// `logits` NULL: the routing decision is already in the handle's topk buffers; only the tables are built.
 int launch_route_and_dispatch(xabe_moe* m, cudaStream_t st, const float* logits) {
     const auto& g = m->g;
     size_t hist_bytes = (size_t)(g.num_experts + 1) * sizeof(int);
@@ -470,7 +471,7 @@ int launch_route_and_dispatch(xabe_moe* m, cudaStream_t st, const float* logits)
         // decode widths: one single-CTA launch
         size_t smem = (size_t)(3 * kSmallPairs + 11 * g.num_experts + 2) * sizeof(int);
         const float* fused_logits = logits;
-        if (g.max_tokens > 8) {  // more than one token per warp: route on many SMs first
+        if (logits && g.max_tokens > 8) {  // more than one token per warp: route on many SMs first
             k_route<<<(g.max_tokens + 7) / 8, 256, 0, st>>>(logits, m->valid_tokens, (int)g.num_experts,
                                                            (int)g.experts_per_token, m->topk_ids, m->topk_weights);
             CUDA_TRY(cudaGetLastError());
@@ -489,9 +490,11 @@ int launch_route_and_dispatch(xabe_moe* m, cudaStream_t st, const float* logits)
         }
         return XABE_OK;
     }
-    k_route<<<(g.max_tokens + 7) / 8, 256, 0, st>>>(logits, m->valid_tokens, (int)g.num_experts,
-                                                   (int)g.experts_per_token, m->topk_ids, m->topk_weights);
-    CUDA_TRY(cudaGetLastError());
+    if (logits) {
+        k_route<<<(g.max_tokens + 7) / 8, 256, 0, st>>>(logits, m->valid_tokens, (int)g.num_experts,
+                                                       (int)g.experts_per_token, m->topk_ids, m->topk_weights);
+        CUDA_TRY(cudaGetLastError());
+    }
     k_align_count<<<m->n_chunks, 32, hist_bytes, st>>>(m->topk_ids, m->valid_tokens, (int)g.experts_per_token,
                                                       (int)g.num_experts, m->n_chunks, (int)m->sorted_capacity,
                                                       (int)m->block_capacity, m->chunk_hist,
@@ -567,7 +570,9 @@ int xabe_moe_create(const xabe_moe_geometry* geometry, int device, int scope, fl
     if (g.hidden % 256 != 0) return bad("hidden must be a multiple of the 256-element superblock");
     if (g.intermediate % 256 != 0) return bad("intermediate must be a multiple of the 256-element superblock");
     if (g.block_size > 8 * kMaxNB) return bad("block_size exceeds the slots the tensor-core tile stages");
-    if (g.max_tokens > 65535) return bad("max_tokens exceeds the 65535 grid limit");
+    // The reference caps this at 65535 because it puts max_tokens on grid.y; here it only ever rides
+    // grid.x, so the cap is a sanity bound on the scratch size.
+    if (g.max_tokens > (1u << 20)) return bad("max_tokens exceeds the 1048576 sanity limit");
     uint64_t cap = scope == XABE_SCOPE_ROUTED ? sorted_capacity_of(g) : 0;
     uint64_t shared_tiles = (g.max_tokens + g.block_size - 1) / g.block_size;
     if (cap / g.block_size + shared_tiles > 65535)
@@ -688,6 +693,38 @@ int xabe_moe_route_and_dispatch(xabe_moe* m, void* stream, const float* logits) 
     int rc = check_routed(m, "route_and_dispatch");
     if (rc) return rc;
     return launch_route_and_dispatch(m, (cudaStream_t)stream, logits ? logits : m->logits);
+}
+
+int xabe_moe_build_dispatch(xabe_moe* m, void* stream, const int32_t* topk_ids, const float* topk_weights) {
+    if (!m) return fail(XABE_ERR_INVALID_ARGUMENT, "null handle");
+    int rc = check_routed(m, "build_dispatch");
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    size_t n = (size_t)m->g.max_tokens * m->g.experts_per_token;
+    if (topk_ids)
+        CUDA_TRY(cudaMemcpyAsync(m->topk_ids, topk_ids, n * sizeof(int), cudaMemcpyDeviceToDevice, st));
+    if (topk_weights)
+        CUDA_TRY(cudaMemcpyAsync(m->topk_weights, topk_weights, n * sizeof(float), cudaMemcpyDeviceToDevice, st));
+    return launch_route_and_dispatch(m, st, nullptr);
+}
+
+int xabe_moe_gate_and_combine(xabe_moe* m, void* stream, const float* shared_gate_inp, const float* residual,
+                              size_t residual_len, float* ffn_out, size_t ffn_out_len, float* l_out,
+                              size_t l_out_len) {
+    if (!m || !shared_gate_inp || !residual || !ffn_out || !l_out)
+        return fail(XABE_ERR_INVALID_ARGUMENT, "null argument to gate_and_combine");
+    int rc = check_routed(m, "gate_and_combine");
+    if (rc) return rc;
+    const auto& g = m->g;
+    size_t n = (size_t)g.max_tokens * g.hidden;
+    if (residual_len != n || ffn_out_len != n || l_out_len != n)
+        return fail(XABE_ERR_BUFFER_LENGTH, "gate_and_combine buffers must hold %zu floats", n);
+    dim3 grid(g.max_tokens, (g.hidden + 255) / 256);
+    k_gate_and_combine<<<grid, 256, 0, (cudaStream_t)stream>>>(
+        shared_gate_inp, m->normed, m->partial, m->shexp, residual, m->valid_tokens, (int)g.experts_per_token,
+        (int)g.hidden, m->gate, m->routed, ffn_out, l_out);
+    CUDA_TRY(cudaGetLastError());
+    return XABE_OK;
 }
 
 int xabe_moe_grouped_forward_partial(xabe_moe* m, void* stream, xabe_quant_tensor gate, xabe_quant_tensor up,

@@ -151,6 +151,18 @@ class MoeKernels:
     def route_and_dispatch(self, logits: torch.Tensor | None = None, stream=None) -> None:
         _check(_lib.lib().xabe_moe_route_and_dispatch(self._h, _stream_ptr(stream), _ptr(logits)))
 
+    # -- MoeKernels::build_dispatch, moe.rs:5623
+    def build_dispatch(self, topk_ids: torch.Tensor | None = None, topk_weights: torch.Tensor | None = None,
+                       stream=None) -> None:
+        _check(_lib.lib().xabe_moe_build_dispatch(self._h, _stream_ptr(stream), _ptr(topk_ids), _ptr(topk_weights)))
+
+    # -- the last launch of MoeBlock::forward, block/moe.rs:1297-1326
+    def gate_and_combine(self, shared_gate_inp: torch.Tensor, residual: torch.Tensor, ffn_out: torch.Tensor,
+                         l_out: torch.Tensor, stream=None) -> None:
+        _check(_lib.lib().xabe_moe_gate_and_combine(self._h, _stream_ptr(stream), shared_gate_inp.data_ptr(),
+                                                    residual.data_ptr(), residual.numel(), ffn_out.data_ptr(),
+                                                    ffn_out.numel(), l_out.data_ptr(), l_out.numel()))
+
     # -- MoeKernels::grouped_forward_partial, moe.rs:5727
     def grouped_forward_partial(self, gate: QuantTensor, up: QuantTensor, down: QuantTensor,
                                 hidden_states: torch.Tensor | None = None, stream=None) -> None:

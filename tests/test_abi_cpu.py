@@ -46,7 +46,7 @@ def test_capacity_formulas_through_the_abi(kats):
     (dict(hidden=2048 + 128), "hidden must be a multiple"),
     (dict(intermediate=384), "intermediate must be a multiple"),
     (dict(block_size=128), "block_size exceeds"),
-    (dict(max_tokens=70000), "max_tokens exceeds"),
+    (dict(max_tokens=2_000_000), "max_tokens exceeds"),
 ])
 def test_geometry_is_validated_before_any_device_call(kw, reason):
     """MoeKernels::new rejects these (crates/xabe-cuda/src/kernels/moe.rs:5043-5111)."""

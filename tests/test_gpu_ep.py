@@ -1,0 +1,100 @@
+"""Expert-parallel block on the GPU.
+
+World 1 (always runs): EpMoeBlock over CudaEpBackend must reproduce MoeBlock.forward bit for bit --
+same kernels, same reduction order, the routing weight applied after the (identity) exchange.
+World 2 (runs when two devices are visible): two NCCL ranks, experts sharded 128 + 128, tokens split;
+the concatenated result must equal the one-GPU block bit for bit as well.
+"""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+from helpers import bits, device_layer, run_block
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _slice_stack(qt, first, count, num_experts):
+    from llmxabe_b200.moe import QuantTensor
+    per = qt.bytes.numel() // num_experts
+    return QuantTensor(qt.bytes[first * per:(first + count) * per].clone(), qt.quant)
+
+
+def _ep_forward(torch, L, x_np, rank, world, exact):
+    from llmxabe_b200.ep import CudaEpBackend, EpMoeBlock
+    from llmxabe_b200.moe import MoeGeometry
+    E, K, H = L.num_experts, L.top_k, L.hidden
+    w = device_layer(L)
+    per = x_np.shape[0] // world
+    mine = x_np[rank * per:(rank + 1) * per]
+    g = MoeGeometry(E, K, H, L.inter, 16, per)
+    epr = E // world
+    backend = CudaEpBackend(g, epr, x_np.shape[0] * K, w,
+                            _slice_stack(w.gate_exps, rank * epr, epr, E),
+                            _slice_stack(w.up_exps, rank * epr, epr, E),
+                            _slice_stack(w.down_exps, rank * epr, epr, E), exact_decode=exact)
+    blk = EpMoeBlock(backend, E, K, rank, world)
+    res = torch.from_numpy(mine.copy()).cuda()
+    ffn = torch.zeros(per, H, device="cuda")
+    lo = torch.zeros(per, H, device="cuda")
+    blk.forward(res, per, ffn, lo)
+    torch.cuda.synchronize()
+    assert backend.front_k.device_status() == 0 and backend.back_k.device_status() == 0
+    return ffn.cpu().numpy(), lo.cpu().numpy()
+
+
+@pytest.mark.parametrize("tokens", [1, 24])
+def test_one_rank_expert_parallel_equals_the_plain_block(tokens):
+    import torch
+    if not torch.cuda.is_available():
+        pytest.fail("gpu-marked test collected without a CUDA device")
+    from llmxabe_b200 import synth
+    from llmxabe_b200.moe import MoeBlock, MoeGeometry
+    L = synth.moe_layer(seed=21, num_experts=8, top_k=2, hidden=512, inter=256, zipf=True)
+    x = synth.activations(tokens, 512, seed=21)
+    plain = run_block(MoeBlock(MoeGeometry(8, 2, 512, 256, 16, tokens)), device_layer(L), x, tokens)
+    ffn, lo = _ep_forward(torch, L, x, 0, 1, exact=False)
+    assert (bits(lo) == bits(plain["l_out"])).all() and (bits(ffn) == bits(plain["ffn_out"])).all()
+
+
+def _rank_main(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import torch
+    import torch.distributed as dist
+    from llmxabe_b200 import synth
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    L = synth.moe_layer(seed=22, num_experts=8, top_k=2, hidden=512, inter=256, zipf=True)
+    x = synth.activations(32, 512, seed=22)
+    ffn, lo = _ep_forward(torch, L, x, rank, world, exact=True)
+    np.save(os.path.join(out_dir, f"l_out_{rank}.npy"), lo)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_rank_expert_parallel_equals_the_plain_block(tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    from llmxabe_b200 import synth
+    from llmxabe_b200.moe import MoeBlock, MoeGeometry
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    mp.spawn(_rank_main, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    L = synth.moe_layer(seed=22, num_experts=8, top_k=2, hidden=512, inter=256, zipf=True)
+    x = synth.activations(32, 512, seed=22)
+    blk = MoeBlock(MoeGeometry(8, 2, 512, 256, 16, 32))
+    blk.set_exact_decode_regime(True)
+    plain = run_block(blk, device_layer(L), x, 32)
+    got = np.concatenate([np.load(tmp_path / f"l_out_{r}.npy") for r in range(2)])
+    assert (bits(got) == bits(plain["l_out"])).all()
