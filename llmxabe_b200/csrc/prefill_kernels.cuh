@@ -145,25 +145,6 @@ __device__ __forceinline__ uint32_t swz_off(int row, int chunk) {
     return (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4));
 }
 
-// Nine aligned words covering the 32 (+2) bytes at the 2-byte-aligned global
-// address p, returned as the eight words that start at p.
-__device__ __forceinline__ void ldg_32bytes(const uint8_t* p, uint32_t (&w)[8]) {
-    uintptr_t a = (uintptr_t)p;
-    const uint32_t* q = (const uint32_t*)(a & ~(uintptr_t)3);
-    if (a & 2) {
-        uint32_t prev = __ldg(q);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            uint32_t next = __ldg(q + i + 1);
-            w[i] = __funnelshift_r(prev, next, 16);
-            prev = next;
-        }
-    } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) w[i] = __ldg(q + i);
-    }
-}
-
 // Eight exact codes (two words of four bytes) -> four half2 scaled by ds2.
 __device__ __forceinline__ uint4 codes8_to_h8(uint32_t c0, uint32_t c1, uint32_t bias, __half2 ds2) {
     uint4 o;
@@ -176,101 +157,97 @@ __device__ __forceinline__ uint4 codes8_to_h8(uint32_t c0, uint32_t c1, uint32_t
     return o;
 }
 
-// Five aligned words covering the 16 (+2) bytes at the 2-byte-aligned global
-// address p, returned as the four words that start at p.
-__device__ __forceinline__ void ldg_16bytes(const uint8_t* p, uint32_t (&w)[4]) {
-    uintptr_t a = (uintptr_t)p;
-    const uint32_t* q = (const uint32_t*)(a & ~(uintptr_t)3);
-    if (a & 2) {
-        uint32_t prev = __ldg(q);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            uint32_t next = __ldg(q + i + 1);
-            w[i] = __funnelshift_r(prev, next, 16);
-            prev = next;
-        }
-    } else {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) w[i] = __ldg(q + i);
-    }
+// 16-byte asynchronous copy global -> shared (zero-filled when src_bytes is 0), and the arrival it
+// triggers on an mbarrier once all of this thread's earlier copies have landed.  The arrival does
+// not raise the barrier's pending count: the count it was initialised with includes it.
+__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src), "r"(src_bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-// One producer thread's share of a PAIR of contraction chunks (128 elements of
-// one weight row), fetched one pair ahead of its use.
-//   Q6_K: the pair is one half of a superblock.  The thread owns positions
-//     l in [16*part, 16*part + 16) of all four 32-element groups: 16 nibble
-//     bytes from each of the two ql runs, 16 bit-pair bytes, four scales.
-//     Every byte of the half is fetched exactly once per tile.
-//   Q8_0: the thread owns elements [64*part, 64*part + 64): two blocks.
-struct Raw128 {
-    uint32_t a[8];  // Q6_K: ql run 0 (4 words), ql run 1 (4 words); Q8_0: block 0 codes
-    uint32_t b[8];  // Q6_K: qh (4 words, rest unused);               Q8_0: block 1 codes
-    float s[4];     // Q6_K: scale of group j (for this thread's l range); Q8_0: s[0], s[1] block scales
+// What one lane holds for one producer pass.  A pass is eight weight rows x one PAIR of chunks
+// (128 contraction elements); lane (rrow = lane / 4, j = lane % 4) serves row rrow:
+//   Q6_K  positions l = 8j..8j+7 of all four 32-element groups of half a superblock
+//         (element map of crates/xabe-kernels/src/quant.rs:175-198): 8 bytes of each ql run,
+//         8 bytes of bit pairs, the four group scales and d  -> 32 weights
+//   Q8_0  block j of the pair's four blocks: 32 codes and d   -> 32 weights
+// The four lanes of a row read consecutive bytes, so a load touches few cache lines.
+struct RawQ6 {
+    uint32_t ql0[2], ql1[2], qh[2];
+    int sc[4];
+    uint32_t d;
+};
+struct RawQ8 {
+    uint32_t w[8];
+    uint32_t d;
 };
 
-template <int QUANT>
-__device__ __forceinline__ void load_raw128(const uint8_t* row_ptr, int pair, int part, Raw128& r) {
-    if (QUANT == QUANT_Q6K) {
-        // element map of crates/xabe-kernels/src/quant.rs:175-198
-        const uint8_t* blk = row_ptr + (size_t)(pair >> 1) * kQ6KBlockBytes;
-        const int half = pair & 1;
-        uint32_t w[4];
-        ldg_16bytes(blk + half * 64 + 16 * part, w);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) r.a[i] = w[i];
-        ldg_16bytes(blk + half * 64 + 32 + 16 * part, w);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) r.a[4 + i] = w[i];
-        ldg_16bytes(blk + 128 + half * 32 + 16 * part, w);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) r.b[i] = w[i];
-        float d = __half2float(__ushort_as_half(__ldg((const unsigned short*)(blk + 208)))) * kPfWeightScale;
-#pragma unroll
-        for (int j = 0; j < 4; ++j)  // scale index half*8 + 2*j + l/16, l/16 == part
-            r.s[j] = d * (float)(int)(int8_t)__ldg(blk + 192 + half * 8 + 2 * j + part);
-    } else {
-        const uint8_t* blk = row_ptr + (size_t)(pair * 4 + part * 2) * kQ8BlockBytes;
-        ldg_32bytes(blk + 2, r.a);
-        ldg_32bytes(blk + kQ8BlockBytes + 2, r.b);
-        r.s[0] = __half2float(__ushort_as_half(__ldg((const unsigned short*)blk))) * kPfWeightScale;
-        r.s[1] = __half2float(__ushort_as_half(__ldg((const unsigned short*)(blk + kQ8BlockBytes)))) * kPfWeightScale;
-        r.s[2] = r.s[3] = 0.f;
-    }
+// Eight bytes that start `sh / 8` (0 or 2) bytes after the 4-byte-aligned address q.  The third
+// word read lies inside the same superblock for every piece this is used on.
+__device__ __forceinline__ void ldg8_shifted(const uint8_t* q, uint32_t sh, uint32_t (&o)[2]) {
+    const uint32_t* w = (const uint32_t*)q;
+    uint32_t a = __ldg(w), b = __ldg(w + 1), c = __ldg(w + 2);
+    o[0] = __funnelshift_r(a, b, sh);
+    o[1] = __funnelshift_r(b, c, sh);
 }
 
-// Unpack, scale and store into the A tiles of the pair's two stages.
-template <int QUANT>
-__device__ __forceinline__ void store_raw128(const Raw128& r, int part, uint8_t* a_tile0, uint8_t* a_tile1,
-                                             int tile_row) {
-    if (QUANT == QUANT_Q6K) {
+// `pa`: 4-byte-aligned address at or 2 bytes below (superblock + h*64 + 8j); `pb` likewise for
+// (superblock + 128 + h*32 + 8j); `ps` = superblock + 192 + h*8 + j/2; `pd` = superblock + 208.
+__device__ __forceinline__ void load_pass(const uint8_t* pa, const uint8_t* pb, const uint8_t* ps,
+                                          const uint8_t* pd, uint32_t sh, RawQ6& r) {
+    ldg8_shifted(pa, sh, r.ql0);
+    ldg8_shifted(pa + 32, sh, r.ql1);
+    ldg8_shifted(pb, sh, r.qh);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            // group j: nibbles of ql run (j & 1), low for j < 2 and high otherwise; bit pair j of qh
-            __half2 ds2 = __float2half2_rn(r.s[j]);
-            uint8_t* tile = (j >> 1) ? a_tile1 : a_tile0;
-            uint32_t raw[4];
+    for (int g = 0; g < 4; ++g) r.sc[g] = (int)(int8_t)__ldg(ps + 2 * g);  // scale index h*8 + 2g + l/16
+    r.d = __ldg((const unsigned short*)pd);
+}
+// `blk`: the lane's 34-byte block (2-byte aligned).
+__device__ __forceinline__ void load_pass(const uint8_t* blk, RawQ8& r) {
+    const uint32_t mis = ((uintptr_t)blk & 2) ? 0u : 1u;  // the codes start at blk + 2
+    const uint32_t* w = (const uint32_t*)(blk + 2 - 2 * mis);
+    uint32_t a[8];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                uint32_t q = r.a[(j & 1) * 4 + i];
-                uint32_t lo = (j < 2 ? q : (q >> 4)) & 0x0F0F0F0Fu;
-                uint32_t hi = ((r.b[i] >> (2 * j)) & 0x03030303u) << 4;
-                raw[i] = lo | hi;
-            }
-            // 16 elements at (j & 1) * 32 + 16 * part of the stage's 64: two 16-byte chunks
-            const int chunk = (j & 1) * 4 + 2 * part;
-            *(uint4*)(tile + swz_off(tile_row, chunk)) = codes8_to_h8(raw[0], raw[1], 0x64206420u, ds2);
-            *(uint4*)(tile + swz_off(tile_row, chunk + 1)) = codes8_to_h8(raw[2], raw[3], 0x64206420u, ds2);
+    for (int i = 0; i < 8; ++i) a[i] = __ldg(w + i);
+    // misaligned codes: a[0] starts with d and the last two codes follow a[7]; aligned: d precedes a[0]
+    uint32_t extra = __ldg((const unsigned short*)(blk + 32 * mis));
+    r.d = mis ? (a[0] & 0xFFFFu) : extra;
+    const uint32_t sh = 16 * mis;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) r.w[i] = __funnelshift_r(a[i], i < 7 ? a[i + 1] : extra, sh);
+}
+
+// Unpack, scale and store the lane's 32 weights: four 16-byte chunks.  `t0`/`t1`: shared-memory
+// addresses of the lane's row inside the A tiles of the pair's two stages, with the row's swizzle
+// already applied to chunk `c0x` (= chunk index XOR row % 8, times 16).
+__device__ __forceinline__ void store_pass(const RawQ6& r, uint8_t* row0, uint8_t* row1, uint32_t cx) {
+    const float d = __half2float(__ushort_as_half((unsigned short)r.d)) * kPfWeightScale;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        const uint32_t* ql = (g & 1) ? r.ql1 : r.ql0;
+        uint32_t c[2];
+#pragma unroll
+        for (int w = 0; w < 2; ++w) {
+            uint32_t nib = (g >> 1) ? (ql[w] >> 4) : ql[w];
+            uint32_t two = g == 0 ? (r.qh[w] << 4) : g == 1 ? (r.qh[w] << 2) : g == 2 ? r.qh[w] : (r.qh[w] >> 2);
+            c[w] = (nib & 0x0F0F0F0Fu) | (two & 0x30303030u);
         }
-    } else {
-        uint8_t* tile = part ? a_tile1 : a_tile0;  // elements [64 * part, 64 * part + 64) are one whole stage row
-        __half2 d0 = __float2half2_rn(r.s[0]), d1 = __float2half2_rn(r.s[1]);
+        __half2 ds2 = __float2half2_rn(d * (float)r.sc[g]);
+        uint4 v = codes8_to_h8(c[0], c[1], 0x64206420u, ds2);
+        // group g: elements (g % 2) * 32 + 8j.. of stage g / 2: chunk (g % 2) * 4 + j
+        uint8_t* row = (g >> 1) ? row1 : row0;
+        *(uint4*)(row + (cx ^ ((g & 1) << 6))) = v;
+    }
+}
+__device__ __forceinline__ void store_pass(const RawQ8& r, uint8_t* row, uint32_t cx) {
+    __half2 ds2 = __float2half2_rn(__half2float(__ushort_as_half((unsigned short)r.d)) * kPfWeightScale);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            *(uint4*)(tile + swz_off(tile_row, c)) =
-                codes8_to_h8(r.a[2 * c] ^ 0x80808080u, r.a[2 * c + 1] ^ 0x80808080u, 0x64806480u, d0);
-            *(uint4*)(tile + swz_off(tile_row, 4 + c)) =
-                codes8_to_h8(r.b[2 * c] ^ 0x80808080u, r.b[2 * c + 1] ^ 0x80808080u, 0x64806480u, d1);
-        }
+    for (int t = 0; t < 4; ++t) {
+        uint4 v = codes8_to_h8(r.w[2 * t] ^ 0x80808080u, r.w[2 * t + 1] ^ 0x80808080u, 0x64806480u, ds2);
+        *(uint4*)(row + (cx ^ (t << 4))) = v;  // chunk (j % 2) * 4 + t
     }
 }
 
@@ -322,6 +299,111 @@ __global__ void k_build_prefill_items(int num_experts, const int* __restrict__ e
     }
 }
 
+template <int QUANT> struct RawOf;
+template <> struct RawOf<QUANT_Q6K> { using T = RawQ6; };
+template <> struct RawOf<QUANT_Q8_0> { using T = RawQ8; };
+
+// What a producer warp needs to know; everything here is fixed for the tile.
+struct PfProducer {
+    uint8_t* stages;
+    uint64_t* full_bar;
+    uint64_t* empty_bar;
+    volatile int* abortp;
+    int* status;
+    int n_stages, n_pairs, pgroup, gw, lane;
+    const uint8_t* row_ptr0;  // the lane's weight row of pass 0; pass 1 is eight rows further
+    size_t pass_stride;
+    const uint4* x4;          // activations in 16-byte units
+    int xoff[4];              // the thread's four token rows: row * (K / 8) + piece, or -1 (zero column)
+};
+
+template <int QUANT>
+__device__ __forceinline__ void pf_load(const PfProducer& P, int pr, typename RawOf<QUANT>::T (&raw)[2]) {
+    const int j = P.lane & 3;
+    if constexpr (QUANT == QUANT_Q6K) {
+        const int h = pr & 1;
+        const uint8_t* blk = P.row_ptr0 + (size_t)(pr >> 1) * kQ6KBlockBytes;
+        const uint32_t mis = (uint32_t)((uintptr_t)blk & 2);
+        const uint8_t* pa = blk - mis + h * 64 + 8 * j;
+        const uint8_t* pb = blk - mis + 128 + h * 32 + 8 * j;
+        const uint8_t* ps = blk + 192 + h * 8 + (j >> 1);
+        const uint8_t* pd = blk + 208;
+#pragma unroll
+        for (int q = 0; q < 2; ++q)
+            load_pass(pa + q * P.pass_stride, pb + q * P.pass_stride, ps + q * P.pass_stride,
+                      pd + q * P.pass_stride, mis * 8, raw[q]);
+    } else {
+        const uint8_t* blk = P.row_ptr0 + (size_t)(pr * 4 + j) * kQ8BlockBytes;
+#pragma unroll
+        for (int q = 0; q < 2; ++q) load_pass(blk + q * P.pass_stride, raw[q]);
+    }
+}
+
+// Fills the stage pair of contraction pair `pr` from `raw`: waits for the two stages to be free,
+// starts the asynchronous copies of the token rows (B tiles), writes the unpacked weights (A tiles).
+template <int QUANT>
+__device__ __forceinline__ bool pf_fill(const PfProducer& P, int pr, const typename RawOf<QUANT>::T (&raw)[2]) {
+    const int S = P.n_stages;
+    const int kc0 = 2 * pr, kc1 = 2 * pr + 1;
+    const int st0 = kc0 % S, st1 = kc1 % S;
+    if (kc0 / S >= 1 && !stream_wait_pf(&P.empty_bar[st0], (kc0 / S - 1) & 1, P.abortp, P.status)) return false;
+    if (kc1 / S >= 1 && !stream_wait_pf(&P.empty_bar[st1], (kc1 / S - 1) & 1, P.abortp, P.status)) return false;
+    uint8_t* a0 = P.stages + (size_t)st0 * kPfStageBytes;
+    uint8_t* a1 = P.stages + (size_t)st1 * kPfStageBytes;
+    const int lane = P.lane, gw = P.gw;
+    {   // B tiles: rows r0 + 32m, 16-byte piece lane % 8
+        const int r0 = gw * 4 + (lane >> 3), piece = lane & 7;
+        const uint32_t boff = (uint32_t)(kPfTileM * kPfChunkK * 2) + swz_off(r0, piece);
+        const uint32_t b0 = smem_u32(a0) + boff, b1 = smem_u32(a1) + boff;
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+            const bool live = P.xoff[m] >= 0;
+            const uint4* src = P.x4 + (live ? (size_t)P.xoff[m] + (size_t)pr * 16 : 0);
+            cp_async16(b0 + m * 4096, src, live ? 16u : 0u);
+            cp_async16(b1 + m * 4096, src + (live ? 8 : 0), live ? 16u : 0u);
+        }
+        cp_async_arrive_noinc(&P.full_bar[st0]);
+        cp_async_arrive_noinc(&P.full_bar[st1]);
+    }
+    const int rrow = lane >> 2, j = lane & 3;
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+        const uint32_t rowoff = (uint32_t)((2 * gw + q) * 1024 + rrow * 128);
+        if constexpr (QUANT == QUANT_Q6K) {
+            store_pass(raw[q], a0 + rowoff, a1 + rowoff, (uint32_t)((j ^ rrow) << 4));
+        } else {
+            store_pass(raw[q], ((j >> 1) ? a1 : a0) + rowoff, (uint32_t)(((((j & 1) << 2)) ^ rrow) << 4));
+        }
+    }
+    fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
+    __syncwarp();
+    if (lane == 0) {
+        mbar_arrive_pf(&P.full_bar[st0]);
+        mbar_arrive_pf(&P.full_bar[st1]);
+    }
+    return true;
+}
+
+// The producer loop of one warp: its group takes every second pair; the raw bytes of the group's
+// next pair are in flight while the current one is unpacked.
+template <int QUANT>
+__device__ __forceinline__ void pf_produce(const PfProducer& P) {
+    typename RawOf<QUANT>::T ra[2], rb[2];
+    const int step = kPfProducerGroups;
+    int pr = P.pgroup;
+    if (pr < P.n_pairs) pf_load<QUANT>(P, pr, ra);
+    while (pr < P.n_pairs) {
+        if (pr + step < P.n_pairs) pf_load<QUANT>(P, pr + step, rb);
+        if (!pf_fill<QUANT>(P, pr, ra)) break;
+        pr += step;
+        if (pr >= P.n_pairs) break;
+        if (pr + step < P.n_pairs) pf_load<QUANT>(P, pr + step, ra);
+        if (!pf_fill<QUANT>(P, pr, rb)) break;
+        pr += step;
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+}
+
 // MODE_GATEUP (0): TMEM lane m = 32q + i holds gate row r0 + 16q + i for i < 16 and up row
 // r0 + 16q + (i - 16) otherwise (r0 = 64 * blockIdx.x), so SwiGLU pairs two lanes of one warp.
 // MODE_DOWN (1): lane m holds row 128 * blockIdx.x + m.
@@ -365,7 +447,8 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L)
     if (tid == 0) {
         abort_flag = 0;
         for (int i = 0; i < S; ++i) {
-            mbar_init(&full_bar[i], kPfProducerWarps);
+            // one arrival per producer warp (A tile written) + one per producer thread (its B-tile copies landed)
+            mbar_init(&full_bar[i], kPfProducerWarps + kPfProducerWarps * 32);
             mbar_init(&empty_bar[i], 1);
         }
         mbar_init(&accum_bar, 1);
@@ -401,59 +484,45 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L)
     const int pgroup = prod_id / kPfProducerWarps;        // which stage pairs: pgroup, pgroup + 2, ...
     if (warp != 4) {
         // ------------------------------ producers ------------------------------
-        const int p = (prod_id % kPfProducerWarps) * 32 + lane;  // 0..255
-        const int row = p & (kPfTileM - 1);  // tile row = TMEM lane, and B token column
-        const int part = p >> 7;             // which 32-element half of the 64-element chunk
-        const uint8_t* wbase;
-        size_t wrow;
-        if (MODE == MODE_GATEUP) {
-            int q = row >> 5, i = row & 31;
-            wbase = i < 16 ? (shared ? L.s_a : L.r_a) : (shared ? L.s_b : L.r_b);
-            wrow = (size_t)blockIdx.x * 64 + q * 16 + (i & 15);
-        } else {
-            wbase = shared ? L.s_a : L.r_a;
-            wrow = (size_t)blockIdx.x * kPfTileM + row;
-        }
-        const uint8_t* wptr = wbase + ((shared ? 0 : (size_t)expert * L.rows) + wrow) * row_bytes;
-        const int src = col_src[row];
-        const __half* xptr = (shared ? L.x_shared : L.x_routed) + (size_t)(src < 0 ? 0 : src) * L.k;
-        // The contraction is walked in PAIRS of chunks (128 elements, stages 2*pr and 2*pr + 1),
-        // so that each byte of a Q6_K half-superblock is fetched once; the bytes of pair pr + 1
-        // are in flight while pair pr is unpacked.  The thread fills row `row` of the A tiles and
-        // row `row`, elements [64 * part, +64) of the pair, of the B tiles.
-        bool ok = true;
-        const int n_pairs = n_chunks >> 1;  // the contraction is a multiple of 256
-        Raw128 raw;
-        uint4 xv[8];
-        const uint4 zero4 = make_uint4(0, 0, 0, 0);
-        for (int pr = pgroup; pr < n_pairs && ok; pr += kPfProducerGroups) {
-            // the other producer group and the second CTA-resident warps hide this latency
-            if (quant == QUANT_Q6K) load_raw128<QUANT_Q6K>(wptr, pr, part, raw);
-            else load_raw128<QUANT_Q8_0>(wptr, pr, part, raw);
+        // A producer group (8 warps) fills one PAIR of stages (128 contraction elements) at a time:
+        // sixteen passes of eight weight rows, two per warp, 32 weights per lane; and the 2 x 128
+        // token rows of the B tiles by asynchronous 16-byte copies, eight per thread.
+        PfProducer P;
+        P.stages = stages;
+        P.full_bar = full_bar;
+        P.empty_bar = empty_bar;
+        P.abortp = abortp;
+        P.status = L.status;
+        P.n_stages = S;
+        P.n_pairs = n_chunks >> 1;  // the contraction is a multiple of 256
+        P.pgroup = pgroup;
+        P.gw = prod_id % kPfProducerWarps;
+        P.lane = lane;
+        {
+            // tile rows 16gw..16gw+15 are consecutive weight rows of one matrix (in the gate/up
+            // interleave: half of one 32-row group)
+            const int gw = P.gw, rrow = lane >> 2;
+            const uint8_t* base = shared ? L.s_a : L.r_a;
+            size_t wrow;
+            if (MODE == MODE_GATEUP) {
+                if (gw & 1) base = shared ? L.s_b : L.r_b;
+                wrow = (size_t)blockIdx.x * 64 + (gw >> 1) * 16 + rrow;
+            } else {
+                wrow = (size_t)blockIdx.x * kPfTileM + 16 * gw + rrow;
+            }
+            const size_t expert_row0 = shared ? 0 : (size_t)expert * L.rows;
+            P.row_ptr0 = base + (expert_row0 + wrow) * row_bytes;
+            P.pass_stride = (size_t)8 * row_bytes;
+            P.x4 = (const uint4*)(shared ? L.x_shared : L.x_routed);
+            const int r0 = gw * 4 + (lane >> 3);
 #pragma unroll
-            for (int c = 0; c < 8; ++c)
-                xv[c] = src < 0 ? zero4 : __ldg((const uint4*)(xptr + pr * 128 + 64 * part) + c);
-            const Raw128& cur = raw;
-            const uint4* xc = xv;
-            const int kc0 = 2 * pr, kc1 = 2 * pr + 1;
-            const int st0 = kc0 % S, st1 = kc1 % S;
-            if (kc0 / S >= 1) ok = stream_wait_pf(&empty_bar[st0], (kc0 / S - 1) & 1, abortp, L.status);
-            if (ok && kc1 / S >= 1) ok = stream_wait_pf(&empty_bar[st1], (kc1 / S - 1) & 1, abortp, L.status);
-            if (!ok) break;
-            uint8_t* a0 = stages + (size_t)st0 * kPfStageBytes;
-            uint8_t* a1 = stages + (size_t)st1 * kPfStageBytes;
-            if (quant == QUANT_Q6K) store_raw128<QUANT_Q6K>(cur, part, a0, a1, row);
-            else store_raw128<QUANT_Q8_0>(cur, part, a0, a1, row);
-            uint8_t* b_tile = (part ? a1 : a0) + kPfTileM * kPfChunkK * 2;
-#pragma unroll
-            for (int c = 0; c < 8; ++c) *(uint4*)(b_tile + swz_off(row, c)) = xc[c];
-            fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive_pf(&full_bar[st0]);
-                mbar_arrive_pf(&full_bar[st1]);
+            for (int m = 0; m < 4; ++m) {
+                const int srow = col_src[r0 + 32 * m];
+                P.xoff[m] = srow < 0 ? -1 : srow * (L.k >> 3) + (lane & 7);
             }
         }
+        if (quant == QUANT_Q6K) pf_produce<QUANT_Q6K>(P);
+        else pf_produce<QUANT_Q8_0>(P);
     } else {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
@@ -464,6 +533,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L)
                 ok = stream_wait_pf(&full_bar[st], (kc / S) & 1, abortp, L.status);
                 if (!ok) break;
                 tc_fence_after();
+                fence_proxy_async_smem();  // the B tile arrived by cp.async, not through the async proxy
                 const uint32_t a_addr = smem_u32(stages + (size_t)st * kPfStageBytes);
                 const uint64_t adesc = umma_smem_desc(a_addr);
                 const uint64_t bdesc = umma_smem_desc(a_addr + kPfTileM * kPfChunkK * 2);

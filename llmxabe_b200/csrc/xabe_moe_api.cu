@@ -509,11 +509,15 @@ int launch_route_and_dispatch(xabe_moe* m, cudaStream_t st, const float* logits)
                                                         (int)g.experts_per_token, (int)g.num_experts,
                                                         m->chunk_hist, m->sorted_token_ids);
     CUDA_TRY(cudaGetLastError());
-    k_build_work<<<1, threads, hist_bytes, st>>>((int)g.num_experts, m->expert_offsets, m->expert_counts,
-                                                 m->sorted_token_ids, m->topk_weights, m->work_items, m->n_work);
-    CUDA_TRY(cudaGetLastError());
-    k_build_prefill_items<<<1, threads, hist_bytes, st>>>((int)g.num_experts, m->expert_offsets, m->expert_counts,
-                                                          m->pf_items, m->pf_n_items);
+    // Only the work list of the kernels that will run: the regime must be chosen before this call.
+    if (prefill_applies(m, (int)g.intermediate, (int)g.hidden, (int)g.hidden, (int)g.intermediate)) {
+        k_build_prefill_items<<<1, threads, hist_bytes, st>>>((int)g.num_experts, m->expert_offsets,
+                                                              m->expert_counts, m->pf_items, m->pf_n_items);
+    } else {
+        k_build_work<<<1, threads, hist_bytes, st>>>((int)g.num_experts, m->expert_offsets, m->expert_counts,
+                                                     m->sorted_token_ids, m->topk_weights, m->work_items,
+                                                     m->n_work);
+    }
     CUDA_TRY(cudaGetLastError());
     return XABE_OK;
 }
