@@ -1,18 +1,25 @@
-// Prefill-shaped expert projections: a grouped GEMM on the 5th-generation
-// tensor cores (tcgen05.mma, accumulators in TMEM).
+// Prefill-shaped expert projections: a persistent, warp-specialised grouped
+// GEMM on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM).
 //
-// One CTA computes one output tile D[128 weight rows][128 token columns] of
-// one expert (or of the shared expert).  The contraction runs in chunks of 64
-// elements through a ring of shared-memory stages:
-//   * sixteen producer warps (two groups on alternate stage pairs) read the raw GGUF bytes (Q6_K superblocks or Q8_0
-//     blocks) of the tile's 128 weight rows, unpack them, scale them and write
-//     f16 values into the stage's A tile in the 128-byte-swizzled K-major
-//     layout the tensor core reads; they also gather the 128 token rows of f16
-//     activations into the B tile, same layout;
-//   * one thread issues four tcgen05.mma (M128 N128 K16, f16 x f16 -> f32)
-//     per stage and commits them to the stage's "empty" barrier;
-//   * four of the producer warps then read the accumulator from TMEM with
-//     tcgen05.ld and apply SwiGLU (gate/up) or the routing weight (down).
+// A tile is D[128 weight rows][128 token columns] of one expert (or of the
+// shared expert); every CTA (one per SM) walks tiles blockIdx.x, + gridDim.x,
+// ...  The contraction runs in chunks of 64 elements.  Four roles:
+//   * two loader warps: asynchronous 16-byte copies (cp.async, sixteen lanes per
+//     weight row so that a row's bytes are read as whole cache lines) bring the
+//     raw GGUF bytes of a 256-element span of all 128 rows (a 210-byte Q6_K
+//     superblock or eight 34-byte Q8_0 blocks per row, widened to 16-byte
+//     boundaries) into a ring of raw slots.  One bulk copy (TMA) per row was
+//     tried first: at 224 bytes per copy the copy engine, not memory, set the pace;
+//   * sixteen unpack warps: read the raw bytes from shared memory, unpack,
+//     scale and write f16 values into the A tile of a stage in the
+//     128-byte-swizzled K-major layout the tensor core reads, and start the
+//     asynchronous 16-byte copies that gather the 128 token rows (B tile);
+//   * one thread issues four tcgen05.mma (M128 N128 K16, f16 x f16 -> f32) per
+//     stage and commits them to the stage's "empty" barrier; two accumulators
+//     in TMEM alternate between tiles;
+//   * four epilogue warps read a finished accumulator with tcgen05.ld and
+//     apply SwiGLU (gate/up) or the routing weight (down) while the other
+//     roles are already on the next tile.
 //
 // Numerics: weights are rounded to f16 after the fp32-exact code is multiplied
 // by the f16-rounded group scale (times 256, undone in the epilogue, which
@@ -21,7 +28,7 @@
 // (exact codes, fp32 scales) by the weight rounding, about 2e-4 relative per
 // weight, and stays inside the rel-L2 <= 1e-3 gate.
 //
-// Every wait is bounded; TMEM is freed on every exit path that allocated it.
+// Every wait is bounded; TMEM is freed on every exit path.
 #pragma once
 
 #include "common.cuh"
@@ -33,14 +40,21 @@ constexpr int kPfTileM = 128;       // weight rows per tile (TMEM lanes)
 constexpr int kPfTileN = 128;       // token columns per tile
 constexpr int kPfChunkK = 64;       // contraction elements per stage (one 128-byte swizzle row of f16)
 constexpr int kPfStageBytes = 2 * kPfTileM * kPfChunkK * 2;  // A tile + B tile, 16 KB each
-constexpr int kPfProducerWarps = 8;   // warps that fill one stage pair
-constexpr int kPfProducerGroups = 2;  // groups working on alternate stage pairs
-// warp 4 issues the MMAs; every other warp is a producer, and warps 0-3 (one per TMEM lane quadrant)
-// also run the epilogue once the contraction is done
-constexpr int kPfThreads = 32 * (1 + kPfProducerWarps * kPfProducerGroups);
-constexpr int kPfMaxStages = 6;
+constexpr int kPfUnpackWarps = 16;
+constexpr int kPfWarpMma = 16;
+constexpr int kPfWarpLoad = 17;     // two loader warps
+constexpr int kPfLoadWarps = 2;
+constexpr int kPfWarpEpi0 = 19;     // four epilogue warps; warp % 4 is the TMEM lane quadrant a warp may read
+constexpr int kPfThreads = 32 * 23;
+constexpr int kPfMaxStages = 4;     // two pairs of chunks
+constexpr int kPfMaxRaw = 3;        // raw slots (one span of all 128 rows each)
+constexpr int kPfAccums = 2;
+constexpr int kPfRawPitchQ6K = 224;   // 210 bytes starting up to 14 bytes into a 16-byte unit
+constexpr int kPfRawPitchQ8 = 288;    // 272 bytes likewise
 constexpr float kPfWeightScale = 256.0f;
 constexpr int kPfItemInts = 4;  // expert, first slot (or first token), columns, pad
+
+__host__ __device__ inline int pf_raw_pitch(int quant) { return quant == QUANT_Q6K ? kPfRawPitchQ6K : kPfRawPitchQ8; }
 
 struct PrefillLaunch {
     const uint8_t* r_a;  // routed gate (or down)
@@ -63,7 +77,10 @@ struct PrefillLaunch {
     float* partial;
     float* shexp;
     int* status;
-    int n_stages;
+    int n_stages;    // A/B stages (even)
+    int n_raw;       // raw slots
+    int slot_bytes;  // 128 * the larger raw pitch of the formats in this launch
+    int row_tiles;   // tiles along the weight rows: gate/up rows / 64, down rows / 128
     int max_tokens;
 };
 
@@ -168,87 +185,112 @@ __device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-// What one lane holds for one producer pass.  A pass is eight weight rows x one PAIR of chunks
-// (128 contraction elements); lane (rrow = lane / 4, j = lane % 4) serves row rrow:
-//   Q6_K  positions l = 8j..8j+7 of all four 32-element groups of half a superblock
-//         (element map of crates/xabe-kernels/src/quant.rs:175-198): 8 bytes of each ql run,
-//         8 bytes of bit pairs, the four group scales and d  -> 32 weights
-//   Q8_0  block j of the pair's four blocks: 32 codes and d   -> 32 weights
-// The four lanes of a row read consecutive bytes, so a load touches few cache lines.
-struct RawQ6 {
-    uint32_t ql0[2], ql1[2], qh[2];
-    int sc[4];
-    uint32_t d;
-};
-struct RawQ8 {
-    uint32_t w[8];
-    uint32_t d;
-};
-
-// Eight bytes that start `sh / 8` (0 or 2) bytes after the 4-byte-aligned address q.  The third
-// word read lies inside the same superblock for every piece this is used on.
-__device__ __forceinline__ void ldg8_shifted(const uint8_t* q, uint32_t sh, uint32_t (&o)[2]) {
-    const uint32_t* w = (const uint32_t*)q;
-    uint32_t a = __ldg(w), b = __ldg(w + 1), c = __ldg(w + 2);
+// Shared-memory accesses of the unpack warps, by 32-bit shared address plus a compile-time
+// offset, so that the per-lane address arithmetic is done once per span and not per access.
+template <int OFF> __device__ __forceinline__ uint32_t lds_u32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(a), "n"(OFF));
+    return v;
+}
+template <int OFF> __device__ __forceinline__ int lds_s8(uint32_t a) {
+    int v;
+    asm volatile("ld.shared.s8 %0, [%1+%2];" : "=r"(v) : "r"(a), "n"(OFF));
+    return v;
+}
+template <int OFF> __device__ __forceinline__ uint32_t lds_u16(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u16 %0, [%1+%2];" : "=r"(v) : "r"(a), "n"(OFF));
+    return v;
+}
+template <int OFF> __device__ __forceinline__ void sts_v4(uint32_t a, uint4 v) {
+    asm volatile("st.shared.v4.b32 [%0+%1], {%2, %3, %4, %5};" ::"r"(a), "n"(OFF), "r"(v.x), "r"(v.y), "r"(v.z),
+                 "r"(v.w)
+                 : "memory");
+}
+// Eight bytes that start sh / 8 (0 or 2) bytes after the word-aligned shared address al + OFF.
+// The third word read lies inside the same raw row for every piece this is used on.
+template <int OFF> __device__ __forceinline__ void lds8_shifted(uint32_t al, uint32_t sh, uint32_t (&o)[2]) {
+    uint32_t a = lds_u32<OFF>(al), b = lds_u32<OFF + 4>(al), c = lds_u32<OFF + 8>(al);
     o[0] = __funnelshift_r(a, b, sh);
     o[1] = __funnelshift_r(b, c, sh);
 }
 
-// `pa`: 4-byte-aligned address at or 2 bytes below (superblock + h*64 + 8j); `pb` likewise for
-// (superblock + 128 + h*32 + 8j); `ps` = superblock + 192 + h*8 + j/2; `pd` = superblock + 208.
-__device__ __forceinline__ void load_pass(const uint8_t* pa, const uint8_t* pb, const uint8_t* ps,
-                                          const uint8_t* pd, uint32_t sh, RawQ6& r) {
-    ldg8_shifted(pa, sh, r.ql0);
-    ldg8_shifted(pa + 32, sh, r.ql1);
-    ldg8_shifted(pb, sh, r.qh);
-#pragma unroll
-    for (int g = 0; g < 4; ++g) r.sc[g] = (int)(int8_t)__ldg(ps + 2 * g);  // scale index h*8 + 2g + l/16
-    r.d = __ldg((const unsigned short*)pd);
-}
-// `blk`: the lane's 34-byte block (2-byte aligned).
-__device__ __forceinline__ void load_pass(const uint8_t* blk, RawQ8& r) {
-    const uint32_t mis = ((uintptr_t)blk & 2) ? 0u : 1u;  // the codes start at blk + 2
-    const uint32_t* w = (const uint32_t*)(blk + 2 - 2 * mis);
-    uint32_t a[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) a[i] = __ldg(w + i);
-    // misaligned codes: a[0] starts with d and the last two codes follow a[7]; aligned: d precedes a[0]
-    uint32_t extra = __ldg((const unsigned short*)(blk + 32 * mis));
-    r.d = mis ? (a[0] & 0xFFFFu) : extra;
-    const uint32_t sh = 16 * mis;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) r.w[i] = __funnelshift_r(a[i], i < 7 ? a[i + 1] : extra, sh);
-}
-
-// Unpack, scale and store the lane's 32 weights: four 16-byte chunks.  `t0`/`t1`: shared-memory
-// addresses of the lane's row inside the A tiles of the pair's two stages, with the row's swizzle
-// already applied to chunk `c0x` (= chunk index XOR row % 8, times 16).
-__device__ __forceinline__ void store_pass(const RawQ6& r, uint8_t* row0, uint8_t* row1, uint32_t cx) {
-    const float d = __half2float(__ushort_as_half((unsigned short)r.d)) * kPfWeightScale;
+// One unpack pass: eight weight rows x one PAIR of chunks (128 contraction elements); lane
+// (rrow = lane / 4, j = lane % 4) serves row rrow and produces 32 weights (four 16-byte chunks).
+//
+// Q6_K, half H of the row's superblock (element map of crates/xabe-kernels/src/quant.rs:175-198):
+// positions l = 8j..8j+7 of the four 32-element groups.  aj: word-aligned address of (superblock
+// + 8j), sh its distance in bits to the true start; ps: superblock + 192 + j/2; d: the super-scale
+// times 256.  Group g goes to chunk (g % 2) * 4 + j of stage g / 2: `dst` is the lane's row and
+// chunk j in the first stage's A tile (swizzle applied); chunk 4 + j is dst ^ 64.
+template <int H>
+__device__ __forceinline__ void unpack_q6k(uint32_t aj, uint32_t sh, uint32_t ps, float d, uint32_t dst) {
+    uint32_t ql0[2], ql1[2], qh[2];
+    lds8_shifted<H * 64>(aj, sh, ql0);
+    lds8_shifted<H * 64 + 32>(aj, sh, ql1);
+    lds8_shifted<128 + H * 32>(aj, sh, qh);
+    int sc[4];
+    sc[0] = lds_s8<H * 8 + 0>(ps);  // scale index H*8 + 2g + l/16
+    sc[1] = lds_s8<H * 8 + 2>(ps);
+    sc[2] = lds_s8<H * 8 + 4>(ps);
+    sc[3] = lds_s8<H * 8 + 6>(ps);
+    const uint32_t dstx = dst ^ 64u;
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
-        const uint32_t* ql = (g & 1) ? r.ql1 : r.ql0;
+        const uint32_t* ql = (g & 1) ? ql1 : ql0;
         uint32_t c[2];
 #pragma unroll
         for (int w = 0; w < 2; ++w) {
             uint32_t nib = (g >> 1) ? (ql[w] >> 4) : ql[w];
-            uint32_t two = g == 0 ? (r.qh[w] << 4) : g == 1 ? (r.qh[w] << 2) : g == 2 ? r.qh[w] : (r.qh[w] >> 2);
+            uint32_t two = g == 0 ? (qh[w] << 4) : g == 1 ? (qh[w] << 2) : g == 2 ? qh[w] : (qh[w] >> 2);
             c[w] = (nib & 0x0F0F0F0Fu) | (two & 0x30303030u);
         }
-        __half2 ds2 = __float2half2_rn(d * (float)r.sc[g]);
+        __half2 ds2 = __float2half2_rn(d * (float)sc[g]);
         uint4 v = codes8_to_h8(c[0], c[1], 0x64206420u, ds2);
-        // group g: elements (g % 2) * 32 + 8j.. of stage g / 2: chunk (g % 2) * 4 + j
-        uint8_t* row = (g >> 1) ? row1 : row0;
-        *(uint4*)(row + (cx ^ ((g & 1) << 6))) = v;
+        if (g == 0) sts_v4<0>(dst, v);
+        else if (g == 1) sts_v4<0>(dstx, v);
+        else if (g == 2) sts_v4<kPfStageBytes>(dst, v);
+        else sts_v4<kPfStageBytes>(dstx, v);
     }
 }
-__device__ __forceinline__ void store_pass(const RawQ8& r, uint8_t* row, uint32_t cx) {
-    __half2 ds2 = __float2half2_rn(__half2float(__ushort_as_half((unsigned short)r.d)) * kPfWeightScale);
+// Q8_0, pair H of the span: the lane's block is number 4H + j of the row's eight.  rj: the row's
+// raw bytes + 34j (2-byte aligned).  `dst`: the lane's row, chunk (j % 2) * 4 of stage j / 2
+// (swizzle applied); chunk + t is dst ^ (16 t).
+template <int H>
+__device__ __forceinline__ void unpack_q8(uint32_t rj, uint32_t dst) {
+    const uint32_t p = rj + 2;  // the codes
+    const uint32_t al = p & ~3u, sh = (p & 2u) * 8;
+    uint32_t a[9];
+    a[0] = lds_u32<H * 136 + 0>(al);
+    a[1] = lds_u32<H * 136 + 4>(al);
+    a[2] = lds_u32<H * 136 + 8>(al);
+    a[3] = lds_u32<H * 136 + 12>(al);
+    a[4] = lds_u32<H * 136 + 16>(al);
+    a[5] = lds_u32<H * 136 + 20>(al);
+    a[6] = lds_u32<H * 136 + 24>(al);
+    a[7] = lds_u32<H * 136 + 28>(al);
+    a[8] = lds_u32<H * 136 + 32>(al);  // may lie past the block: the raw ring ends with padding for it
+    const float d = __half2float(__ushort_as_half((unsigned short)lds_u16<H * 136>(rj))) * kPfWeightScale;
+    __half2 ds2 = __float2half2_rn(d);
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
-        uint4 v = codes8_to_h8(r.w[2 * t] ^ 0x80808080u, r.w[2 * t + 1] ^ 0x80808080u, 0x64806480u, ds2);
-        *(uint4*)(row + (cx ^ (t << 4))) = v;  // chunk (j % 2) * 4 + t
+        uint32_t w0 = __funnelshift_r(a[2 * t], a[2 * t + 1], sh) ^ 0x80808080u;
+        uint32_t w1 = __funnelshift_r(a[2 * t + 1], a[2 * t + 2], sh) ^ 0x80808080u;
+        sts_v4<0>(dst ^ (uint32_t)(t << 4), codes8_to_h8(w0, w1, 0x64806480u, ds2));
     }
+}
+
+template <int DST_OFF, int SRC_OFF>
+__device__ __forceinline__ void cp_async16_off(uint32_t dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0+%1], [%2+%3], 16;" ::"r"(dst_smem), "n"(DST_OFF), "l"(src),
+                 "n"(SRC_OFF)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_arrive_noinc32(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive32(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
 __device__ __forceinline__ void mbar_arrive_pf(uint64_t* bar) {
@@ -299,287 +341,364 @@ __global__ void k_build_prefill_items(int num_experts, const int* __restrict__ e
     }
 }
 
-template <int QUANT> struct RawOf;
-template <> struct RawOf<QUANT_Q6K> { using T = RawQ6; };
-template <> struct RawOf<QUANT_Q8_0> { using T = RawQ8; };
+// One tile of the walk: which expert (or the shared expert), which token columns, which row tile.
+struct PfTile {
+    int shared, expert, first, ncols, bx;
+};
+__device__ __forceinline__ PfTile pf_tile(const PrefillLaunch& L, int t, int n_routed, int valid) {
+    PfTile T;
+    const int y = t / L.row_tiles;
+    T.bx = t - y * L.row_tiles;
+    T.shared = y >= n_routed;
+    if (!T.shared) {
+        const int* it = L.items + (size_t)y * kPfItemInts;
+        T.expert = __ldg(it);
+        T.first = __ldg(it + 1);
+        T.ncols = __ldg(it + 2);
+    } else {
+        T.expert = 0;
+        T.first = (y - n_routed) * kPfTileN;
+        T.ncols = min(kPfTileN, valid - T.first);
+    }
+    return T;
+}
 
-// What a producer warp needs to know; everything here is fixed for the tile.
-struct PfProducer {
-    uint8_t* stages;
-    uint64_t* full_bar;
-    uint64_t* empty_bar;
-    volatile int* abortp;
-    int* status;
-    int n_stages, n_pairs, pgroup, gw, lane;
-    const uint8_t* row_ptr0;  // the lane's weight row of pass 0; pass 1 is eight rows further
-    size_t pass_stride;
-    const uint4* x4;          // activations in 16-byte units
-    int xoff[4];              // the thread's four token rows: row * (K / 8) + piece, or -1 (zero column)
+// Address of tile row r's weight row.  Gate/up tiles interleave the two matrices in groups of 16
+// rows: tile row 32q + i is gate row 64 bx + 16q + i for i < 16, up row 64 bx + 16q + (i - 16) otherwise.
+template <int MODE>
+__device__ __forceinline__ const uint8_t* pf_row_ptr(const PrefillLaunch& L, const PfTile& T, int r,
+                                                     size_t row_bytes) {
+    const uint8_t* base;
+    size_t wrow;
+    if (MODE == MODE_GATEUP) {
+        const int i = r & 31;
+        base = i < 16 ? (T.shared ? L.s_a : L.r_a) : (T.shared ? L.s_b : L.r_b);
+        wrow = (size_t)T.bx * 64 + (r >> 5) * 16 + (i & 15);
+    } else {
+        base = T.shared ? L.s_a : L.r_a;
+        wrow = (size_t)T.bx * kPfTileM + r;
+    }
+    return base + ((T.shared ? 0 : (size_t)T.expert * L.rows) + wrow) * row_bytes;
+}
+
+// Shared-memory control block of the kernel.
+struct PfCtl {
+    uint64_t full_bar[kPfMaxStages];    // unpack warps + their B-tile copies -> MMA
+    uint64_t empty_bar[kPfMaxStages];   // MMA (tcgen05.commit) -> unpack warps
+    uint64_t raw_full[kPfMaxRaw];       // bulk copies landed -> unpack warps
+    uint64_t raw_empty[kPfMaxRaw];      // unpack warps -> loader
+    uint64_t acc_full[kPfAccums];       // MMA (tcgen05.commit) -> epilogue
+    uint64_t acc_empty[kPfAccums];      // epilogue -> MMA
+    uint32_t tmem_base;
+    int abort_flag;
 };
 
-template <int QUANT>
-__device__ __forceinline__ void pf_load(const PfProducer& P, int pr, typename RawOf<QUANT>::T (&raw)[2]) {
-    const int j = P.lane & 3;
-    if constexpr (QUANT == QUANT_Q6K) {
-        const int h = pr & 1;
-        const uint8_t* blk = P.row_ptr0 + (size_t)(pr >> 1) * kQ6KBlockBytes;
-        const uint32_t mis = (uint32_t)((uintptr_t)blk & 2);
-        const uint8_t* pa = blk - mis + h * 64 + 8 * j;
-        const uint8_t* pb = blk - mis + 128 + h * 32 + 8 * j;
-        const uint8_t* ps = blk + 192 + h * 8 + (j >> 1);
-        const uint8_t* pd = blk + 208;
-#pragma unroll
-        for (int q = 0; q < 2; ++q)
-            load_pass(pa + q * P.pass_stride, pb + q * P.pass_stride, ps + q * P.pass_stride,
-                      pd + q * P.pass_stride, mis * 8, raw[q]);
-    } else {
-        const uint8_t* blk = P.row_ptr0 + (size_t)(pr * 4 + j) * kQ8BlockBytes;
-#pragma unroll
-        for (int q = 0; q < 2; ++q) load_pass(blk + q * P.pass_stride, raw[q]);
-    }
-}
-
-// Fills the stage pair of contraction pair `pr` from `raw`: waits for the two stages to be free,
-// starts the asynchronous copies of the token rows (B tiles), writes the unpacked weights (A tiles).
-template <int QUANT>
-__device__ __forceinline__ bool pf_fill(const PfProducer& P, int pr, const typename RawOf<QUANT>::T (&raw)[2]) {
-    const int S = P.n_stages;
-    const int kc0 = 2 * pr, kc1 = 2 * pr + 1;
-    const int st0 = kc0 % S, st1 = kc1 % S;
-    if (kc0 / S >= 1 && !stream_wait_pf(&P.empty_bar[st0], (kc0 / S - 1) & 1, P.abortp, P.status)) return false;
-    if (kc1 / S >= 1 && !stream_wait_pf(&P.empty_bar[st1], (kc1 / S - 1) & 1, P.abortp, P.status)) return false;
-    uint8_t* a0 = P.stages + (size_t)st0 * kPfStageBytes;
-    uint8_t* a1 = P.stages + (size_t)st1 * kPfStageBytes;
-    const int lane = P.lane, gw = P.gw;
-    {   // B tiles: rows r0 + 32m, 16-byte piece lane % 8
-        const int r0 = gw * 4 + (lane >> 3), piece = lane & 7;
-        const uint32_t boff = (uint32_t)(kPfTileM * kPfChunkK * 2) + swz_off(r0, piece);
-        const uint32_t b0 = smem_u32(a0) + boff, b1 = smem_u32(a1) + boff;
-#pragma unroll
-        for (int m = 0; m < 4; ++m) {
-            const bool live = P.xoff[m] >= 0;
-            const uint4* src = P.x4 + (live ? (size_t)P.xoff[m] + (size_t)pr * 16 : 0);
-            cp_async16(b0 + m * 4096, src, live ? 16u : 0u);
-            cp_async16(b1 + m * 4096, src + (live ? 8 : 0), live ? 16u : 0u);
-        }
-        cp_async_arrive_noinc(&P.full_bar[st0]);
-        cp_async_arrive_noinc(&P.full_bar[st1]);
-    }
-    const int rrow = lane >> 2, j = lane & 3;
-#pragma unroll
-    for (int q = 0; q < 2; ++q) {
-        const uint32_t rowoff = (uint32_t)((2 * gw + q) * 1024 + rrow * 128);
-        if constexpr (QUANT == QUANT_Q6K) {
-            store_pass(raw[q], a0 + rowoff, a1 + rowoff, (uint32_t)((j ^ rrow) << 4));
-        } else {
-            store_pass(raw[q], ((j >> 1) ? a1 : a0) + rowoff, (uint32_t)(((((j & 1) << 2)) ^ rrow) << 4));
-        }
-    }
-    fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
-    __syncwarp();
-    if (lane == 0) {
-        mbar_arrive_pf(&P.full_bar[st0]);
-        mbar_arrive_pf(&P.full_bar[st1]);
-    }
-    return true;
-}
-
-// The producer loop of one warp: its group takes every second pair; the raw bytes of the group's
-// next pair are in flight while the current one is unpacked.
-template <int QUANT>
-__device__ __forceinline__ void pf_produce(const PfProducer& P) {
-    typename RawOf<QUANT>::T ra[2], rb[2];
-    const int step = kPfProducerGroups;
-    int pr = P.pgroup;
-    if (pr < P.n_pairs) pf_load<QUANT>(P, pr, ra);
-    while (pr < P.n_pairs) {
-        if (pr + step < P.n_pairs) pf_load<QUANT>(P, pr + step, rb);
-        if (!pf_fill<QUANT>(P, pr, ra)) break;
-        pr += step;
-        if (pr >= P.n_pairs) break;
-        if (pr + step < P.n_pairs) pf_load<QUANT>(P, pr + step, ra);
-        if (!pf_fill<QUANT>(P, pr, rb)) break;
-        pr += step;
-    }
-    asm volatile("cp.async.wait_all;" ::: "memory");
-}
-
 // MODE_GATEUP (0): TMEM lane m = 32q + i holds gate row r0 + 16q + i for i < 16 and up row
-// r0 + 16q + (i - 16) otherwise (r0 = 64 * blockIdx.x), so SwiGLU pairs two lanes of one warp.
-// MODE_DOWN (1): lane m holds row 128 * blockIdx.x + m.
-// grid: (row tiles, routed item capacity + shared token tiles); block kPfThreads.
+// r0 + 16q + (i - 16) otherwise (r0 = 64 * bx), so SwiGLU pairs two lanes of one warp.
+// MODE_DOWN (1): lane m holds row 128 * bx + m.
+// grid: one CTA per SM (or fewer); block kPfThreads.
 template <int MODE, int QR, int QS>
 __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t full_bar[kPfMaxStages];
-    __shared__ __align__(8) uint64_t empty_bar[kPfMaxStages];
-    __shared__ __align__(8) uint64_t accum_bar;
-    __shared__ uint32_t tmem_base_s;
-    __shared__ int abort_flag;
-    __shared__ int col_src[kPfTileN];
-    __shared__ int col_flat[kPfTileN];
-    __shared__ float col_wgt[kPfTileN];
+    __shared__ __align__(8) PfCtl ctl;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int valid = *L.valid_tokens;
     const int n_routed = L.has_routed ? *L.n_items : 0;
     const int n_shared = L.has_shared ? (valid + kPfTileN - 1) / kPfTileN : 0;
-    const int y = blockIdx.y;
-    if (y >= n_routed + n_shared) return;  // uniform: nothing allocated yet
-    const bool shared = y >= n_routed;
-    int expert = 0, first, ncols;
-    if (!shared) {
-        const int* it = L.items + (size_t)y * kPfItemInts;
-        expert = it[0];
-        first = it[1];
-        ncols = it[2];
-    } else {
-        first = (y - n_routed) * kPfTileN;
-        ncols = min(kPfTileN, valid - first);
-    }
-    const int quant = shared ? QS : QR;
-    const int S = L.n_stages;
-    const int n_chunks = L.k / kPfChunkK;
-    const int row_bytes = L.k / kSpanElems * span_bytes_of(quant);
-    uint8_t* stages = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    volatile int* abortp = &abort_flag;
+    const int n_tiles = (n_routed + n_shared) * L.row_tiles;
+    const int R = L.n_raw;
+    const int n_spans = L.k / kSpanElems;
+    uint8_t* stages = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t* raw_ring = stages + (size_t)kPfMaxStages * kPfStageBytes;
+    volatile int* abortp = &ctl.abort_flag;
 
     if (tid == 0) {
-        abort_flag = 0;
-        for (int i = 0; i < S; ++i) {
-            // one arrival per producer warp (A tile written) + one per producer thread (its B-tile copies landed)
-            mbar_init(&full_bar[i], kPfProducerWarps + kPfProducerWarps * 32);
-            mbar_init(&empty_bar[i], 1);
+        ctl.abort_flag = 0;
+        for (int i = 0; i < kPfMaxStages; ++i) {
+            // one arrival per unpack warp (A tile written) + one per unpack thread (its B-tile copies landed)
+            mbar_init(&ctl.full_bar[i], kPfUnpackWarps + kPfUnpackWarps * 32);
+            mbar_init(&ctl.empty_bar[i], 1);
         }
-        mbar_init(&accum_bar, 1);
+        for (int i = 0; i < R; ++i) {
+            mbar_init(&ctl.raw_full[i], kPfLoadWarps * 32);  // every loader lane's copies landed
+            mbar_init(&ctl.raw_empty[i], kPfUnpackWarps);
+        }
+        for (int i = 0; i < kPfAccums; ++i) {
+            mbar_init(&ctl.acc_full[i], 1);
+            mbar_init(&ctl.acc_empty[i], 4);
+        }
         fence_mbar_init();
     }
-    if (tid < kPfTileN) {
-        int c = tid;
-        int src = -1, flat = 0;
-        float wgt = 0.f;
-        if (c < ncols) {
-            if (shared) {
-                src = first + c;
-            } else {
-                flat = L.sorted_token_ids[first + c];
-                wgt = L.topk_weights[flat];
-                src = MODE == MODE_GATEUP ? flat / L.top_k : first + c;
-            }
-        }
-        col_src[c] = src;
-        col_flat[c] = flat;
-        col_wgt[c] = wgt;
-    }
-    if (warp == 4) {
-        tmem_alloc(&tmem_base_s, kPfTileN);  // 128 fp32 columns
+    if (warp == kPfWarpMma) {
+        tmem_alloc(&ctl.tmem_base, kPfAccums * kPfTileN);  // two accumulators of 128 fp32 columns
         tmem_relinquish();
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_base = tmem_base_s;
+    const uint32_t tmem_base = ctl.tmem_base;
 
-    const int prod_id = warp < 4 ? warp : warp - 1;        // producer warp index 0..15 (warp 4 is the MMA issuer)
-    const int pgroup = prod_id / kPfProducerWarps;        // which stage pairs: pgroup, pgroup + 2, ...
-    if (warp != 4) {
-        // ------------------------------ producers ------------------------------
-        // A producer group (8 warps) fills one PAIR of stages (128 contraction elements) at a time:
-        // sixteen passes of eight weight rows, two per warp, 32 weights per lane; and the 2 x 128
-        // token rows of the B tiles by asynchronous 16-byte copies, eight per thread.
-        PfProducer P;
-        P.stages = stages;
-        P.full_bar = full_bar;
-        P.empty_bar = empty_bar;
-        P.abortp = abortp;
-        P.status = L.status;
-        P.n_stages = S;
-        P.n_pairs = n_chunks >> 1;  // the contraction is a multiple of 256
-        P.pgroup = pgroup;
-        P.gw = prod_id % kPfProducerWarps;
-        P.lane = lane;
-        {
-            // tile rows 16gw..16gw+15 are consecutive weight rows of one matrix (in the gate/up
-            // interleave: half of one 32-row group)
-            const int gw = P.gw, rrow = lane >> 2;
-            const uint8_t* base = shared ? L.s_a : L.r_a;
-            size_t wrow;
-            if (MODE == MODE_GATEUP) {
-                if (gw & 1) base = shared ? L.s_b : L.r_b;
-                wrow = (size_t)blockIdx.x * 64 + (gw >> 1) * 16 + rrow;
-            } else {
-                wrow = (size_t)blockIdx.x * kPfTileM + 16 * gw + rrow;
-            }
-            const size_t expert_row0 = shared ? 0 : (size_t)expert * L.rows;
-            P.row_ptr0 = base + (expert_row0 + wrow) * row_bytes;
-            P.pass_stride = (size_t)8 * row_bytes;
-            P.x4 = (const uint4*)(shared ? L.x_shared : L.x_routed);
-            const int r0 = gw * 4 + (lane >> 3);
+    constexpr int S = kPfMaxStages;
+    if (warp < kPfUnpackWarps) {
+        // ------------------------------ unpack warps ------------------------------
+        // Per pair of chunks: this warp unpacks tile rows 8w..8w+7 (32 weights per lane) and every
+        // thread starts up to four 16-byte copies of the B tiles (token columns tid/8 and tid/8 + 64
+        // of both stages; columns the tile does not have are skipped, the tensor core never reads them).
+        const int rrow = lane >> 2, j = lane & 3;
+        const int trow = 8 * warp + rrow;
+        const int r0 = tid >> 3, piece = tid & 7;
+        const uint32_t stages32 = smem_u32(stages), raw32 = smem_u32(raw_ring);
+        const uint32_t boff = (uint32_t)(kPfTileM * kPfChunkK * 2) + swz_off(r0, piece);
+        const uint32_t rowoff = (uint32_t)(warp * 1024 + rrow * 128);
+        const uint32_t dst6 = rowoff + (uint32_t)((j ^ rrow) << 4);
+        const uint32_t dst8 = rowoff + (uint32_t)((((j & 1) << 2) ^ rrow) << 4) + (uint32_t)(j >> 1) * kPfStageBytes;
+        const uint32_t full32 = smem_u32(&ctl.full_bar[0]), empty32 = smem_u32(&ctl.empty_bar[0]);
+        uint32_t kc = 0;              // chunks since the kernel started
+        int slot = 0, rphase = 0;     // raw ring position
+        bool ok = true;
+        // Tile metadata runs two tiles ahead of the work (the tile record) and one ahead (the token
+        // rows, whose addresses come from the record), so no tile starts by waiting for global loads.
+        auto token_rows = [&](const PfTile& T, int (&xo)[2]) {
 #pragma unroll
-            for (int m = 0; m < 4; ++m) {
-                const int srow = col_src[r0 + 32 * m];
-                P.xoff[m] = srow < 0 ? -1 : srow * (L.k >> 3) + (lane & 7);
+            for (int m = 0; m < 2; ++m) {
+                const int c = r0 + 64 * m;
+                int src = -1;
+                if (c < T.ncols) {
+                    if (T.shared || MODE == MODE_DOWN) src = T.first + c;
+                    else src = __ldg(L.sorted_token_ids + T.first + c) / L.top_k;
+                }
+                xo[m] = src;
             }
+        };
+        const int G = gridDim.x;
+        PfTile T{}, T1{}, T2{};
+        int xrow[2] = {-1, -1}, xrow1[2] = {-1, -1};
+        if ((int)blockIdx.x < n_tiles) {
+            T = pf_tile(L, blockIdx.x, n_routed, valid);
+            token_rows(T, xrow);
         }
-        if (quant == QUANT_Q6K) pf_produce<QUANT_Q6K>(P);
-        else pf_produce<QUANT_Q8_0>(P);
-    } else {
+        if ((int)blockIdx.x + G < n_tiles) T1 = pf_tile(L, blockIdx.x + G, n_routed, valid);
+        for (int t = blockIdx.x; t < n_tiles && ok; t += G) {
+            if (t + G < n_tiles) token_rows(T1, xrow1);
+            if (t + 2 * G < n_tiles) T2 = pf_tile(L, t + 2 * G, n_routed, valid);
+            const int quant = T.shared ? QS : QR;
+            const int pitch = pf_raw_pitch(quant);
+            const int span_bytes = span_bytes_of(quant);
+            // where in its 16-byte unit the lane's weight row starts (the loaders copy whole units)
+            const uint32_t rowlo =
+                (uint32_t)(uintptr_t)pf_row_ptr<MODE>(L, T, trow, (size_t)n_spans * span_bytes);
+            const __half* xb = T.shared ? L.x_shared : L.x_routed;
+            const __half* xp0 = xb + (size_t)(xrow[0] < 0 ? 0 : xrow[0]) * L.k + piece * 8;
+            const __half* xp1 = xb + (size_t)(xrow[1] < 0 ? 0 : xrow[1]) * L.k + piece * 8;
+            const bool live0 = xrow[0] >= 0, live1 = xrow[1] >= 0;
+            for (int s = 0; s < n_spans && ok; ++s) {
+                ok = stream_wait_pf(&ctl.raw_full[slot], rphase, abortp, L.status);
+                if (!ok) break;
+                const uint32_t rawrow =
+                    raw32 + (uint32_t)slot * L.slot_bytes + trow * pitch + ((rowlo + s * span_bytes) & 15u);
+                // Q6_K
+                const uint32_t aj = (rawrow & ~3u) + 8 * j, sh = (rawrow & 2u) * 8, ps = rawrow + 192 + (j >> 1);
+                float d6 = 0.f;
+                if (quant == QUANT_Q6K)
+                    d6 = __half2float(__ushort_as_half((unsigned short)lds_u16<208>(rawrow))) * kPfWeightScale;
+                // Q8_0
+                const uint32_t rj = rawrow + j * kQ8BlockBytes;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint32_t st0 = kc & (S - 1);  // even: the pair's stages are st0 and st0 + 1
+                    if (kc >= (uint32_t)S) {
+                        const uint32_t par = ((kc / S) & 1) ^ 1;
+                        ok = stream_wait_pf(&ctl.empty_bar[st0], par, abortp, L.status) &&
+                             stream_wait_pf(&ctl.empty_bar[st0 + 1], par, abortp, L.status);
+                        if (!ok) break;
+                    }
+                    const uint32_t a0 = stages32 + st0 * kPfStageBytes;
+                    const uint32_t fb = full32 + st0 * 8;
+                    if (live0) {
+                        cp_async16_off<0, 0>(a0 + boff, xp0);
+                        cp_async16_off<kPfStageBytes, 128>(a0 + boff, xp0);
+                    }
+                    if (live1) {
+                        cp_async16_off<8192, 0>(a0 + boff, xp1);
+                        cp_async16_off<kPfStageBytes + 8192, 128>(a0 + boff, xp1);
+                    }
+                    cp_async_arrive_noinc32(fb);
+                    cp_async_arrive_noinc32(fb + 8);
+                    xp0 += 2 * kPfChunkK;
+                    xp1 += 2 * kPfChunkK;
+                    if (quant == QUANT_Q6K) {
+                        if (h == 0) unpack_q6k<0>(aj, sh, ps, d6, a0 + dst6);
+                        else unpack_q6k<1>(aj, sh, ps, d6, a0 + dst6);
+                    } else {
+                        if (h == 0) unpack_q8<0>(rj, a0 + dst8);
+                        else unpack_q8<1>(rj, a0 + dst8);
+                    }
+                    fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive32(fb);
+                        mbar_arrive32(fb + 8);
+                    }
+                    kc += 2;
+                }
+                __syncwarp();
+                if (ok && lane == 0) mbar_arrive_pf(&ctl.raw_empty[slot]);
+                if (++slot == R) {
+                    slot = 0;
+                    rphase ^= 1;
+                }
+            }
+            T = T1;
+            T1 = T2;
+            xrow[0] = xrow1[0];
+            xrow[1] = xrow1[1];
+        }
+        asm volatile("cp.async.wait_all;" ::: "memory");
+    } else if (warp == kPfWarpMma) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc_f16(kPfTileM, kPfTileN);
+            const int n_chunks = L.k / kPfChunkK;
+            const int G = gridDim.x;
+            uint32_t kc = 0, n = 0;
             bool ok = true;
-            for (int kc = 0; kc < n_chunks && ok; ++kc) {
-                const int st = kc % S;
-                ok = stream_wait_pf(&full_bar[st], (kc / S) & 1, abortp, L.status);
-                if (!ok) break;
-                tc_fence_after();
-                fence_proxy_async_smem();  // the B tile arrived by cp.async, not through the async proxy
-                const uint32_t a_addr = smem_u32(stages + (size_t)st * kPfStageBytes);
-                const uint64_t adesc = umma_smem_desc(a_addr);
-                const uint64_t bdesc = umma_smem_desc(a_addr + kPfTileM * kPfChunkK * 2);
+            int ncols = (int)blockIdx.x < n_tiles ? pf_tile(L, blockIdx.x, n_routed, valid).ncols : 0;
+            for (int t = blockIdx.x; t < n_tiles && ok; t += G, ++n) {
+                // the tensor core computes only as many token columns as the tile has (in steps of 16)
+                const uint32_t idesc = umma_idesc_f16(kPfTileM, max(16, (ncols + 15) & ~15));
+                if (t + G < n_tiles) ncols = pf_tile(L, t + G, n_routed, valid).ncols;  // in flight during this tile
+                const uint32_t acc = n % kPfAccums;
+                if (n >= (uint32_t)kPfAccums) {
+                    ok = stream_wait_pf(&ctl.acc_empty[acc], (n / kPfAccums - 1) & 1, abortp, L.status);
+                    if (!ok) break;
+                    tc_fence_after();
+                }
+                const uint32_t tmem_d = tmem_base + acc * kPfTileN;
+                for (int c = 0; c < n_chunks && ok; ++c, ++kc) {
+                    const int st = kc & (S - 1);
+                    ok = stream_wait_pf(&ctl.full_bar[st], (kc / S) & 1, abortp, L.status);
+                    if (!ok) break;
+                    tc_fence_after();
+                    fence_proxy_async_smem();  // the B tile arrived by cp.async, not through the async proxy
+                    const uint32_t a_addr = smem_u32(stages + (size_t)st * kPfStageBytes);
+                    const uint64_t adesc = umma_smem_desc(a_addr);
+                    const uint64_t bdesc = umma_smem_desc(a_addr + kPfTileM * kPfChunkK * 2);
 #pragma unroll
-                for (int k4 = 0; k4 < kPfChunkK / 16; ++k4)  // 32 bytes per K16 step inside the swizzle row
-                    umma_f16(tmem_base, adesc + 2 * k4, bdesc + 2 * k4, idesc, (kc > 0 || k4 > 0) ? 1u : 0u);
-                umma_commit(&empty_bar[st]);  // the stage is free once these MMAs have read it
+                    for (int k4 = 0; k4 < kPfChunkK / 16; ++k4)  // 32 bytes per K16 step inside the swizzle row
+                        umma_f16(tmem_d, adesc + 2 * k4, bdesc + 2 * k4, idesc, (c > 0 || k4 > 0) ? 1u : 0u);
+                    umma_commit(&ctl.empty_bar[st]);  // the stage is free once these MMAs have read it
+                }
+                if (ok) umma_commit(&ctl.acc_full[acc]);
             }
-            if (ok) umma_commit(&accum_bar);
         }
-    }
-    if (warp < 4) {
-        // ------------------------------- epilogue -------------------------------
-        bool ok = stream_wait_pf(&accum_bar, 0, abortp, L.status);
-        tc_fence_after();
-        const float inv = 1.0f / kPfWeightScale;
-        if (ok) {
-            for (int cb = 0; cb * 32 < ncols; ++cb) {
-                uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cb * 32), r);
-                tmem_ld_wait();
-                if (MODE == MODE_GATEUP) {
-                    const int out_row = blockIdx.x * 64 + warp * 16 + (lane & 15);
-                    __half* dst_base = shared ? L.inter_shared : L.inter_routed;
+    } else if (warp < kPfWarpEpi0) {
+        // -------------------------------- loaders --------------------------------
+        // Copy i of a span serves tile rows 4i + 2lw + (lane / 16) (lw: which loader warp): sixteen
+        // lanes per row, 16 bytes each, as many as the row's widened bytes need.
+        const int lw = warp - kPfWarpLoad, hw = lane >> 4, part = lane & 15;
+        const uint32_t raw32 = smem_u32(raw_ring), rawfull32 = smem_u32(&ctl.raw_full[0]);
+        int slot = 0, rphase = 0;
+        bool ok = true, wrapped = false;
+        const int G = gridDim.x;
+        PfTile T{}, T1{};
+        if ((int)blockIdx.x < n_tiles) T = pf_tile(L, blockIdx.x, n_routed, valid);
+        for (int t = blockIdx.x; t < n_tiles && ok; t += G) {
+            if (t + G < n_tiles) T1 = pf_tile(L, t + G, n_routed, valid);  // in flight during this tile
+            const int quant = T.shared ? QS : QR;
+            const uint32_t pitch = pf_raw_pitch(quant);
+            const uint32_t span_bytes = span_bytes_of(quant);
+            const size_t row_bytes = (size_t)n_spans * span_bytes;
+            // rows 2lw + hw of the first gate group and of the first up group (down: the same row twice)
+            const uint8_t* pg = pf_row_ptr<MODE>(L, T, 2 * lw + hw, row_bytes);
+            const uint8_t* pu = MODE == MODE_GATEUP ? pf_row_ptr<MODE>(L, T, 16 + 2 * lw + hw, row_bytes) : pg;
+            for (int s = 0; s < n_spans && ok; ++s) {
+                if (wrapped) {  // the slot is free once every unpack warp has left its previous span
+                    ok = stream_wait_pf(&ctl.raw_empty[slot], rphase ^ 1, abortp, L.status);
+                    if (!ok) break;
+                }
+                const uint32_t dst0 = raw32 + (uint32_t)slot * L.slot_bytes + (uint32_t)(2 * lw + hw) * pitch + part * 16;
+                const uint8_t* sg = pg + (size_t)s * span_bytes;
+                const uint8_t* su = pu + (size_t)s * span_bytes;
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        float mine = __uint_as_float(r[j]) * inv;
+                for (int i = 0; i < 32; ++i) {
+                    // tile row 4i + c (c = 2lw + hw): in the gate/up interleave rows 4i..4i+3 of the tile are
+                    // rows (i / 8) * 16 + 4 (i % 4) + c of the gate (i % 8 < 4) or up matrix
+                    const int wr = MODE == MODE_GATEUP ? (i >> 3) * 16 + 4 * (i & 3) : 4 * i;
+                    const uint8_t* p = ((MODE == MODE_GATEUP && (i & 4)) ? su : sg) + (size_t)wr * row_bytes;
+                    const uint32_t mis = (uint32_t)(uintptr_t)p & 15u;
+                    const uint32_t units = (mis + span_bytes + 15u) >> 4;  // ends at or before the tensor's end
+                    const uint8_t* src = p - mis + part * 16;
+                    const uint32_t dst = dst0 + (uint32_t)(4 * i) * pitch;
+                    if ((uint32_t)part < units) cp_async16(dst, src, 16u);
+                    if ((uint32_t)part + 16u < units) cp_async16(dst + 256, src + 256, 16u);
+                }
+                cp_async_arrive_noinc32(rawfull32 + slot * 8);
+                if (++slot == R) {
+                    slot = 0;
+                    rphase ^= 1;
+                    wrapped = true;
+                }
+            }
+            T = T1;
+        }
+        asm volatile("cp.async.wait_all;" ::: "memory");
+    } else {
+        // ------------------------------- epilogue -------------------------------
+        const int quad = warp & 3;  // TMEM lanes 32 * quad .. 32 * quad + 31
+        const float inv = 1.0f / kPfWeightScale;
+        uint32_t n = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++n) {
+            const PfTile T = pf_tile(L, t, n_routed, valid);
+            const uint32_t acc = n % kPfAccums;
+            ok = stream_wait_pf(&ctl.acc_full[acc], (n / kPfAccums) & 1, abortp, L.status);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + acc * kPfTileN + ((uint32_t)(quad * 32) << 16);
+            for (int cb = 0; cb * 32 < T.ncols; ++cb) {
+                uint32_t r[32];
+                tmem_ld32(taddr + (uint32_t)(cb * 32), r);
+                tmem_ld_wait();
+                if ((cb + 1) * 32 >= T.ncols) {  // last read of this accumulator: hand it back before the stores
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_pf(&ctl.acc_empty[acc]);
+                }
+                if (MODE == MODE_GATEUP) {
+                    const int out_row = T.bx * 64 + quad * 16 + (lane & 15);
+                    __half* dst_base = T.shared ? L.inter_shared : L.inter_routed;
+#pragma unroll
+                    for (int jj = 0; jj < 32; ++jj) {
+                        float mine = __uint_as_float(r[jj]) * inv;
                         float other = __shfl_xor_sync(0xffffffffu, mine, 16);
-                        bool do_it = (lane < 16) == (j < 16);  // lanes 0-15 finish columns 0-15, lanes 16-31 the rest
-                        int col = cb * 32 + j;
-                        if (do_it && col < ncols) {
+                        bool do_it = (lane < 16) == (jj < 16);  // lanes 0-15 finish columns 0-15, lanes 16-31 the rest
+                        int col = cb * 32 + jj;
+                        if (do_it && col < T.ncols) {
                             float gv = lane < 16 ? mine : other;
                             float uv = lane < 16 ? other : mine;
                             float v = __fdiv_rn(gv, 1.0f + expf(-gv)) * uv;
-                            dst_base[(size_t)(first + col) * L.rows + out_row] = __float2half_rn(v);
+                            dst_base[(size_t)(T.first + col) * L.rows + out_row] = __float2half_rn(v);
                         }
                     }
                 } else {
-                    const int out_row = blockIdx.x * kPfTileM + warp * 32 + lane;
+                    const int out_row = T.bx * kPfTileM + quad * 32 + lane;
+                    // lane c holds the flat (token, k) id and the routing weight of column 32 cb + c
+                    int my_flat = 0;
+                    float my_wgt = 0.f;
+                    const int mycol = cb * 32 + lane;
+                    if (!T.shared && mycol < T.ncols) {
+                        my_flat = __ldg(L.sorted_token_ids + T.first + mycol);
+                        my_wgt = __ldg(L.topk_weights + my_flat);
+                    }
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        int col = cb * 32 + j;
-                        if (col < ncols) {
-                            float v = __uint_as_float(r[j]) * inv;
-                            if (shared) L.shexp[(size_t)(first + col) * L.rows + out_row] = v;
-                            else L.partial[(size_t)col_flat[col] * L.rows + out_row] = col_wgt[col] * v;
+                    for (int jj = 0; jj < 32; ++jj) {
+                        const int col = cb * 32 + jj;
+                        const int flat = __shfl_sync(0xffffffffu, my_flat, jj);
+                        const float wgt = __shfl_sync(0xffffffffu, my_wgt, jj);
+                        if (col < T.ncols) {
+                            float v = __uint_as_float(r[jj]) * inv;
+                            if (T.shared) L.shexp[(size_t)(T.first + col) * L.rows + out_row] = v;
+                            else L.partial[(size_t)flat * L.rows + out_row] = wgt * v;
                         }
                     }
                 }
@@ -589,7 +708,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L)
     // every thread of the CTA arrives here on every path, so TMEM is always returned
     tc_fence_before();
     __syncthreads();
-    if (warp == 4) tmem_dealloc(tmem_base, kPfTileN);
+    if (warp == kPfWarpMma) tmem_dealloc(tmem_base, kPfAccums * kPfTileN);
 }
 
 }  // namespace xabe

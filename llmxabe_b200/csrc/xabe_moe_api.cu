@@ -326,13 +326,25 @@ int run_experts(xabe_moe* m, cudaStream_t st, const MlpWeights& routed, const Ml
         P.status = m->status;
         P.max_tokens = (int)g.max_tokens;
         P.n_stages = kPfMaxStages;
-        size_t smem_pf = (size_t)P.n_stages * kPfStageBytes + 1024;
-        unsigned ycap = (routed.present ? (unsigned)m->pf_capacity : 0u) +
-                        (shared.present ? (g.max_tokens + kPfTileN - 1) / kPfTileN : 0u);
+        // one CTA per SM walks the tiles; raw slots as many as fit beside the stages
+        dim3 pf_grid((unsigned)m->sm_count);
+        auto pf_smem = [&](int q_routed, int q_shared) {
+            int pitch = 0;
+            if (routed.present) pitch = pf_raw_pitch(q_routed == XABE_QUANT_Q6_K ? QUANT_Q6K : QUANT_Q8_0);
+            if (shared.present) {
+                int ps = pf_raw_pitch(q_shared == XABE_QUANT_Q6_K ? QUANT_Q6K : QUANT_Q8_0);
+                if (ps > pitch) pitch = ps;
+            }
+            P.slot_bytes = kPfTileM * pitch;
+            P.n_raw = pitch == kPfRawPitchQ6K ? kPfMaxRaw : 2;
+            return (size_t)1024 + (size_t)P.n_stages * kPfStageBytes + (size_t)P.n_raw * P.slot_bytes + 16;
+        };
         P.r_a = L.r_a; P.r_b = L.r_b; P.s_a = L.s_a; P.s_b = L.s_b;
         P.rows = (int)g.intermediate; P.k = (int)g.hidden;
         P.x_routed = m->normed_h; P.x_shared = m->normed_h;
-        int rcp = launch_prefill<MODE_GATEUP>(st, P, dim3(g.intermediate / 64, ycap), smem_pf, qr, qs);
+        P.row_tiles = (int)g.intermediate / 64;
+        const size_t smem_gu = pf_smem(qr, qs);
+        int rcp = launch_prefill<MODE_GATEUP>(st, P, pf_grid, smem_gu, qr, qs);
         if (rcp) return rcp;
         if (mark_between >= 0) prof_mark(m, st, mark_between);
         int qrd = routed.present ? routed.down.quant : shared.down.quant;
@@ -343,7 +355,9 @@ int run_experts(xabe_moe* m, cudaStream_t st, const MlpWeights& routed, const Ml
         P.s_b = nullptr;
         P.rows = (int)g.hidden; P.k = (int)g.intermediate;
         P.x_routed = m->inter_routed; P.x_shared = m->inter_shared;
-        return launch_prefill<MODE_DOWN>(st, P, dim3(g.hidden / kPfTileM, ycap), smem_pf, qrd, qsd);
+        P.row_tiles = (int)g.hidden / kPfTileM;
+        const size_t smem_dn = pf_smem(qrd, qsd);
+        return launch_prefill<MODE_DOWN>(st, P, pf_grid, smem_dn, qrd, qsd);
     }
     StreamLaunch SL{};
     SL.top_k = L.top_k;
