@@ -142,6 +142,122 @@ __global__ void __launch_bounds__(128) k_router_logits(const float* __restrict__
 }
 
 // ---------------------------------------------------------------------------
+// Router logits for wide passes (hundreds of tokens and more): same values,
+// same order of additions as k_router_logits, arranged for the FMA pipe.
+// A CTA of 256 threads IS the 256 lanes of the reference kernel: thread v sums
+// j = v, v + 256, ... ascending.  It keeps sixteen expert rows in shared memory
+// (one bulk TMA copy) and walks its share of the tokens four at a time, so a
+// thread holds 64 accumulators and does 64 multiply-adds per 16 shared-memory
+// and 4 (prefetched) global loads.  The shuffle-down tree of each group of 32
+// lanes is then evaluated by ONE thread per (output, group) on a transposed
+// copy in shared memory, in the tree's exact pairing, and the eight group
+// totals are added in ascending order starting from +0: five shuffles and five
+// adds per accumulator per lane become 31 adds per output per group.
+// grid: (E / 16, token shares); block 256;
+// dynamic shared memory: 16 * hidden * 4 + 64 * 257 * 4 + 512 * 4 bytes.
+// ---------------------------------------------------------------------------
+constexpr int kRwExperts = 16;
+constexpr int kRwTokens = 4;
+constexpr int kRwOutputs = kRwExperts * kRwTokens;
+constexpr int kRwPitch = 257;  // odd: the tree threads read 32 rows at one column without bank conflicts
+
+__host__ __device__ inline size_t router_wide_smem(int hidden) {
+    return (size_t)kRwExperts * hidden * 4 + (size_t)kRwOutputs * kRwPitch * 4 + 512 * 4;
+}
+
+template <int NI>
+__global__ void __launch_bounds__(256, 1) k_router_logits_wide(const float* __restrict__ w,
+                                                               const float* __restrict__ x,
+                                                               const int* __restrict__ valid_tokens,
+                                                               int num_experts, const float* __restrict__ bias,
+                                                               float* __restrict__ logits,
+                                                               int* __restrict__ status) {
+    constexpr int hidden = NI * 256;
+    extern __shared__ __align__(128) float rw_smem[];
+    float* w_s = rw_smem;                                 // [16][hidden]
+    float* red = rw_smem + kRwExperts * hidden;           // [64][257]: accumulators, transposed
+    float* group_tot = red + kRwOutputs * kRwPitch;       // [64][8]
+    __shared__ __align__(8) uint64_t bar;
+    const int tid = threadIdx.x;
+    const int e0 = blockIdx.x * kRwExperts;
+    const int live = *valid_tokens;
+    const int tiles_total = (live + kRwTokens - 1) / kRwTokens;
+    const int tiles_per = (tiles_total + gridDim.y - 1) / gridDim.y;
+    const int tile0 = blockIdx.y * tiles_per;
+    const int tile1 = min(tiles_total, tile0 + tiles_per);
+    if (tile0 >= tile1) return;
+    if (tid == 0) {
+        const uint32_t bytes = (uint32_t)kRwExperts * hidden * 4u;
+        mbar_init(&bar, 1);
+        fence_mbar_init();
+        mbar_expect_tx(&bar, bytes);
+        tma_bulk_g2s(w_s, w + (size_t)e0 * hidden, bytes, &bar);
+    }
+    float xn[kRwTokens][NI];
+    auto load_tile = [&](int tile) {
+#pragma unroll
+        for (int u = 0; u < kRwTokens; ++u) {
+            const int t = min(tile * kRwTokens + u, live - 1);
+            const float* xr = x + (size_t)t * hidden + tid;
+#pragma unroll
+            for (int i = 0; i < NI; ++i) xn[u][i] = __ldg(xr + i * 256);
+        }
+    };
+    load_tile(tile0);
+    __syncthreads();
+    if (!__syncthreads_and(mbar_wait_bounded(&bar, 0, status))) return;
+    for (int tile = tile0; tile < tile1; ++tile) {
+        float xc[kRwTokens][NI];
+#pragma unroll
+        for (int u = 0; u < kRwTokens; ++u)
+#pragma unroll
+            for (int i = 0; i < NI; ++i) xc[u][i] = xn[u][i];
+        if (tile + 1 < tile1) load_tile(tile + 1);  // in flight during this tile's arithmetic
+        float acc[kRwExperts][kRwTokens];
+#pragma unroll
+        for (int e = 0; e < kRwExperts; ++e)
+#pragma unroll
+            for (int u = 0; u < kRwTokens; ++u) acc[e][u] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < NI; ++i) {
+#pragma unroll
+            for (int e = 0; e < kRwExperts; ++e) {
+                const float wv = w_s[e * hidden + i * 256 + tid];
+#pragma unroll
+                for (int u = 0; u < kRwTokens; ++u) acc[e][u] = fmaf(wv, xc[u][i], acc[e][u]);
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < kRwExperts; ++e)
+#pragma unroll
+            for (int u = 0; u < kRwTokens; ++u) red[(e * kRwTokens + u) * kRwPitch + tid] = acc[e][u];
+        __syncthreads();
+        // thread -> output o = tid % 64, lane groups g = tid / 64 and g + 4
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int o = tid & 63, g = (tid >> 6) + 4 * k;
+            const float* src = red + o * kRwPitch + g * 32;
+            float v[32];
+#pragma unroll
+            for (int l = 0; l < 32; ++l) v[l] = src[l];
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+                for (int l = 0; l < off; ++l) v[l] = v[l] + v[l + off];  // what lane l holds after shuffle-down by off
+            group_tot[o * 8 + g] = v[0];
+        }
+        __syncthreads();
+        if (tid < kRwOutputs) {
+            float total = 0.0f;
+#pragma unroll
+            for (int g = 0; g < 8; ++g) total += group_tot[tid * 8 + g];
+            const int e = e0 + (tid >> 2), t = tile * kRwTokens + (tid & 3);
+            if (t < live && e < num_experts) logits[(size_t)t * num_experts + e] = bias ? __fadd_rn(total, bias[e]) : total;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Routing: stable softmax over all experts, k selection passes by
 // (probability desc, index asc), renormalise over the selected k in selection
 // order (crates/xabe-kernels/src/moe/router.rs:32-76).  One warp per token.

@@ -216,7 +216,7 @@ template <int OFF> __device__ __forceinline__ void lds8_shifted(uint32_t al, uin
 }
 
 // One unpack pass: eight weight rows x one PAIR of chunks (128 contraction elements); lane
-// (rrow = lane / 4, j = lane % 4) serves row rrow and produces 32 weights (four 16-byte chunks).
+// (row rrow of the eight, j = lane % 4) produces 32 weights (four 16-byte chunks).
 //
 // Q6_K, half H of the row's superblock (element map of crates/xabe-kernels/src/quant.rs:175-198):
 // positions l = 8j..8j+7 of the four 32-element groups.  aj: word-aligned address of (superblock
@@ -445,7 +445,10 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L)
         // Per pair of chunks: this warp unpacks tile rows 8w..8w+7 (32 weights per lane) and every
         // thread starts up to four 16-byte copies of the B tiles (token columns tid/8 and tid/8 + 64
         // of both stages; columns the tile does not have are skipped, the tensor core never reads them).
-        const int rrow = lane >> 2, j = lane & 3;
+        // Lanes 4q..4q+3 serve one row; eight consecutive lanes (the unit a 128-bit shared store is
+        // processed in) serve rows r and r + 4, whose chunks fall into different halves of the
+        // swizzled 128-byte line, so the A-tile stores are free of bank conflicts.
+        const int rrow = ((lane >> 2) & 1) * 4 + (lane >> 3), j = lane & 3;
         const int trow = 8 * warp + rrow;
         const int r0 = tid >> 3, piece = tid & 7;
         const uint32_t stages32 = smem_u32(stages), raw32 = smem_u32(raw_ring);

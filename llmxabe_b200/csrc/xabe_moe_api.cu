@@ -458,6 +458,23 @@ int launch_router(xabe_moe* m, cudaStream_t st, const float* router, const float
     const auto& g = m->g;
     if (((uintptr_t)router & 15) != 0)
         return fail(XABE_ERR_INVALID_ARGUMENT, "router weights must be 16-byte aligned");
+    // wide passes: sixteen expert rows per CTA, the tokens shared out over the SMs
+    if (g.max_tokens >= 256 && g.num_experts % kRwExperts == 0 && (g.hidden == 2048 || g.hidden == 1024)) {
+        const size_t smem_w = router_wide_smem((int)g.hidden);
+        unsigned gx = g.num_experts / kRwExperts;
+        unsigned gy = (unsigned)m->sm_count / gx;
+        unsigned tiles = (g.max_tokens + kRwTokens - 1) / kRwTokens;
+        if (gy < 1) gy = 1;
+        if (gy > tiles) gy = tiles;
+        auto go_wide = [&](auto kern) -> int {
+            CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_w));
+            kern<<<dim3(gx, gy), 256, smem_w, st>>>(router, m->normed, m->valid_tokens, (int)g.num_experts, bias,
+                                                   m->logits, m->status);
+            CUDA_TRY(cudaGetLastError());
+            return XABE_OK;
+        };
+        return g.hidden == 2048 ? go_wide(k_router_logits_wide<8>) : go_wide(k_router_logits_wide<4>);
+    }
     dim3 block(128);
     size_t smem = (size_t)4 * g.hidden * sizeof(float);
     if (smem > 200 * 1024) return fail(XABE_ERR_UNSUPPORTED_GEOMETRY, "router rows do not fit shared memory");
