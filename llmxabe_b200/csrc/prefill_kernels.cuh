@@ -296,13 +296,17 @@ __device__ __forceinline__ void mbar_arrive32(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_pf(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// Bounded wait that also gives up when another warp of the CTA already has.
+// Bounded wait that also gives up when another warp of the CTA already has.  try_wait itself
+// suspends the thread for a hardware-defined slice, so the roles inside the per-pair pipeline poll
+// without sleeping (a sleeping waiter adds its sleep to every hand-over); only the epilogue warps,
+// which wait for a whole tile, back off.
+template <bool BACKOFF = false>
 __device__ __forceinline__ bool stream_wait_pf(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                                int* status) {
     for (uint32_t it = 0; it < kWaitLimit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 63u) == 63u && *abort_flag) return false;
-        if (it >= 16u) __nanosleep(it < 256u ? 32u : 256u);  // long waits back off and leave the issue slots to working warps
+        if (BACKOFF && it >= 16u) __nanosleep(it < 256u ? 32u : 256u);
     }
     *abort_flag = 1;
     if (status) atomicExch(status, STATUS_TMA_TIMEOUT);
@@ -383,8 +387,8 @@ __device__ __forceinline__ const uint8_t* pf_row_ptr(const PrefillLaunch& L, con
 
 // Shared-memory control block of the kernel.
 struct PfCtl {
-    uint64_t full_bar[kPfMaxStages];    // unpack warps + their B-tile copies -> MMA
-    uint64_t empty_bar[kPfMaxStages];   // MMA (tcgen05.commit) -> unpack warps
+    uint64_t full_bar[kPfMaxStages / 2];    // per PAIR of stages: unpack warps + their B-tile copies -> MMA
+    uint64_t empty_bar[kPfMaxStages / 2];   // MMA (tcgen05.commit) -> unpack warps
     uint64_t raw_full[kPfMaxRaw];       // bulk copies landed -> unpack warps
     uint64_t raw_empty[kPfMaxRaw];      // unpack warps -> loader
     uint64_t acc_full[kPfAccums];       // MMA (tcgen05.commit) -> epilogue
@@ -415,8 +419,8 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L)
 
     if (tid == 0) {
         ctl.abort_flag = 0;
-        for (int i = 0; i < kPfMaxStages; ++i) {
-            // one arrival per unpack warp (A tile written) + one per unpack thread (its B-tile copies landed)
+        for (int i = 0; i < kPfMaxStages / 2; ++i) {
+            // one arrival per unpack warp (A tiles written) + one per unpack thread (its B-tile copies landed)
             mbar_init(&ctl.full_bar[i], kPfUnpackWarps + kPfUnpackWarps * 32);
             mbar_init(&ctl.empty_bar[i], 1);
         }
@@ -512,12 +516,11 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L)
                     const uint32_t st0 = kc & (S - 1);  // even: the pair's stages are st0 and st0 + 1
                     if (kc >= (uint32_t)S) {
                         const uint32_t par = ((kc / S) & 1) ^ 1;
-                        ok = stream_wait_pf(&ctl.empty_bar[st0], par, abortp, L.status) &&
-                             stream_wait_pf(&ctl.empty_bar[st0 + 1], par, abortp, L.status);
+                        ok = stream_wait_pf(&ctl.empty_bar[st0 >> 1], par, abortp, L.status);
                         if (!ok) break;
                     }
                     const uint32_t a0 = stages32 + st0 * kPfStageBytes;
-                    const uint32_t fb = full32 + st0 * 8;
+                    const uint32_t fb = full32 + (st0 >> 1) * 8;
                     if (live0) {
                         cp_async16_off<0, 0>(a0 + boff, xp0);
                         cp_async16_off<kPfStageBytes, 128>(a0 + boff, xp0);
@@ -527,7 +530,6 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L)
                         cp_async16_off<kPfStageBytes + 8192, 128>(a0 + boff, xp1);
                     }
                     cp_async_arrive_noinc32(fb);
-                    cp_async_arrive_noinc32(fb + 8);
                     xp0 += 2 * kPfChunkK;
                     xp1 += 2 * kPfChunkK;
                     if (quant == QUANT_Q6K) {
@@ -539,10 +541,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L)
                     }
                     fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
                     __syncwarp();
-                    if (lane == 0) {
-                        mbar_arrive32(fb);
-                        mbar_arrive32(fb + 8);
-                    }
+                    if (lane == 0) mbar_arrive32(fb);
                     kc += 2;
                 }
                 __syncwarp();
@@ -577,19 +576,23 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L)
                     tc_fence_after();
                 }
                 const uint32_t tmem_d = tmem_base + acc * kPfTileN;
-                for (int c = 0; c < n_chunks && ok; ++c, ++kc) {
-                    const int st = kc & (S - 1);
-                    ok = stream_wait_pf(&ctl.full_bar[st], (kc / S) & 1, abortp, L.status);
+                for (int c = 0; c < n_chunks && ok; c += 2, kc += 2) {
+                    const int st = kc & (S - 1);  // the pair's stages are st and st + 1
+                    ok = stream_wait_pf(&ctl.full_bar[st >> 1], (kc / S) & 1, abortp, L.status);
                     if (!ok) break;
                     tc_fence_after();
-                    fence_proxy_async_smem();  // the B tile arrived by cp.async, not through the async proxy
+                    fence_proxy_async_smem();  // the B tiles arrived by cp.async, not through the async proxy
                     const uint32_t a_addr = smem_u32(stages + (size_t)st * kPfStageBytes);
-                    const uint64_t adesc = umma_smem_desc(a_addr);
-                    const uint64_t bdesc = umma_smem_desc(a_addr + kPfTileM * kPfChunkK * 2);
 #pragma unroll
-                    for (int k4 = 0; k4 < kPfChunkK / 16; ++k4)  // 32 bytes per K16 step inside the swizzle row
-                        umma_f16(tmem_d, adesc + 2 * k4, bdesc + 2 * k4, idesc, (c > 0 || k4 > 0) ? 1u : 0u);
-                    umma_commit(&ctl.empty_bar[st]);  // the stage is free once these MMAs have read it
+                    for (int half = 0; half < 2; ++half) {
+                        const uint64_t adesc = umma_smem_desc(a_addr + half * kPfStageBytes);
+                        const uint64_t bdesc = umma_smem_desc(a_addr + half * kPfStageBytes + kPfTileM * kPfChunkK * 2);
+#pragma unroll
+                        for (int k4 = 0; k4 < kPfChunkK / 16; ++k4)  // 32 bytes per K16 step inside the swizzle row
+                            umma_f16(tmem_d, adesc + 2 * k4, bdesc + 2 * k4, idesc,
+                                     (c > 0 || half > 0 || k4 > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&ctl.empty_bar[st >> 1]);  // the pair is free once these MMAs have read it
                 }
                 if (ok) umma_commit(&ctl.acc_full[acc]);
             }
@@ -654,7 +657,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L)
         for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++n) {
             const PfTile T = pf_tile(L, t, n_routed, valid);
             const uint32_t acc = n % kPfAccums;
-            ok = stream_wait_pf(&ctl.acc_full[acc], (n / kPfAccums) & 1, abortp, L.status);
+            ok = stream_wait_pf<true>(&ctl.acc_full[acc], (n / kPfAccums) & 1, abortp, L.status);
             if (!ok) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + acc * kPfTileN + ((uint32_t)(quad * 32) << 16);
