@@ -398,6 +398,11 @@ def run_ep(args) -> dict:
     barrier()
     clocks = sampler.stop()
     rows = sum(blk.last_plan.recv_counts)
+    # one more, untimed, pass with per-phase events (per layer, this rank)
+    blk.enable_phase_timing()
+    step(0)
+    phases = {k: v / n_layers for k, v in blk.phase_times_ms().items()}
+    blk._events = None
     if world > 1:
         t = torch.tensor([ms, float(rows)], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -414,7 +419,7 @@ def run_ep(args) -> dict:
                    "parallelism": f"ep{world} ({epr} experts/rank), NCCL all-to-all-v dispatch + combine",
                    "max_rows_received_by_a_rank_last_layer": rows,
                    "l2": "every layer has its own weights; a pass streams all of them"},
-        "clocks": clocks, "device_status": status,
+        "clocks": clocks, "device_status": status, "phase_ms_per_layer_rank0": phases,
         "roofline": {"bound": "tensor", "achieved": flops / (ms * 1e-3) / 1e12 / world, "unit": "TFLOP/s per GPU",
                      "peak": 1628.8, "frac": flops / (ms * 1e-3) / 1e12 / world / 1628.8, "traffic": None},
         "gpu_launches": None,

@@ -181,6 +181,40 @@ int xabe_moe_grouped_forward_partial(xabe_moe* m, void* stream, xabe_quant_tenso
                                      xabe_quant_tensor up, xabe_quant_tensor down,
                                      const float* hidden_states);
 
+/* grouped_forward_partial over caller-provided f16 rows ([n_rows][hidden],
+ * 16-byte aligned), read in place: row r is "token" r of the current dispatch
+ * tables.  No counterpart in the reference (whose multi-GPU model is one
+ * replica per device): expert parallelism uses it on the rank that owns the
+ * experts, directly on the buffer the dispatch exchange filled. */
+int xabe_moe_grouped_forward_partial_f16(xabe_moe* m, void* stream, xabe_quant_tensor gate,
+                                         xabe_quant_tensor up, xabe_quant_tensor down,
+                                         const void* rows_f16, size_t n_rows);
+
+/* Expert parallelism, sender side; no counterpart in the reference.
+ * ep_pack: for i < n_pairs, send_rows_f16[i] = the handle's normalised f16
+ * activation row of the token of flat (token, k) pair order[i];
+ * send_local_expert[i] = topk_ids[order[i]] % experts_per_rank;
+ * inverse[order[i]] = i.  `order` holds every live pair once, grouped by
+ * owner rank.
+ * ep_combine: gate_and_combine with the routed term taken from `back_rows`
+ * ([n_rows][hidden] f32, unweighted expert outputs in the order of `order`):
+ * routed[t] = sum over ascending k of topk_weights[t][k] *
+ * back_rows[inverse[t*k_per_token + k]], each product rounded before it is
+ * added, which is bit-identical to the one-GPU block. */
+/* ep_plan_pack: ep_pack with the send order taken from the dispatch tables the
+ * handle already holds (pairs sorted by expert are grouped by owner rank):
+ * fills the same three outputs for all live pairs and writes the number of
+ * pairs bound for each rank to send_counts[num_experts / experts_per_rank]
+ * (device memory).  No counterpart in the reference. */
+int xabe_moe_ep_plan_pack(xabe_moe* m, void* stream, int experts_per_rank, void* send_rows_f16,
+                          int32_t* send_local_expert, int32_t* inverse, int32_t* send_counts);
+int xabe_moe_ep_pack(xabe_moe* m, void* stream, const int64_t* order, size_t n_pairs, int experts_per_rank,
+                     void* send_rows_f16, int32_t* send_local_expert, int32_t* inverse);
+int xabe_moe_ep_combine(xabe_moe* m, void* stream, const float* back_rows, size_t n_rows,
+                        const int32_t* inverse, const float* shared_gate_inp, const float* residual,
+                        size_t residual_len, float* ffn_out, size_t ffn_out_len, float* l_out,
+                        size_t l_out_len);
+
 /* MoeKernels::grouped_forward (moe.rs:6345-6375): the above plus the
  * ascending-k sum of moe_reduce (moe.rs:4049-4065) into `out`
  * [max_tokens][hidden]. */

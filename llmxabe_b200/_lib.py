@@ -48,6 +48,10 @@ SYMBOLS = {
     "xabe_moe_route_and_dispatch": (_i, [_vp, _vp, _vp]),
     "xabe_moe_build_dispatch": (_i, [_vp, _vp, _vp, _vp]),
     "xabe_moe_gate_and_combine": (_i, [_vp, _vp, _vp, _vp, _sz, _vp, _sz, _vp, _sz]),
+    "xabe_moe_grouped_forward_partial_f16": (_i, [_vp, _vp, QuantTensorC, QuantTensorC, QuantTensorC, _vp, _sz]),
+    "xabe_moe_ep_pack": (_i, [_vp, _vp, _vp, _sz, _i, _vp, _vp, _vp]),
+    "xabe_moe_ep_plan_pack": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp]),
+    "xabe_moe_ep_combine": (_i, [_vp, _vp, _vp, _sz, _vp, _vp, _vp, _sz, _vp, _sz, _vp, _sz]),
     "xabe_moe_grouped_forward_partial": (_i, [_vp, _vp, QuantTensorC, QuantTensorC, QuantTensorC, _vp]),
     "xabe_moe_grouped_forward": (_i, [_vp, _vp, QuantTensorC, QuantTensorC, QuantTensorC, _vp, _vp]),
     "xabe_moe_shared_expert": (_i, [_vp, _vp, QuantTensorC, QuantTensorC, QuantTensorC, _vp, _vp]),

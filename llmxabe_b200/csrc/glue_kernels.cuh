@@ -715,6 +715,109 @@ __global__ void __launch_bounds__(256) k_gate_and_combine(
     l_out[base + j] = v + residual[base + j];
 }
 
+// ---------------------------------------------------------------------------
+// Expert parallelism, sender side.  (No counterpart in the reference, whose
+// multi-GPU model is one replica per device.)
+// k_ep_pack: row i of the send buffer is the f16 activation row of the token of
+// flat (token, k) pair order[i]; also the pair's expert id local to its owner
+// rank and the inverse map flat -> i.  grid: pairs, block 256.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) k_ep_pack(const long long* __restrict__ order, const __half* __restrict__ normed_h,
+                                                 const int* __restrict__ topk_ids, int top_k, int hidden,
+                                                 int experts_per_rank, __half* __restrict__ send_rows,
+                                                 int* __restrict__ send_local_expert, int* __restrict__ inverse) {
+    const int i = blockIdx.x;
+    const int flat = (int)order[i];
+    const uint4* src = (const uint4*)(normed_h + (size_t)(flat / top_k) * hidden);
+    uint4* dst = (uint4*)(send_rows + (size_t)i * hidden);
+    for (int u = threadIdx.x; u < hidden / 8; u += 256) dst[u] = __ldg(src + u);
+    if (threadIdx.x == 0) {
+        send_local_expert[i] = topk_ids[flat] % experts_per_rank;
+        inverse[flat] = i;
+    }
+}
+
+// k_ep_plan + k_ep_pack_sorted: the same send buffer straight from the dispatch
+// tables the handle already holds.  Pairs sorted by expert are also grouped by
+// owner rank (a rank owns a contiguous range of experts), so the send order is
+// the dispatch order with the padding slots dropped.
+// k_ep_plan: one block, one thread per expert: compact[e] = live pairs of the
+// experts before e; send_counts[r] = live pairs of rank r's experts.
+__global__ void k_ep_plan(int num_experts, int experts_per_rank, const int* __restrict__ expert_counts,
+                          int* __restrict__ compact, int* __restrict__ send_counts) {
+    extern __shared__ int cnt_s[];  // [num_experts + 1]
+    int e = threadIdx.x;
+    if (e < num_experts) cnt_s[e] = expert_counts[e];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int i = 0; i < num_experts; ++i) {
+            int c = cnt_s[i];
+            cnt_s[i] = run;
+            run += c;
+        }
+        cnt_s[num_experts] = run;
+    }
+    __syncthreads();
+    if (e <= num_experts) compact[e] = cnt_s[e];
+    int world = num_experts / experts_per_rank;
+    if (e < world) send_counts[e] = cnt_s[(e + 1) * experts_per_rank] - cnt_s[e * experts_per_rank];
+}
+// grid: sorted_capacity slots, block 256.
+__global__ void __launch_bounds__(256) k_ep_pack_sorted(
+    const int* __restrict__ sorted_token_ids, const int* __restrict__ expert_ids,
+    const int* __restrict__ expert_offsets, const int* __restrict__ compact,
+    const int* __restrict__ num_tokens_post_pad, const int* __restrict__ valid_tokens,
+    const __half* __restrict__ normed_h, int top_k, int hidden, int block_size, int experts_per_rank,
+    __half* __restrict__ send_rows, int* __restrict__ send_local_expert, int* __restrict__ inverse) {
+    const int s = blockIdx.x;
+    if (s >= *num_tokens_post_pad) return;
+    const int flat = sorted_token_ids[s];
+    if (flat >= *valid_tokens * top_k) return;  // padding slot
+    const int e = expert_ids[s / block_size];
+    const int i = compact[e] + (s - expert_offsets[e]);
+    const uint4* src = (const uint4*)(normed_h + (size_t)(flat / top_k) * hidden);
+    uint4* dst = (uint4*)(send_rows + (size_t)i * hidden);
+    for (int u = threadIdx.x; u < hidden / 8; u += 256) dst[u] = __ldg(src + u);
+    if (threadIdx.x == 0) {
+        send_local_expert[i] = e % experts_per_rank;
+        inverse[flat] = i;
+    }
+}
+
+// k_ep_combine: k_gate_and_combine with the routed term read through the
+// inverse map from the rows that came back from the owner ranks (unweighted):
+// routed = sum over ascending k of weight[t][k] * back[inverse[t*K + k]], each
+// product rounded to fp32 before it is added -- the value the one-GPU path
+// stores in `partial` and sums, so the result is bit-identical to it.
+__global__ void __launch_bounds__(256) k_ep_combine(
+    const float* __restrict__ w, const float* __restrict__ normed, const float* __restrict__ back,
+    const int* __restrict__ inverse, const float* __restrict__ topk_weights, const float* __restrict__ shexp,
+    const float* __restrict__ residual, const int* __restrict__ valid_tokens, int top_k, int hidden,
+    float* __restrict__ gate, float* __restrict__ routed, float* __restrict__ ffn_out, float* __restrict__ l_out) {
+    __shared__ float scratch[32];
+    int t = blockIdx.x;
+    if (t >= *valid_tokens) return;
+    size_t base = (size_t)t * hidden;
+    const float* xs = normed + base;
+    float s = 0.0f;
+    for (int j = threadIdx.x; j < hidden; j += 256) s = fmaf(w[j], xs[j], s);
+    s = block_reduce_sum_pinned(s, scratch);
+    float g = __fdiv_rn(1.0f, 1.0f + expf(-s));
+    if (threadIdx.x == 0 && blockIdx.y == 0) gate[t] = g;
+    int j = blockIdx.y * blockDim.x + threadIdx.x;
+    if (j >= hidden) return;
+    float r = 0.0f;
+    for (int k = 0; k < top_k; ++k) {
+        const int flat = t * top_k + k;
+        r = __fadd_rn(r, __fmul_rn(topk_weights[flat], back[(size_t)inverse[flat] * hidden + j]));
+    }
+    float v = fmaf(shexp[base + j], g, r);
+    routed[base + j] = r;
+    ffn_out[base + j] = v;
+    l_out[base + j] = v + residual[base + j];
+}
+
 // Dense FFN epilogue (crates/xabe-engine/src/block/dense_ffn.rs:234-251):
 // l_out = ffn_out + residual for the live rows.
 __global__ void k_add_residual(const float* __restrict__ ffn, const float* __restrict__ residual,

@@ -90,6 +90,8 @@ struct xabe_moe {
     bool force_tile_kernels = false;  // use the one-tile-per-CTA kernels even where the streaming ones apply
     float* normed = nullptr;
     __half* normed_h = nullptr;
+    int* ep_compact = nullptr;  // [num_experts + 1] live pairs before each expert (expert parallelism)
+    const __half* x_routed_override = nullptr;  // caller-provided f16 rows for one grouped pass
     float* logits = nullptr;
     __half* inter_routed = nullptr;
     __half* inter_shared = nullptr;
@@ -305,7 +307,8 @@ int run_experts(xabe_moe* m, cudaStream_t st, const MlpWeights& routed, const Ml
     L.s_b = shared.present ? (const uint8_t*)shared.up.dev_bytes : nullptr;
     L.rows = (int)g.intermediate;
     L.k = (int)g.hidden;
-    L.x_routed = m->normed_h;
+    const __half* x_routed = m->x_routed_override ? m->x_routed_override : m->normed_h;
+    L.x_routed = x_routed;
     L.x_shared = m->normed_h;
     L.inter_routed = m->inter_routed;
     L.inter_shared = m->inter_shared;
@@ -341,7 +344,7 @@ int run_experts(xabe_moe* m, cudaStream_t st, const MlpWeights& routed, const Ml
         };
         P.r_a = L.r_a; P.r_b = L.r_b; P.s_a = L.s_a; P.s_b = L.s_b;
         P.rows = (int)g.intermediate; P.k = (int)g.hidden;
-        P.x_routed = m->normed_h; P.x_shared = m->normed_h;
+        P.x_routed = x_routed; P.x_shared = m->normed_h;
         P.row_tiles = (int)g.intermediate / 64;
         const size_t smem_gu = pf_smem(qr, qs);
         int rcp = launch_prefill<MODE_GATEUP>(st, P, pf_grid, smem_gu, qr, qs);
@@ -378,7 +381,7 @@ int run_experts(xabe_moe* m, cudaStream_t st, const MlpWeights& routed, const Ml
     if (gu.ok && !m->force_tile_kernels) {
         SL.r_a = L.r_a; SL.r_b = L.r_b; SL.s_a = L.s_a; SL.s_b = L.s_b;
         SL.rows = L.rows; SL.k = L.k;
-        SL.x_routed = m->normed_h; SL.x_shared = m->normed_h;
+        SL.x_routed = x_routed; SL.x_shared = m->normed_h;
         SL.n_stages = gu.n_stages; SL.tile_cap = gu.tile_cap; SL.x_stride = gu.x_stride;
         int rcs = launch_stream<MODE_GATEUP>(m, st, SL, gu.smem, qr, qs);
         if (rcs) return rcs;
@@ -659,6 +662,7 @@ int xabe_moe_create(const xabe_moe_geometry* geometry, int device, int scope, fl
         A(dev_alloc(&m->chunk_hist, (size_t)m->n_chunks * E));
         A(dev_alloc(&m->expert_offsets, E + 1));
         A(dev_alloc(&m->expert_counts, E + 1));
+        A(dev_alloc(&m->ep_compact, E + 1));
         m->work_capacity = (T * K + 7) / 8 + (E < T * K ? E : T * K) + 1;
         A(dev_alloc(&m->work_items, (size_t)m->work_capacity * kWorkItemInts));
         A(dev_alloc(&m->n_work, 1));
@@ -683,8 +687,8 @@ void xabe_moe_destroy(xabe_moe* m) {
     if (!m) return;
     cudaSetDevice(m->device);
     void* dev[] = {m->valid_tokens, m->status, m->topk_ids, m->topk_weights, m->sorted_token_ids, m->expert_ids,
-                   m->num_tokens_post_pad, m->chunk_hist, m->expert_offsets, m->expert_counts, m->work_items, m->n_work, m->pf_items, m->pf_n_items,
-                   m->normed, m->normed_h, m->logits,
+                   m->num_tokens_post_pad, m->chunk_hist, m->expert_offsets, m->expert_counts, m->ep_compact, m->work_items, m->n_work, m->pf_items,
+                   m->pf_n_items, m->normed, m->normed_h, m->logits,
                    m->inter_routed, m->inter_shared, m->partial, m->routed, m->shexp, m->gate, m->stage_in,
                    m->stage_ffn, m->stage_out};
     for (void* p : dev)
@@ -776,6 +780,90 @@ int xabe_moe_grouped_forward_partial(xabe_moe* m, void* stream, xabe_quant_tenso
     r.up = up;
     r.down = down;
     return run_experts(m, st, r, MlpWeights{}, nullptr);
+}
+
+int xabe_moe_grouped_forward_partial_f16(xabe_moe* m, void* stream, xabe_quant_tensor gate, xabe_quant_tensor up,
+                                         xabe_quant_tensor down, const void* rows_f16, size_t n_rows) {
+    if (!m || !rows_f16) return fail(XABE_ERR_INVALID_ARGUMENT, "null argument to grouped_forward_partial_f16");
+    int rc = check_routed(m, "grouped_forward");
+    if (rc) return rc;
+    if ((rc = check_mlp(m, "routed", gate, up, down, m->g.num_experts))) return rc;
+    if (((uintptr_t)rows_f16 & 15) != 0)
+        return fail(XABE_ERR_INVALID_ARGUMENT, "f16 rows must be 16-byte aligned");
+    if (n_rows > m->g.max_tokens)
+        return fail(XABE_ERR_TOO_MANY_TOKENS, "%zu rows exceed max_tokens %u", n_rows, m->g.max_tokens);
+    MlpWeights r;
+    r.present = true;
+    r.gate = gate;
+    r.up = up;
+    r.down = down;
+    m->x_routed_override = (const __half*)rows_f16;
+    rc = run_experts(m, (cudaStream_t)stream, r, MlpWeights{}, nullptr);
+    m->x_routed_override = nullptr;
+    return rc;
+}
+
+int xabe_moe_ep_pack(xabe_moe* m, void* stream, const int64_t* order, size_t n_pairs, int experts_per_rank,
+                     void* send_rows_f16, int32_t* send_local_expert, int32_t* inverse) {
+    if (!m || !order || !send_rows_f16 || !send_local_expert || !inverse)
+        return fail(XABE_ERR_INVALID_ARGUMENT, "null argument to ep_pack");
+    int rc = check_routed(m, "ep_pack");
+    if (rc) return rc;
+    const auto& g = m->g;
+    if (n_pairs > (size_t)g.max_tokens * g.experts_per_token)
+        return fail(XABE_ERR_TOO_MANY_TOKENS, "%zu pairs exceed max_tokens * k", n_pairs);
+    if (experts_per_rank <= 0 || g.hidden % 8 != 0 || ((uintptr_t)send_rows_f16 & 15) != 0)
+        return fail(XABE_ERR_INVALID_ARGUMENT, "ep_pack: bad experts_per_rank, hidden or alignment");
+    if (n_pairs == 0) return XABE_OK;
+    k_ep_pack<<<(unsigned)n_pairs, 256, 0, (cudaStream_t)stream>>>(
+        (const long long*)order, m->normed_h, m->topk_ids, (int)g.experts_per_token, (int)g.hidden,
+        experts_per_rank, (__half*)send_rows_f16, send_local_expert, inverse);
+    CUDA_TRY(cudaGetLastError());
+    return XABE_OK;
+}
+
+int xabe_moe_ep_plan_pack(xabe_moe* m, void* stream, int experts_per_rank, void* send_rows_f16,
+                          int32_t* send_local_expert, int32_t* inverse, int32_t* send_counts) {
+    if (!m || !send_rows_f16 || !send_local_expert || !inverse || !send_counts)
+        return fail(XABE_ERR_INVALID_ARGUMENT, "null argument to ep_plan_pack");
+    int rc = check_routed(m, "ep_plan_pack");
+    if (rc) return rc;
+    const auto& g = m->g;
+    if (experts_per_rank <= 0 || g.num_experts % experts_per_rank != 0 || g.hidden % 8 != 0 ||
+        ((uintptr_t)send_rows_f16 & 15) != 0)
+        return fail(XABE_ERR_INVALID_ARGUMENT, "ep_plan_pack: bad experts_per_rank, hidden or alignment");
+    cudaStream_t st = (cudaStream_t)stream;
+    int threads = ((int)g.num_experts + 1 + 31) / 32 * 32;
+    k_ep_plan<<<1, threads, (g.num_experts + 1) * sizeof(int), st>>>((int)g.num_experts, experts_per_rank,
+                                                                     m->expert_counts, m->ep_compact, send_counts);
+    CUDA_TRY(cudaGetLastError());
+    k_ep_pack_sorted<<<(unsigned)m->sorted_capacity, 256, 0, st>>>(
+        m->sorted_token_ids, m->expert_ids, m->expert_offsets, m->ep_compact, m->num_tokens_post_pad,
+        m->valid_tokens, m->normed_h, (int)g.experts_per_token, (int)g.hidden, (int)g.block_size, experts_per_rank,
+        (__half*)send_rows_f16, send_local_expert, inverse);
+    CUDA_TRY(cudaGetLastError());
+    return XABE_OK;
+}
+
+int xabe_moe_ep_combine(xabe_moe* m, void* stream, const float* back_rows, size_t n_rows, const int32_t* inverse,
+                        const float* shared_gate_inp, const float* residual, size_t residual_len, float* ffn_out,
+                        size_t ffn_out_len, float* l_out, size_t l_out_len) {
+    if (!m || !back_rows || !inverse || !shared_gate_inp || !residual || !ffn_out || !l_out)
+        return fail(XABE_ERR_INVALID_ARGUMENT, "null argument to ep_combine");
+    int rc = check_routed(m, "ep_combine");
+    if (rc) return rc;
+    const auto& g = m->g;
+    size_t n = (size_t)g.max_tokens * g.hidden;
+    if (residual_len != n || ffn_out_len != n || l_out_len != n)
+        return fail(XABE_ERR_BUFFER_LENGTH, "ep_combine buffers must hold %zu floats", n);
+    if (n_rows > (size_t)g.max_tokens * g.experts_per_token)
+        return fail(XABE_ERR_TOO_MANY_TOKENS, "%zu rows exceed max_tokens * k", n_rows);
+    dim3 grid(g.max_tokens, (g.hidden + 255) / 256);
+    k_ep_combine<<<grid, 256, 0, (cudaStream_t)stream>>>(
+        shared_gate_inp, m->normed, back_rows, inverse, m->topk_weights, m->shexp, residual, m->valid_tokens,
+        (int)g.experts_per_token, (int)g.hidden, m->gate, m->routed, ffn_out, l_out);
+    CUDA_TRY(cudaGetLastError());
+    return XABE_OK;
 }
 
 int xabe_moe_grouped_forward(xabe_moe* m, void* stream, xabe_quant_tensor gate, xabe_quant_tensor up,

@@ -7,10 +7,12 @@ per device, docs/ARCHITECTURE.md:25-30); this module is the sharded form of
   1. every rank normalises, routes and picks the top-k for ITS tokens
   2. dispatch   all-to-all-v: each (token, k) pair sends the token's f16 row and
                 the local expert id to the rank that owns expert e  (e // E_local)
+     (meanwhile every rank runs the shared expert over its own tokens)
   3. the owner runs expert_mlp for every row it received (weight 1)
   4. combine    all-to-all-v back, in the pair order of the sender
   5. the sender multiplies by the routing weights, sums ascending k, adds the
-     gated shared expert and the residual
+     gated shared expert and the residual (one kernel, reading the returned rows
+     through the inverse of the send order)
 
 Per-row arithmetic on the owning rank is the same kernels with the same
 reduction order as on one GPU, and the weighting and the ascending-k sum stay
@@ -31,7 +33,7 @@ import torch.distributed as dist
 
 @dataclass
 class EpPlan:
-    order: torch.Tensor        # [pairs] flat (token, k) ids grouped by destination rank, ascending inside a rank
+    order: torch.Tensor | None # [pairs] flat (token, k) ids grouped by destination rank (None: order lives on the device)
     send_counts: list[int]     # pairs per destination rank
     recv_counts: list[int]     # rows per source rank
 
@@ -47,6 +49,17 @@ def make_plan(topk_ids: torch.Tensor, experts_per_rank: int, world: int, group=N
     recv = torch.empty_like(send)
     dist.all_to_all_single(recv, send, group=group)
     return EpPlan(order, [int(v) for v in send.tolist()], [int(v) for v in recv.tolist()])
+
+
+def exchange_counts(send_counts: torch.Tensor, total: int, world: int, group=None) -> EpPlan:
+    """The pair counts per destination live on the device; all_to_all_single wants host integers, so
+    this is the one host read-back of a layer (send and receive counts together)."""
+    if world == 1:
+        return EpPlan(None, [total], [total])
+    recv = torch.empty_like(send_counts)
+    dist.all_to_all_single(recv, send_counts, group=group)
+    both = torch.stack([send_counts, recv]).tolist()
+    return EpPlan(None, [int(v) for v in both[0]], [int(v) for v in both[1]])
 
 
 def all_to_all_rows(send: torch.Tensor, send_counts: list[int], recv_counts: list[int], world: int,
@@ -71,29 +84,58 @@ class EpMoeBlock:
         self.rank, self.world, self.group = rank, world, group
         self.experts_per_rank = num_experts // world
         self.last_plan: EpPlan | None = None
+        self._events = None
 
     def forward(self, residual: torch.Tensor, tokens: int, ffn_out: torch.Tensor, l_out: torch.Tensor) -> None:
-        b, K = self.backend, self.k
-        rows, ids, weights = b.front(residual, tokens)             # [T,H], [T,K] int32, [T,K] f32
-        plan = make_plan(ids[:tokens], self.experts_per_rank, self.world, self.group)
+        b = self.backend
+        mark = self._mark
+        mark("start")
+        ids, weights = b.front(residual, tokens)                    # [T,K] int32, [T,K] f32
+        mark("front")
+        # rows grouped by owner rank (by expert inside a rank), and how many go to each rank
+        send_rows, send_eid, inverse, send_counts = b.plan_pack(self.experts_per_rank, self.world)
+        b.shared()   # needs only this rank's tokens: keeps the GPU busy while the host reads the counts back
+        plan = exchange_counts(send_counts, tokens * self.k, self.world, self.group)
         self.last_plan = plan
-        token_of = plan.order // K
-        send_rows = rows[:tokens].index_select(0, token_of)
-        send_eid = (ids[:tokens].reshape(-1).to(torch.int64).index_select(0, plan.order)
-                    % self.experts_per_rank).to(torch.int32)
+        mark("plan_pack")
+        send_rows, send_eid = send_rows[:tokens * self.k], send_eid[:tokens * self.k]
         recv_rows = all_to_all_rows(send_rows, plan.send_counts, plan.recv_counts, self.world, self.group)
         recv_eid = all_to_all_rows(send_eid, plan.send_counts, plan.recv_counts, self.world, self.group)
+        mark("dispatch_exchange")
         out = b.experts(recv_rows, recv_eid)                        # [R,H] f32, unweighted
+        mark("experts")
         back = all_to_all_rows(out, plan.recv_counts, plan.send_counts, self.world, self.group)
-        w = weights[:tokens].reshape(-1).index_select(0, plan.order)
-        contrib = torch.empty((tokens * K, back.shape[1]), dtype=torch.float32, device=back.device)
-        contrib.index_copy_(0, plan.order, back * w[:, None])       # weight * value, as the down kernel stores it
-        b.finish(contrib, residual, tokens, ffn_out, l_out)
+        mark("combine_exchange")
+        b.finish(back, inverse, residual, tokens, ffn_out, l_out)  # weight, sum ascending k, shared expert, residual
+        mark("finish")
+
+    # -- optional per-phase device timing (CUDA events on the current stream), for the benchmark
+    def enable_phase_timing(self) -> None:
+        self._events = []
+
+    def _mark(self, name: str) -> None:
+        if self._events is None:
+            return
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        self._events.append((name, ev))
+
+    def phase_times_ms(self) -> dict:
+        """Total device time per phase since enable_phase_timing(); synchronises."""
+        torch.cuda.synchronize()
+        out: dict = {}
+        ev = self._events or []
+        for (_, e0), (name, e1) in zip(ev, ev[1:]):
+            if name != "start":
+                out[name] = out.get(name, 0.0) + e0.elapsed_time(e1)
+        self._events = []
+        return out
 
 
 class CudaEpBackend:
     """The product backend: two C-ABI handles per rank (front: routing, shared expert, combine;
-    back: the local experts over received rows, k = 1)."""
+    back: the local experts over received rows, k = 1).  Rows travel as f16 and are read in place by
+    the expert kernels; expert outputs travel as f32 and are weighted and summed by the sender."""
 
     def __init__(self, geometry, experts_per_rank: int, max_rows: int, front_weights, local_gate, local_up,
                  local_down, eps: float = 1e-6, exact_decode: bool = False):
@@ -112,9 +154,16 @@ class CudaEpBackend:
         self.local = (local_gate, local_up, local_down)  # QuantTensor stacks of this rank's experts
         dev = self.fb.normed.device
         self.max_rows = max_rows
+        pairs = geometry.max_tokens * geometry.experts_per_token
         self.ids_buf = torch.zeros(max_rows, 1, dtype=torch.int32, device=dev)
         self.ones = torch.ones(max_rows, 1, dtype=torch.float32, device=dev)
-        self.rows_f32 = torch.zeros(max_rows, geometry.hidden, dtype=torch.float32, device=dev)
+        self.send_rows = torch.empty(pairs, geometry.hidden, dtype=torch.float16, device=dev)
+        self.send_eid = torch.empty(pairs, dtype=torch.int32, device=dev)
+        self.inverse = torch.empty(pairs, dtype=torch.int32, device=dev)
+        self.send_counts = torch.zeros(geometry.num_experts, dtype=torch.int32, device=dev)
+        # the owner applies no weights: set them to one, once (no live rows yet, so the tables stay empty)
+        self.back_k.set_valid_tokens(0)
+        self.back_k.build_dispatch(self.ids_buf, self.ones)
 
     def set_layer(self, front_weights, local_gate, local_up, local_down) -> None:
         self.w = front_weights
@@ -126,7 +175,11 @@ class CudaEpBackend:
         k.rms_norm(residual, self.w.post_norm)
         k.router_logits(self.w.router, self.w.router_bias)
         k.route_and_dispatch()
-        return self.fb.normed.to(torch.float16), self.fb.topk_ids, self.fb.topk_weights
+        return self.fb.topk_ids, self.fb.topk_weights
+
+    def plan_pack(self, experts_per_rank, world):
+        self.front_k.ep_plan_pack(experts_per_rank, self.send_rows, self.send_eid, self.inverse, self.send_counts[:world])
+        return self.send_rows, self.send_eid, self.inverse, self.send_counts[:world]
 
     def experts(self, rows, local_expert):
         R = rows.shape[0]
@@ -136,13 +189,13 @@ class CudaEpBackend:
         k = self.back_k
         k.set_valid_tokens(R)
         self.ids_buf[:R, 0] = local_expert
-        self.rows_f32[:R] = rows.to(torch.float32)   # f16 -> f32 is exact; the kernels round back to the same f16
-        k.build_dispatch(self.ids_buf, self.ones)
-        k.grouped_forward_partial(self.local[0], self.local[1], self.local[2], self.rows_f32)
+        k.build_dispatch(self.ids_buf, None)
+        k.grouped_forward_partial_f16(self.local[0], self.local[1], self.local[2], rows)
         return self.bb.partial[:R]
 
-    def finish(self, contrib, residual, tokens, ffn_out, l_out):
+    def shared(self):
+        self.front_k.shared_expert(self.w.shared_gate, self.w.shared_up, self.w.shared_down)
+
+    def finish(self, back, inverse, residual, tokens, ffn_out, l_out):
         k = self.front_k
-        self.fb.partial[: contrib.shape[0]] = contrib
-        k.shared_expert(self.w.shared_gate, self.w.shared_up, self.w.shared_down)
-        k.gate_and_combine(self.w.shared_gate_inp, residual, ffn_out, l_out)
+        k.ep_combine(back, inverse, self.w.shared_gate_inp, residual, ffn_out, l_out)

@@ -163,6 +163,31 @@ class MoeKernels:
                                                     residual.data_ptr(), residual.numel(), ffn_out.data_ptr(),
                                                     ffn_out.numel(), l_out.data_ptr(), l_out.numel()))
 
+    # -- expert parallelism (no counterpart in the reference): see include/xabe_moe.h
+    def grouped_forward_partial_f16(self, gate: QuantTensor, up: QuantTensor, down: QuantTensor,
+                                    rows_f16: torch.Tensor, stream=None) -> None:
+        _check(_lib.lib().xabe_moe_grouped_forward_partial_f16(self._h, _stream_ptr(stream), gate._c(), up._c(),
+                                                               down._c(), rows_f16.data_ptr(), rows_f16.shape[0]))
+
+    def ep_pack(self, order: torch.Tensor, experts_per_rank: int, send_rows: torch.Tensor,
+                send_local_expert: torch.Tensor, inverse: torch.Tensor, stream=None) -> None:
+        _check(_lib.lib().xabe_moe_ep_pack(self._h, _stream_ptr(stream), order.data_ptr(), order.numel(),
+                                           experts_per_rank, send_rows.data_ptr(), send_local_expert.data_ptr(),
+                                           inverse.data_ptr()))
+
+    def ep_plan_pack(self, experts_per_rank: int, send_rows: torch.Tensor, send_local_expert: torch.Tensor,
+                     inverse: torch.Tensor, send_counts: torch.Tensor, stream=None) -> None:
+        _check(_lib.lib().xabe_moe_ep_plan_pack(self._h, _stream_ptr(stream), experts_per_rank,
+                                                send_rows.data_ptr(), send_local_expert.data_ptr(),
+                                                inverse.data_ptr(), send_counts.data_ptr()))
+
+    def ep_combine(self, back_rows: torch.Tensor, inverse: torch.Tensor, shared_gate_inp: torch.Tensor,
+                   residual: torch.Tensor, ffn_out: torch.Tensor, l_out: torch.Tensor, stream=None) -> None:
+        _check(_lib.lib().xabe_moe_ep_combine(self._h, _stream_ptr(stream), back_rows.data_ptr(),
+                                              back_rows.shape[0], inverse.data_ptr(), shared_gate_inp.data_ptr(),
+                                              residual.data_ptr(), residual.numel(), ffn_out.data_ptr(),
+                                              ffn_out.numel(), l_out.data_ptr(), l_out.numel()))
+
     # -- MoeKernels::grouped_forward_partial, moe.rs:5727
     def grouped_forward_partial(self, gate: QuantTensor, up: QuantTensor, down: QuantTensor,
                                 hidden_states: torch.Tensor | None = None, stream=None) -> None:

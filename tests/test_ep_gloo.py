@@ -48,8 +48,25 @@ class OracleBackend:
         logits = o.router_logits_dev(L.router, self.normed)
         if L.router_bias is not None:
             logits = logits + L.router_bias[None, :]
-        ids, w = o.route_batch(logits.astype(np.float32), L.top_k)
-        return t.from_numpy(self.normed), t.from_numpy(ids), t.from_numpy(w)
+        self.ids, self.w = o.route_batch(logits.astype(np.float32), L.top_k)
+        return t.from_numpy(self.ids), t.from_numpy(self.w)
+
+    def plan_pack(self, experts_per_rank, world):
+        t = self.torch
+        K = self.L.top_k
+        flat_ids = self.ids.reshape(-1)
+        order = np.lexsort((np.arange(flat_ids.size), flat_ids))  # by expert, ascending flat id inside an expert
+        rows = self.normed[order // K]
+        eid = (flat_ids[order] % experts_per_rank).astype(np.int32)
+        inverse = np.empty(order.size, np.int32)
+        inverse[order] = np.arange(order.size, dtype=np.int32)
+        counts = np.bincount(flat_ids // experts_per_rank, minlength=world).astype(np.int32)
+        return t.from_numpy(rows.copy()), t.from_numpy(eid), t.from_numpy(inverse), t.from_numpy(counts)
+
+    def shared(self):
+        o, L = self.o, self.L
+        self.shexp = o.mlp_forward_q(L.shared_gate, L.shared_quant, L.shared_up, L.shared_quant, L.shared_down,
+                                     L.shared_quant, L.hidden, L.inter, self.normed)
 
     def experts(self, rows, local_expert):
         out = np.empty((rows.shape[0], self.L.hidden), np.float32)
@@ -58,15 +75,15 @@ class OracleBackend:
             out[r] = self.o.expert_mlp(self.gate[e], self.up[e], self.down[e], rows[r].numpy())
         return self.torch.from_numpy(out)
 
-    def finish(self, contrib, residual, tokens, ffn_out, l_out):
+    def finish(self, back, inverse, residual, tokens, ffn_out, l_out):
         o, L = self.o, self.L
         K, H = L.top_k, L.hidden
-        c = contrib.numpy().reshape(tokens, K, H)
+        contrib = back.numpy()[inverse.numpy()] * self.w.reshape(-1)[:, None]  # weight * value, flat (token, k) order
+        c = contrib.reshape(tokens, K, H)
         routed = np.zeros((tokens, H), np.float32)
         for k in range(K):
             routed = routed + c[:, k]
-        shexp = o.mlp_forward_q(L.shared_gate, L.shared_quant, L.shared_up, L.shared_quant, L.shared_down,
-                                L.shared_quant, H, L.inter, self.normed)
+        shexp = self.shexp
         for t in range(tokens):
             g = np.float32(o.sigmoid(o.shared_gate_dot_dev(L.shared_gate_inp, self.normed[t])))
             v = routed[t] + shexp[t] * g
