@@ -244,10 +244,17 @@ int launch_stream(xabe_moe* m, cudaStream_t st, const StreamLaunch& L, uint32_t 
 // Wide passes only: the launch shape comes from max_tokens, as every other one.
 
 bool prefill_applies(const xabe_moe* m, int gateup_rows, int down_rows, int hidden, int inter) {
-    if (m->exact_decode || m->force_tile_kernels) return false;
+    if (m->force_tile_kernels) return false;
     if (const char* e = getenv("XABE_MOE_NO_PREFILL_KERNELS")) if (e[0] == '1') return false;
-    if (m->g.max_tokens < kPrefillMinTokens) return false;
-    return gateup_rows % 64 == 0 && down_rows % kPfTileM == 0 && hidden % kPfChunkK == 0 && inter % kPfChunkK == 0;
+    if (!(gateup_rows % 64 == 0 && down_rows % kPfTileM == 0 && hidden % kSpanElems == 0 && inter % kSpanElems == 0))
+        return false;
+    // Contractions too long for the decode kernels (the dense 27B block: 5120 and 17408) go through
+    // these kernels at every width; there the exact-decode switch has nothing to select.
+    const bool decode_kernels_serve = stream_shape(MODE_GATEUP, gateup_rows, hidden, XABE_QUANT_Q8_0, XABE_QUANT_Q8_0).ok &&
+                                      stream_shape(MODE_DOWN, down_rows, inter, XABE_QUANT_Q8_0, XABE_QUANT_Q8_0).ok;
+    if (!decode_kernels_serve) return true;
+    if (m->exact_decode) return false;
+    return m->g.max_tokens >= kPrefillMinTokens;
 }
 
 template <int MODE, int QR, int QS>
