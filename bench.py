@@ -36,6 +36,11 @@ WORKLOADS = {
     "prefill2048": (2048, 32, True),  # BASELINE config 2
     # BASELINE config 3 (expert-parallel stack, strong scaling): run_ep() below; tokens/layers from --ep-*
     "ep_prefill_stack": (16384, 64, True),
+    # BASELINE config 4 (dense 27B block, hidden 5120 / intermediate 17408, Q6_K): run_dense() below;
+    # under torchrun the intermediate dimension is sharded over the ranks (tensor parallel)
+    "dense1": (1, 64, False),
+    "dense64": (64, 64, False),
+    "dense4096": (4096, 64, False),
 }
 
 Q6K_EXPERT_BYTES = 3 * (512 * 2048 // 256) * 210   # 2,580,480
@@ -430,6 +435,128 @@ def run_ep(args) -> dict:
     return out if rank == 0 else {}
 
 
+def run_dense(args) -> dict:
+    """BASELINE config 4: the dense SwiGLU block of the 27B sibling, Q6_K.  One rank: DenseFfnBlock.
+    Several ranks: the intermediate dimension sharded (llmxabe_b200.tp), one all-reduce per layer;
+    strong scaling (the token batch is the same on every rank)."""
+    import torch
+    import torch.distributed as dist
+
+    from llmxabe_b200 import synth
+    from llmxabe_b200.moe import QuantTensor
+    from llmxabe_b200.tp import CudaTpBackend, TpDenseFfnBlock, shard_bounds
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    H, I = 5120, 17408
+    tokens = WORKLOADS[args.workload][0]
+    n_layers = max(args.layers, 2)
+    i0, i1 = shard_bounds(I, rank, world)
+    blocks = []
+    for li in range(n_layers):
+        gen = torch.Generator(device="cuda")
+        gen.manual_seed(4000 + li)           # every rank generates the full matrices and keeps its shard
+        full = [QuantTensor(synth._device_quant_bytes(torch, synth.Q6K, H * I, gen, "cuda"), synth.Q6K)
+                for _ in range(3)]
+        backend = CudaTpBackend(H, I, tokens, rank, world, torch.ones(H, device="cuda"), *full)
+        if world > 1:
+            backend.gate = QuantTensor(backend.gate.bytes.clone(), synth.Q6K)
+            backend.up = QuantTensor(backend.up.bytes.clone(), synth.Q6K)
+        else:
+            backend.down = full[2]
+        del full
+        blocks.append(TpDenseFfnBlock(backend, rank, world))
+    torch.cuda.empty_cache()
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(99)
+    x0 = torch.randn(tokens, H, device="cuda", generator=gen)
+    bufs = [torch.empty(tokens, H, device="cuda") for _ in range(2)]
+    ffn = torch.empty(tokens, H, device="cuda")
+
+    def step(i):
+        blocks[i % n_layers].forward(x0, tokens, ffn, bufs[i & 1])
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    barrier()
+    clocks = sampler.stop()
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0].item())
+    status = 0
+    for b in blocks:
+        status |= b.backend.k.device_status()
+    # end to end: host rows in, host rows out
+    hx = torch.randn(tokens, H).pin_memory()
+    hout = torch.empty(tokens, H).pin_memory()
+    dx = torch.empty(tokens, H, device="cuda")
+    barrier()
+    e0.record()
+    e2e_steps = max(3, min(args.steps, 20))
+    for i in range(e2e_steps):
+        dx.copy_(hx, non_blocking=True)
+        blocks[i % n_layers].forward(dx, tokens, ffn, bufs[0])
+        hout.copy_(bufs[0], non_blocking=True)
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t[0].item())
+    peak, peak_src = measured_peaks()
+    weight_bytes = 3 * (H * I // 256) * 210
+    alg_bytes = weight_bytes // world + tokens * H * 4 * 3
+    flops = 2.0 * tokens * 3 * H * I
+    hbm_bound = tokens <= 256
+    roof = ({"bound": "hbm", "achieved": alg_bytes / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+             "frac": alg_bytes / (ms * 1e-3) / 1e9 / peak, "traffic": None, "peak_source": peak_src,
+             "algorithmic_bytes_per_launch": alg_bytes, "note": "whole layer per rank (norm, gate/up, down, residual)"}
+            if hbm_bound else
+            {"bound": "tensor", "achieved": flops / world / (ms * 1e-3) / 1e12, "peak": 1628.8, "unit": "TFLOP/s",
+             "frac": flops / world / (ms * 1e-3) / 1e12 / 1628.8, "traffic": None,
+             "peak_source": "measured (MEASURED_PEAKS.json, burst)", "note": "whole layer per rank"})
+    out = {
+        "metric": "dense_layer_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None,
+        "dtype": "f16 x f16 -> f32 (tcgen05), Q6_K weights dequantised to f16 on the fly", "data": "synthetic",
+        "config": {"workload": args.workload, "tokens": tokens, "hidden": H, "intermediate": I, "quant": "Q6_K",
+                   "resident_layers": n_layers,
+                   "parallelism": f"tp{world} (intermediate {i1 - i0} of {I} per rank), NCCL all-reduce",
+                   "l2": f"layers rotate every step; a layer's shard is {weight_bytes // world >> 20} MiB (> 126 MB L2)"
+                         if weight_bytes // world > 126 << 20 else "layers rotate every step"},
+        "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": tokens * H * 4, "d2h_bytes_per_step": tokens * H * 4},
+        "gpu_launches": args.steps * 5, "clocks": clocks, "roofline": roof, "device_status": status,
+    }
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return out if rank == 0 else {}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -448,7 +575,12 @@ def main():
             return
         print(json.dumps(run_reference(args)), flush=True)
         return
-    out = run_ep(args) if args.workload == "ep_prefill_stack" else run_ours(args)
+    if args.workload == "ep_prefill_stack":
+        out = run_ep(args)
+    elif args.workload.startswith("dense"):
+        out = run_dense(args)
+    else:
+        out = run_ours(args)
     if out:
         print(json.dumps(out), flush=True)
 
