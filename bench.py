@@ -43,6 +43,10 @@ WORKLOADS = {
     "dense4096": (4096, 64, False),
 }
 
+# DRAM bytes (read + write) of the dominant kernel per launch, from the ncu captures summarised under
+# profiles/ (k_expert_stream_decode64.md, k_prefill_gemm_prefill2048.md); none taken for the others
+NCU_TRAFFIC_BYTES = {"decode64": 332.6e6 + 0.6e6, "prefill2048": 467.0e6 + 16.5e6}
+
 Q6K_EXPERT_BYTES = 3 * (512 * 2048 // 256) * 210   # 2,580,480
 ROUTER_BYTES = 256 * 2048 * 4
 VEC_BYTES = 2 * 2048 * 4                           # post-norm weight + shared-gate vector
@@ -278,6 +282,25 @@ def run_ours(args) -> dict:
     else:
         ms = ms_eager
     clocks = sampler.stop()
+    # distribution over repeats of the timed region (median and best), same method
+    reps = []
+    for _ in range(5):
+        reps.append(timed(replay, steps_g) if graph is not None else timed(step, args.steps))
+    reps.sort()
+    # calibration row: a pure streaming read of one resident layer's expert weights
+    from llmxabe_b200.moe import stream_read
+    sink = torch.zeros(1, dtype=torch.int32, device="cuda")
+    w0 = layers[0]
+    cal_tensors = [w0.gate_exps.bytes, w0.up_exps.bytes, w0.down_exps.bytes]
+    cal_bytes = sum(int(t.numel()) for t in cal_tensors)
+
+    def cal_step(i):
+        w = layers[i % args.layers]
+        for t in (w.gate_exps.bytes, w.up_exps.bytes, w.down_exps.bytes):
+            stream_read(t, sink)
+    for i in range(3):
+        cal_step(i)
+    cal_ms = timed(cal_step, max(8, min(args.steps, 40)))
     # the same region again with per-stage CUDA events, for the dominant kernel's duration
     block.moe.stage_profile(True)
     timed(step, min(args.steps, 256))
@@ -310,11 +333,15 @@ def run_ours(args) -> dict:
         "gpu_launches": launches_per_step * args.steps, "ms_per_step_eager": ms_eager, "cuda_graph": graph is not None,
         "clocks": clocks,
         "roofline": {"bound": "hbm", "kernel": "k_expert_gateup", "achieved": achieved, "peak": peak,
-                     "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                     "unit": "GB/s", "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+                     "peak_source": peak_src,
                      "algorithmic_bytes_per_launch": gu_bytes, "ms_per_launch": gateup_ms},
         "layer_roofline": {"algorithmic_bytes": layer_bytes, "achieved_gbs": layer_bytes / (ms * 1e-3) / 1e9,
                            "frac": layer_bytes / (ms * 1e-3) / 1e9 / peak},
         "stage_ms": {k: v / max(calls, 1) for k, v in stage_ms.items()},
+        "ms_per_step_repeats": {"median": reps[len(reps) // 2], "min": reps[0], "max": reps[-1], "n": len(reps)},
+        "calibration": {"what": "pure 128-bit streaming read of one layer's routed expert weights, no arithmetic",
+                        "bytes": cal_bytes, "ms": cal_ms, "gbs": cal_bytes / (cal_ms * 1e-3) / 1e9},
         "device_status": status,
     }
     if rank == 0 and world == 1 and not args.no_cpu:

@@ -306,6 +306,24 @@ int xabe_shared_expert_noalloc(void* stream, xabe_quant_tensor gate, xabe_quant_
                                xabe_quant_tensor down, int hidden, int intermediate,
                                const float* hidden_states, int tokens, float* out);
 
+/* MoeBlock::forward with a dtype tag on the residual stream: XABE_DTYPE_F32 is
+ * xabe_moe_block_forward; XABE_DTYPE_BF16 takes [max_tokens][hidden] bf16 rows
+ * (a prefill chunk as the layers before it produce it), widens the live rows
+ * exactly (a 16-bit shift) and proceeds as above; ffn_out and l_out stay f32,
+ * and the residual added into l_out is the widened value.  The reference's
+ * block takes f32 only (block/moe.rs:1091-1099). */
+#define XABE_DTYPE_F32 0
+#define XABE_DTYPE_BF16 1
+int xabe_moe_block_forward_typed(xabe_moe* m, void* stream, const xabe_moe_layer_weights* w,
+                                 const void* residual, int residual_dtype, size_t residual_len, int tokens,
+                                 float* ffn_out, size_t ffn_out_len, float* l_out, size_t l_out_len);
+
+/* Benchmark calibration, no counterpart in the reference's kernel set (its
+ * benchmark prints the same row, docs/BENCHMARKS.md:448-452): one pass of
+ * 128-bit coalesced loads over [dev_bytes, dev_bytes + n_bytes) with no
+ * arithmetic.  `sink` is 4 bytes of device memory (practically never written). */
+int xabe_stream_read(void* stream, const void* dev_bytes, size_t n_bytes, void* sink);
+
 #ifdef __cplusplus
 }
 #endif

@@ -65,6 +65,8 @@ SYMBOLS = {
     "xabe_moe_stage_profile": (_i, [_vp, _i]),
     "xabe_moe_stage_times": (_i, [_vp, _vp, C.POINTER(C.c_float), C.POINTER(_i)]),
     "xabe_dequantize": (_i, [_vp, QuantTensorC, _vp]),
+    "xabe_stream_read": (_i, [_vp, _vp, _sz, _vp]),
+    "xabe_moe_block_forward_typed": (_i, [_vp, _vp, _vp, _vp, _i, _sz, _i, _vp, _sz, _vp, _sz]),
     "xabe_shared_expert_noalloc": (_i, [_vp, QuantTensorC, QuantTensorC, QuantTensorC, _i, _i, _vp, _i, _vp]),
 }
 

@@ -828,6 +828,33 @@ __global__ void k_add_residual(const float* __restrict__ ffn, const float* __res
     for (int j = threadIdx.x; j < hidden; j += blockDim.x) l_out[base + j] = ffn[base + j] + residual[base + j];
 }
 
+// bf16 rows -> fp32 rows for the live tokens: the widening is a 16-bit shift,
+// exact (crates/xabe-kernels/src/quant.rs:1350-1358 pins the same for tensors).
+__global__ void k_rows_bf16_to_f32(const unsigned short* __restrict__ x, float* __restrict__ out,
+                                   const int* __restrict__ valid_tokens, int width) {
+    int row = blockIdx.x;
+    if (row >= *valid_tokens) return;
+    size_t base = (size_t)row * width;
+    for (int j = threadIdx.x; j < width; j += blockDim.x)
+        out[base + j] = __uint_as_float((unsigned)x[base + j] << 16);
+}
+
+// Calibration for the benchmark: a pure 128-bit coalesced streaming read of a
+// byte range, no arithmetic beyond the XOR that keeps the loads alive -- what
+// the card streams, as opposed to what a kernel achieves on the same bytes
+// (the reference prints the same row, docs/BENCHMARKS.md:448-452).
+__global__ void __launch_bounds__(256) k_stream_read(const uint4* __restrict__ src, size_t n_units,
+                                                     unsigned* __restrict__ sink) {
+    uint4 acc = make_uint4(0, 0, 0, 0);
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_units; i += stride) {
+        uint4 v = __ldg(src + i);
+        acc.x ^= v.x; acc.y ^= v.y; acc.z ^= v.z; acc.w ^= v.w;
+    }
+    unsigned r = acc.x ^ acc.y ^ acc.z ^ acc.w;
+    if (r == 0x9E3779B9u) *sink = r;  // practically never: the result is not needed
+}
+
 // ---------------------------------------------------------------------------
 // Standalone dequantisation, bit-identical to the scalar reference because
 // reconstruction is multiplications only: Q6_K (d * sc) * q

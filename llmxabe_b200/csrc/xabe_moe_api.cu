@@ -970,6 +970,30 @@ int xabe_moe_block_forward_host(xabe_moe* m, void* stream, const xabe_moe_layer_
     return XABE_OK;
 }
 
+int xabe_moe_block_forward_typed(xabe_moe* m, void* stream, const xabe_moe_layer_weights* w, const void* residual,
+                                 int residual_dtype, size_t residual_len, int tokens, float* ffn_out,
+                                 size_t ffn_out_len, float* l_out, size_t l_out_len) {
+    if (residual_dtype == XABE_DTYPE_F32)
+        return xabe_moe_block_forward(m, stream, w, (const float*)residual, residual_len, tokens, ffn_out,
+                                      ffn_out_len, l_out, l_out_len);
+    if (residual_dtype != XABE_DTYPE_BF16)
+        return fail(XABE_ERR_INVALID_ARGUMENT, "unknown activation dtype tag %d", residual_dtype);
+    if (!m || !residual) return fail(XABE_ERR_INVALID_ARGUMENT, "null argument to block_forward_typed");
+    const auto& g = m->g;
+    size_t n = (size_t)g.max_tokens * g.hidden;
+    if (residual_len != n)
+        return fail(XABE_ERR_BUFFER_LENGTH, "residual must hold %zu elements, holds %zu", n, residual_len);
+    if (tokens < 0 || (uint32_t)tokens > g.max_tokens)
+        return fail(XABE_ERR_TOO_MANY_TOKENS, "%d tokens exceeds the %u this block was sized for", tokens,
+                    g.max_tokens);
+    int rc = xabe_moe_set_valid_tokens(m, stream, tokens);
+    if (rc) return rc;
+    k_rows_bf16_to_f32<<<g.max_tokens, 256, 0, (cudaStream_t)stream>>>((const unsigned short*)residual, m->stage_in,
+                                                                      m->valid_tokens, (int)g.hidden);
+    CUDA_TRY(cudaGetLastError());
+    return xabe_moe_block_forward(m, stream, w, m->stage_in, n, tokens, ffn_out, ffn_out_len, l_out, l_out_len);
+}
+
 int xabe_dense_ffn_block_forward(xabe_moe* m, void* stream, const float* post_norm, xabe_quant_tensor gate,
                                  xabe_quant_tensor up, xabe_quant_tensor down, const float* residual,
                                  size_t residual_len, int tokens, float* ffn_out, size_t ffn_out_len,
@@ -1033,6 +1057,17 @@ int xabe_moe_device_status(xabe_moe* m, void* stream, int* status_out) {
     *status_out = *m->h_status;
     if (*status_out != 0)
         return fail(XABE_ERR_DEVICE_STATUS, "a kernel's bounded wait ran out (device status %d)", *status_out);
+    return XABE_OK;
+}
+
+int xabe_stream_read(void* stream, const void* dev_bytes, size_t n_bytes, void* sink) {
+    if (!dev_bytes || !sink || ((uintptr_t)dev_bytes & 15) != 0)
+        return fail(XABE_ERR_INVALID_ARGUMENT, "stream_read: null or misaligned argument");
+    int dev = 0, sms = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    k_stream_read<<<sms * 8, 256, 0, (cudaStream_t)stream>>>((const uint4*)dev_bytes, n_bytes / 16, (unsigned*)sink);
+    CUDA_TRY(cudaGetLastError());
     return XABE_OK;
 }
 

@@ -282,6 +282,12 @@ def dequantize(t: QuantTensor, stream=None) -> torch.Tensor:
     return out
 
 
+def stream_read(data: torch.Tensor, sink: torch.Tensor, stream=None) -> None:
+    """Benchmark calibration: one pure streaming read of `data`'s bytes (see include/xabe_moe.h)."""
+    _check(_lib.lib().xabe_stream_read(_stream_ptr(stream), data.data_ptr(), data.numel() * data.element_size(),
+                                       sink.data_ptr()))
+
+
 def shared_expert_noalloc(gate: QuantTensor, up: QuantTensor, down: QuantTensor, hidden: int, intermediate: int,
                           hidden_states: torch.Tensor, tokens: int, out: torch.Tensor, stream=None) -> None:
     """Shared-expert MLP for callers that cannot allocate device memory (no handle, static scratch).
@@ -391,8 +397,17 @@ class MoeBlock:
 
     def forward(self, w: MoeLayerWeights, residual: torch.Tensor, tokens: int, ffn_out: torch.Tensor,
                 l_out: torch.Tensor, stream=None) -> None:
-        """block/moe.rs:1091-1329.  All three buffers are [max_tokens][hidden] float32 on the device."""
+        """block/moe.rs:1091-1329.  All three buffers are [max_tokens][hidden] on the device; ffn_out and
+        l_out float32; the residual float32 (as in the reference) or bfloat16 (widened exactly inside)."""
         wc = w._c()
+        if residual.dtype == torch.bfloat16:
+            _check(_lib.lib().xabe_moe_block_forward_typed(self.moe._h, _stream_ptr(stream), C.byref(wc),
+                                                           residual.data_ptr(), 1, residual.numel(), tokens,
+                                                           ffn_out.data_ptr(), ffn_out.numel(), l_out.data_ptr(),
+                                                           l_out.numel()))
+            return
+        if residual.dtype != torch.float32:
+            raise InvalidArgument(f"residual must be float32 or bfloat16, got {residual.dtype}")
         _check(_lib.lib().xabe_moe_block_forward(self.moe._h, _stream_ptr(stream), C.byref(wc),
                                                  residual.data_ptr(), residual.numel(), tokens,
                                                  ffn_out.data_ptr(), ffn_out.numel(), l_out.data_ptr(),
