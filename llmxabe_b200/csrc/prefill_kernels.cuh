@@ -31,6 +31,8 @@
 // Every wait is bounded; TMEM is freed on every exit path.
 #pragma once
 
+#include <cuda.h>  // CUtensorMap (types only; the encoder is looked up at run time)
+
 #include "common.cuh"
 #include "glue_kernels.cuh"
 
@@ -39,7 +41,8 @@ namespace xabe {
 constexpr int kPfTileM = 128;       // weight rows per tile (TMEM lanes)
 constexpr int kPfTileN = 128;       // token columns per tile
 constexpr int kPfChunkK = 64;       // contraction elements per stage (one 128-byte swizzle row of f16)
-constexpr int kPfStageBytes = 2 * kPfTileM * kPfChunkK * 2;  // A tile + B tile, 16 KB each
+constexpr int kPfTileBytes = kPfTileM * kPfChunkK * 2;        // one A or B chunk tile: 16 KB
+constexpr int kPfStageBytes = 2 * kPfTileBytes;                // A tile + B tile
 constexpr int kPfUnpackWarps = 16;
 constexpr int kPfWarpMma = 16;
 constexpr int kPfWarpLoad = 17;     // two loader warps
@@ -81,6 +84,11 @@ struct PrefillLaunch {
     int n_raw;       // raw slots
     int slot_bytes;  // 128 * the larger raw pitch of the formats in this launch
     int row_tiles;   // tiles along the weight rows: gate/up rows / 64, down rows / 128
+    int item_cols;   // token columns per item: 128, or 512 for k_prefill_gemm_wide
+    int n_b_units;   // k_prefill_gemm_wide: depth of the B ring
+    // k_prefill_gemm_wide: 2-D tiled maps ([rows][k] f16, box 64 x 128, 128-byte swizzle) of the routed
+    // and the shared activation rows; a routed item's columns are CONSECUTIVE rows of its source
+    CUtensorMap tm_routed, tm_shared;
     int max_tokens;
 };
 
@@ -223,7 +231,7 @@ template <int OFF> __device__ __forceinline__ void lds8_shifted(uint32_t al, uin
 // + 8j), sh its distance in bits to the true start; ps: superblock + 192 + j/2; d: the super-scale
 // times 256.  Group g goes to chunk (g % 2) * 4 + j of stage g / 2: `dst` is the lane's row and
 // chunk j in the first stage's A tile (swizzle applied); chunk 4 + j is dst ^ 64.
-template <int H>
+template <int H, int OFF2 = kPfStageBytes>
 __device__ __forceinline__ void unpack_q6k(uint32_t aj, uint32_t sh, uint32_t ps, float d, uint32_t dst) {
     uint32_t ql0[2], ql1[2], qh[2];
     lds8_shifted<H * 64>(aj, sh, ql0);
@@ -249,8 +257,8 @@ __device__ __forceinline__ void unpack_q6k(uint32_t aj, uint32_t sh, uint32_t ps
         uint4 v = codes8_to_h8(c[0], c[1], 0x64206420u, ds2);
         if (g == 0) sts_v4<0>(dst, v);
         else if (g == 1) sts_v4<0>(dstx, v);
-        else if (g == 2) sts_v4<kPfStageBytes>(dst, v);
-        else sts_v4<kPfStageBytes>(dstx, v);
+        else if (g == 2) sts_v4<OFF2>(dst, v);  // OFF2: distance from the pair's first A tile to its second
+        else sts_v4<OFF2>(dstx, v);
     }
 }
 // Q8_0, pair H of the span: the lane's block is number 4H + j of the row's eight.  rj: the row's
@@ -315,13 +323,14 @@ __device__ __forceinline__ bool stream_wait_pf(uint64_t* bar, uint32_t parity, v
 
 // Token tiles of the routed experts for the prefill kernels: the live slots of
 // expert e are contiguous from expert_offsets[e]; they are cut into runs of up
-// to 128.  One block, one thread per expert.
+// to `item_cols` (128, or 512 for the kernel that keeps four accumulators).  One block, one thread
+// per expert.
 __global__ void k_build_prefill_items(int num_experts, const int* __restrict__ expert_offsets,
                                       const int* __restrict__ expert_counts, int* __restrict__ items,
-                                      int* __restrict__ n_items) {
+                                      int* __restrict__ n_items, int item_cols) {
     extern __shared__ int base_s[];
     int e = threadIdx.x;
-    if (e < num_experts) base_s[e] = (expert_counts[e] + kPfTileN - 1) / kPfTileN;
+    if (e < num_experts) base_s[e] = (expert_counts[e] + item_cols - 1) / item_cols;
     __syncthreads();
     if (threadIdx.x == 0) {
         int run = 0;
@@ -335,11 +344,11 @@ __global__ void k_build_prefill_items(int num_experts, const int* __restrict__ e
     __syncthreads();
     if (e < num_experts) {
         int count = expert_counts[e], start = expert_offsets[e];
-        for (int i = 0; i * kPfTileN < count; ++i) {
+        for (int i = 0; i * item_cols < count; ++i) {
             int* it = items + (size_t)(base_s[e] + i) * kPfItemInts;
             it[0] = e;
-            it[1] = start + i * kPfTileN;
-            it[2] = min(kPfTileN, count - i * kPfTileN);
+            it[1] = start + i * item_cols;
+            it[2] = min(item_cols, count - i * item_cols);
             it[3] = 0;
         }
     }
@@ -361,8 +370,8 @@ __device__ __forceinline__ PfTile pf_tile(const PrefillLaunch& L, int t, int n_r
         T.ncols = __ldg(it + 2);
     } else {
         T.expert = 0;
-        T.first = (y - n_routed) * kPfTileN;
-        T.ncols = min(kPfTileN, valid - T.first);
+        T.first = (y - n_routed) * L.item_cols;
+        T.ncols = min(L.item_cols, valid - T.first);
     }
     return T;
 }
@@ -409,7 +418,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int valid = *L.valid_tokens;
     const int n_routed = L.has_routed ? *L.n_items : 0;
-    const int n_shared = L.has_shared ? (valid + kPfTileN - 1) / kPfTileN : 0;
+    const int n_shared = L.has_shared ? (valid + L.item_cols - 1) / L.item_cols : 0;
     const int n_tiles = (n_routed + n_shared) * L.row_tiles;
     const int R = L.n_raw;
     const int n_spans = L.k / kSpanElems;

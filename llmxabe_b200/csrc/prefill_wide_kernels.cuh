@@ -1,0 +1,410 @@
+// The tcgen05 grouped GEMM for experts that meet many tokens: one unpacked pair of weight chunks
+// is multiplied against up to FOUR 128-column token tiles (four accumulators fill TMEM's 512
+// columns), so the dequantisation work per weight is shared by up to 512 tokens instead of 128.
+//
+// Same roles and the same arithmetic as k_prefill_gemm (prefill_kernels.cuh); what differs:
+//   * an item is one expert x up to 512 token columns; a tile is an item x one 128-row weight tile;
+//   * the A ring (two pairs of chunks) and the B ring (units of one pair x one column tile, two
+//     16 KB chunk tiles each) are separate.  B tiles come by TMA (2-D tiled, 128-byte swizzle,
+//     two copies per unit issued by one thread of a dedicated warp, as far ahead as the ring
+//     allows); that needs an item's token columns to be consecutive rows of the source, so the
+//     routed gate/up pass reads a copy of the activations permuted into dispatch order
+//     (k_permute_rows), the other passes read buffers that are in that order already;
+//     a first version whose unpack warps issued 16-byte copies for B between their unpack passes
+//     was slower than the one-accumulator kernel: B latency was exposed once per unit;
+//   * the four accumulator slots are handed over one by one: the epilogue warps drain a slot and
+//     release it, the next tile's MMAs into that slot may start while the others are drained;
+//     tiles with fewer column tiles use fewer slots, so small tiles still overlap fully.
+// Every wait is bounded; TMEM is freed on every exit path; no multicast, no clusters.
+#pragma once
+
+#include "prefill_kernels.cuh"
+
+namespace xabe {
+
+constexpr int kPfWideMaxCt = 4;             // column tiles (accumulators) per item
+constexpr int kPfWideItemCols = kPfWideMaxCt * kPfTileN;
+constexpr int kPfWideMaxBUnits = 3;
+constexpr int kPfWideRaw = 2;
+
+struct PfWideCtl {
+    uint64_t a_full[2], a_empty[2];                       // pair slots of the A ring
+    uint64_t b_full[kPfWideMaxBUnits], b_empty[kPfWideMaxBUnits];
+    uint64_t raw_full[kPfWideRaw], raw_empty[kPfWideRaw];
+    uint64_t acc_full[kPfWideMaxCt], acc_empty[kPfWideMaxCt];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+constexpr int kPfWideWarpB = kPfWarpEpi0 + 4;        // one more warp: the B loader
+constexpr int kPfWideThreads = 32 * (kPfWideWarpB + 1);
+
+// 2-D tiled TMA load: box {64 elements, 128 rows} at (x = first element, y = first row) -> dst
+// (1024-byte aligned shared memory); completes `bytes` on the mbarrier.  x * 2 bytes is a multiple
+// of 16 for every x this kernel uses (multiples of 64).
+__device__ __forceinline__ void tma_load_tile_2d(uint32_t dst, const CUtensorMap* tm, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            dst),
+        "l"((uint64_t)tm), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx32(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+// Activation rows in dispatch order: slot s of the sorted table gets the f16 row of its token
+// (the reference permutes the same way before its grouped GEMM, moe.rs:5727-5760); padding slots
+// are skipped.  grid: sorted_capacity, block 256.
+__global__ void __launch_bounds__(256) k_permute_rows(const int* __restrict__ sorted_token_ids,
+                                                      const int* __restrict__ num_tokens_post_pad,
+                                                      const int* __restrict__ valid_tokens, int top_k, int hidden,
+                                                      const __half* __restrict__ x, __half* __restrict__ x_sorted) {
+    const int s = blockIdx.x;
+    if (s >= *num_tokens_post_pad) return;
+    const int flat = sorted_token_ids[s];
+    if (flat >= *valid_tokens * top_k) return;
+    const uint4* src = (const uint4*)(x + (size_t)(flat / top_k) * hidden);
+    uint4* dst = (uint4*)(x_sorted + (size_t)s * hidden);
+    for (int u = threadIdx.x; u < hidden / 8; u += 256) dst[u] = __ldg(src + u);
+}
+
+// grid: one CTA per SM (or fewer); block kPfThreads.
+template <int MODE, int QR, int QS>
+__global__ void __launch_bounds__(kPfWideThreads, 1) k_prefill_gemm_wide(const __grid_constant__ PrefillLaunch L) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) PfWideCtl ctl;
+    constexpr int kTile = kPfTileM * kPfChunkK * 2;  // one 16 KB A or B chunk tile
+    constexpr int kUnit = 2 * kTile;                 // a pair of chunk tiles
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int valid = *L.valid_tokens;
+    const int n_routed = L.has_routed ? *L.n_items : 0;
+    const int n_shared = L.has_shared ? (valid + L.item_cols - 1) / L.item_cols : 0;
+    const int n_tiles = (n_routed + n_shared) * L.row_tiles;
+    const int R = L.n_raw, NBU = L.n_b_units;
+    const int n_spans = L.k / kSpanElems;
+    uint8_t* a_ring = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t* b_ring = a_ring + 2 * kUnit;
+    uint8_t* raw_ring = b_ring + (size_t)NBU * kUnit;
+    volatile int* abortp = &ctl.abort_flag;
+
+    if (tid == 0) {
+        ctl.abort_flag = 0;
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&ctl.a_full[i], kPfUnpackWarps);
+            mbar_init(&ctl.a_empty[i], 1);
+        }
+        for (int i = 0; i < NBU; ++i) {
+            mbar_init(&ctl.b_full[i], 1);  // the B loader's expect_tx arrival; the two TMA copies complete the bytes
+            mbar_init(&ctl.b_empty[i], 1);
+        }
+        for (int i = 0; i < R; ++i) {
+            mbar_init(&ctl.raw_full[i], kPfLoadWarps * 32);
+            mbar_init(&ctl.raw_empty[i], kPfUnpackWarps);
+        }
+        for (int i = 0; i < kPfWideMaxCt; ++i) {
+            mbar_init(&ctl.acc_full[i], 1);
+            mbar_init(&ctl.acc_empty[i], 4);
+        }
+        fence_mbar_init();
+    }
+    if (warp == kPfWarpMma) {
+        tmem_alloc(&ctl.tmem_base, kPfWideMaxCt * kPfTileN);  // all 512 columns: four accumulators
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ctl.tmem_base;
+    const int G = gridDim.x;
+
+    if (warp < kPfUnpackWarps) {
+        // ------------------------------ unpack warps ------------------------------
+        const int rrow = ((lane >> 2) & 1) * 4 + (lane >> 3), j = lane & 3;
+        const int trow = 8 * warp + rrow;
+        const uint32_t a32 = smem_u32(a_ring), raw32 = smem_u32(raw_ring);
+        const uint32_t rowoff = (uint32_t)(warp * 1024 + rrow * 128);
+        const uint32_t dst6 = rowoff + (uint32_t)((j ^ rrow) << 4);
+        const uint32_t dst8 = rowoff + (uint32_t)((((j & 1) << 2) ^ rrow) << 4) + (uint32_t)(j >> 1) * kTile;
+        const uint32_t afull32 = smem_u32(&ctl.a_full[0]);
+        uint32_t pc = 0;                 // pairs since the kernel started
+        int slot = 0, rphase = 0;        // raw ring position
+        bool ok = true;
+        PfTile T{}, T1{};
+        if ((int)blockIdx.x < n_tiles) T = pf_tile(L, blockIdx.x, n_routed, valid);
+        for (int t = blockIdx.x; t < n_tiles && ok; t += G) {
+            if (t + G < n_tiles) T1 = pf_tile(L, t + G, n_routed, valid);  // in flight during this tile
+            const int quant = T.shared ? QS : QR;
+            const int pitch = pf_raw_pitch(quant);
+            const int span_bytes = span_bytes_of(quant);
+            const uint32_t rowlo =
+                (uint32_t)(uintptr_t)pf_row_ptr<MODE>(L, T, trow, (size_t)n_spans * span_bytes);
+            for (int s = 0; s < n_spans && ok; ++s) {
+                ok = stream_wait_pf(&ctl.raw_full[slot], rphase, abortp, L.status);
+                if (!ok) break;
+                const uint32_t rawrow =
+                    raw32 + (uint32_t)slot * L.slot_bytes + trow * pitch + ((rowlo + s * span_bytes) & 15u);
+                const uint32_t aj = (rawrow & ~3u) + 8 * j, sh = (rawrow & 2u) * 8, ps = rawrow + 192 + (j >> 1);
+                float d6 = 0.f;
+                if (quant == QUANT_Q6K)
+                    d6 = __half2float(__ushort_as_half((unsigned short)lds_u16<208>(rawrow))) * kPfWeightScale;
+                const uint32_t rj = rawrow + j * kQ8BlockBytes;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint32_t aslot = pc & 1;
+                    if (pc >= 2u) {
+                        ok = stream_wait_pf(&ctl.a_empty[aslot], ((pc >> 1) & 1) ^ 1, abortp, L.status);
+                        if (!ok) break;
+                    }
+                    const uint32_t a0 = a32 + aslot * kUnit;
+                    if (quant == QUANT_Q6K) {
+                        if (h == 0) unpack_q6k<0, kTile>(aj, sh, ps, d6, a0 + dst6);
+                        else unpack_q6k<1, kTile>(aj, sh, ps, d6, a0 + dst6);
+                    } else {
+                        if (h == 0) unpack_q8<0>(rj, a0 + dst8);
+                        else unpack_q8<1>(rj, a0 + dst8);
+                    }
+                    fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive32(afull32 + aslot * 8);
+                    ++pc;
+                }
+                __syncwarp();
+                if (ok && lane == 0) mbar_arrive_pf(&ctl.raw_empty[slot]);
+                if (++slot == R) {
+                    slot = 0;
+                    rphase ^= 1;
+                }
+            }
+            T = T1;
+        }
+    } else if (warp == kPfWideWarpB) {
+        // -------------------------------- B loader --------------------------------
+        // One thread: for every pair of chunks and every column tile of the item, two TMA copies
+        // (chunk k0 and k0 + 64, token rows first + 128 ct .. + 127) into the next unit of the B ring.
+        // Rows past the item's last column belong to a neighbour or are out of bounds (zero-filled);
+        // the tensor core is told the tile's width and their columns are never stored.
+        if (lane == 0) {
+            const int n_pairs = L.k / (2 * kPfChunkK);
+            const uint32_t b32 = smem_u32(b_ring), bfull32 = smem_u32(&ctl.b_full[0]);
+            int bslot = 0, bphase = 0;
+            bool ok = true, wrapped = false;
+            PfTile T{}, T1{};
+            if ((int)blockIdx.x < n_tiles) T = pf_tile(L, blockIdx.x, n_routed, valid);
+            for (int t = blockIdx.x; t < n_tiles && ok; t += G) {
+                if (t + G < n_tiles) T1 = pf_tile(L, t + G, n_routed, valid);  // in flight during this tile
+                const CUtensorMap* tm = T.shared ? &L.tm_shared : &L.tm_routed;
+                const int nct = (T.ncols + kPfTileN - 1) / kPfTileN;
+                for (int p = 0; p < n_pairs && ok; ++p) {
+                    for (int ct = 0; ct < nct && ok; ++ct) {
+                        if (wrapped) {
+                            ok = stream_wait_pf(&ctl.b_empty[bslot], bphase ^ 1, abortp, L.status);
+                            if (!ok) break;
+                        }
+                        const uint32_t bar = bfull32 + bslot * 8;
+                        const uint32_t dst = b32 + (uint32_t)bslot * kUnit;
+                        mbar_expect_tx32(bar, kUnit);
+                        tma_load_tile_2d(dst, tm, p * 2 * kPfChunkK, T.first + ct * kPfTileN, bar);
+                        tma_load_tile_2d(dst + kTile, tm, p * 2 * kPfChunkK + kPfChunkK, T.first + ct * kPfTileN, bar);
+                        if (++bslot == NBU) {
+                            bslot = 0;
+                            bphase ^= 1;
+                            wrapped = true;
+                        }
+                    }
+                }
+                T = T1;
+            }
+            // an abort elsewhere: give the copies this thread started time to land before the shared
+            // memory goes to the next CTA (a TMA copy completes within microseconds)
+            if (!ok)
+                for (int i = 0; i < 64; ++i) __nanosleep(1000);
+        }
+    } else if (warp == kPfWarpMma) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            const int n_pairs = L.k / (2 * kPfChunkK);
+            const uint32_t a32 = smem_u32(a_ring), b32 = smem_u32(b_ring);
+            uint32_t pc = 0;
+            int bslot = 0, bphase = 0;
+            uint32_t acc_base = 0, acc_used = 0, acc_par = 0;  // per-slot: used before / parity of the next wait
+            bool ok = true;
+            int ncols = (int)blockIdx.x < n_tiles ? pf_tile(L, blockIdx.x, n_routed, valid).ncols : 0;
+            for (int t = blockIdx.x; t < n_tiles && ok; t += G) {
+                const int nct = (ncols + kPfTileN - 1) / kPfTileN;
+                uint32_t idesc[kPfWideMaxCt];
+#pragma unroll
+                for (int ct = 0; ct < kPfWideMaxCt; ++ct) {
+                    int c = min(kPfTileN, ncols - ct * kPfTileN);
+                    idesc[ct] = umma_idesc_f16(kPfTileM, max(16, (c + 15) & ~15));
+                }
+                if (t + G < n_tiles) ncols = pf_tile(L, t + G, n_routed, valid).ncols;  // in flight during this tile
+                for (int p = 0; p < n_pairs && ok; ++p, ++pc) {
+                    const uint32_t aslot = pc & 1;
+                    ok = stream_wait_pf(&ctl.a_full[aslot], (pc >> 1) & 1, abortp, L.status);
+                    if (!ok) break;
+                    const uint32_t a_addr = a32 + aslot * kUnit;
+#pragma unroll
+                    for (int ct = 0; ct < kPfWideMaxCt; ++ct) {
+                        if (ct >= nct) break;
+                        const uint32_t as = (acc_base + ct) & 3u;
+                        if (p == 0 && (acc_used >> as & 1u)) {  // the slot's previous tile must have been drained
+                            ok = stream_wait_pf(&ctl.acc_empty[as], acc_par >> as & 1u, abortp, L.status);
+                            if (!ok) break;
+                            acc_par ^= 1u << as;
+                        }
+                        ok = stream_wait_pf(&ctl.b_full[bslot], bphase, abortp, L.status);
+                        if (!ok) break;
+                        tc_fence_after();
+                        fence_proxy_async_smem();  // the B tiles arrived by cp.async, not through the async proxy
+                        const uint32_t b_addr = b32 + (uint32_t)bslot * kUnit;
+                        const uint32_t tmem_d = tmem_base + as * kPfTileN;
+#pragma unroll
+                        for (int half = 0; half < 2; ++half) {
+                            const uint64_t adesc = umma_smem_desc(a_addr + half * kTile);
+                            const uint64_t bdesc = umma_smem_desc(b_addr + half * kTile);
+#pragma unroll
+                            for (int k4 = 0; k4 < kPfChunkK / 16; ++k4)
+                                umma_f16(tmem_d, adesc + 2 * k4, bdesc + 2 * k4, idesc[ct],
+                                         (p > 0 || half > 0 || k4 > 0) ? 1u : 0u);
+                        }
+                        umma_commit(&ctl.b_empty[bslot]);  // the unit is free once these MMAs have read it
+                        if (++bslot == NBU) {
+                            bslot = 0;
+                            bphase ^= 1;
+                        }
+                    }
+                    if (!ok) break;
+                    umma_commit(&ctl.a_empty[aslot]);
+                }
+                if (!ok) break;
+                for (int ct = 0; ct < nct; ++ct) {
+                    const uint32_t as = (acc_base + ct) & 3u;
+                    umma_commit(&ctl.acc_full[as]);
+                    acc_used |= 1u << as;
+                }
+                acc_base = (acc_base + nct) & 3u;
+            }
+        }
+    } else if (warp >= kPfWarpLoad && warp < kPfWarpEpi0) {
+        // -------------------------------- loaders --------------------------------
+        const int lw = warp - kPfWarpLoad, hw = lane >> 4, part = lane & 15;
+        const uint32_t raw32 = smem_u32(raw_ring), rawfull32 = smem_u32(&ctl.raw_full[0]);
+        int slot = 0, rphase = 0;
+        bool ok = true, wrapped = false;
+        PfTile T{}, T1{};
+        if ((int)blockIdx.x < n_tiles) T = pf_tile(L, blockIdx.x, n_routed, valid);
+        for (int t = blockIdx.x; t < n_tiles && ok; t += G) {
+            if (t + G < n_tiles) T1 = pf_tile(L, t + G, n_routed, valid);  // in flight during this tile
+            const int quant = T.shared ? QS : QR;
+            const uint32_t pitch = pf_raw_pitch(quant);
+            const uint32_t span_bytes = span_bytes_of(quant);
+            const size_t row_bytes = (size_t)n_spans * span_bytes;
+            const uint8_t* pg = pf_row_ptr<MODE>(L, T, 2 * lw + hw, row_bytes);
+            const uint8_t* pu = MODE == MODE_GATEUP ? pf_row_ptr<MODE>(L, T, 16 + 2 * lw + hw, row_bytes) : pg;
+            for (int s = 0; s < n_spans && ok; ++s) {
+                if (wrapped) {
+                    ok = stream_wait_pf(&ctl.raw_empty[slot], rphase ^ 1, abortp, L.status);
+                    if (!ok) break;
+                }
+                const uint32_t dst0 = raw32 + (uint32_t)slot * L.slot_bytes + (uint32_t)(2 * lw + hw) * pitch + part * 16;
+                const uint8_t* sg = pg + (size_t)s * span_bytes;
+                const uint8_t* su = pu + (size_t)s * span_bytes;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int wr = MODE == MODE_GATEUP ? (i >> 3) * 16 + 4 * (i & 3) : 4 * i;
+                    const uint8_t* p = ((MODE == MODE_GATEUP && (i & 4)) ? su : sg) + (size_t)wr * row_bytes;
+                    const uint32_t mis = (uint32_t)(uintptr_t)p & 15u;
+                    const uint32_t units = (mis + span_bytes + 15u) >> 4;
+                    const uint8_t* src = p - mis + part * 16;
+                    const uint32_t dst = dst0 + (uint32_t)(4 * i) * pitch;
+                    if ((uint32_t)part < units) cp_async16(dst, src, 16u);
+                    if ((uint32_t)part + 16u < units) cp_async16(dst + 256, src + 256, 16u);
+                }
+                cp_async_arrive_noinc32(rawfull32 + slot * 8);
+                if (++slot == R) {
+                    slot = 0;
+                    rphase ^= 1;
+                    wrapped = true;
+                }
+            }
+            T = T1;
+        }
+        asm volatile("cp.async.wait_all;" ::: "memory");
+    } else {
+        // ------------------------------- epilogue -------------------------------
+        const int quad = warp & 3;
+        const float inv = 1.0f / kPfWeightScale;
+        uint32_t acc_base = 0, acc_par = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < n_tiles && ok; t += G) {
+            const PfTile T = pf_tile(L, t, n_routed, valid);
+            const int nct = (T.ncols + kPfTileN - 1) / kPfTileN;
+            for (int ct = 0; ct < nct && ok; ++ct) {
+                const uint32_t as = (acc_base + ct) & 3u;
+                const int first = T.first + ct * kPfTileN;
+                const int ncols = min(kPfTileN, T.ncols - ct * kPfTileN);
+                ok = stream_wait_pf<true>(&ctl.acc_full[as], acc_par >> as & 1u, abortp, L.status);
+                if (!ok) break;
+                acc_par ^= 1u << as;
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + as * kPfTileN + ((uint32_t)(quad * 32) << 16);
+                for (int cb = 0; cb * 32 < ncols; ++cb) {
+                    uint32_t r[32];
+                    tmem_ld32(taddr + (uint32_t)(cb * 32), r);
+                    tmem_ld_wait();
+                    if ((cb + 1) * 32 >= ncols) {  // last read of this accumulator: hand it back before the stores
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_pf(&ctl.acc_empty[as]);
+                    }
+                    if (MODE == MODE_GATEUP) {
+                        const int out_row = T.bx * 64 + quad * 16 + (lane & 15);
+                        __half* dst_base = T.shared ? L.inter_shared : L.inter_routed;
+#pragma unroll
+                        for (int jj = 0; jj < 32; ++jj) {
+                            float mine = __uint_as_float(r[jj]) * inv;
+                            float other = __shfl_xor_sync(0xffffffffu, mine, 16);
+                            bool do_it = (lane < 16) == (jj < 16);
+                            int col = cb * 32 + jj;
+                            if (do_it && col < ncols) {
+                                float gv = lane < 16 ? mine : other;
+                                float uv = lane < 16 ? other : mine;
+                                float v = __fdiv_rn(gv, 1.0f + expf(-gv)) * uv;
+                                dst_base[(size_t)(first + col) * L.rows + out_row] = __float2half_rn(v);
+                            }
+                        }
+                    } else {
+                        const int out_row = T.bx * kPfTileM + quad * 32 + lane;
+                        int my_flat = 0;
+                        float my_wgt = 0.f;
+                        const int mycol = cb * 32 + lane;
+                        if (!T.shared && mycol < ncols) {
+                            my_flat = __ldg(L.sorted_token_ids + first + mycol);
+                            my_wgt = __ldg(L.topk_weights + my_flat);
+                        }
+#pragma unroll
+                        for (int jj = 0; jj < 32; ++jj) {
+                            const int col = cb * 32 + jj;
+                            const int flat = __shfl_sync(0xffffffffu, my_flat, jj);
+                            const float wgt = __shfl_sync(0xffffffffu, my_wgt, jj);
+                            if (col < ncols) {
+                                float v = __uint_as_float(r[jj]) * inv;
+                                if (T.shared) L.shexp[(size_t)(first + col) * L.rows + out_row] = v;
+                                else L.partial[(size_t)flat * L.rows + out_row] = wgt * v;
+                            }
+                        }
+                    }
+                }
+            }
+            acc_base = (acc_base + nct) & 3u;
+        }
+    }
+    // every thread of the CTA arrives here on every path, so TMEM is always returned
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kPfWarpMma) tmem_dealloc(tmem_base, kPfWideMaxCt * kPfTileN);
+}
+
+}  // namespace xabe

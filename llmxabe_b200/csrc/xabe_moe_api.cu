@@ -13,11 +13,14 @@
 #include "expert_kernels.cuh"
 #include "glue_kernels.cuh"
 #include "stream_kernels.cuh"
-#include "prefill_kernels.cuh"
+#include "prefill_wide_kernels.cuh"
 
 using namespace xabe;
 
 namespace {
+
+// Handles sized for this many tokens use k_prefill_gemm_wide (set from measurements).
+constexpr uint32_t kPrefillWideMinTokens = 1024;
 
 // Wide passes only take the tcgen05 prefill kernels; the launch shape comes from max_tokens.
 constexpr uint32_t kPrefillMinTokens = 512;
@@ -87,10 +90,13 @@ struct xabe_moe {
     int* pf_items = nullptr;    // token tiles for the tcgen05 prefill kernels
     int* pf_n_items = nullptr;
     uint64_t pf_capacity = 0;
+    int pf_item_cols = 128;     // token columns per item: 128 (k_prefill_gemm) or 512 (k_prefill_gemm_wide)
     bool force_tile_kernels = false;  // use the one-tile-per-CTA kernels even where the streaming ones apply
     float* normed = nullptr;
     __half* normed_h = nullptr;
     int* ep_compact = nullptr;  // [num_experts + 1] live pairs before each expert (expert parallelism)
+    __half* x_sorted = nullptr;  // activations in dispatch order (k_prefill_gemm_wide's routed gate/up source)
+    CUtensorMap tm_routed_gu{}, tm_routed_dn{}, tm_shared_gu{}, tm_shared_dn{};
     const __half* x_routed_override = nullptr;  // caller-provided f16 rows for one grouped pass
     float* logits = nullptr;
     __half* inter_routed = nullptr;
@@ -243,6 +249,38 @@ int launch_stream(xabe_moe* m, cudaStream_t st, const StreamLaunch& L, uint32_t 
 // ---- prefill (tcgen05) expert kernels ---------------------------------------
 // Wide passes only: the launch shape comes from max_tokens, as every other one.
 
+// cuTensorMapEncodeTiled, looked up through the runtime so that the library does not link libcuda.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+// [rows][k] f16 row-major, box 64 elements x 128 rows, 128-byte swizzle, out-of-bounds rows read as zero.
+int make_rows_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t k) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return fail(XABE_ERR_DRIVER, "cuTensorMapEncodeTiled is not available from this driver");
+    if (((uintptr_t)base & 15) != 0 || k % 64 != 0 || rows == 0)
+        return fail(XABE_ERR_INVALID_ARGUMENT, "tensor map source must be 16-byte aligned with k a multiple of 64");
+    cuuint64_t dims[2] = {k, rows};
+    cuuint64_t strides[1] = {k * 2};
+    cuuint32_t box[2] = {(cuuint32_t)kPfChunkK, (cuuint32_t)kPfTileN};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(XABE_ERR_DRIVER, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+    return XABE_OK;
+}
+
 bool prefill_applies(const xabe_moe* m, int gateup_rows, int down_rows, int hidden, int inter) {
     if (m->force_tile_kernels) return false;
     if (const char* e = getenv("XABE_MOE_NO_PREFILL_KERNELS")) if (e[0] == '1') return false;
@@ -258,20 +296,20 @@ bool prefill_applies(const xabe_moe* m, int gateup_rows, int down_rows, int hidd
 }
 
 template <int MODE, int QR, int QS>
-int launch_prefill_t(cudaStream_t st, const PrefillLaunch& L, dim3 grid, size_t smem) {
-    auto kern = k_prefill_gemm<MODE, QR, QS>;
+int launch_prefill_t(cudaStream_t st, const PrefillLaunch& L, dim3 grid, size_t smem, bool wide) {
+    auto kern = wide ? k_prefill_gemm_wide<MODE, QR, QS> : k_prefill_gemm<MODE, QR, QS>;
     CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, kPfThreads, smem, st>>>(L);
+    kern<<<grid, wide ? kPfWideThreads : kPfThreads, smem, st>>>(L);
     CUDA_TRY(cudaGetLastError());
     return XABE_OK;
 }
 template <int MODE>
-int launch_prefill(cudaStream_t st, const PrefillLaunch& L, dim3 grid, size_t smem, int qr, int qs) {
+int launch_prefill(cudaStream_t st, const PrefillLaunch& L, dim3 grid, size_t smem, int qr, int qs, bool wide) {
     if (qr == XABE_QUANT_Q6_K)
-        return qs == XABE_QUANT_Q6_K ? launch_prefill_t<MODE, QUANT_Q6K, QUANT_Q6K>(st, L, grid, smem)
-                                     : launch_prefill_t<MODE, QUANT_Q6K, QUANT_Q8_0>(st, L, grid, smem);
-    return qs == XABE_QUANT_Q6_K ? launch_prefill_t<MODE, QUANT_Q8_0, QUANT_Q6K>(st, L, grid, smem)
-                                 : launch_prefill_t<MODE, QUANT_Q8_0, QUANT_Q8_0>(st, L, grid, smem);
+        return qs == XABE_QUANT_Q6_K ? launch_prefill_t<MODE, QUANT_Q6K, QUANT_Q6K>(st, L, grid, smem, wide)
+                                     : launch_prefill_t<MODE, QUANT_Q6K, QUANT_Q8_0>(st, L, grid, smem, wide);
+    return qs == XABE_QUANT_Q6_K ? launch_prefill_t<MODE, QUANT_Q8_0, QUANT_Q6K>(st, L, grid, smem, wide)
+                                 : launch_prefill_t<MODE, QUANT_Q8_0, QUANT_Q8_0>(st, L, grid, smem, wide);
 }
 
 struct MlpWeights {
@@ -336,7 +374,9 @@ int run_experts(xabe_moe* m, cudaStream_t st, const MlpWeights& routed, const Ml
         P.status = m->status;
         P.max_tokens = (int)g.max_tokens;
         P.n_stages = kPfMaxStages;
-        // one CTA per SM walks the tiles; raw slots as many as fit beside the stages
+        P.item_cols = m->pf_item_cols;
+        const bool wide = m->pf_item_cols > kPfTileN;
+        // one CTA per SM walks the tiles; the rings take what fits beside each other
         dim3 pf_grid((unsigned)m->sm_count);
         auto pf_smem = [&](int q_routed, int q_shared) {
             int pitch = 0;
@@ -346,6 +386,11 @@ int run_experts(xabe_moe* m, cudaStream_t st, const MlpWeights& routed, const Ml
                 if (ps > pitch) pitch = ps;
             }
             P.slot_bytes = kPfTileM * pitch;
+            if (wide) {  // A ring 64 KB, two raw slots, B ring three units (two beside the longer Q8_0 rows)
+                P.n_raw = kPfWideRaw;
+                P.n_b_units = pitch == kPfRawPitchQ6K ? kPfWideMaxBUnits : 2;
+                return (size_t)1024 + (size_t)(2 + P.n_b_units) * 2 * kPfTileBytes + (size_t)P.n_raw * P.slot_bytes + 16;
+            }
             P.n_raw = pitch == kPfRawPitchQ6K ? kPfMaxRaw : 2;
             return (size_t)1024 + (size_t)P.n_stages * kPfStageBytes + (size_t)P.n_raw * P.slot_bytes + 16;
         };
@@ -354,7 +399,17 @@ int run_experts(xabe_moe* m, cudaStream_t st, const MlpWeights& routed, const Ml
         P.x_routed = x_routed; P.x_shared = m->normed_h;
         P.row_tiles = (int)g.intermediate / 64;
         const size_t smem_gu = pf_smem(qr, qs);
-        int rcp = launch_prefill<MODE_GATEUP>(st, P, pf_grid, smem_gu, qr, qs);
+        if (wide) {
+            P.tm_routed = m->tm_routed_gu;
+            P.tm_shared = m->tm_shared_gu;
+            if (routed.present) {  // activation rows in dispatch order, so that an item's columns are consecutive rows
+                k_permute_rows<<<(unsigned)m->sorted_capacity, 256, 0, st>>>(
+                    m->sorted_token_ids, m->num_tokens_post_pad, m->valid_tokens, (int)g.experts_per_token,
+                    (int)g.hidden, x_routed, m->x_sorted);
+                CUDA_TRY(cudaGetLastError());
+            }
+        }
+        int rcp = launch_prefill<MODE_GATEUP>(st, P, pf_grid, smem_gu, qr, qs, wide);
         if (rcp) return rcp;
         if (mark_between >= 0) prof_mark(m, st, mark_between);
         int qrd = routed.present ? routed.down.quant : shared.down.quant;
@@ -367,7 +422,11 @@ int run_experts(xabe_moe* m, cudaStream_t st, const MlpWeights& routed, const Ml
         P.x_routed = m->inter_routed; P.x_shared = m->inter_shared;
         P.row_tiles = (int)g.hidden / kPfTileM;
         const size_t smem_dn = pf_smem(qrd, qsd);
-        return launch_prefill<MODE_DOWN>(st, P, pf_grid, smem_dn, qrd, qsd);
+        if (wide) {
+            P.tm_routed = m->tm_routed_dn;
+            P.tm_shared = m->tm_shared_dn;
+        }
+        return launch_prefill<MODE_DOWN>(st, P, pf_grid, smem_dn, qrd, qsd, wide);
     }
     StreamLaunch SL{};
     SL.top_k = L.top_k;
@@ -526,7 +585,7 @@ int launch_route_and_dispatch(xabe_moe* m, cudaStream_t st, const float* logits)
         if (g.max_tokens >= kPrefillMinTokens) {  // few experts, many tokens: the prefill kernels still apply
             int threads = ((int)g.num_experts + 31) / 32 * 32;
             k_build_prefill_items<<<1, threads, hist_bytes, st>>>((int)g.num_experts, m->expert_offsets,
-                                                                  m->expert_counts, m->pf_items, m->pf_n_items);
+                                                                  m->expert_counts, m->pf_items, m->pf_n_items, m->pf_item_cols);
             CUDA_TRY(cudaGetLastError());
         }
         return XABE_OK;
@@ -553,7 +612,7 @@ int launch_route_and_dispatch(xabe_moe* m, cudaStream_t st, const float* logits)
     // Only the work list of the kernels that will run: the regime must be chosen before this call.
     if (prefill_applies(m, (int)g.intermediate, (int)g.hidden, (int)g.hidden, (int)g.intermediate)) {
         k_build_prefill_items<<<1, threads, hist_bytes, st>>>((int)g.num_experts, m->expert_offsets,
-                                                              m->expert_counts, m->pf_items, m->pf_n_items);
+                                                              m->expert_counts, m->pf_items, m->pf_n_items, m->pf_item_cols);
     } else {
         k_build_work<<<1, threads, hist_bytes, st>>>((int)g.num_experts, m->expert_offsets, m->expert_counts,
                                                      m->sorted_token_ids, m->topk_weights, m->work_items,
@@ -636,6 +695,17 @@ int xabe_moe_create(const xabe_moe_geometry* geometry, int device, int scope, fl
     xabe_moe* m = new (std::nothrow) xabe_moe();
     if (!m) return fail(XABE_ERR_DRIVER, "out of host memory");
     m->sm_count = prop.multiProcessorCount;
+    // Items of up to 512 token columns (four accumulators per unpacked weight pair, B tiles by TMA):
+    // measured faster only where every item is full and the contraction is long -- the dense block at
+    // prefill width (3.40 vs 3.77 ms per layer at 4096 tokens); with the routed experts the extra
+    // pass that permutes the activations costs more than the shared unpack work returns.
+    // XABE_MOE_PF_WIDE=0/1 overrides the choice (tuning aid, read when the handle is created).
+    m->pf_item_cols = (scope == XABE_SCOPE_SHARED_ONLY && g.max_tokens >= kPrefillWideMinTokens) ? kPfWideItemCols
+                                                                                                 : kPfTileN;
+    if (const char* e = getenv("XABE_MOE_PF_WIDE")) {
+        if (e[0] == '1') m->pf_item_cols = kPfWideItemCols;
+        if (e[0] == '0') m->pf_item_cols = kPfTileN;
+    }
     // debugging aid: XABE_MOE_FORCE_TILE_KERNELS=1 keeps the streaming kernels out of the way
     if (const char* e = getenv("XABE_MOE_FORCE_TILE_KERNELS")) m->force_tile_kernels = e[0] == '1';
     m->g = g;
@@ -678,6 +748,7 @@ int xabe_moe_create(const xabe_moe_geometry* geometry, int device, int scope, fl
         A(dev_alloc(&m->pf_n_items, 1));
         A(dev_alloc(&m->logits, T * E));
         A(dev_alloc(&m->inter_routed, (size_t)cap * I));
+        if (m->pf_item_cols > kPfTileN) A(dev_alloc(&m->x_sorted, (size_t)cap * H));
         A(dev_alloc(&m->partial, T * K * H));
         A(dev_alloc(&m->routed, T * H));
         A(dev_alloc(&m->gate, T));
@@ -685,6 +756,19 @@ int xabe_moe_create(const xabe_moe_geometry* geometry, int device, int scope, fl
     if (e != cudaSuccess) {
         xabe_moe_destroy(m);
         return fail(XABE_ERR_DRIVER, "CUDA driver error: %s (allocating MoE buffers)", cudaGetErrorString(e));
+    }
+    if (m->pf_item_cols > kPfTileN && H % kSpanElems == 0 && I % kSpanElems == 0) {
+        // the four activation sources of k_prefill_gemm_wide, all handle-owned: maps are made once
+        int rc = make_rows_map(&m->tm_shared_gu, m->normed_h, T, H);
+        if (!rc) rc = make_rows_map(&m->tm_shared_dn, m->inter_shared, T, I);
+        if (!rc && scope == XABE_SCOPE_ROUTED) {
+            rc = make_rows_map(&m->tm_routed_gu, m->x_sorted, cap, H);
+            if (!rc) rc = make_rows_map(&m->tm_routed_dn, m->inter_routed, cap, I);
+        }
+        if (rc) {
+            xabe_moe_destroy(m);
+            return rc;
+        }
     }
     *out = m;
     return XABE_OK;
@@ -696,7 +780,7 @@ void xabe_moe_destroy(xabe_moe* m) {
     void* dev[] = {m->valid_tokens, m->status, m->topk_ids, m->topk_weights, m->sorted_token_ids, m->expert_ids,
                    m->num_tokens_post_pad, m->chunk_hist, m->expert_offsets, m->expert_counts, m->ep_compact, m->work_items, m->n_work, m->pf_items,
                    m->pf_n_items, m->normed, m->normed_h, m->logits,
-                   m->inter_routed, m->inter_shared, m->partial, m->routed, m->shexp, m->gate, m->stage_in,
+                   m->inter_routed, m->inter_shared, m->x_sorted, m->partial, m->routed, m->shexp, m->gate, m->stage_in,
                    m->stage_ffn, m->stage_out};
     for (void* p : dev)
         if (p) cudaFree(p);
