@@ -148,6 +148,24 @@ __device__ __forceinline__ StreamPlan stream_plan(const StreamLaunch& L, int row
 }
 
 
+// it / S and it % S for the ring depths this kernel is launched with (2, 3 or 4) without an
+// integer division in the per-tile path.
+__device__ __forceinline__ void ring_pos(uint32_t it, int S, uint32_t& use, int& st) {
+    if (S == 4) {
+        use = it >> 2;
+        st = (int)(it & 3u);
+    } else if (S == 2) {
+        use = it >> 1;
+        st = (int)(it & 1u);
+    } else if (S == 3) {
+        use = __umulhi(it, 0xAAAAAAABu) >> 1;
+        st = (int)(it - 3u * use);
+    } else {
+        use = it / (uint32_t)S;
+        st = (int)(it - use * (uint32_t)S);
+    }
+}
+
 template <bool MIS>
 __device__ __forceinline__ uint32_t ldw(const uint8_t* p) {
     if (MIS) {  // p is 2 modulo 4
@@ -397,8 +415,9 @@ __global__ void __launch_bounds__(kStreamThreads, 1) k_expert_stream(StreamLaunc
             const int t_begin = run * plan.tiles_per_unit;
             const int t_end = min(plan.row_tiles, t_begin + plan.tiles_per_unit);
             for (int tile = t_begin; tile < t_end; ++tile, ++it) {
-                const int st = it % S;
-                const uint32_t use = it / S;
+                int st;
+                uint32_t use;
+                ring_pos(it, S, use, st);
                 if (use >= 1 && !stream_wait(&bars.empty[st], (use - 1) & 1, abortp, L.status)) return;
                 const size_t start = (row0 + (size_t)tile * ROWS_PER_TILE) * row_bytes;
                 const uint32_t tile_bytes = (uint32_t)ROWS_PER_TILE * row_bytes;
@@ -460,8 +479,10 @@ __global__ void __launch_bounds__(kStreamThreads, 1) k_expert_stream(StreamLaunc
         const int t_end = min(plan.row_tiles, t_begin + plan.tiles_per_unit);
         for (int tile = t_begin; tile < t_end; ++tile, ++it) {
             if ((int)(it % kStreamGroups) != gi) continue;
-            const int st = it % S;
-            if (!stream_wait(&bars.full[st], (it / S) & 1, abortp, L.status)) return;
+            int st;
+            uint32_t use;
+            ring_pos(it, S, use, st);
+            if (!stream_wait(&bars.full[st], use & 1, abortp, L.status)) return;
             const uint8_t* tb = smem + lay.stages + (uint32_t)st * stage_bytes +
                                 (uint32_t)((phase + (size_t)tile * ROWS_PER_TILE * row_bytes) & 15);
             float acc[4] = {0.f, 0.f, 0.f, 0.f};

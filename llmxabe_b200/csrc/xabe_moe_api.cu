@@ -528,7 +528,7 @@ int launch_router(xabe_moe* m, cudaStream_t st, const float* router, const float
     if (((uintptr_t)router & 15) != 0)
         return fail(XABE_ERR_INVALID_ARGUMENT, "router weights must be 16-byte aligned");
     // wide passes: sixteen expert rows per CTA, the tokens shared out over the SMs
-    if (g.max_tokens >= 256 && g.num_experts % kRwExperts == 0 && (g.hidden == 2048 || g.hidden == 1024)) {
+    if (g.max_tokens >= 32 && g.num_experts % kRwExperts == 0 && (g.hidden == 2048 || g.hidden == 1024)) {
         const size_t smem_w = router_wide_smem((int)g.hidden);
         unsigned gx = g.num_experts / kRwExperts;
         unsigned gy = (unsigned)m->sm_count / gx;
