@@ -352,7 +352,7 @@ def run_ours(args) -> dict:
                 "h2d_bytes_per_step": tokens * H * 4, "d2h_bytes_per_step": tokens * H * 4},
         "gpu_launches": launches_per_step * args.steps, "ms_per_step_eager": ms_eager, "cuda_graph": graph is not None,
         "clocks": clocks,
-        "roofline": {"bound": "hbm", "kernel": "k_expert_gateup", "achieved": achieved, "peak": peak,
+        "roofline": {"bound": "hbm", "kernel": "gate/up + SwiGLU launch (k_expert_stream<GATEUP>; k_prefill_gemm<GATEUP> from 512 tokens)", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
                      "peak_source": peak_src,
                      "algorithmic_bytes_per_launch": gu_bytes, "ms_per_launch": gateup_ms},
@@ -370,6 +370,15 @@ def run_ours(args) -> dict:
         out["cpu_baseline"] = {"value": tps, "unit": UNIT, "cores": threads, "kind": "port",
                                "sample": f"{sample} of {tokens} tokens x {steps} passes over layer 0 "
                                          f"({cms:.0f} ms per pass)"}
+        # the same code on one thread (the reference's scalar path is single-threaded), a smaller sample
+        from oracle import xabe_oracle as oracle
+        n1 = min(4, tokens)
+        x1 = xs[0][:n1].cpu().numpy()
+        oracle.moe_block_forward(layer, x1, dev_order=False, threads=1)
+        t0 = time.perf_counter()
+        oracle.moe_block_forward(layer, x1, dev_order=False, threads=1)
+        out["cpu_baseline"]["single_thread"] = {"value": n1 / (time.perf_counter() - t0), "unit": UNIT,
+                                                "sample": f"{n1} tokens, one pass, dequantisation included"}
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
