@@ -421,7 +421,11 @@ def run_ep(args) -> dict:
         local = [QuantTensor(synth._device_quant_bytes(torch, synth.Q6K, n, gen, "cuda"), front.gate_exps.quant)
                  for _ in range(3)]
         layers.append((front, local))
-    backend = CudaEpBackend(g, epr, max_rows, layers[0][0], *layers[0][1])
+    if args.ep_peer_memory:
+        from llmxabe_b200.ep import PeerMemoryEpBackend
+        backend = PeerMemoryEpBackend(g, epr, rank, world, layers[0][0], *layers[0][1])
+    else:
+        backend = CudaEpBackend(g, epr, max_rows, layers[0][0], *layers[0][1])
     blk = EpMoeBlock(backend, E, K, rank, world)
     gen = torch.Generator(device="cuda")
     gen.manual_seed(31 + rank)
@@ -477,7 +481,9 @@ def run_ep(args) -> dict:
         "data": "synthetic",
         "config": {"workload": "ep_prefill_stack", "tokens_global": tokens, "layers": n_layers, "experts": E,
                    "top_k": K, "hidden": H, "intermediate": I, "quant": "Q6_K experts, Q8_0 shared",
-                   "parallelism": f"ep{world} ({epr} experts/rank), NCCL all-to-all-v dispatch + combine",
+                   "parallelism": f"ep{world} ({epr} experts/rank), " +
+                                  ("peer-memory (NVLink) dispatch + combine, device-side counts and flags"
+                                   if args.ep_peer_memory else "NCCL all-to-all-v dispatch + combine"),
                    "max_rows_received_by_a_rank_last_layer": rows,
                    "l2": "every layer has its own weights; a pass streams all of them"},
         "clocks": clocks, "device_status": status, "phase_ms_per_layer_rank0": phases,
@@ -624,6 +630,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the timed CPU baseline")
     ap.add_argument("--ep-tokens", type=int, default=16384)
     ap.add_argument("--ep-layers", type=int, default=40)
+    ap.add_argument("--ep-peer-memory", action="store_true",
+                    help="exchange rows and results by peer stores over NVLink instead of NCCL all-to-alls")
     ap.add_argument("--no-graph", dest="graph", action="store_false", help="time eager launches instead of CUDA-graph replay")
     args = ap.parse_args()
     if args.impl == "reference":

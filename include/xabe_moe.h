@@ -306,6 +306,41 @@ int xabe_shared_expert_noalloc(void* stream, xabe_quant_tensor gate, xabe_quant_
                                xabe_quant_tensor down, int hidden, int intermediate,
                                const float* hidden_states, int tokens, float* out);
 
+/* Expert-parallel exchange over peer memory (NVLink) instead of a library
+ * all-to-all; no counterpart in the reference.  Every rank owns six buffers
+ * that the other ranks have mapped (CUDA IPC); entry r of each array is rank
+ * r's buffer as THIS process sees it (entry `rank` = the rank's own).
+ * G = world, C = cap = the most pairs one rank can send (its max_tokens x k):
+ *   rows      [G][C][hidden] f16   region s is written by rank s
+ *   eid       [G][C] int32         expert id local to the owner
+ *   meta      [G][2] int32         {rows rank s sent, their start in s's send order}
+ *   flag_in   [G] int32            rank s stores `step` once rows and meta are written
+ *   back      [C][hidden] f32      owners write results in this rank's send order
+ *   flag_back [G] int32            owner d stores `step` once its results are written
+ * `step` must grow by one per layer call (flags are never reset; start the
+ * buffers at zero).  Call order per layer: on the tokens' handle, after
+ * route_and_dispatch: ep_p2p_send; on the owner-side handle (k = 1, max_tokens
+ * = G*C): ep_p2p_receive -> build_dispatch(ids) -> grouped_forward_partial_f16
+ * (rows = this rank's `rows` buffer) -> ep_p2p_return; on the tokens' handle:
+ * ep_p2p_wait_results -> ep_combine(back).  Waits on other ranks are bounded: a
+ * timeout sets device status 3 and the step's output is meaningless. */
+typedef struct xabe_ep_peers {
+    void* rows[8];
+    void* eid[8];
+    void* meta[8];
+    void* flag_in[8];
+    void* back[8];
+    void* flag_back[8];
+} xabe_ep_peers;
+int xabe_moe_ep_p2p_send(xabe_moe* m, void* stream, int experts_per_rank, int world, int rank, int cap,
+                         const xabe_ep_peers* peers, int step, int32_t* inverse);
+int xabe_moe_ep_p2p_receive(xabe_moe* m, void* stream, int world, int rank, int cap, const xabe_ep_peers* peers,
+                            int step, int32_t* ids_out, void* result_dst);
+int xabe_moe_ep_p2p_return(xabe_moe* m, void* stream, int world, int rank, int cap, const xabe_ep_peers* peers,
+                           int step, const void* result_dst);
+int xabe_moe_ep_p2p_wait_results(xabe_moe* m, void* stream, int world, int rank, const xabe_ep_peers* peers,
+                                 int step);
+
 /* MoeBlock::forward with a dtype tag on the residual stream: XABE_DTYPE_F32 is
  * xabe_moe_block_forward; XABE_DTYPE_BF16 takes [max_tokens][hidden] bf16 rows
  * (a prefill chunk as the layers before it produce it), widens the live rows

@@ -10,6 +10,10 @@ from . import build as _build
 _LIB = None
 
 
+class EpPeersC(C.Structure):
+    _fields_ = [(n, C.c_void_p * 8) for n in ("rows", "eid", "meta", "flag_in", "back", "flag_back")]
+
+
 class QuantTensorC(C.Structure):
     _fields_ = [("dev_bytes", C.c_void_p), ("n_bytes", C.c_size_t), ("quant", C.c_int32)]
 
@@ -51,6 +55,10 @@ SYMBOLS = {
     "xabe_moe_grouped_forward_partial_f16": (_i, [_vp, _vp, QuantTensorC, QuantTensorC, QuantTensorC, _vp, _sz]),
     "xabe_moe_ep_pack": (_i, [_vp, _vp, _vp, _sz, _i, _vp, _vp, _vp]),
     "xabe_moe_ep_plan_pack": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp]),
+    "xabe_moe_ep_p2p_send": (_i, [_vp, _vp, _i, _i, _i, _i, _vp, _i, _vp]),
+    "xabe_moe_ep_p2p_receive": (_i, [_vp, _vp, _i, _i, _i, _vp, _i, _vp, _vp]),
+    "xabe_moe_ep_p2p_return": (_i, [_vp, _vp, _i, _i, _i, _vp, _i, _vp]),
+    "xabe_moe_ep_p2p_wait_results": (_i, [_vp, _vp, _i, _i, _vp, _i]),
     "xabe_moe_ep_combine": (_i, [_vp, _vp, _vp, _sz, _vp, _vp, _vp, _sz, _vp, _sz, _vp, _sz]),
     "xabe_moe_grouped_forward_partial": (_i, [_vp, _vp, QuantTensorC, QuantTensorC, QuantTensorC, _vp]),
     "xabe_moe_grouped_forward": (_i, [_vp, _vp, QuantTensorC, QuantTensorC, QuantTensorC, _vp, _vp]),

@@ -1,0 +1,150 @@
+// Expert-parallel exchange over peer memory (NVLink): rows are written straight into the owner
+// rank's receive regions, results straight back into the sender's buffer, counts and "done" flags
+// travel the same way -- no library collective and no host read-back on the data path.
+// (No counterpart in the reference, whose multi-GPU model is one replica per device.)
+//
+// Buffers, all of them ordinary device memory of one rank that the other ranks have mapped
+// (CUDA IPC), G = ranks, C = the most pairs one rank can send (its tokens x k):
+//   recv_rows [G][C][hidden] f16, recv_eid [G][C] int32   region s is written by rank s
+//   recv_meta [G][2] int32    {rows rank s sent here, where they start in rank s's send order}
+//   flag_in   [G] int32       rank s stores the step number once its rows and meta are written
+//   back_rows [C][hidden] f32 the owners write the results of this rank's pairs, in its send order
+//   flag_back [G] int32       owner d stores the step number once its results are written
+// Step numbers only grow, so nothing is ever reset.  Every wait is bounded: on a timeout the kernel
+// records STATUS_PEER_TIMEOUT and goes on (the step's output is then meaningless; the host reads
+// the status word).  Plain peer stores and loads only: no multimem, no multicast.
+#pragma once
+
+#include "common.cuh"
+
+namespace xabe {
+
+constexpr int STATUS_PEER_TIMEOUT = 3;
+constexpr int kEpMaxRanks = 8;
+constexpr uint32_t kPeerWaitLimit = 1u << 24;  // x 200 ns of sleep: several seconds
+
+struct EpPeers {
+    void* p[kEpMaxRanks];
+};
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Sender, one block, one thread per expert: compact[e] = live pairs of the experts before e;
+// rank_start[d] / send_counts[d] = where rank d's pairs start in the send order / how many.
+__global__ void k_ep_plan_ranks(int num_experts, int experts_per_rank, const int* __restrict__ expert_counts,
+                                int* __restrict__ compact, int* __restrict__ rank_start,
+                                int* __restrict__ send_counts) {
+    extern __shared__ int cnt_s[];  // [num_experts + 1]
+    int e = threadIdx.x;
+    if (e < num_experts) cnt_s[e] = expert_counts[e];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int i = 0; i < num_experts; ++i) {
+            int c = cnt_s[i];
+            cnt_s[i] = run;
+            run += c;
+        }
+        cnt_s[num_experts] = run;
+    }
+    __syncthreads();
+    if (e <= num_experts) compact[e] = cnt_s[e];
+    int world = num_experts / experts_per_rank;
+    if (e < world) {
+        rank_start[e] = cnt_s[e * experts_per_rank];
+        send_counts[e] = cnt_s[(e + 1) * experts_per_rank] - cnt_s[e * experts_per_rank];
+    }
+}
+
+// Sender: every live slot of the dispatch tables -> the owner's receive region of this rank.
+// grid: sorted_capacity, block 256.
+__global__ void __launch_bounds__(256) k_ep_push_rows(
+    const int* __restrict__ sorted_token_ids, const int* __restrict__ expert_ids,
+    const int* __restrict__ expert_offsets, const int* __restrict__ compact, const int* __restrict__ rank_start,
+    const int* __restrict__ num_tokens_post_pad, const int* __restrict__ valid_tokens,
+    const __half* __restrict__ normed_h, int top_k, int hidden, int block_size, int experts_per_rank, int me,
+    int cap, EpPeers peer_rows, EpPeers peer_eid, int* __restrict__ inverse) {
+    const int s = blockIdx.x;
+    if (s >= *num_tokens_post_pad) return;
+    const int flat = sorted_token_ids[s];
+    if (flat >= *valid_tokens * top_k) return;  // padding slot
+    const int e = expert_ids[s / block_size];
+    const int d = e / experts_per_rank;
+    const int i = compact[e] + (s - expert_offsets[e]);  // position in this rank's send order
+    const int j = i - rank_start[d];                     // position among the rows bound for rank d
+    const uint4* src = (const uint4*)(normed_h + (size_t)(flat / top_k) * hidden);
+    uint4* dst = (uint4*)((__half*)peer_rows.p[d] + ((size_t)me * cap + j) * hidden);
+    for (int u = threadIdx.x; u < hidden / 8; u += 256) dst[u] = __ldg(src + u);
+    if (threadIdx.x == 0) {
+        ((int*)peer_eid.p[d])[(size_t)me * cap + j] = e % experts_per_rank;
+        inverse[flat] = i;
+    }
+    __threadfence_system();
+}
+
+// Sender, after k_ep_push_rows on the same stream: thread d tells rank d how many rows it got and
+// where they sit in this rank's send order, then raises its flag there.
+__global__ void k_ep_signal_rows(int world, int me, const int* __restrict__ send_counts,
+                                 const int* __restrict__ rank_start, EpPeers peer_meta, EpPeers peer_flag_in,
+                                 int step) {
+    int d = threadIdx.x;
+    if (d >= world) return;
+    int* meta = (int*)peer_meta.p[d] + 2 * me;
+    meta[0] = send_counts[d];
+    meta[1] = rank_start[d];
+    __threadfence_system();
+    st_release_sys((int*)peer_flag_in.p[d] + me, step);
+}
+
+// One block, `world` threads: wait (bounded) until every flag has reached `step`.
+__global__ void k_ep_wait_flags(int world, const int* __restrict__ flags, int step, int* __restrict__ status) {
+    int s = threadIdx.x;
+    if (s >= world) return;
+    for (uint32_t it = 0; it < kPeerWaitLimit; ++it) {
+        if (ld_acquire_sys(flags + s) >= step) return;
+        __nanosleep(200);
+    }
+    atomicExch(status, STATUS_PEER_TIMEOUT);
+}
+
+// Owner: expert id of every receive slot (-1 where region s holds no row) and where the slot's
+// result goes: the sender's back_rows at (its start for this rank + j).  grid: ceil(G*C/256), block 256.
+__global__ void k_ep_fill_slots(int world, int cap, int hidden, const int* __restrict__ recv_meta,
+                                const int* __restrict__ recv_eid, EpPeers peer_back, int* __restrict__ ids,
+                                float** __restrict__ result_dst) {
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)world * cap) return;
+    int s = (int)(idx / cap), j = (int)(idx % cap);
+    int count = recv_meta[2 * s], start = recv_meta[2 * s + 1];
+    bool live = j < count;
+    ids[idx] = live ? recv_eid[idx] : -1;
+    result_dst[idx] = live ? (float*)peer_back.p[s] + (size_t)(start + j) * hidden : nullptr;
+}
+
+// Owner: copy each live slot's result row to its sender.  grid: G*C, block 256.
+__global__ void __launch_bounds__(256) k_ep_push_results(const float* __restrict__ partial,
+                                                         float* const* __restrict__ result_dst, int hidden) {
+    float* dst = result_dst[blockIdx.x];
+    if (!dst) return;
+    const uint4* src = (const uint4*)(partial + (size_t)blockIdx.x * hidden);
+    uint4* d4 = (uint4*)dst;
+    for (int u = threadIdx.x; u < hidden / 4; u += 256) d4[u] = src[u];
+    __threadfence_system();
+}
+
+// Owner, after k_ep_push_results on the same stream: raise this rank's flag at every sender.
+__global__ void k_ep_signal_results(int world, int me, EpPeers peer_flag_back, int step) {
+    int s = threadIdx.x;
+    if (s >= world) return;
+    __threadfence_system();
+    st_release_sys((int*)peer_flag_back.p[s] + me, step);
+}
+
+}  // namespace xabe

@@ -372,7 +372,10 @@ __global__ void __launch_bounds__(32) k_align_count(const int* __restrict__ topk
     for (int e = lane; e < num_experts; e += 32) hist[e] = 0;
     __syncwarp();
     int begin = c * kAlignChunk;
-    for (int i = begin + lane; i < begin + kAlignChunk && i < numel; i += 32) atomicAdd(&hist[topk_ids[i]], 1);
+    for (int i = begin + lane; i < begin + kAlignChunk && i < numel; i += 32) {
+        int e = topk_ids[i];
+        if (e >= 0) atomicAdd(&hist[e], 1);  // a negative id marks a row that holds nothing (expert-parallel receive slots)
+    }
     __syncwarp();
     for (int e = lane; e < num_experts; e += 32) chunk_hist[(size_t)c * num_experts + e] = hist[e];
     // sentinel / inactive fill over this chunk's share of the capacity
@@ -432,10 +435,10 @@ __global__ void __launch_bounds__(32) k_align_scatter(const int* __restrict__ to
     __syncwarp();
     for (int i0 = begin; i0 < begin + kAlignChunk && i0 < numel; i0 += 32) {
         int i = i0 + lane;
-        bool on = i < numel;
+        int e = i < numel ? topk_ids[i] : -1;
+        bool on = e >= 0;
         unsigned active = __ballot_sync(0xffffffffu, on);
         if (on) {
-            int e = topk_ids[i];
             unsigned same = __match_any_sync(active, e);
             int rank = __popc(same & ((1u << lane) - 1u));
             int pos = cursor[e] + rank;
@@ -551,7 +554,10 @@ __global__ void __launch_bounds__(256) k_route_dispatch_small(
     // warp w owns flat pairs [w * chunk, (w + 1) * chunk), chunk a multiple of 32
     int chunk = ((numel + 7) / 8 + 31) / 32 * 32;
     int begin = warp * chunk, end = min(numel, begin + chunk);
-    for (int i = begin + lane; i < end; i += 32) atomicAdd(&hist[warp * num_experts + ids_s[i]], 1);
+    for (int i = begin + lane; i < end; i += 32) {
+        int e = ids_s[i];
+        if (e >= 0) atomicAdd(&hist[warp * num_experts + e], 1);  // negative: a row that holds nothing
+    }
     __syncthreads();
     for (int e = tid; e < num_experts; e += 256) {
         int total = 0;
@@ -608,10 +614,10 @@ __global__ void __launch_bounds__(256) k_route_dispatch_small(
     int* cursor = hist + warp * num_experts;
     for (int i0 = begin; i0 < end; i0 += 32) {
         int i = i0 + lane;
-        bool on = i < end;
+        int e = i < end ? ids_s[i] : -1;
+        bool on = e >= 0;
         unsigned active = __ballot_sync(0xffffffffu, on);
         if (on) {
-            int e = ids_s[i];
             unsigned same = __match_any_sync(active, e);
             int rank = __popc(same & ((1u << lane) - 1u));
             int pos = cursor[e] + rank;

@@ -13,6 +13,7 @@
 #include "expert_kernels.cuh"
 #include "glue_kernels.cuh"
 #include "stream_kernels.cuh"
+#include "ep_kernels.cuh"
 #include "prefill_wide_kernels.cuh"
 
 using namespace xabe;
@@ -95,6 +96,8 @@ struct xabe_moe {
     float* normed = nullptr;
     __half* normed_h = nullptr;
     int* ep_compact = nullptr;  // [num_experts + 1] live pairs before each expert (expert parallelism)
+    int* ep_rank_start = nullptr;   // [kEpMaxRanks] where each rank's pairs start in the send order
+    int* ep_send_counts = nullptr;  // [kEpMaxRanks]
     __half* x_sorted = nullptr;  // activations in dispatch order (k_prefill_gemm_wide's routed gate/up source)
     CUtensorMap tm_routed_gu{}, tm_routed_dn{}, tm_shared_gu{}, tm_shared_dn{};
     const __half* x_routed_override = nullptr;  // caller-provided f16 rows for one grouped pass
@@ -740,6 +743,8 @@ int xabe_moe_create(const xabe_moe_geometry* geometry, int device, int scope, fl
         A(dev_alloc(&m->expert_offsets, E + 1));
         A(dev_alloc(&m->expert_counts, E + 1));
         A(dev_alloc(&m->ep_compact, E + 1));
+        A(dev_alloc(&m->ep_rank_start, kEpMaxRanks));
+        A(dev_alloc(&m->ep_send_counts, kEpMaxRanks));
         m->work_capacity = (T * K + 7) / 8 + (E < T * K ? E : T * K) + 1;
         A(dev_alloc(&m->work_items, (size_t)m->work_capacity * kWorkItemInts));
         A(dev_alloc(&m->n_work, 1));
@@ -778,7 +783,7 @@ void xabe_moe_destroy(xabe_moe* m) {
     if (!m) return;
     cudaSetDevice(m->device);
     void* dev[] = {m->valid_tokens, m->status, m->topk_ids, m->topk_weights, m->sorted_token_ids, m->expert_ids,
-                   m->num_tokens_post_pad, m->chunk_hist, m->expert_offsets, m->expert_counts, m->ep_compact, m->work_items, m->n_work, m->pf_items,
+                   m->num_tokens_post_pad, m->chunk_hist, m->expert_offsets, m->expert_counts, m->ep_compact, m->ep_rank_start, m->ep_send_counts, m->work_items, m->n_work, m->pf_items,
                    m->pf_n_items, m->normed, m->normed_h, m->logits,
                    m->inter_routed, m->inter_shared, m->x_sorted, m->partial, m->routed, m->shexp, m->gate, m->stage_in,
                    m->stage_ffn, m->stage_out};
@@ -932,6 +937,97 @@ int xabe_moe_ep_plan_pack(xabe_moe* m, void* stream, int experts_per_rank, void*
         m->sorted_token_ids, m->expert_ids, m->expert_offsets, m->ep_compact, m->num_tokens_post_pad,
         m->valid_tokens, m->normed_h, (int)g.experts_per_token, (int)g.hidden, (int)g.block_size, experts_per_rank,
         (__half*)send_rows_f16, send_local_expert, inverse);
+    CUDA_TRY(cudaGetLastError());
+    return XABE_OK;
+}
+
+namespace {
+EpPeers peers_of(void* const* p, int world) {
+    EpPeers e{};
+    for (int i = 0; i < world && i < kEpMaxRanks; ++i) e.p[i] = p[i];
+    return e;
+}
+int check_p2p(const xabe_moe* m, const xabe_ep_peers* peers, int world, int rank, int cap, const char* what) {
+    if (!m || !peers) return fail(XABE_ERR_INVALID_ARGUMENT, "null argument to %s", what);
+    if (world < 1 || world > kEpMaxRanks || rank < 0 || rank >= world || cap < 1)
+        return fail(XABE_ERR_INVALID_ARGUMENT, "%s: world %d (at most %d), rank %d, cap %d", what, world,
+                    kEpMaxRanks, rank, cap);
+    for (int i = 0; i < world; ++i)
+        if (!peers->rows[i] || !peers->eid[i] || !peers->meta[i] || !peers->flag_in[i] || !peers->back[i] ||
+            !peers->flag_back[i])
+            return fail(XABE_ERR_INVALID_ARGUMENT, "%s: rank %d's buffers are not mapped", what, i);
+    return XABE_OK;
+}
+}  // namespace
+
+int xabe_moe_ep_p2p_send(xabe_moe* m, void* stream, int experts_per_rank, int world, int rank, int cap,
+                         const xabe_ep_peers* peers, int step, int32_t* inverse) {
+    int rc = check_p2p(m, peers, world, rank, cap, "ep_p2p_send");
+    if (rc) return rc;
+    if ((rc = check_routed(m, "ep_p2p_send"))) return rc;
+    const auto& g = m->g;
+    if (!inverse || experts_per_rank <= 0 || (int)g.num_experts != experts_per_rank * world || g.hidden % 8 != 0)
+        return fail(XABE_ERR_INVALID_ARGUMENT, "ep_p2p_send: experts do not split as %d x %d", world, experts_per_rank);
+    if ((uint64_t)g.max_tokens * g.experts_per_token > (uint64_t)cap)
+        return fail(XABE_ERR_TOO_MANY_TOKENS, "ep_p2p_send: %u x %u pairs exceed the receive regions of %d rows",
+                    g.max_tokens, g.experts_per_token, cap);
+    cudaStream_t st = (cudaStream_t)stream;
+    int threads = ((int)g.num_experts + 1 + 31) / 32 * 32;
+    k_ep_plan_ranks<<<1, threads, (g.num_experts + 1) * sizeof(int), st>>>(
+        (int)g.num_experts, experts_per_rank, m->expert_counts, m->ep_compact, m->ep_rank_start, m->ep_send_counts);
+    CUDA_TRY(cudaGetLastError());
+    k_ep_push_rows<<<(unsigned)m->sorted_capacity, 256, 0, st>>>(
+        m->sorted_token_ids, m->expert_ids, m->expert_offsets, m->ep_compact, m->ep_rank_start,
+        m->num_tokens_post_pad, m->valid_tokens, m->normed_h, (int)g.experts_per_token, (int)g.hidden,
+        (int)g.block_size, experts_per_rank, rank, cap, peers_of(peers->rows, world), peers_of(peers->eid, world),
+        inverse);
+    CUDA_TRY(cudaGetLastError());
+    k_ep_signal_rows<<<1, 32, 0, st>>>(world, rank, m->ep_send_counts, m->ep_rank_start,
+                                       peers_of(peers->meta, world), peers_of(peers->flag_in, world), step);
+    CUDA_TRY(cudaGetLastError());
+    return XABE_OK;
+}
+
+int xabe_moe_ep_p2p_receive(xabe_moe* m, void* stream, int world, int rank, int cap, const xabe_ep_peers* peers,
+                            int step, int32_t* ids_out, void* result_dst) {
+    int rc = check_p2p(m, peers, world, rank, cap, "ep_p2p_receive");
+    if (rc) return rc;
+    if (!ids_out || !result_dst) return fail(XABE_ERR_INVALID_ARGUMENT, "null output of ep_p2p_receive");
+    if ((uint64_t)world * cap > m->g.max_tokens)
+        return fail(XABE_ERR_TOO_MANY_TOKENS, "ep_p2p_receive: %d x %d slots exceed max_tokens %u", world, cap,
+                    m->g.max_tokens);
+    cudaStream_t st = (cudaStream_t)stream;
+    k_ep_wait_flags<<<1, 32, 0, st>>>(world, (const int*)peers->flag_in[rank], step, m->status);
+    CUDA_TRY(cudaGetLastError());
+    size_t slots = (size_t)world * cap;
+    k_ep_fill_slots<<<(unsigned)((slots + 255) / 256), 256, 0, st>>>(
+        world, cap, (int)m->g.hidden, (const int*)peers->meta[rank], (const int*)peers->eid[rank],
+        peers_of(peers->back, world), ids_out, (float**)result_dst);
+    CUDA_TRY(cudaGetLastError());
+    return XABE_OK;
+}
+
+int xabe_moe_ep_p2p_return(xabe_moe* m, void* stream, int world, int rank, int cap, const xabe_ep_peers* peers,
+                           int step, const void* result_dst) {
+    int rc = check_p2p(m, peers, world, rank, cap, "ep_p2p_return");
+    if (rc) return rc;
+    if ((rc = check_routed(m, "ep_p2p_return"))) return rc;
+    if (!result_dst || (uint64_t)world * cap > m->g.max_tokens || m->g.experts_per_token != 1 || m->g.hidden % 4 != 0)
+        return fail(XABE_ERR_INVALID_ARGUMENT, "ep_p2p_return: needs the owner-side handle (k = 1) and its slot table");
+    cudaStream_t st = (cudaStream_t)stream;
+    k_ep_push_results<<<(unsigned)((size_t)world * cap), 256, 0, st>>>(m->partial, (float* const*)result_dst,
+                                                                       (int)m->g.hidden);
+    CUDA_TRY(cudaGetLastError());
+    k_ep_signal_results<<<1, 32, 0, st>>>(world, rank, peers_of(peers->flag_back, world), step);
+    CUDA_TRY(cudaGetLastError());
+    return XABE_OK;
+}
+
+int xabe_moe_ep_p2p_wait_results(xabe_moe* m, void* stream, int world, int rank, const xabe_ep_peers* peers,
+                                 int step) {
+    int rc = check_p2p(m, peers, world, rank, 1, "ep_p2p_wait_results");
+    if (rc) return rc;
+    k_ep_wait_flags<<<1, 32, 0, (cudaStream_t)stream>>>(world, (const int*)peers->flag_back[rank], step, m->status);
     CUDA_TRY(cudaGetLastError());
     return XABE_OK;
 }

@@ -92,6 +92,17 @@ class EpMoeBlock:
         mark("start")
         ids, weights = b.front(residual, tokens)                    # [T,K] int32, [T,K] f32
         mark("front")
+        if getattr(b, "peer_memory", False):
+            # rows, counts and completion flags travel by peer stores over NVLink: no library
+            # collective, no host read-back; the three calls below only enqueue kernels
+            b.p2p_send()
+            b.shared()
+            mark("plan_pack")
+            b.p2p_experts()
+            mark("experts")
+            b.p2p_finish(residual, tokens, ffn_out, l_out)
+            mark("finish")
+            return
         # rows grouped by owner rank (by expert inside a rank), and how many go to each rank
         send_rows, send_eid, inverse, send_counts = b.plan_pack(self.experts_per_rank, self.world)
         b.shared()   # needs only this rank's tokens: keeps the GPU busy while the host reads the counts back
@@ -199,3 +210,74 @@ class CudaEpBackend:
     def finish(self, back, inverse, residual, tokens, ffn_out, l_out):
         k = self.front_k
         k.ep_combine(back, inverse, self.w.shared_gate_inp, residual, ffn_out, l_out)
+
+
+def share_with_ranks(t: torch.Tensor, rank: int, world: int, group=None) -> list[torch.Tensor]:
+    """Maps the same-shaped tensor of every rank of this node into this process (CUDA IPC, peer access
+    over NVLink): entry r is rank r's tensor; entry `rank` is `t` itself.  The caller keeps the list
+    alive for as long as kernels use the mappings."""
+    if world == 1:
+        return [t]
+    handle = t.untyped_storage()._share_cuda_()
+    meta = (handle, t.storage_offset(), tuple(t.shape), tuple(t.stride()))
+    gathered: list = [None] * world
+    dist.all_gather_object(gathered, meta, group=group)
+    out = []
+    for r, (h, off, shape, stride) in enumerate(gathered):
+        if r == rank:
+            out.append(t)
+            continue
+        storage = torch.UntypedStorage._new_shared_cuda(*h)
+        out.append(torch.empty(0, dtype=t.dtype, device=t.device).set_(storage, off, shape, stride))
+    return out
+
+
+class PeerMemoryEpBackend(CudaEpBackend):
+    """CudaEpBackend whose two exchanges are peer stores over NVLink (`csrc/ep_kernels.cuh`) instead of
+    NCCL all-to-alls.  The owner-side handle sees `world` receive regions of `cap` rows each (cap = the
+    most pairs one rank can send), most of them empty; rows that hold nothing carry expert id -1."""
+
+    peer_memory = True
+
+    def __init__(self, geometry, experts_per_rank: int, rank: int, world: int, front_weights, local_gate, local_up,
+                 local_down, eps: float = 1e-6, exact_decode: bool = False, group=None):
+        from . import _lib
+        cap = geometry.max_tokens * geometry.experts_per_token
+        super().__init__(geometry, experts_per_rank, world * cap, front_weights, local_gate, local_up, local_down,
+                         eps=eps, exact_decode=exact_decode)
+        self.rank, self.world, self.cap, self.epr = rank, world, cap, experts_per_rank
+        dev, H = self.fb.normed.device, geometry.hidden
+        z = lambda *shape, dtype: torch.zeros(*shape, dtype=dtype, device=dev)
+        own = {"rows": z(world * cap, H, dtype=torch.float16), "eid": z(world * cap, dtype=torch.int32),
+               "meta": z(world * 2, dtype=torch.int32), "flag_in": z(world, dtype=torch.int32),
+               "back": z(cap, H, dtype=torch.float32), "flag_back": z(world, dtype=torch.int32)}
+        torch.cuda.synchronize()
+        self._own = own
+        self._mapped = {name: share_with_ranks(t, rank, world, group) for name, t in own.items()}
+        self.peers = _lib.EpPeersC()
+        for name, tensors in self._mapped.items():
+            arr = getattr(self.peers, name)
+            for r, t in enumerate(tensors):
+                arr[r] = t.data_ptr()
+        self.slot_ids = torch.full((world * cap, 1), -1, dtype=torch.int32, device=dev)
+        self.result_dst = torch.zeros(world * cap, dtype=torch.int64, device=dev)
+        self.step = 0
+        self.back_k.set_valid_tokens(world * cap)     # every receive slot is a "token"; empty ones are skipped by id
+        if world > 1:
+            dist.barrier(group=group)                 # nobody writes into a peer before all mappings exist
+
+    def p2p_send(self):
+        self.step += 1
+        self.front_k.ep_p2p_send(self.epr, self.world, self.rank, self.cap, self.peers, self.step, self.inverse)
+
+    def p2p_experts(self):
+        k = self.back_k
+        k.ep_p2p_receive(self.world, self.rank, self.cap, self.peers, self.step, self.slot_ids, self.result_dst)
+        k.build_dispatch(self.slot_ids, None)
+        k.grouped_forward_partial_f16(self.local[0], self.local[1], self.local[2], self._own["rows"])
+        k.ep_p2p_return(self.world, self.rank, self.cap, self.peers, self.step, self.result_dst)
+
+    def p2p_finish(self, residual, tokens, ffn_out, l_out):
+        k = self.front_k
+        k.ep_p2p_wait_results(self.world, self.rank, self.peers, self.step)
+        k.ep_combine(self._own["back"], self.inverse, self.w.shared_gate_inp, residual, ffn_out, l_out)

@@ -181,6 +181,26 @@ class MoeKernels:
                                                 send_rows.data_ptr(), send_local_expert.data_ptr(),
                                                 inverse.data_ptr(), send_counts.data_ptr()))
 
+    # -- expert-parallel exchange over peer memory: see include/xabe_moe.h (xabe_ep_peers)
+    def ep_p2p_send(self, experts_per_rank: int, world: int, rank: int, cap: int, peers, step: int,
+                    inverse: torch.Tensor, stream=None) -> None:
+        _check(_lib.lib().xabe_moe_ep_p2p_send(self._h, _stream_ptr(stream), experts_per_rank, world, rank, cap,
+                                               C.byref(peers), step, inverse.data_ptr()))
+
+    def ep_p2p_receive(self, world: int, rank: int, cap: int, peers, step: int, ids_out: torch.Tensor,
+                       result_dst: torch.Tensor, stream=None) -> None:
+        _check(_lib.lib().xabe_moe_ep_p2p_receive(self._h, _stream_ptr(stream), world, rank, cap, C.byref(peers),
+                                                  step, ids_out.data_ptr(), result_dst.data_ptr()))
+
+    def ep_p2p_return(self, world: int, rank: int, cap: int, peers, step: int, result_dst: torch.Tensor,
+                      stream=None) -> None:
+        _check(_lib.lib().xabe_moe_ep_p2p_return(self._h, _stream_ptr(stream), world, rank, cap, C.byref(peers),
+                                                 step, result_dst.data_ptr()))
+
+    def ep_p2p_wait_results(self, world: int, rank: int, peers, step: int, stream=None) -> None:
+        _check(_lib.lib().xabe_moe_ep_p2p_wait_results(self._h, _stream_ptr(stream), world, rank, C.byref(peers),
+                                                       step))
+
     def ep_combine(self, back_rows: torch.Tensor, inverse: torch.Tensor, shared_gate_inp: torch.Tensor,
                    residual: torch.Tensor, ffn_out: torch.Tensor, l_out: torch.Tensor, stream=None) -> None:
         _check(_lib.lib().xabe_moe_ep_combine(self._h, _stream_ptr(stream), back_rows.data_ptr(),

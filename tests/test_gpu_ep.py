@@ -24,8 +24,10 @@ def _slice_stack(qt, first, count, num_experts):
     return QuantTensor(qt.bytes[first * per:(first + count) * per].clone(), qt.quant)
 
 
-def _ep_forward(torch, L, x_np, rank, world, exact):
-    from llmxabe_b200.ep import CudaEpBackend, EpMoeBlock
+def _ep_forward(torch, L, x_np, rank, world, exact, peer_memory=False, live=None, layers=1):
+    """One rank's share of the block.  `live`: tokens of this rank that are live (default: all);
+    `layers`: how many times the block is applied in a row (the exchange's step counter advances)."""
+    from llmxabe_b200.ep import CudaEpBackend, EpMoeBlock, PeerMemoryEpBackend
     from llmxabe_b200.moe import MoeGeometry
     E, K, H = L.num_experts, L.top_k, L.hidden
     w = device_layer(L)
@@ -33,18 +35,22 @@ def _ep_forward(torch, L, x_np, rank, world, exact):
     mine = x_np[rank * per:(rank + 1) * per]
     g = MoeGeometry(E, K, H, L.inter, 16, per)
     epr = E // world
-    backend = CudaEpBackend(g, epr, x_np.shape[0] * K, w,
-                            _slice_stack(w.gate_exps, rank * epr, epr, E),
-                            _slice_stack(w.up_exps, rank * epr, epr, E),
-                            _slice_stack(w.down_exps, rank * epr, epr, E), exact_decode=exact)
+    stacks = (_slice_stack(w.gate_exps, rank * epr, epr, E), _slice_stack(w.up_exps, rank * epr, epr, E),
+              _slice_stack(w.down_exps, rank * epr, epr, E))
+    if peer_memory:
+        backend = PeerMemoryEpBackend(g, epr, rank, world, w, *stacks, exact_decode=exact)
+    else:
+        backend = CudaEpBackend(g, epr, x_np.shape[0] * K, w, *stacks, exact_decode=exact)
     blk = EpMoeBlock(backend, E, K, rank, world)
     res = torch.from_numpy(mine.copy()).cuda()
+    n = per if live is None else live
     ffn = torch.zeros(per, H, device="cuda")
     lo = torch.zeros(per, H, device="cuda")
-    blk.forward(res, per, ffn, lo)
+    for _ in range(layers):
+        blk.forward(res, n, ffn, lo)
     torch.cuda.synchronize()
     assert backend.front_k.device_status() == 0 and backend.back_k.device_status() == 0
-    return ffn.cpu().numpy(), lo.cpu().numpy()
+    return ffn.cpu().numpy()[:n], lo.cpu().numpy()[:n]
 
 
 @pytest.mark.parametrize("tokens", [1, 24])
@@ -61,7 +67,21 @@ def test_one_rank_expert_parallel_equals_the_plain_block(tokens):
     assert (bits(lo) == bits(plain["l_out"])).all() and (bits(ffn) == bits(plain["ffn_out"])).all()
 
 
-def _rank_main(rank, world, port, out_dir):
+@pytest.mark.parametrize("tokens,live", [(1, 1), (24, 24), (24, 17)])
+def test_one_rank_peer_memory_exchange_equals_the_plain_block(tokens, live):
+    """The NVLink exchange kernels with a single rank (its own buffers are the "peers"): every kernel of
+    the path runs, and repeating the layer advances the step counter the flags compare against."""
+    import torch
+    from llmxabe_b200 import synth
+    from llmxabe_b200.moe import MoeBlock, MoeGeometry
+    L = synth.moe_layer(seed=23, num_experts=8, top_k=2, hidden=512, inter=256, zipf=True)
+    x = synth.activations(tokens, 512, seed=23)
+    plain = run_block(MoeBlock(MoeGeometry(8, 2, 512, 256, 16, tokens)), device_layer(L), x[:live], tokens)
+    ffn, lo = _ep_forward(torch, L, x, 0, 1, exact=False, peer_memory=True, live=live, layers=3)
+    assert (bits(lo) == bits(plain["l_out"])).all() and (bits(ffn) == bits(plain["ffn_out"])).all()
+
+
+def _rank_main(rank, world, port, out_dir, peer_memory=False):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import torch
@@ -73,13 +93,14 @@ def _rank_main(rank, world, port, out_dir):
                             device_id=torch.device("cuda", rank))
     L = synth.moe_layer(seed=22, num_experts=8, top_k=2, hidden=512, inter=256, zipf=True)
     x = synth.activations(32, 512, seed=22)
-    ffn, lo = _ep_forward(torch, L, x, rank, world, exact=True)
+    ffn, lo = _ep_forward(torch, L, x, rank, world, exact=True, peer_memory=peer_memory, layers=2 if peer_memory else 1)
     np.save(os.path.join(out_dir, f"l_out_{rank}.npy"), lo)
     dist.barrier()
     dist.destroy_process_group()
 
 
-def test_two_rank_expert_parallel_equals_the_plain_block(tmp_path):
+@pytest.mark.parametrize("peer_memory", [False, True])
+def test_two_rank_expert_parallel_equals_the_plain_block(tmp_path, peer_memory):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -90,7 +111,7 @@ def test_two_rank_expert_parallel_equals_the_plain_block(tmp_path):
     s.bind(("127.0.0.1", 0))
     port = s.getsockname()[1]
     s.close()
-    mp.spawn(_rank_main, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_rank_main, args=(2, port, str(tmp_path), peer_memory), nprocs=2, join=True)
     L = synth.moe_layer(seed=22, num_experts=8, top_k=2, hidden=512, inter=256, zipf=True)
     x = synth.activations(32, 512, seed=22)
     blk = MoeBlock(MoeGeometry(8, 2, 512, 256, 16, 32))
