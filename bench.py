@@ -462,7 +462,7 @@ def run_ep(args) -> dict:
     ms = e0.elapsed_time(e1) / args.steps
     barrier()
     clocks = sampler.stop()
-    rows = sum(blk.last_plan.recv_counts)
+    rows = sum(blk.last_plan.recv_counts) if blk.last_plan is not None else 0  # not known on the host with peer memory
     # one more, untimed, pass with per-phase events (per layer, this rank)
     blk.enable_phase_timing()
     step(0)

@@ -324,6 +324,16 @@ int xabe_shared_expert_noalloc(void* stream, xabe_quant_tensor gate, xabe_quant_
  * (rows = this rank's `rows` buffer) -> ep_p2p_return; on the tokens' handle:
  * ep_p2p_wait_results -> ep_combine(back).  Waits on other ranks are bounded: a
  * timeout sets device status 3 and the step's output is meaningless. */
+/* Buffers for the peer-memory exchange: device memory of the CURRENT device
+ * that another process of this node can map.  ipc_alloc: cudaMalloc, zeroed,
+ * plus its 64-byte CUDA IPC handle (send it to the other ranks by any means);
+ * ipc_open: maps a peer's buffer into this process with peer access from the
+ * current device; ipc_close / ipc_free undo them.  Set-up time only. */
+int xabe_ipc_alloc(size_t bytes, void** dev_ptr, unsigned char* handle64);
+int xabe_ipc_open(const unsigned char* handle64, void** dev_ptr);
+int xabe_ipc_close(void* dev_ptr);
+int xabe_ipc_free(void* dev_ptr);
+
 typedef struct xabe_ep_peers {
     void* rows[8];
     void* eid[8];
@@ -338,6 +348,14 @@ int xabe_moe_ep_p2p_receive(xabe_moe* m, void* stream, int world, int rank, int 
                             int step, int32_t* ids_out, void* result_dst);
 int xabe_moe_ep_p2p_return(xabe_moe* m, void* stream, int world, int rank, int cap, const xabe_ep_peers* peers,
                            int step, const void* result_dst);
+/* Fused form of the result push: while `table` (the `result_dst` array that
+ * ep_p2p_receive filled: one destination row pointer per receive slot) is set,
+ * the down projection stores weight * value of row r through table[r] -- peer
+ * stores over NVLink straight from the GEMM epilogue -- instead of into the
+ * handle's `partial`, and ep_p2p_return with the same table only raises the
+ * flags.  NULL restores the normal destination.  No counterpart in the
+ * reference. */
+int xabe_moe_set_result_destinations(xabe_moe* m, const void* table);
 int xabe_moe_ep_p2p_wait_results(xabe_moe* m, void* stream, int world, int rank, const xabe_ep_peers* peers,
                                  int step);
 

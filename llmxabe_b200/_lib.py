@@ -58,6 +58,11 @@ SYMBOLS = {
     "xabe_moe_ep_p2p_send": (_i, [_vp, _vp, _i, _i, _i, _i, _vp, _i, _vp]),
     "xabe_moe_ep_p2p_receive": (_i, [_vp, _vp, _i, _i, _i, _vp, _i, _vp, _vp]),
     "xabe_moe_ep_p2p_return": (_i, [_vp, _vp, _i, _i, _i, _vp, _i, _vp]),
+    "xabe_ipc_alloc": (_i, [_sz, _vp, _vp]),
+    "xabe_ipc_open": (_i, [_vp, _vp]),
+    "xabe_ipc_close": (_i, [_vp]),
+    "xabe_ipc_free": (_i, [_vp]),
+    "xabe_moe_set_result_destinations": (_i, [_vp, _vp]),
     "xabe_moe_ep_p2p_wait_results": (_i, [_vp, _vp, _i, _i, _vp, _i]),
     "xabe_moe_ep_combine": (_i, [_vp, _vp, _vp, _sz, _vp, _vp, _vp, _sz, _vp, _sz, _vp, _sz]),
     "xabe_moe_grouped_forward_partial": (_i, [_vp, _vp, QuantTensorC, QuantTensorC, QuantTensorC, _vp]),

@@ -121,6 +121,13 @@ __device__ __forceinline__ uint32_t bytes23_to_h2(uint32_t w, uint32_t bias_h2) 
     return *(uint32_t*)&r;
 }
 
+// Where the down projection stores result row `flat`: the handle's own [flat][rows] buffer, or,
+// under expert parallelism, wherever the row's table entry points (the sender's buffer on a peer
+// GPU: plain stores over NVLink straight from the epilogue).
+__device__ __forceinline__ float* result_row(float* partial, float* const* partial_rows, int flat, int rows) {
+    return partial_rows ? partial_rows[flat] : partial + (size_t)flat * rows;
+}
+
 // The reference's block_reduce_sum (crates/xabe-cuda/src/kernels/layer_ops.rs:93-110,
 // crates/xabe-engine/src/block/moe.rs:209-226): shuffle-down inside each warp,
 // then the warp totals added in ascending order by thread 0.  The order is

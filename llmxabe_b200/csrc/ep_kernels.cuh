@@ -86,7 +86,8 @@ __global__ void __launch_bounds__(256) k_ep_push_rows(
         ((int*)peer_eid.p[d])[(size_t)me * cap + j] = e % experts_per_rank;
         inverse[flat] = i;
     }
-    __threadfence_system();
+    // no fence here: the kernel is complete only when its stores are, and the flag is raised by the
+    // next kernel on the stream (k_ep_signal_rows), after a system-scope fence of its own
 }
 
 // Sender, after k_ep_push_rows on the same stream: thread d tells rank d how many rows it got and
@@ -136,7 +137,6 @@ __global__ void __launch_bounds__(256) k_ep_push_results(const float* __restrict
     const uint4* src = (const uint4*)(partial + (size_t)blockIdx.x * hidden);
     uint4* d4 = (uint4*)dst;
     for (int u = threadIdx.x; u < hidden / 4; u += 256) d4[u] = src[u];
-    __threadfence_system();
 }
 
 // Owner, after k_ep_push_results on the same stream: raise this rank's flag at every sender.

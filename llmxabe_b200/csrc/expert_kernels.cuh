@@ -52,6 +52,7 @@ struct ExpertLaunch {
     __half* inter_routed;  // [slot][rows]    (gate/up)
     __half* inter_shared;  // [token][rows]   (gate/up)
     float* partial;        // [flat][rows]    (down, routed) = weight * value
+    float* const* partial_rows;  // optional: where row `flat` goes instead (a peer's buffer under expert parallelism; NULL entries are skipped)
     float* shexp;          // [token][rows]   (down, shared)
     int* status;
 };
@@ -355,7 +356,7 @@ __device__ __forceinline__ void down_tile(const ExpertLaunch& L, const Bucket& b
                 } else {
                     int flat = slot_ids[col];
                     float wgt = L.topk_weights[flat];
-                    float* dst = L.partial + (size_t)flat * L.rows;
+                    float* dst = result_row(L.partial, L.partial_rows, flat, L.rows);
                     dst[row] = wgt * acc[nb][i];
                     dst[row + 8] = wgt * acc[nb][2 + i];
                 }

@@ -78,6 +78,7 @@ struct PrefillLaunch {
     __half* inter_routed;
     __half* inter_shared;
     float* partial;
+    float* const* partial_rows;  // optional: destination of result row `flat` instead of partial (NULL: use partial)
     float* shexp;
     int* status;
     int n_stages;    // A/B stages (even)
@@ -700,20 +701,22 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L)
                     // lane c holds the flat (token, k) id and the routing weight of column 32 cb + c
                     int my_flat = 0;
                     float my_wgt = 0.f;
+                    float* my_row = nullptr;  // lane c: where the result row of column 32 cb + c goes
                     const int mycol = cb * 32 + lane;
                     if (!T.shared && mycol < T.ncols) {
                         my_flat = __ldg(L.sorted_token_ids + T.first + mycol);
                         my_wgt = __ldg(L.topk_weights + my_flat);
+                        my_row = result_row(L.partial, L.partial_rows, my_flat, L.rows);
                     }
 #pragma unroll
                     for (int jj = 0; jj < 32; ++jj) {
                         const int col = cb * 32 + jj;
-                        const int flat = __shfl_sync(0xffffffffu, my_flat, jj);
                         const float wgt = __shfl_sync(0xffffffffu, my_wgt, jj);
+                        float* row = (float*)__shfl_sync(0xffffffffu, (unsigned long long)my_row, jj);
                         if (col < T.ncols) {
                             float v = __uint_as_float(r[jj]) * inv;
                             if (T.shared) L.shexp[(size_t)(T.first + col) * L.rows + out_row] = v;
-                            else L.partial[(size_t)flat * L.rows + out_row] = wgt * v;
+                            else if (row) row[out_row] = wgt * v;
                         }
                     }
                 }

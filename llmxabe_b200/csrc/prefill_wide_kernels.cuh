@@ -379,20 +379,22 @@ __global__ void __launch_bounds__(kPfWideThreads, 1) k_prefill_gemm_wide(const _
                         const int out_row = T.bx * kPfTileM + quad * 32 + lane;
                         int my_flat = 0;
                         float my_wgt = 0.f;
+                        float* my_row = nullptr;  // lane c: where the result row of column 32 cb + c goes
                         const int mycol = cb * 32 + lane;
                         if (!T.shared && mycol < ncols) {
                             my_flat = __ldg(L.sorted_token_ids + first + mycol);
                             my_wgt = __ldg(L.topk_weights + my_flat);
+                            my_row = result_row(L.partial, L.partial_rows, my_flat, L.rows);
                         }
 #pragma unroll
                         for (int jj = 0; jj < 32; ++jj) {
                             const int col = cb * 32 + jj;
-                            const int flat = __shfl_sync(0xffffffffu, my_flat, jj);
                             const float wgt = __shfl_sync(0xffffffffu, my_wgt, jj);
+                            float* row = (float*)__shfl_sync(0xffffffffu, (unsigned long long)my_row, jj);
                             if (col < ncols) {
                                 float v = __uint_as_float(r[jj]) * inv;
                                 if (T.shared) L.shexp[(size_t)(first + col) * L.rows + out_row] = v;
-                                else L.partial[(size_t)flat * L.rows + out_row] = wgt * v;
+                                else if (row) row[out_row] = wgt * v;
                             }
                         }
                     }

@@ -56,6 +56,7 @@ struct StreamLaunch {
     __half* inter_routed;    // gate/up out, [slot][rows]
     __half* inter_shared;    // gate/up out, [token][rows]
     float* partial;          // down out, [flat][rows]
+    float* const* partial_rows;  // optional: destination of result row `flat` instead (NULL: use partial)
     float* shexp;            // down out, [token][rows]
     int* status;
     int n_stages;
@@ -563,12 +564,12 @@ __global__ void __launch_bounds__(kStreamThreads, 1) k_expert_stream(StreamLaunc
                     }
                 } else {
                     if (2 * t < ncols) {
-                        float* dst = L.partial + (size_t)flat0 * L.rows;
+                        float* dst = result_row(L.partial, L.partial_rows, flat0, L.rows);
                         dst[row_lo] = wgt0 * acc[0];
                         dst[row_hi] = wgt0 * acc[2];
                     }
                     if (2 * t + 1 < ncols) {
-                        float* dst = L.partial + (size_t)flat1 * L.rows;
+                        float* dst = result_row(L.partial, L.partial_rows, flat1, L.rows);
                         dst[row_lo] = wgt1 * acc[1];
                         dst[row_hi] = wgt1 * acc[3];
                     }

@@ -100,6 +100,7 @@ struct xabe_moe {
     int* ep_send_counts = nullptr;  // [kEpMaxRanks]
     __half* x_sorted = nullptr;  // activations in dispatch order (k_prefill_gemm_wide's routed gate/up source)
     CUtensorMap tm_routed_gu{}, tm_routed_dn{}, tm_shared_gu{}, tm_shared_dn{};
+    float* const* partial_rows = nullptr;  // optional per-row destinations of the down projection (expert parallelism)
     const __half* x_routed_override = nullptr;  // caller-provided f16 rows for one grouped pass
     float* logits = nullptr;
     __half* inter_routed = nullptr;
@@ -373,6 +374,7 @@ int run_experts(xabe_moe* m, cudaStream_t st, const MlpWeights& routed, const Ml
         P.inter_routed = m->inter_routed;
         P.inter_shared = m->inter_shared;
         P.partial = m->partial;
+        P.partial_rows = m->partial_rows;
         P.shexp = shexp_out;
         P.status = m->status;
         P.max_tokens = (int)g.max_tokens;
@@ -442,6 +444,7 @@ int run_experts(xabe_moe* m, cudaStream_t st, const MlpWeights& routed, const Ml
     SL.inter_routed = m->inter_routed;
     SL.inter_shared = m->inter_shared;
     SL.partial = m->partial;
+    SL.partial_rows = m->partial_rows;
     SL.shexp = shexp_out;
     SL.num_experts = (int)g.num_experts;
     SL.max_tokens = (int)g.max_tokens;
@@ -477,6 +480,7 @@ int run_experts(xabe_moe* m, cudaStream_t st, const MlpWeights& routed, const Ml
     L.x_routed = m->inter_routed;
     L.x_shared = m->inter_shared;
     L.partial = m->partial;
+    L.partial_rows = m->partial_rows;
     L.shexp = shexp_out;
     StreamShape dn = stream_shape(MODE_DOWN, (int)g.hidden, (int)g.intermediate, qr, qs);
     if (dn.ok && !m->force_tile_kernels) {
@@ -1007,6 +1011,48 @@ int xabe_moe_ep_p2p_receive(xabe_moe* m, void* stream, int world, int rank, int 
     return XABE_OK;
 }
 
+int xabe_ipc_alloc(size_t bytes, void** dev_ptr, unsigned char* handle64) {
+    if (!dev_ptr || !handle64 || bytes == 0) return fail(XABE_ERR_INVALID_ARGUMENT, "bad argument to ipc_alloc");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    void* p = nullptr;
+    CUDA_TRY(cudaMalloc(&p, bytes));
+    cudaError_t e = cudaMemset(p, 0, bytes);
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        return fail(XABE_ERR_DRIVER, "CUDA driver error: %s (ipc_alloc)", cudaGetErrorString(e));
+    }
+    memcpy(handle64, &h, 64);
+    *dev_ptr = p;
+    return XABE_OK;
+}
+
+int xabe_ipc_open(const unsigned char* handle64, void** dev_ptr) {
+    if (!dev_ptr || !handle64) return fail(XABE_ERR_INVALID_ARGUMENT, "bad argument to ipc_open");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    CUDA_TRY(cudaIpcOpenMemHandle(dev_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return XABE_OK;
+}
+
+int xabe_ipc_close(void* dev_ptr) {
+    if (dev_ptr) CUDA_TRY(cudaIpcCloseMemHandle(dev_ptr));
+    return XABE_OK;
+}
+
+int xabe_ipc_free(void* dev_ptr) {
+    if (dev_ptr) CUDA_TRY(cudaFree(dev_ptr));
+    return XABE_OK;
+}
+
+int xabe_moe_set_result_destinations(xabe_moe* m, const void* table) {
+    if (!m) return fail(XABE_ERR_INVALID_ARGUMENT, "null handle");
+    m->partial_rows = (float* const*)table;
+    return XABE_OK;
+}
+
 int xabe_moe_ep_p2p_return(xabe_moe* m, void* stream, int world, int rank, int cap, const xabe_ep_peers* peers,
                            int step, const void* result_dst) {
     int rc = check_p2p(m, peers, world, rank, cap, "ep_p2p_return");
@@ -1015,9 +1061,11 @@ int xabe_moe_ep_p2p_return(xabe_moe* m, void* stream, int world, int rank, int c
     if (!result_dst || (uint64_t)world * cap > m->g.max_tokens || m->g.experts_per_token != 1 || m->g.hidden % 4 != 0)
         return fail(XABE_ERR_INVALID_ARGUMENT, "ep_p2p_return: needs the owner-side handle (k = 1) and its slot table");
     cudaStream_t st = (cudaStream_t)stream;
-    k_ep_push_results<<<(unsigned)((size_t)world * cap), 256, 0, st>>>(m->partial, (float* const*)result_dst,
-                                                                       (int)m->g.hidden);
-    CUDA_TRY(cudaGetLastError());
+    if (m->partial_rows != (float* const*)result_dst) {  // the down projection did not store through this table itself
+        k_ep_push_results<<<(unsigned)((size_t)world * cap), 256, 0, st>>>(m->partial, (float* const*)result_dst,
+                                                                           (int)m->g.hidden);
+        CUDA_TRY(cudaGetLastError());
+    }
     k_ep_signal_results<<<1, 32, 0, st>>>(world, rank, peers_of(peers->flag_back, world), step);
     CUDA_TRY(cudaGetLastError());
     return XABE_OK;

@@ -212,24 +212,46 @@ class CudaEpBackend:
         k.ep_combine(back, inverse, self.w.shared_gate_inp, residual, ffn_out, l_out)
 
 
-def share_with_ranks(t: torch.Tensor, rank: int, world: int, group=None) -> list[torch.Tensor]:
-    """Maps the same-shaped tensor of every rank of this node into this process (CUDA IPC, peer access
-    over NVLink): entry r is rank r's tensor; entry `rank` is `t` itself.  The caller keeps the list
-    alive for as long as kernels use the mappings."""
-    if world == 1:
-        return [t]
-    handle = t.untyped_storage()._share_cuda_()
-    meta = (handle, t.storage_offset(), tuple(t.shape), tuple(t.stride()))
-    gathered: list = [None] * world
-    dist.all_gather_object(gathered, meta, group=group)
-    out = []
-    for r, (h, off, shape, stride) in enumerate(gathered):
-        if r == rank:
-            out.append(t)
-            continue
-        storage = torch.UntypedStorage._new_shared_cuda(*h)
-        out.append(torch.empty(0, dtype=t.dtype, device=t.device).set_(storage, off, shape, stride))
-    return out
+class SharedBuffer:
+    """A zeroed device buffer of this rank that every rank of the node has mapped (CUDA IPC, peer access
+    over NVLink).  `ptrs[r]` is rank r's buffer as this process sees it; `own` is a tensor over this rank's."""
+
+    def __init__(self, shape, dtype: torch.dtype, rank: int, world: int, group=None):
+        import ctypes as C
+
+        from . import _lib
+        from .moe import _check, _view
+        lib = _lib.lib()
+        nbytes = int(torch.empty((), dtype=dtype).element_size())
+        for d in shape:
+            nbytes *= int(d)
+        own_ptr, handle = C.c_void_p(), (C.c_ubyte * 64)()
+        _check(lib.xabe_ipc_alloc(nbytes, C.byref(own_ptr), handle))
+        self._own_ptr, self._opened, self._lib = own_ptr.value, [], lib
+        dev = torch.cuda.current_device()
+        self.own = _view(own_ptr.value, tuple(shape), dtype, dev, self)
+        self.ptrs = [own_ptr.value]
+        if world > 1:
+            gathered: list = [None] * world
+            dist.all_gather_object(gathered, bytes(handle), group=group)
+            self.ptrs = []
+            for r, h in enumerate(gathered):
+                if r == rank:
+                    self.ptrs.append(own_ptr.value)
+                    continue
+                p = C.c_void_p()
+                _check(lib.xabe_ipc_open((C.c_ubyte * 64).from_buffer_copy(h), C.byref(p)))
+                self._opened.append(p.value)
+                self.ptrs.append(p.value)
+
+    def release(self) -> None:
+        """Unmaps the peers' buffers and frees this rank's; call on every rank after a barrier."""
+        for p in self._opened:
+            self._lib.xabe_ipc_close(p)
+        self._opened = []
+        if self._own_ptr:
+            self._lib.xabe_ipc_free(self._own_ptr)
+            self._own_ptr = None
 
 
 class PeerMemoryEpBackend(CudaEpBackend):
@@ -240,25 +262,24 @@ class PeerMemoryEpBackend(CudaEpBackend):
     peer_memory = True
 
     def __init__(self, geometry, experts_per_rank: int, rank: int, world: int, front_weights, local_gate, local_up,
-                 local_down, eps: float = 1e-6, exact_decode: bool = False, group=None):
+                 local_down, eps: float = 1e-6, exact_decode: bool = False, group=None, fused_return: bool = True):
         from . import _lib
+        self.fused_return = fused_return
         cap = geometry.max_tokens * geometry.experts_per_token
         super().__init__(geometry, experts_per_rank, world * cap, front_weights, local_gate, local_up, local_down,
                          eps=eps, exact_decode=exact_decode)
         self.rank, self.world, self.cap, self.epr = rank, world, cap, experts_per_rank
         dev, H = self.fb.normed.device, geometry.hidden
-        z = lambda *shape, dtype: torch.zeros(*shape, dtype=dtype, device=dev)
-        own = {"rows": z(world * cap, H, dtype=torch.float16), "eid": z(world * cap, dtype=torch.int32),
-               "meta": z(world * 2, dtype=torch.int32), "flag_in": z(world, dtype=torch.int32),
-               "back": z(cap, H, dtype=torch.float32), "flag_back": z(world, dtype=torch.int32)}
-        torch.cuda.synchronize()
-        self._own = own
-        self._mapped = {name: share_with_ranks(t, rank, world, group) for name, t in own.items()}
+        mk = lambda shape, dtype: SharedBuffer(shape, dtype, rank, world, group)
+        self._shared = {"rows": mk((world * cap, H), torch.float16), "eid": mk((world * cap,), torch.int32),
+                        "meta": mk((world * 2,), torch.int32), "flag_in": mk((world,), torch.int32),
+                        "back": mk((cap, H), torch.float32), "flag_back": mk((world,), torch.int32)}
+        self._own = {name: b.own for name, b in self._shared.items()}
         self.peers = _lib.EpPeersC()
-        for name, tensors in self._mapped.items():
+        for name, b in self._shared.items():
             arr = getattr(self.peers, name)
-            for r, t in enumerate(tensors):
-                arr[r] = t.data_ptr()
+            for r, p in enumerate(b.ptrs):
+                arr[r] = p
         self.slot_ids = torch.full((world * cap, 1), -1, dtype=torch.int32, device=dev)
         self.result_dst = torch.zeros(world * cap, dtype=torch.int64, device=dev)
         self.step = 0
@@ -274,8 +295,11 @@ class PeerMemoryEpBackend(CudaEpBackend):
         k = self.back_k
         k.ep_p2p_receive(self.world, self.rank, self.cap, self.peers, self.step, self.slot_ids, self.result_dst)
         k.build_dispatch(self.slot_ids, None)
+        if self.fused_return:   # the down projection's epilogue stores each result row at its sender
+            k.set_result_destinations(self.result_dst)
         k.grouped_forward_partial_f16(self.local[0], self.local[1], self.local[2], self._own["rows"])
         k.ep_p2p_return(self.world, self.rank, self.cap, self.peers, self.step, self.result_dst)
+        k.set_result_destinations(None)
 
     def p2p_finish(self, residual, tokens, ffn_out, l_out):
         k = self.front_k

@@ -197,6 +197,9 @@ class MoeKernels:
         _check(_lib.lib().xabe_moe_ep_p2p_return(self._h, _stream_ptr(stream), world, rank, cap, C.byref(peers),
                                                  step, result_dst.data_ptr()))
 
+    def set_result_destinations(self, table: torch.Tensor | None) -> None:
+        _check(_lib.lib().xabe_moe_set_result_destinations(self._h, _ptr(table)))
+
     def ep_p2p_wait_results(self, world: int, rank: int, peers, step: int, stream=None) -> None:
         _check(_lib.lib().xabe_moe_ep_p2p_wait_results(self._h, _stream_ptr(stream), world, rank, C.byref(peers),
                                                        step))

@@ -38,7 +38,8 @@ def _ep_forward(torch, L, x_np, rank, world, exact, peer_memory=False, live=None
     stacks = (_slice_stack(w.gate_exps, rank * epr, epr, E), _slice_stack(w.up_exps, rank * epr, epr, E),
               _slice_stack(w.down_exps, rank * epr, epr, E))
     if peer_memory:
-        backend = PeerMemoryEpBackend(g, epr, rank, world, w, *stacks, exact_decode=exact)
+        backend = PeerMemoryEpBackend(g, epr, rank, world, w, *stacks, exact_decode=exact,
+                                      fused_return=peer_memory != "push")
     else:
         backend = CudaEpBackend(g, epr, x_np.shape[0] * K, w, *stacks, exact_decode=exact)
     blk = EpMoeBlock(backend, E, K, rank, world)
@@ -67,8 +68,9 @@ def test_one_rank_expert_parallel_equals_the_plain_block(tokens):
     assert (bits(lo) == bits(plain["l_out"])).all() and (bits(ffn) == bits(plain["ffn_out"])).all()
 
 
+@pytest.mark.parametrize("mode", ["fused", "push"])
 @pytest.mark.parametrize("tokens,live", [(1, 1), (24, 24), (24, 17)])
-def test_one_rank_peer_memory_exchange_equals_the_plain_block(tokens, live):
+def test_one_rank_peer_memory_exchange_equals_the_plain_block(tokens, live, mode):
     """The NVLink exchange kernels with a single rank (its own buffers are the "peers"): every kernel of
     the path runs, and repeating the layer advances the step counter the flags compare against."""
     import torch
@@ -77,7 +79,7 @@ def test_one_rank_peer_memory_exchange_equals_the_plain_block(tokens, live):
     L = synth.moe_layer(seed=23, num_experts=8, top_k=2, hidden=512, inter=256, zipf=True)
     x = synth.activations(tokens, 512, seed=23)
     plain = run_block(MoeBlock(MoeGeometry(8, 2, 512, 256, 16, tokens)), device_layer(L), x[:live], tokens)
-    ffn, lo = _ep_forward(torch, L, x, 0, 1, exact=False, peer_memory=True, live=live, layers=3)
+    ffn, lo = _ep_forward(torch, L, x, 0, 1, exact=False, peer_memory=mode, live=live, layers=3)
     assert (bits(lo) == bits(plain["l_out"])).all() and (bits(ffn) == bits(plain["ffn_out"])).all()
 
 
@@ -99,7 +101,7 @@ def _rank_main(rank, world, port, out_dir, peer_memory=False):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("peer_memory", [False, True])
+@pytest.mark.parametrize("peer_memory", [False, "fused", "push"])
 def test_two_rank_expert_parallel_equals_the_plain_block(tmp_path, peer_memory):
     import torch
     if torch.cuda.device_count() < 2:
