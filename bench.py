@@ -630,8 +630,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the timed CPU baseline")
     ap.add_argument("--ep-tokens", type=int, default=16384)
     ap.add_argument("--ep-layers", type=int, default=40)
-    ap.add_argument("--ep-peer-memory", action="store_true",
-                    help="exchange rows and results by peer stores over NVLink instead of NCCL all-to-alls")
+    ap.add_argument("--ep-nccl", dest="ep_peer_memory", action="store_false",
+                    help="exchange rows and results with NCCL all-to-alls instead of peer stores over NVLink")
     ap.add_argument("--no-graph", dest="graph", action="store_false", help="time eager launches instead of CUDA-graph replay")
     args = ap.parse_args()
     if args.impl == "reference":
