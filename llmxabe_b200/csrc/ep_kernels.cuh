@@ -26,6 +26,14 @@ constexpr uint32_t kPeerWaitLimit = 1u << 24;  // x 200 ns of sleep: several sec
 struct EpPeers {
     void* p[kEpMaxRanks];
 };
+// Entry d of a by-value table: a chain of selects on the kernel parameter, so that the table is
+// never copied to local memory (which indexing it with a run-time d would make every thread do).
+__device__ __forceinline__ void* peer_at(const EpPeers& e, int d) {
+    void* r = e.p[0];
+#pragma unroll
+    for (int i = 1; i < kEpMaxRanks; ++i) r = d == i ? e.p[i] : r;
+    return r;
+}
 
 __device__ __forceinline__ void st_release_sys(int* p, int v) {
     asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -80,10 +88,10 @@ __global__ void __launch_bounds__(256) k_ep_push_rows(
     const int i = compact[e] + (s - expert_offsets[e]);  // position in this rank's send order
     const int j = i - rank_start[d];                     // position among the rows bound for rank d
     const uint4* src = (const uint4*)(normed_h + (size_t)(flat / top_k) * hidden);
-    uint4* dst = (uint4*)((__half*)peer_rows.p[d] + ((size_t)me * cap + j) * hidden);
+    uint4* dst = (uint4*)((__half*)peer_at(peer_rows, d) + ((size_t)me * cap + j) * hidden);
     for (int u = threadIdx.x; u < hidden / 8; u += 256) dst[u] = __ldg(src + u);
     if (threadIdx.x == 0) {
-        ((int*)peer_eid.p[d])[(size_t)me * cap + j] = e % experts_per_rank;
+        ((int*)peer_at(peer_eid, d))[(size_t)me * cap + j] = e % experts_per_rank;
         inverse[flat] = i;
     }
     // no fence here: the kernel is complete only when its stores are, and the flag is raised by the
@@ -97,11 +105,11 @@ __global__ void k_ep_signal_rows(int world, int me, const int* __restrict__ send
                                  int step) {
     int d = threadIdx.x;
     if (d >= world) return;
-    int* meta = (int*)peer_meta.p[d] + 2 * me;
+    int* meta = (int*)peer_at(peer_meta, d) + 2 * me;
     meta[0] = send_counts[d];
     meta[1] = rank_start[d];
     __threadfence_system();
-    st_release_sys((int*)peer_flag_in.p[d] + me, step);
+    st_release_sys((int*)peer_at(peer_flag_in, d) + me, step);
 }
 
 // One block, `world` threads: wait (bounded) until every flag has reached `step`.
@@ -126,7 +134,7 @@ __global__ void k_ep_fill_slots(int world, int cap, int hidden, const int* __res
     int count = recv_meta[2 * s], start = recv_meta[2 * s + 1];
     bool live = j < count;
     ids[idx] = live ? recv_eid[idx] : -1;
-    result_dst[idx] = live ? (float*)peer_back.p[s] + (size_t)(start + j) * hidden : nullptr;
+    result_dst[idx] = live ? (float*)peer_at(peer_back, s) + (size_t)(start + j) * hidden : nullptr;
 }
 
 // Owner: copy each live slot's result row to its sender.  grid: G*C, block 256.
@@ -144,7 +152,7 @@ __global__ void k_ep_signal_results(int world, int me, EpPeers peer_flag_back, i
     int s = threadIdx.x;
     if (s >= world) return;
     __threadfence_system();
-    st_release_sys((int*)peer_flag_back.p[s] + me, step);
+    st_release_sys((int*)peer_at(peer_flag_back, s) + me, step);
 }
 
 }  // namespace xabe

@@ -667,6 +667,22 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L)
         for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++n) {
             const PfTile T = pf_tile(L, t, n_routed, valid);
             const uint32_t acc = n % kPfAccums;
+            // Down, routed: lane c fetches the flat (token, k) id, the routing weight and the result row of
+            // columns c, c + 32, c + 64, c + 96 now -- three dependent loads each -- so that they are
+            // in flight while the accumulator is still being computed, not after it is ready.
+            float col_wgt[4] = {0.f, 0.f, 0.f, 0.f};
+            float* col_row[4] = {nullptr, nullptr, nullptr, nullptr};
+            if (MODE == MODE_DOWN && !T.shared) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int mycol = q * 32 + lane;
+                    if (mycol < T.ncols) {
+                        const int flat = __ldg(L.sorted_token_ids + T.first + mycol);
+                        col_wgt[q] = __ldg(L.topk_weights + flat);
+                        col_row[q] = result_row(L.partial, L.partial_rows, flat, L.rows);
+                    }
+                }
+            }
             ok = stream_wait_pf<true>(&ctl.acc_full[acc], (n / kPfAccums) & 1, abortp, L.status);
             if (!ok) break;
             tc_fence_after();
@@ -698,16 +714,11 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L)
                     }
                 } else {
                     const int out_row = T.bx * kPfTileM + quad * 32 + lane;
-                    // lane c holds the flat (token, k) id and the routing weight of column 32 cb + c
-                    int my_flat = 0;
-                    float my_wgt = 0.f;
-                    float* my_row = nullptr;  // lane c: where the result row of column 32 cb + c goes
-                    const int mycol = cb * 32 + lane;
-                    if (!T.shared && mycol < T.ncols) {
-                        my_flat = __ldg(L.sorted_token_ids + T.first + mycol);
-                        my_wgt = __ldg(L.topk_weights + my_flat);
-                        my_row = result_row(L.partial, L.partial_rows, my_flat, L.rows);
-                    }
+                    float my_wgt = col_wgt[0];
+                    float* my_row = col_row[0];
+                    if (cb == 1) { my_wgt = col_wgt[1]; my_row = col_row[1]; }
+                    if (cb == 2) { my_wgt = col_wgt[2]; my_row = col_row[2]; }
+                    if (cb == 3) { my_wgt = col_wgt[3]; my_row = col_row[3]; }
 #pragma unroll
                     for (int jj = 0; jj < 32; ++jj) {
                         const int col = cb * 32 + jj;

@@ -345,6 +345,20 @@ __global__ void __launch_bounds__(kPfWideThreads, 1) k_prefill_gemm_wide(const _
                 const uint32_t as = (acc_base + ct) & 3u;
                 const int first = T.first + ct * kPfTileN;
                 const int ncols = min(kPfTileN, T.ncols - ct * kPfTileN);
+                // down, routed: the three dependent loads per column are issued before the wait
+                float col_wgt[4] = {0.f, 0.f, 0.f, 0.f};
+                float* col_row[4] = {nullptr, nullptr, nullptr, nullptr};
+                if (MODE == MODE_DOWN && !T.shared) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int mycol = q * 32 + lane;
+                        if (mycol < ncols) {
+                            const int flat = __ldg(L.sorted_token_ids + first + mycol);
+                            col_wgt[q] = __ldg(L.topk_weights + flat);
+                            col_row[q] = result_row(L.partial, L.partial_rows, flat, L.rows);
+                        }
+                    }
+                }
                 ok = stream_wait_pf<true>(&ctl.acc_full[as], acc_par >> as & 1u, abortp, L.status);
                 if (!ok) break;
                 acc_par ^= 1u << as;
@@ -377,15 +391,11 @@ __global__ void __launch_bounds__(kPfWideThreads, 1) k_prefill_gemm_wide(const _
                         }
                     } else {
                         const int out_row = T.bx * kPfTileM + quad * 32 + lane;
-                        int my_flat = 0;
-                        float my_wgt = 0.f;
-                        float* my_row = nullptr;  // lane c: where the result row of column 32 cb + c goes
-                        const int mycol = cb * 32 + lane;
-                        if (!T.shared && mycol < ncols) {
-                            my_flat = __ldg(L.sorted_token_ids + first + mycol);
-                            my_wgt = __ldg(L.topk_weights + my_flat);
-                            my_row = result_row(L.partial, L.partial_rows, my_flat, L.rows);
-                        }
+                        float my_wgt = col_wgt[0];
+                        float* my_row = col_row[0];
+                        if (cb == 1) { my_wgt = col_wgt[1]; my_row = col_row[1]; }
+                        if (cb == 2) { my_wgt = col_wgt[2]; my_row = col_row[2]; }
+                        if (cb == 3) { my_wgt = col_wgt[3]; my_row = col_row[3]; }
 #pragma unroll
                         for (int jj = 0; jj < 32; ++jj) {
                             const int col = cb * 32 + jj;
