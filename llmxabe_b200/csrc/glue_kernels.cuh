@@ -358,11 +358,13 @@ __global__ void __launch_bounds__(256) k_route(const float* __restrict__ logits,
 // ascending flat order with warp match ranks.  The sentinel is
 // valid_tokens * top_k (dispatch.rs:24-26), inactive blocks are -1.
 // ---------------------------------------------------------------------------
-constexpr int kAlignChunk = 1024;  // flat pairs per chunk (one warp each)
+// Flat pairs per chunk (one warp each): small chunks put more warps to work, large ones keep the
+// one-thread-per-expert scan over the chunks short.
+__host__ __device__ inline int align_chunk_pairs(uint64_t pairs) { return pairs <= 65536 ? 256 : 1024; }
 
 __global__ void __launch_bounds__(32) k_align_count(const int* __restrict__ topk_ids,
                                                     const int* __restrict__ valid_tokens, int top_k,
-                                                    int num_experts, int n_chunks, int sorted_capacity,
+                                                    int num_experts, int n_chunks, int chunk, int sorted_capacity,
                                                     int block_capacity, int* __restrict__ chunk_hist,
                                                     int* __restrict__ sorted_token_ids,
                                                     int* __restrict__ expert_ids) {
@@ -371,8 +373,8 @@ __global__ void __launch_bounds__(32) k_align_count(const int* __restrict__ topk
     int numel = *valid_tokens * top_k;
     for (int e = lane; e < num_experts; e += 32) hist[e] = 0;
     __syncwarp();
-    int begin = c * kAlignChunk;
-    for (int i = begin + lane; i < begin + kAlignChunk && i < numel; i += 32) {
+    int begin = c * chunk;
+    for (int i = begin + lane; i < begin + chunk && i < numel; i += 32) {
         int e = topk_ids[i];
         if (e >= 0) atomicAdd(&hist[e], 1);  // a negative id marks a row that holds nothing (expert-parallel receive slots)
     }
@@ -393,10 +395,15 @@ __global__ void k_align_scan(int num_experts, int n_chunks, int block_size, int*
     int e = threadIdx.x;
     int total = 0;
     if (e < num_experts) {
-        for (int c = 0; c < n_chunks; ++c) {
-            int h = chunk_hist[(size_t)c * num_experts + e];
-            chunk_hist[(size_t)c * num_experts + e] = total;  // exclusive prefix over chunks
-            total += h;
+        for (int c0 = 0; c0 < n_chunks; c0 += 8) {  // eight loads in flight, then their exclusive prefixes
+            int h[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) h[u] = c0 + u < n_chunks ? chunk_hist[(size_t)(c0 + u) * num_experts + e] : 0;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (c0 + u < n_chunks) chunk_hist[(size_t)(c0 + u) * num_experts + e] = total;
+                total += h[u];
+            }
         }
         padded[e] = (total + block_size - 1) / block_size * block_size;
         expert_counts[e] = total;
@@ -424,16 +431,17 @@ __global__ void k_align_scan(int num_experts, int n_chunks, int block_size, int*
 
 __global__ void __launch_bounds__(32) k_align_scatter(const int* __restrict__ topk_ids,
                                                       const int* __restrict__ valid_tokens, int top_k,
-                                                      int num_experts, const int* __restrict__ chunk_hist,
+                                                      int num_experts, int chunk,
+                                                      const int* __restrict__ chunk_hist,
                                                       int* __restrict__ sorted_token_ids) {
     extern __shared__ int cursor[];
     int c = blockIdx.x, lane = threadIdx.x;
     int numel = *valid_tokens * top_k;
-    int begin = c * kAlignChunk;
+    int begin = c * chunk;
     if (begin >= numel) return;
     for (int e = lane; e < num_experts; e += 32) cursor[e] = chunk_hist[(size_t)c * num_experts + e];
     __syncwarp();
-    for (int i0 = begin; i0 < begin + kAlignChunk && i0 < numel; i0 += 32) {
+    for (int i0 = begin; i0 < begin + chunk && i0 < numel; i0 += 32) {
         int i = i0 + lane;
         int e = i < numel ? topk_ids[i] : -1;
         bool on = e >= 0;

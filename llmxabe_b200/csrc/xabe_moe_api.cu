@@ -71,6 +71,7 @@ struct xabe_moe {
     bool exact_decode = false;
     uint64_t sorted_capacity = 0, block_capacity = 0;
     int n_chunks = 0;
+    int align_chunk = 1024;
     int published_tokens = -1;
     int* h_status = nullptr;  // pinned
     // device scratch
@@ -603,7 +604,7 @@ int launch_route_and_dispatch(xabe_moe* m, cudaStream_t st, const float* logits)
         CUDA_TRY(cudaGetLastError());
     }
     k_align_count<<<m->n_chunks, 32, hist_bytes, st>>>(m->topk_ids, m->valid_tokens, (int)g.experts_per_token,
-                                                      (int)g.num_experts, m->n_chunks, (int)m->sorted_capacity,
+                                                      (int)g.num_experts, m->n_chunks, m->align_chunk, (int)m->sorted_capacity,
                                                       (int)m->block_capacity, m->chunk_hist,
                                                       m->sorted_token_ids, m->expert_ids);
     CUDA_TRY(cudaGetLastError());
@@ -614,7 +615,7 @@ int launch_route_and_dispatch(xabe_moe* m, cudaStream_t st, const float* logits)
     CUDA_TRY(cudaGetLastError());
     k_align_scatter<<<m->n_chunks, 32, hist_bytes, st>>>(m->topk_ids, m->valid_tokens,
                                                         (int)g.experts_per_token, (int)g.num_experts,
-                                                        m->chunk_hist, m->sorted_token_ids);
+                                                        m->align_chunk, m->chunk_hist, m->sorted_token_ids);
     CUDA_TRY(cudaGetLastError());
     // Only the work list of the kernels that will run: the regime must be chosen before this call.
     if (prefill_applies(m, (int)g.intermediate, (int)g.hidden, (int)g.hidden, (int)g.intermediate)) {
@@ -722,7 +723,8 @@ int xabe_moe_create(const xabe_moe_geometry* geometry, int device, int scope, fl
     m->sorted_capacity = cap;
     m->block_capacity = cap / g.block_size;
     uint64_t pairs = (uint64_t)g.max_tokens * (scope == XABE_SCOPE_ROUTED ? g.experts_per_token : 0);
-    m->n_chunks = (int)((pairs + kAlignChunk - 1) / kAlignChunk);
+    m->align_chunk = align_chunk_pairs(pairs);
+    m->n_chunks = (int)((pairs + m->align_chunk - 1) / m->align_chunk);
     if (m->n_chunks < 1) m->n_chunks = 1;
     size_t T = g.max_tokens, H = g.hidden, I = g.intermediate, E = g.num_experts, K = g.experts_per_token;
     cudaError_t e = cudaSuccess;
