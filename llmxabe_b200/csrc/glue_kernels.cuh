@@ -701,7 +701,7 @@ __global__ void k_reduce(const float* __restrict__ partial, const int* __restric
 // lanes at stride 256 and block_reduce_sum; routed = ascending-k sum of
 // partial; ffn_out = routed + shexp * g (routed on the left); l_out =
 // ffn_out + residual (the pre-norm input).
-// grid: (max_tokens, ceil(hidden / 256)), block 256.
+// grid: (max_tokens, 1 or hidden / 256), block 256.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) k_gate_and_combine(
     const float* __restrict__ w, const float* __restrict__ normed, const float* __restrict__ partial,
@@ -718,15 +718,25 @@ __global__ void __launch_bounds__(256) k_gate_and_combine(
     s = block_reduce_sum_pinned(s, scratch);
     float g = __fdiv_rn(1.0f, 1.0f + expf(-s));
     if (threadIdx.x == 0 && blockIdx.y == 0) gate[t] = g;
-    int j = blockIdx.y * blockDim.x + threadIdx.x;
-    if (j >= hidden) return;
     size_t pbase = (size_t)t * top_k * hidden;
-    float r = 0.0f;
-    for (int k = 0; k < top_k; ++k) r += partial[pbase + (size_t)k * hidden + j];
-    float v = fmaf(shexp[base + j], g, r);
-    routed[base + j] = r;
-    ffn_out[base + j] = v;
-    l_out[base + j] = v + residual[base + j];
+    // gridDim.y blocks share a token's columns: 1 at prefill widths (the gate, a block-wide reduction,
+    // is then computed once per token), hidden / 256 at decode widths (more blocks than SMs)
+    for (int j = blockIdx.y * 256 + threadIdx.x; j < hidden; j += 256 * gridDim.y) {
+        float r = 0.0f;
+        if (top_k == 8) {  // the shipped geometry: all eight loads in flight, then the same ascending-k sum
+            float pv[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) pv[k] = partial[pbase + (size_t)k * hidden + j];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) r += pv[k];
+        } else {
+            for (int k = 0; k < top_k; ++k) r += partial[pbase + (size_t)k * hidden + j];
+        }
+        float v = fmaf(shexp[base + j], g, r);
+        routed[base + j] = r;
+        ffn_out[base + j] = v;
+        l_out[base + j] = v + residual[base + j];
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -819,17 +829,39 @@ __global__ void __launch_bounds__(256) k_ep_combine(
     s = block_reduce_sum_pinned(s, scratch);
     float g = __fdiv_rn(1.0f, 1.0f + expf(-s));
     if (threadIdx.x == 0 && blockIdx.y == 0) gate[t] = g;
-    int j = blockIdx.y * blockDim.x + threadIdx.x;
-    if (j >= hidden) return;
-    float r = 0.0f;
-    for (int k = 0; k < top_k; ++k) {
-        const int flat = t * top_k + k;
-        r = __fadd_rn(r, __fmul_rn(topk_weights[flat], back[(size_t)inverse[flat] * hidden + j]));
+    if (top_k == 8) {  // the shipped geometry: row addresses and weights once per token, eight rows in flight
+        int src[8];
+        float pw[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            src[k] = inverse[t * 8 + k];
+            pw[k] = topk_weights[t * 8 + k];
+        }
+        for (int j = blockIdx.y * 256 + threadIdx.x; j < hidden; j += 256 * gridDim.y) {
+            float pv[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) pv[k] = back[(size_t)src[k] * hidden + j];
+            float r = 0.0f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) r = __fadd_rn(r, __fmul_rn(pw[k], pv[k]));
+            float v = fmaf(shexp[base + j], g, r);
+            routed[base + j] = r;
+            ffn_out[base + j] = v;
+            l_out[base + j] = v + residual[base + j];
+        }
+        return;
     }
-    float v = fmaf(shexp[base + j], g, r);
-    routed[base + j] = r;
-    ffn_out[base + j] = v;
-    l_out[base + j] = v + residual[base + j];
+    for (int j = blockIdx.y * 256 + threadIdx.x; j < hidden; j += 256 * gridDim.y) {
+        float r = 0.0f;
+        for (int k = 0; k < top_k; ++k) {
+            const int flat = t * top_k + k;
+            r = __fadd_rn(r, __fmul_rn(topk_weights[flat], back[(size_t)inverse[flat] * hidden + j]));
+        }
+        float v = fmaf(shexp[base + j], g, r);
+        routed[base + j] = r;
+        ffn_out[base + j] = v;
+        l_out[base + j] = v + residual[base + j];
+    }
 }
 
 // Dense FFN epilogue (crates/xabe-engine/src/block/dense_ffn.rs:234-251):

@@ -860,7 +860,7 @@ int xabe_moe_gate_and_combine(xabe_moe* m, void* stream, const float* shared_gat
     size_t n = (size_t)g.max_tokens * g.hidden;
     if (residual_len != n || ffn_out_len != n || l_out_len != n)
         return fail(XABE_ERR_BUFFER_LENGTH, "gate_and_combine buffers must hold %zu floats", n);
-    dim3 grid(g.max_tokens, (g.hidden + 255) / 256);
+    dim3 grid(g.max_tokens, g.max_tokens >= 512 ? 1u : (g.hidden + 255) / 256);
     k_gate_and_combine<<<grid, 256, 0, (cudaStream_t)stream>>>(
         shared_gate_inp, m->normed, m->partial, m->shexp, residual, m->valid_tokens, (int)g.experts_per_token,
         (int)g.hidden, m->gate, m->routed, ffn_out, l_out);
@@ -1095,7 +1095,7 @@ int xabe_moe_ep_combine(xabe_moe* m, void* stream, const float* back_rows, size_
         return fail(XABE_ERR_BUFFER_LENGTH, "ep_combine buffers must hold %zu floats", n);
     if (n_rows > (size_t)g.max_tokens * g.experts_per_token)
         return fail(XABE_ERR_TOO_MANY_TOKENS, "%zu rows exceed max_tokens * k", n_rows);
-    dim3 grid(g.max_tokens, (g.hidden + 255) / 256);
+    dim3 grid(g.max_tokens, g.max_tokens >= 512 ? 1u : (g.hidden + 255) / 256);
     k_ep_combine<<<grid, 256, 0, (cudaStream_t)stream>>>(
         shared_gate_inp, m->normed, back_rows, inverse, m->topk_weights, m->shexp, residual, m->valid_tokens,
         (int)g.experts_per_token, (int)g.hidden, m->gate, m->routed, ffn_out, l_out);
@@ -1171,7 +1171,7 @@ int xabe_moe_block_forward(xabe_moe* m, void* stream, const xabe_moe_layer_weigh
     s.down = w->shared_down;
     if ((rc = run_experts(m, st, r, s, m->shexp, 4))) return rc;
     prof_mark(m, st, 5);
-    dim3 grid(g.max_tokens, (g.hidden + 255) / 256);
+    dim3 grid(g.max_tokens, g.max_tokens >= 512 ? 1u : (g.hidden + 255) / 256);
     k_gate_and_combine<<<grid, 256, 0, st>>>(w->shared_gate_inp, m->normed, m->partial, m->shexp, residual,
                                              m->valid_tokens, (int)g.experts_per_token, (int)g.hidden, m->gate,
                                              m->routed, ffn_out, l_out);
