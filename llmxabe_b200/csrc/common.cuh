@@ -128,6 +128,14 @@ __device__ __forceinline__ float* result_row(float* partial, float* const* parti
     return partial_rows ? partial_rows[flat] : partial + (size_t)flat * rows;
 }
 
+// Programmatic dependent launch: a kernel launched with the "programmatic stream serialization"
+// attribute may be scheduled while its predecessor in the stream is still running; it must not touch
+// anything the predecessor writes before pdl_wait() returns (which is when the predecessor has
+// completed and its writes are visible).  pdl_launch_dependents() lets the successor's launch
+// begin.  Both are no-ops for a kernel that was launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // The reference's block_reduce_sum (crates/xabe-cuda/src/kernels/layer_ops.rs:93-110,
 // crates/xabe-engine/src/block/moe.rs:209-226): shuffle-down inside each warp,
 // then the warp totals added in ascending order by thread 0.  The order is

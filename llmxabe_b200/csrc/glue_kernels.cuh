@@ -23,6 +23,8 @@ namespace xabe {
 __global__ void k_rms_norm(const float* __restrict__ x, const float* __restrict__ weight,
                            float* __restrict__ out, __half* __restrict__ out_h,
                            const int* __restrict__ valid_tokens, int width, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float scratch[32];
     int row = blockIdx.x;
     if (row >= *valid_tokens) return;
@@ -75,6 +77,8 @@ __global__ void __launch_bounds__(128) k_router_logits(const float* __restrict__
                                                         const float* __restrict__ bias,
                                                         float* __restrict__ logits, int tiles_per_cta,
                                                         int* __restrict__ status) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ __align__(128) float w_rows[];
     __shared__ __align__(8) uint64_t bar;
     int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -172,6 +176,8 @@ __global__ void __launch_bounds__(256, 1) k_router_logits_wide(const float* __re
                                                                int num_experts, const float* __restrict__ bias,
                                                                float* __restrict__ logits,
                                                                int* __restrict__ status) {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr int hidden = NI * 256;
     extern __shared__ __align__(128) float rw_smem[];
     float* w_s = rw_smem;                                 // [16][hidden]
@@ -338,6 +344,8 @@ __global__ void __launch_bounds__(256) k_route(const float* __restrict__ logits,
                                                const int* __restrict__ valid_tokens, int num_experts,
                                                int top_k, int* __restrict__ topk_ids,
                                                float* __restrict__ topk_weights) {
+    pdl_launch_dependents();
+    pdl_wait();
     int lane = threadIdx.x & 31;
     int token = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (token >= *valid_tokens) return;
@@ -529,6 +537,8 @@ __global__ void __launch_bounds__(256) k_route_dispatch_small(
     float* __restrict__ topk_weights, int* __restrict__ sorted_token_ids, int* __restrict__ expert_ids,
     int* __restrict__ num_tokens_post_pad, int* __restrict__ expert_offsets, int* __restrict__ expert_counts,
     int* __restrict__ work_items, int* __restrict__ n_work) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ int sm[];
     int* ids_s = sm;                          // [kSmallPairs]
     int* hist = ids_s + kSmallPairs;          // [8][E] per-warp chunk histograms -> cursors
@@ -708,6 +718,8 @@ __global__ void __launch_bounds__(256) k_gate_and_combine(
     const float* __restrict__ shexp, const float* __restrict__ residual, const int* __restrict__ valid_tokens,
     int top_k, int hidden, float* __restrict__ gate, float* __restrict__ routed, float* __restrict__ ffn_out,
     float* __restrict__ l_out) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float scratch[32];
     int t = blockIdx.x;
     if (t >= *valid_tokens) return;

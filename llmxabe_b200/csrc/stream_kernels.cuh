@@ -321,6 +321,8 @@ __device__ __forceinline__ int gateup_span_of(int w, int h, int n_spans) {
 // ---------------------------------------------------------------------------
 template <int MODE, int QR, int QS>
 __global__ void __launch_bounds__(kStreamThreads, 1) k_expert_stream(StreamLaunch L) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ int abort_flag;
     constexpr int ROWS_PER_TILE = MODE == MODE_GATEUP ? 8 : 128;
