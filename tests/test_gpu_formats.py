@@ -61,3 +61,32 @@ def test_q8_0_router_is_dequantised_bit_exactly_and_routes_like_the_oracle(oracl
     assert (bits(got["logits"]) == bits(want["logits"])).all()
     rel = np.linalg.norm(got["l_out"].astype(np.float64) - want["l_out"]) / np.linalg.norm(want["l_out"].astype(np.float64))
     assert rel <= 1e-3
+
+
+def test_unknown_dtype_tag_is_rejected_before_any_launch():
+    import ctypes as C
+    import torch
+    from llmxabe_b200 import _lib, synth
+    from llmxabe_b200.errors import MoeError
+    from llmxabe_b200.moe import MoeBlock, MoeGeometry, _check
+    L = synth.moe_layer(seed=33, num_experts=8, top_k=2, hidden=512, inter=256, zipf=False)
+    blk = MoeBlock(MoeGeometry(8, 2, 512, 256, 16, 4))
+    w = device_layer(L)
+    wc = w._c()
+    res = torch.zeros(4, 512, device="cuda")
+    out = torch.full((4, 512), 3.0, device="cuda")
+    with pytest.raises(MoeError):
+        _check(_lib.lib().xabe_moe_block_forward_typed(blk.moe._h, torch.cuda.current_stream().cuda_stream,
+                                                       C.byref(wc), res.data_ptr(), 7, res.numel(), 2,
+                                                       out.data_ptr(), out.numel(), out.data_ptr(), out.numel()))
+    torch.cuda.synchronize()
+    assert bool((out == 3.0).all().item())
+
+
+def test_streaming_read_calibration_runs():
+    import torch
+    from llmxabe_b200.moe import stream_read
+    data = torch.randint(0, 255, (1 << 20,), dtype=torch.uint8, device="cuda")
+    sink = torch.zeros(1, dtype=torch.int32, device="cuda")
+    stream_read(data, sink)
+    torch.cuda.synchronize()
