@@ -60,16 +60,21 @@ def measured_peaks():
     return 6650.0, "fallback (no MEASURED_PEAKS.json)"
 
 
-def layer_algorithmic_bytes(distinct: int, tokens: int) -> int:
+Q8_0_EXPERT_BYTES = 3 * (512 * 2048 // 32) * 34    # 3,342,336
+
+
+def layer_algorithmic_bytes(distinct: int, tokens: int, shared_q8: bool = False) -> int:
     """Weights of the experts actually routed + shared expert + router + vectors + x in, ffn_out, l_out."""
-    return distinct * Q6K_EXPERT_BYTES + Q6K_EXPERT_BYTES + ROUTER_BYTES + VEC_BYTES + tokens * 3 * 2048 * 4
+    shared = Q8_0_EXPERT_BYTES if shared_q8 else Q6K_EXPERT_BYTES
+    return distinct * Q6K_EXPERT_BYTES + shared + ROUTER_BYTES + VEC_BYTES + tokens * 3 * 2048 * 4
 
 
-def gateup_algorithmic_bytes(distinct: int, tokens: int) -> int:
+def gateup_algorithmic_bytes(distinct: int, tokens: int, shared_q8: bool = False) -> int:
     """What the gate/up launch must move: gate and up of the routed experts and of the shared one,
     the f16 activations in, the f16 intermediates out."""
     per = 2 * (512 * 2048 // 256) * 210
-    return (distinct + 1) * per + tokens * 2048 * 2 + tokens * 9 * 512 * 2
+    shared = 2 * (512 * 2048 // 32) * 34 if shared_q8 else per
+    return distinct * per + shared + tokens * 2048 * 2 + tokens * 9 * 512 * 2
 
 
 class ClockSampler:
@@ -193,7 +198,8 @@ def run_ours(args) -> dict:
     H = 2048
     g = MoeGeometry.qwen3_6(block_size, tokens)
     block = MoeBlock(g)
-    layers = [synth.moe_layer_on_device(seed=rank, layer=i, zipf=zipf) for i in range(args.layers)]
+    shared_q = synth.Q8_0 if args.shared_quant == "q8_0" else synth.Q6K
+    layers = [synth.moe_layer_on_device(seed=rank, layer=i, zipf=zipf, shared_quant=shared_q) for i in range(args.layers)]
     gen = torch.Generator(device="cuda")
     gen.manual_seed(4242 + rank)
     xs = [torch.randn(tokens, H, device="cuda", generator=gen) for _ in range(args.layers)]
@@ -334,16 +340,17 @@ def run_ours(args) -> dict:
     launches_per_step = 7 if tokens * 8 <= 2048 and tokens > 8 else (6 if tokens <= 8 else 11)
     peak, peak_src = measured_peaks()
     gateup_ms = stage_ms["gate_up"] / max(calls, 1)
-    gu_bytes = gateup_algorithmic_bytes(d_mean, tokens)
+    gu_bytes = gateup_algorithmic_bytes(d_mean, tokens, args.shared_quant == "q8_0")
     achieved = gu_bytes / (gateup_ms * 1e-3) / 1e9 if gateup_ms > 0 else 0.0
-    layer_bytes = layer_algorithmic_bytes(d_mean, tokens)
+    layer_bytes = layer_algorithmic_bytes(d_mean, tokens, args.shared_quant == "q8_0")
     out = {
         "metric": METRIC, "value": world * tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f16 activations x exact Q6_K codes, fp32 scales+accumulate",
         "data": "synthetic",
         "config": {"workload": args.workload, "tokens_per_rank": tokens, "experts": 256, "top_k": 8,
-                   "hidden": 2048, "intermediate": 512, "quant": "Q6_K", "bucket": block_size,
+                   "hidden": 2048, "intermediate": 512, "quant": "Q6_K", "shared_expert_quant": args.shared_quant,
+                   "bucket": block_size,
                    "resident_layers": args.layers, "distinct_experts_mean": d_mean,
                    "l2": f"layers rotate every step; each touches {layer_bytes / 1e6:.0f} MB of weights "
                          f"(> 126 MB L2) out of {args.layers} resident layers",
@@ -628,6 +635,8 @@ def main():
     ap.add_argument("--workload", default="decode64", choices=sorted(WORKLOADS))
     ap.add_argument("--layers", type=int, default=4, help="distinct resident layers the steps rotate over")
     ap.add_argument("--no-cpu", action="store_true", help="skip the timed CPU baseline")
+    ap.add_argument("--shared-quant", default="q6_k", choices=["q6_k", "q8_0"],
+                    help="format of the shared expert in the MoE workloads (the shipped file's is Q8_0)")
     ap.add_argument("--ep-tokens", type=int, default=16384)
     ap.add_argument("--ep-layers", type=int, default=40)
     ap.add_argument("--ep-nccl", dest="ep_peer_memory", action="store_false",

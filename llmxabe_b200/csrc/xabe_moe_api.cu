@@ -353,6 +353,18 @@ int run_experts(xabe_moe* m, cudaStream_t st, const MlpWeights& routed, const Ml
                 float* shexp_out, int mark_between = -1) {
     const auto& g = m->g;
     if (!routed.present && !shared.present) return XABE_OK;
+    // Different formats for the routed experts and the shared expert (the shipped file: Q6_K and Q8_0):
+    // two launches per projection instead of one mixed one.  A mixed launch sizes its rings for the
+    // longer Q8_0 rows and branches on the format per tile; measured, it slowed every tile (64 tokens:
+    // gate/up 0.107 -> 0.131 ms; 2048 tokens: 0.279 -> 0.334 ms), far more than the shared expert's own work.
+    // Below 16 tokens the two extra launches cost more than they save (1 token: 44.5 -> 56.2 us), so the
+    // narrowest handles keep the mixed launch.
+    if (routed.present && shared.present && g.max_tokens >= 16 &&
+        (routed.gate.quant != shared.gate.quant || routed.down.quant != shared.down.quant)) {
+        int rc2 = run_experts(m, st, routed, MlpWeights{}, nullptr, mark_between);
+        if (rc2) return rc2;
+        return run_experts(m, st, MlpWeights{}, shared, shexp_out, -1);
+    }
     if (routed.present && routed.gate.quant != routed.up.quant)
         return fail(XABE_ERR_UNSUPPORTED_EXPERT_TYPE,
                     "routed gate and up stacks must share one format (found tags %d and %d)",
