@@ -513,9 +513,11 @@ void xo_compare(const float* c, const float* r, size_t n, xo_comparison* out) {
 /* selected experts are dequantized, as                                    */
 /* crates/xabe-engine/tests/moe_differential.rs:716-782 does.              */
 /* ===================================================================== */
+/* The processors this process may run on: a launcher that exports OMP_NUM_THREADS=1 for its
+ * ranks does not shrink the CPU baseline to one thread. */
 int xo_max_threads(void) {
 #ifdef _OPENMP
-    return omp_get_max_threads();
+    return omp_get_num_procs();
 #else
     return 1;
 #endif
