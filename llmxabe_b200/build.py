@@ -10,8 +10,8 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libxabe_moe_sm100.so")
 SOURCES = ["xabe_moe_api.cu"]
-HEADERS = ["common.cuh", "glue_kernels.cuh", "expert_kernels.cuh",
-           os.path.join("..", "..", "include", "xabe_moe.h")]
+HEADERS = sorted(f for f in os.listdir(CSRC) if f.endswith(".cuh")) + [
+    os.path.join("..", "..", "include", "xabe_moe.h")]
 
 
 def _nvcc() -> str:

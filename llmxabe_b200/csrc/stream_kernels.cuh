@@ -326,7 +326,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) k_expert_stream(StreamLaunc
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ int abort_flag;
     constexpr int ROWS_PER_TILE = MODE == MODE_GATEUP ? 8 : 128;
-    constexpr int NSP = MODE == MODE_GATEUP ? 1 : 2;  // spans a consumer warp owns
     const StreamSmem lay = stream_smem_layout(MODE, L.n_stages, L.tile_cap, L.x_stride);
     const StreamBars bars = stream_bars(smem, lay);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -462,21 +461,22 @@ __global__ void __launch_bounds__(kStreamThreads, 1) k_expert_stream(StreamLaunc
         // B fragments of this unit: column g of the group (dead columns read stale rows
         // and are never stored)
         const uint8_t* xrow = smem + lay.xbuf + (uint32_t)xb * 8u * L.x_stride + g * L.x_stride;
-        uint2 bf[NSP][16];
+        // MODE_DOWN re-reads its fragments from the activation rows for every tile (32 steps of
+        // fragments in registers spilled), so the rows stay owned until the unit ends.
+        uint2 bf[1][16];
 #pragma unroll
-        for (int sp = 0; sp < NSP; ++sp) {
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                int span = MODE == MODE_GATEUP ? gateup_span_of(w, h, n_spans) : sp;
-                bool on = MODE == MODE_GATEUP ? w < n_spans : sp < n_spans;
-                if (on) {
-                    if (quant == QUANT_Q6K) load_bfrags_half<QUANT_Q6K>(xrow, span, h, t, &bf[sp][8 * h]);
-                    else load_bfrags_half<QUANT_Q8_0>(xrow, span, h, t, &bf[sp][8 * h]);
-                }
+        for (int h = 0; h < 2; ++h) {
+            int span = gateup_span_of(w, h, n_spans);
+            bool on = MODE == MODE_GATEUP && w < n_spans;
+            if (on) {
+                if (quant == QUANT_Q6K) load_bfrags_half<QUANT_Q6K>(xrow, span, h, t, &bf[0][8 * h]);
+                else load_bfrags_half<QUANT_Q8_0>(xrow, span, h, t, &bf[0][8 * h]);
             }
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars.xempty[xb]);
+        if (MODE == MODE_GATEUP) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars.xempty[xb]);
+        }
         const uint32_t phase = (uint32_t)((((shared ? 0 : (size_t)expert * L.rows)) * row_bytes) & 15);
         const int t_begin = run * plan.tiles_per_unit;
         const int t_end = min(plan.row_tiles, t_begin + plan.tiles_per_unit);
@@ -502,15 +502,16 @@ __global__ void __launch_bounds__(kStreamThreads, 1) k_expert_stream(StreamLaunc
             } else {
                 const uint8_t* pa = tb + (size_t)down_row(w, g, 0, L.down_row_step) * row_bytes;
                 const uint8_t* pb = tb + (size_t)down_row(w, g, 1, L.down_row_step) * row_bytes;
+                for (int sp = 0; sp < n_spans; ++sp) {
 #pragma unroll
-                for (int sp = 0; sp < NSP; ++sp) {
-                    if (sp < n_spans) {
-#pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            if (quant == QUANT_Q6K)
-                                half_dispatch<QUANT_Q6K>(pa + sp * 210, pb + sp * 210, h, &bf[sp][8 * h], lane, acc);
-                            else
-                                half_dispatch<QUANT_Q8_0>(pa + sp * 272, pb + sp * 272, h, &bf[sp][8 * h], lane, acc);
+                    for (int h = 0; h < 2; ++h) {
+                        uint2 b1[8];
+                        if (quant == QUANT_Q6K) {
+                            load_bfrags_half<QUANT_Q6K>(xrow, sp, h, t, b1);
+                            half_dispatch<QUANT_Q6K>(pa + sp * 210, pb + sp * 210, h, b1, lane, acc);
+                        } else {
+                            load_bfrags_half<QUANT_Q8_0>(xrow, sp, h, t, b1);
+                            half_dispatch<QUANT_Q8_0>(pa + sp * 272, pb + sp * 272, h, b1, lane, acc);
                         }
                     }
                 }
@@ -577,6 +578,10 @@ __global__ void __launch_bounds__(kStreamThreads, 1) k_expert_stream(StreamLaunc
                     }
                 }
             }
+        }
+        if (MODE == MODE_DOWN) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars.xempty[xb]);
         }
     }
 }
