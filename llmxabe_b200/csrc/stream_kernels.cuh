@@ -32,7 +32,7 @@ namespace xabe {
 constexpr int kStreamGroups = 2;
 constexpr int kStreamGroupWarps = 8;
 constexpr int kStreamConsumerWarps = kStreamGroups * kStreamGroupWarps;
-constexpr int kStreamThreads = 32 * (1 + kStreamConsumerWarps);  // warp 0 is the producer
+constexpr int kStreamThreads = 32 * (2 + kStreamConsumerWarps);  // warp 0 streams weights, the last warp stages activations
 constexpr int kStreamMaxStages = 4;
 constexpr int kXRowPadBytes = 32;  // makes the B-fragment reads bank-conflict free
 
@@ -66,7 +66,15 @@ struct StreamLaunch {
     int x_rows_routed;    // rows the routed activation buffer holds
     int max_tokens;
     int down_row_step;    // MODE_DOWN: rows of one fragment half are this far apart (bank-conflict free reads)
+    int runs_override;    // tuning aid: > 0 fixes the runs per column group
 };
+
+// Buffers for the activation rows of a unit.  The producer stages a unit's rows while the consumers
+// still work on the unit before it, into the buffer of the unit before that one.  gate/up gives
+// its buffer back as soon as the fragments are in registers (two buffers); down reads the rows
+// for every tile and gives it back when the unit ends (three buffers of short rows).
+constexpr int kStreamMaxXBuffers = 3;
+__host__ __device__ constexpr int stream_x_buffers(int mode) { return mode == 0 ? 2 : 3; }
 
 struct StreamSmem {
     // byte offsets into dynamic shared memory, identical on host and device
@@ -79,18 +87,19 @@ __host__ __device__ inline StreamSmem stream_smem_layout(int mode, int n_stages,
     uint32_t stage_bytes = (mode == MODE_GATEUP ? 2u : 1u) * tile_cap;
     L.stages = 0;
     L.xbuf = L.stages + (uint32_t)n_stages * stage_bytes;
-    L.items = L.xbuf + 2u * 8u * x_stride;
-    L.red = L.items + 2u * 96u;
+    const uint32_t nxb = (uint32_t)stream_x_buffers(mode);
+    L.items = L.xbuf + nxb * 8u * x_stride;
+    L.red = L.items + nxb * 96u;
     L.bars = L.red + (mode == MODE_GATEUP ? (uint32_t)(kStreamGroups * 2 * kStreamGroupWarps * 4 * 32 * 4) : 0u);
-    L.total = L.bars + 8u * (2u * kStreamMaxStages + 4u + 4u * kStreamGroups) + 64u;
+    L.total = L.bars + 8u * (2u * kStreamMaxStages + 2u * kStreamMaxXBuffers + 4u * kStreamGroups) + 64u;
     return L;
 }
 
 struct StreamBars {
     uint64_t* full;      // [n_stages]  producer -> consumers (tx bytes)
     uint64_t* empty;     // [n_stages]  8 consumer warps -> producer
-    uint64_t* xfull;     // [2]
-    uint64_t* xempty;    // [2]  16 consumer warps -> producer
+    uint64_t* xfull;     // [kStreamMaxXBuffers]
+    uint64_t* xempty;    // [kStreamMaxXBuffers]  16 consumer warps -> producer
     uint64_t* redfull;   // [groups][2]  8 warps -> epilogue warp
     uint64_t* redempty;  // [groups][2]  epilogue warp -> 8 warps
 };
@@ -100,8 +109,8 @@ __device__ __forceinline__ StreamBars stream_bars(uint8_t* smem, const StreamSme
     b.full = (uint64_t*)(smem + L.bars);
     b.empty = b.full + kStreamMaxStages;
     b.xfull = b.empty + kStreamMaxStages;
-    b.xempty = b.xfull + 2;
-    b.redfull = b.xempty + 2;
+    b.xempty = b.xfull + kStreamMaxXBuffers;
+    b.redfull = b.xempty + kStreamMaxXBuffers;
     b.redempty = b.redfull + 2 * kStreamGroups;
     return b;
 }
@@ -134,16 +143,19 @@ __device__ __forceinline__ StreamPlan stream_plan(const StreamLaunch& L, int row
     int n_shared = L.has_shared ? (valid + 7) >> 3 : 0;
     p.n_groups = p.n_routed + n_shared;
     p.row_tiles = L.rows / rows_per_tile;
-    long total_tiles = (long)p.n_groups * p.row_tiles;
-    // enough units that every CTA gets about four, but runs as long as that allows:
-    // the activation rows are staged once per unit
-    long g = total_tiles / (4L * gridDim.x);
-    if (g < 1) g = 1;
-    if (g > 16) g = 16;
-    if (g > p.row_tiles) g = p.row_tiles;
-    p.tiles_per_unit = (int)g;
+    // Runs per column group: the smallest power of two that gives every CTA about two units or
+    // more.  Measured by sweeping the run count (64-token batch, 264 groups on 148 CTAs: 2 runs
+    // 105 us, 4 runs 108, 8 runs 111, 16 runs 115, 1 run 136; one token, 9 groups: 32 runs best):
+    // a unit has a fixed cost of about one tile time (staging the activation rows, loading the
+    // fragments), so beyond that point shorter runs only add units.
+    int best_r = 1;
+    if (L.runs_override > 0) {
+        best_r = min(L.runs_override, p.row_tiles);
+    } else {
+        while (best_r * 2 <= p.row_tiles && p.n_groups * best_r < 2 * (int)gridDim.x) best_r *= 2;
+    }
+    p.tiles_per_unit = (p.row_tiles + best_r - 1) / best_r;
     p.runs = (p.row_tiles + p.tiles_per_unit - 1) / p.tiles_per_unit;
-    p.tiles_per_unit = (p.row_tiles + p.runs - 1) / p.runs;  // even runs
     p.units = p.n_groups * p.runs;
     return p;
 }
@@ -325,6 +337,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) k_expert_stream(StreamLaunc
     pdl_wait();
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ int abort_flag;
+    __shared__ StreamPlan plan_shared;  // computed once, by thread 0
     constexpr int ROWS_PER_TILE = MODE == MODE_GATEUP ? 8 : 128;
     const StreamSmem lay = stream_smem_layout(MODE, L.n_stages, L.tile_cap, L.x_stride);
     const StreamBars bars = stream_bars(smem, lay);
@@ -336,7 +349,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) k_expert_stream(StreamLaunc
             mbar_init(&bars.full[i], 1);
             mbar_init(&bars.empty[i], kStreamGroupWarps);
         }
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < kStreamMaxXBuffers; ++i) {
             mbar_init(&bars.xfull[i], 1);
             mbar_init(&bars.xempty[i], kStreamConsumerWarps);
         }
@@ -346,24 +359,24 @@ __global__ void __launch_bounds__(kStreamThreads, 1) k_expert_stream(StreamLaunc
         }
         fence_mbar_init();
     }
+    if (threadIdx.x == 0) plan_shared = stream_plan(L, ROWS_PER_TILE);
     __syncthreads();
-    const StreamPlan plan = stream_plan(L, ROWS_PER_TILE);
+    const StreamPlan plan = plan_shared;
     const int n_spans = L.k / kSpanElems;
     const uint32_t stage_bytes = (MODE == MODE_GATEUP ? 2u : 1u) * L.tile_cap;
     volatile int* abortp = &abort_flag;
 
-    if (warp == 0) {
-        // ------------------------------ producer ------------------------------
+    if (warp == 0 || warp == 1 + kStreamConsumerWarps) {
+        // ------------------------------ producers ------------------------------
         if (lane != 0) return;
-        uint32_t it = 0, ux = 0;
-        for (int u = blockIdx.x; u < plan.units; u += gridDim.x, ++ux) {
-            const int cg = u / plan.runs, run = u % plan.runs;
+        constexpr int NXB = stream_x_buffers(MODE);
+        // Stages the activation rows and the descriptor of unit `u` (the CTA's `v`-th) in buffer
+        // xb, whose previous user was the CTA's (v - NXB)-th unit.
+        auto stage_x = [&](int u, uint32_t v, int xb, uint32_t xuse) -> bool {
+            const int cg = u / plan.runs;
             const bool shared = cg >= plan.n_routed;
-            const int quant = shared ? QS : QR;
-            const int row_bytes = n_spans * span_bytes_of(quant);
-            const int xb = ux & 1;
             int* desc = (int*)(smem + lay.items + xb * 96);  // [0..3] written here, [4..] item copy
-            if (ux >= 2 && !stream_wait(&bars.xempty[xb], ((ux >> 1) - 1) & 1, abortp, L.status)) return;
+            if (v >= (uint32_t)NXB && !stream_wait(&bars.xempty[xb], (xuse - 1) & 1, abortp, L.status)) return false;
             int expert, first, ncols;
             const int* item = nullptr;
             if (!shared) {
@@ -395,7 +408,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) k_expert_stream(StreamLaunc
             if (!sane) {
                 *abortp = 1;
                 atomicExch(L.status, STATUS_BAD_WORK_ITEM);
-                return;
+                return false;
             }
             desc[0] = expert;
             desc[1] = first;
@@ -411,6 +424,41 @@ __global__ void __launch_bounds__(kStreamThreads, 1) k_expert_stream(StreamLaunc
                 tma_bulk_g2s(xdst + c * L.x_stride, src, xrow_bytes, &bars.xfull[xb]);
             }
             if (!shared) tma_bulk_g2s(desc + 4, item + 4, 64u, &bars.xfull[xb]);  // flat ids + weights
+            return true;
+        };
+        if (warp != 0) {
+            // ---- activation stager: runs up to NXB units ahead of the consumers; its reads of
+            // the column-group descriptors never hold up the weight stream
+            int xb = 0;
+            uint32_t xuse = 0, v = 0;
+            for (int u = blockIdx.x; u < plan.units; u += gridDim.x, ++v) {
+                if (!stage_x(u, v, xb, xuse)) return;
+                if (++xb == NXB) {
+                    xb = 0;
+                    ++xuse;
+                }
+            }
+            return;
+        }
+        // ---- weight producer
+        uint32_t it = 0;
+        int expert_next = -1;
+        if ((int)blockIdx.x < plan.units) {
+            const int cg0 = (int)blockIdx.x / plan.runs;
+            if (cg0 < plan.n_routed) expert_next = L.work_items[(size_t)cg0 * kWorkItemInts];
+        }
+        for (int u = blockIdx.x; u < plan.units; u += gridDim.x) {
+            const int cg = u / plan.runs, run = u % plan.runs;
+            const bool shared = cg >= plan.n_routed;
+            const int quant = shared ? QS : QR;
+            const int row_bytes = n_spans * span_bytes_of(quant);
+            const int expert = expert_next;
+            {  // the next unit's expert id is fetched while this unit's tiles stream
+                const int un = u + (int)gridDim.x;
+                const int cgn = un / plan.runs;
+                if (un < plan.units && cgn < plan.n_routed) expert_next = L.work_items[(size_t)cgn * kWorkItemInts];
+            }
+            if (!shared && (expert < 0 || expert >= L.num_experts)) return;  // the stager records the bad group
             const uint8_t* wa = shared ? L.s_a : L.r_a;
             const uint8_t* wb = shared ? L.s_b : L.r_b;
             const size_t row0 = (shared ? 0 : (size_t)expert * L.rows);
@@ -440,14 +488,20 @@ __global__ void __launch_bounds__(kStreamThreads, 1) k_expert_stream(StreamLaunc
     const int w = cw % kStreamGroupWarps;   // warp within the group
     const int g = lane >> 2, t = lane & 3;
     float* red = (float*)(smem + lay.red);
-    uint32_t it = 0, ux = 0, gt = 0;  // ring tile counter, unit counter, this group's tile counter
-    for (int u = blockIdx.x; u < plan.units; u += gridDim.x, ++ux) {
+    constexpr int NXB = stream_x_buffers(MODE);
+    uint32_t it = 0, gt = 0;  // ring tile counter, this group's tile counter
+    int xb = -1;              // activation buffer of the unit and how often it was used before
+    uint32_t xuse = 0;
+    for (int u = blockIdx.x; u < plan.units; u += gridDim.x) {
         const int cg = u / plan.runs, run = u % plan.runs;
         const bool shared = cg >= plan.n_routed;
         const int quant = shared ? QS : QR;
         const int row_bytes = n_spans * span_bytes_of(quant);
-        const int xb = ux & 1;
-        if (!stream_wait(&bars.xfull[xb], (ux >> 1) & 1, abortp, L.status)) return;
+        if (++xb == NXB) {
+            xb = 0;
+            ++xuse;
+        }
+        if (!stream_wait(&bars.xfull[xb], xuse & 1, abortp, L.status)) return;
         const int* desc = (const int*)(smem + lay.items + xb * 96);
         const int expert = desc[0], first = desc[1], ncols = desc[2];
         int flat0 = 0, flat1 = 0;

@@ -487,6 +487,7 @@ int run_experts(xabe_moe* m, cudaStream_t st, const MlpWeights& routed, const Ml
     SL.num_experts = (int)g.num_experts;
     SL.max_tokens = (int)g.max_tokens;
     SL.x_rows_routed = (int)m->sorted_capacity;
+    if (const char* e = getenv("XABE_MOE_STREAM_RUNS")) SL.runs_override = atoi(e);  // tuning aid
     StreamShape gu = stream_shape(MODE_GATEUP, (int)g.intermediate, (int)g.hidden, qr, qs);
     if (gu.ok && !m->force_tile_kernels) {
         SL.r_a = L.r_a; SL.r_b = L.r_b; SL.s_a = L.s_a; SL.s_b = L.s_b;
