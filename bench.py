@@ -33,6 +33,8 @@ WORKLOADS = {
     "decode1": (1, 16, False),      # BASELINE config 0
     "decode3": (3, 16, True),       # BASELINE config 1, three sequences
     "decode64": (64, 16, True),     # BASELINE config 1, 64 tokens  (default)
+    "decode16": (16, 16, True),     # widths between the configs, for choosing kernel thresholds
+    "decode32": (32, 16, True),
     "prefill2048": (2048, 32, True),  # BASELINE config 2
     # BASELINE config 3 (expert-parallel stack, strong scaling): run_ep() below; tokens/layers from --ep-*
     "ep_prefill_stack": (16384, 64, True),

@@ -31,6 +31,7 @@ namespace xabe {
 
 constexpr int kStreamGroups = 2;
 constexpr int kStreamGroupWarps = 8;
+constexpr int kGateupSlots = kStreamGroupWarps + 1;  // partial sums of a gate/up row, see gateup_span_of
 constexpr int kStreamConsumerWarps = kStreamGroups * kStreamGroupWarps;
 constexpr int kStreamThreads = 32 * (2 + kStreamConsumerWarps);  // warp 0 streams weights, the last warp stages activations
 constexpr int kStreamMaxStages = 4;
@@ -90,7 +91,7 @@ __host__ __device__ inline StreamSmem stream_smem_layout(int mode, int n_stages,
     const uint32_t nxb = (uint32_t)stream_x_buffers(mode);
     L.items = L.xbuf + nxb * 8u * x_stride;
     L.red = L.items + nxb * 96u;
-    L.bars = L.red + (mode == MODE_GATEUP ? (uint32_t)(kStreamGroups * 2 * kStreamGroupWarps * 4 * 32 * 4) : 0u);
+    L.bars = L.red + (mode == MODE_GATEUP ? (uint32_t)(kStreamGroups * 2 * kGateupSlots * 4 * 32 * 4) : 0u);
     L.total = L.bars + 8u * (2u * kStreamMaxStages + 2u * kStreamMaxXBuffers + 4u * kStreamGroups) + 64u;
     return L;
 }
@@ -323,6 +324,12 @@ __device__ __forceinline__ int down_row(int w, int g, int half, int step) {
 __device__ __forceinline__ int gateup_span_of(int w, int h, int n_spans) {
     return h == 0 ? w : (w + 1) % n_spans;
 }
+// Partial sums of a gate/up row, in the order they are added: slot w < n_spans - 1 is half 0 of
+// span w continued by half 1 of span w + 1; slot n_spans - 1 is half 0 of the last span alone;
+// the idle slots (n_spans < 8) are zero; and half 1 of span 0 is a sum of its own, the "wrap"
+// slot, added last.  Keeping the wrapped-around half out of the last slot lets a kernel that
+// walks the spans in ascending order for one set of rows (k_gateup_rows) form the same sums in
+// the same order without seeing a span twice.
 
 // ---------------------------------------------------------------------------
 // The kernel.  MODE_GATEUP: tile = 8 gate rows + the same 8 up rows (fragment
@@ -520,9 +527,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) k_expert_stream(StreamLaunc
         uint2 bf[1][16];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            int span = gateup_span_of(w, h, n_spans);
-            bool on = MODE == MODE_GATEUP && w < n_spans;
-            if (on) {
+            const int span = gateup_span_of(w, h, n_spans);
+            if (MODE == MODE_GATEUP && w < n_spans) {
                 if (quant == QUANT_Q6K) load_bfrags_half<QUANT_Q6K>(xrow, span, h, t, &bf[0][8 * h]);
                 else load_bfrags_half<QUANT_Q8_0>(xrow, span, h, t, &bf[0][8 * h]);
             }
@@ -543,14 +549,31 @@ __global__ void __launch_bounds__(kStreamThreads, 1) k_expert_stream(StreamLaunc
             const uint8_t* tb = smem + lay.stages + (uint32_t)st * stage_bytes +
                                 (uint32_t)((phase + (size_t)tile * ROWS_PER_TILE * row_bytes) & 15);
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            float wrap[4] = {0.f, 0.f, 0.f, 0.f};  // gate/up, last slot only: half 1 of span 0
+            const bool wraps = MODE == MODE_GATEUP && n_spans > 1 && w == n_spans - 1;
             if (MODE == MODE_GATEUP) {
                 if (w < n_spans) {
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         const uint8_t* pa = tb + g * row_bytes + gateup_span_of(w, h, n_spans) * span_bytes_of(quant);
                         const uint8_t* pb = pa + L.tile_cap;
+                        if (h == 1 && wraps) {  // the wrap slot starts from zero; the last slot is parked in `wrap`
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                wrap[i] = acc[i];
+                                acc[i] = 0.f;
+                            }
+                        }
                         if (quant == QUANT_Q6K) half_dispatch<QUANT_Q6K>(pa, pb, h, &bf[0][8 * h], lane, acc);
                         else half_dispatch<QUANT_Q8_0>(pa, pb, h, &bf[0][8 * h], lane, acc);
+                    }
+                    if (wraps) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float v = acc[i];
+                            acc[i] = wrap[i];
+                            wrap[i] = v;
+                        }
                     }
                 }
             } else {
@@ -574,11 +597,15 @@ __global__ void __launch_bounds__(kStreamThreads, 1) k_expert_stream(StreamLaunc
             if (lane == 0) mbar_arrive(&bars.empty[st]);  // the ring stage may be refilled
             if (MODE == MODE_GATEUP) {
                 const int buf = gt & 1;
-                float* rb = red + ((size_t)(gi * 2 + buf) * kStreamGroupWarps) * 128;
+                float* rb = red + ((size_t)(gi * 2 + buf) * kGateupSlots) * 128;
                 if (gt >= 2 && !stream_wait(&bars.redempty[gi * 2 + buf], ((gt >> 1) - 1) & 1, abortp, L.status))
                     return;
 #pragma unroll
                 for (int i = 0; i < 4; ++i) rb[(w * 4 + i) * 32 + lane] = acc[i];
+                if (wraps) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) rb[(kStreamGroupWarps * 4 + i) * 32 + lane] = wrap[i];
+                }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bars.redfull[gi * 2 + buf]);
                 if (w == (int)(gt % kStreamGroupWarps)) {  // the epilogue rotates over the group's warps
@@ -589,6 +616,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) k_expert_stream(StreamLaunc
                         float s = rb[(0 * 4 + i) * 32 + lane];
 #pragma unroll
                         for (int ww = 1; ww < kStreamGroupWarps; ++ww) s += rb[(ww * 4 + i) * 32 + lane];
+                        if (n_spans > 1) s += rb[(kStreamGroupWarps * 4 + i) * 32 + lane];
                         tot[i] = s;
                     }
                     __syncwarp();
