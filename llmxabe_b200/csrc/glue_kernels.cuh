@@ -64,10 +64,11 @@ __global__ void k_rows_to_half(const float* __restrict__ x, __half* __restrict__
 // carries all 256 lanes of one expert (lane l holds lanes l, l+32, ...), so
 // the result is bit-identical for every token-tile width TT.
 // The four expert rows of a CTA (contiguous in the router tensor) arrive in
-// shared memory through ONE bulk TMA copy: every byte of the row is in flight
-// at once instead of one dependent DRAM round trip per loop iteration.
+// shared memory through ONE bulk TMA copy, and so do the TT activation rows of
+// each token tile (contiguous rows of `x`): every byte is in flight at once
+// instead of one dependent L2 round trip per loop iteration and token.
 // grid: (ceil(E / 4), ceil(max_tokens / (TT * tiles_per_cta))), block 128.
-// dynamic shared memory: 4 * hidden * 4 bytes.
+// dynamic shared memory: (4 + TT) * hidden * 4 bytes.
 // ---------------------------------------------------------------------------
 template <int TT>
 __global__ void __launch_bounds__(128) k_router_logits(const float* __restrict__ w,
@@ -80,7 +81,8 @@ __global__ void __launch_bounds__(128) k_router_logits(const float* __restrict__
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(128) float w_rows[];
-    __shared__ __align__(8) uint64_t bar;
+    __shared__ __align__(8) uint64_t bar, xbar;
+    float* x_rows = w_rows + (size_t)4 * hidden;
     int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     int e0 = blockIdx.x * 4;
     int e = e0 + warp;
@@ -91,40 +93,49 @@ __global__ void __launch_bounds__(128) k_router_logits(const float* __restrict__
         int rows = min(4, num_experts - e0);
         uint32_t bytes = (uint32_t)rows * hidden * 4u;
         mbar_init(&bar, 1);
+        mbar_init(&xbar, 1);
         fence_mbar_init();
         mbar_expect_tx(&bar, bytes);
         tma_bulk_g2s(w_rows, w + (size_t)e0 * hidden, bytes, &bar);
+        uint32_t xbytes = (uint32_t)min(TT, live - t_first) * hidden * 4u;
+        mbar_expect_tx(&xbar, xbytes);
+        tma_bulk_g2s(x_rows, x + (size_t)t_first * hidden, xbytes, &xbar);
     }
     __syncthreads();
     if (!__syncthreads_and(mbar_wait_bounded(&bar, 0, status))) return;
-    if (e >= num_experts) return;
+    const bool active = e < num_experts;
     const float* wrow = w_rows + (size_t)warp * hidden;
     for (int tile = 0; tile < tiles_per_cta; ++tile) {
         int t0 = t_first + tile * TT;
         if (t0 >= live) break;
+        if (tile > 0) {
+            __syncthreads();  // every warp has left the rows of the tile before
+            if (threadIdx.x == 0) {
+                uint32_t xbytes = (uint32_t)min(TT, live - t0) * hidden * 4u;
+                mbar_expect_tx(&xbar, xbytes);
+                tma_bulk_g2s(x_rows, x + (size_t)t0 * hidden, xbytes, &xbar);
+            }
+        }
+        if (!__syncthreads_and(mbar_wait_bounded(&xbar, tile & 1, status))) return;
+        if (!active) continue;
         float acc[8][TT];
 #pragma unroll
         for (int g = 0; g < 8; ++g)
 #pragma unroll
             for (int u = 0; u < TT; ++u) acc[g][u] = 0.0f;
-        const float* xr[TT];
-#pragma unroll
-        for (int u = 0; u < TT; ++u) {
-            int t = t0 + u < live ? t0 + u : live - 1;
-            xr[u] = x + (size_t)t * hidden;
-        }
-        // hidden is a multiple of 256 (checked when the handle is created).  Loads are
-        // issued in batches of eight before the multiply-adds that consume them, so a
-        // warp keeps eight cache lines in flight instead of stalling on each one.
+        // hidden is a multiple of 256 (checked when the handle is created).  Rows of the tile
+        // past the live tokens were not copied; their sums are formed from whatever the buffer
+        // holds and never stored.
         for (int jc = 0; jc < hidden; jc += 256) {
             float wv[8];
 #pragma unroll
             for (int g = 0; g < 8; ++g) wv[g] = wrow[jc + g * 32 + lane];
 #pragma unroll
             for (int u = 0; u < TT; ++u) {
+                const float* xr = x_rows + (size_t)u * hidden;
                 float xv[8];
 #pragma unroll
-                for (int g = 0; g < 8; ++g) xv[g] = __ldg(xr[u] + jc + g * 32 + lane);
+                for (int g = 0; g < 8; ++g) xv[g] = xr[jc + g * 32 + lane];
 #pragma unroll
                 for (int g = 0; g < 8; ++g) acc[g][u] = fmaf(wv[g], xv[g], acc[g][u]);
             }

@@ -686,10 +686,12 @@ int launch_router(xabe_moe* m, cudaStream_t st, const float* router, const float
         return g.hidden == 2048 ? go_wide(k_router_logits_wide<8>) : go_wide(k_router_logits_wide<4>);
     }
     dim3 block(128);
-    size_t smem = (size_t)4 * g.hidden * sizeof(float);
-    if (smem > 200 * 1024) return fail(XABE_ERR_UNSUPPORTED_GEOMETRY, "router rows do not fit shared memory");
+    if (((uintptr_t)m->normed & 15) != 0 || (g.hidden * sizeof(float)) % 16 != 0)
+        return fail(XABE_ERR_INVALID_ARGUMENT, "normed rows must be 16-byte aligned");
     unsigned ex = (g.num_experts + 3) / 4;
     auto go = [&](auto kern, int tt) -> int {
+        const size_t smem = (size_t)(4 + tt) * g.hidden * sizeof(float);  // expert rows + one token tile
+        if (smem > 200 * 1024) return fail(XABE_ERR_UNSUPPORTED_GEOMETRY, "router rows do not fit shared memory");
         // wide passes share one staged copy of the rows between eight token tiles
         int tiles_per_cta = g.max_tokens > 128 ? 8 : 1;
         unsigned ty = (g.max_tokens + tt * tiles_per_cta - 1) / (tt * tiles_per_cta);
@@ -699,9 +701,11 @@ int launch_router(xabe_moe* m, cudaStream_t st, const float* router, const float
                             tiles_per_cta, m->status));
         return XABE_OK;
     };
-    if (g.max_tokens == 1) return go(k_router_logits<1>, 1);
-    if (g.max_tokens <= 4) return go(k_router_logits<4>, 4);
-    return go(k_router_logits<8>, 8);
+    // the widest token tile that the handle can use and that fits beside the four expert rows
+    const size_t row_bytes = (size_t)g.hidden * sizeof(float);
+    if (g.max_tokens > 4 && 12 * row_bytes <= 200 * 1024) return go(k_router_logits<8>, 8);
+    if (g.max_tokens > 1 && 8 * row_bytes <= 200 * 1024) return go(k_router_logits<4>, 4);
+    return go(k_router_logits<1>, 1);
 }
 
 // `logits` NULL: the routing decision is already in the handle's topk buffers; only the tables are built.
