@@ -46,8 +46,8 @@ WORKLOADS = {
 }
 
 # DRAM bytes (read + write) of the dominant kernel per launch, from the ncu captures summarised under
-# profiles/ (k_expert_stream_decode64.md, k_prefill_gemm_prefill2048.md); none taken for the others
-NCU_TRAFFIC_BYTES = {"decode64": 332.6e6 + 0.6e6, "prefill2048": 467.0e6 + 16.5e6}
+# profiles/ (k_gateup_rows_decode64.md, k_prefill_gemm_prefill2048.md); none taken for the others
+NCU_TRAFFIC_BYTES = {"decode64": 329.3e6 + 4.3e6, "prefill2048": 467.0e6 + 16.5e6}
 
 Q6K_EXPERT_BYTES = 3 * (512 * 2048 // 256) * 210   # 2,580,480
 ROUTER_BYTES = 256 * 2048 * 4
@@ -361,7 +361,7 @@ def run_ours(args) -> dict:
                 "h2d_bytes_per_step": tokens * H * 4, "d2h_bytes_per_step": tokens * H * 4},
         "gpu_launches": launches_per_step * args.steps, "ms_per_step_eager": ms_eager, "cuda_graph": graph is not None,
         "clocks": clocks,
-        "roofline": {"bound": "hbm", "kernel": "gate/up + SwiGLU launch (k_expert_stream<GATEUP>; k_prefill_gemm<GATEUP> from 512 tokens)", "achieved": achieved, "peak": peak,
+        "roofline": {"bound": "hbm", "kernel": "gate/up + SwiGLU launch (k_expert_stream<GATEUP> below 16 tokens, k_gateup_rows from 16, k_prefill_gemm<GATEUP> from 512)", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
                      "peak_source": peak_src,
                      "algorithmic_bytes_per_launch": gu_bytes, "ms_per_launch": gateup_ms},
