@@ -35,6 +35,8 @@ WORKLOADS = {
     "decode64": (64, 16, True),     # BASELINE config 1, 64 tokens  (default)
     "decode16": (16, 16, True),     # widths between the configs, for choosing kernel thresholds
     "decode32": (32, 16, True),
+    # the MoE half of Forward::body: --stack-layers layers chained (l_out -> next residual) in ONE graph
+    "decode64_stack": (64, 16, True),
     "prefill2048": (2048, 32, True),  # BASELINE config 2
     # BASELINE config 3 (expert-parallel stack, strong scaling): run_ep() below; tokens/layers from --ep-*
     "ep_prefill_stack": (16384, 64, True),
@@ -394,6 +396,99 @@ def run_ours(args) -> dict:
     return out if rank == 0 else {}
 
 
+def run_stack(args) -> dict:
+    """`--stack-layers` MoE layers of config 1's geometry driven as the reference's Forward::body drives
+    them (crates/xabe-engine/src/forward.rs:3497-3618): one handle, each layer's l_out the next layer's
+    residual, the whole pass one CUDA graph, the token count a device scalar.  A step = one pass over the
+    stack; `value` stays per layer (tokens x layers / time) so it compares with the one-layer workloads."""
+    import torch
+
+    from llmxabe_b200 import synth
+    from llmxabe_b200.moe import MoeGeometry
+    from llmxabe_b200.stack import MoeStack
+
+    if int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        raise RuntimeError("decode64_stack is a one-GPU workload")
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the MoE path has no CPU fallback")
+    torch.cuda.set_device(0)
+    tokens, block_size, zipf = WORKLOADS[args.workload]
+    H, n_layers = 2048, args.stack_layers
+    shared_q = synth.Q8_0 if args.shared_quant == "q8_0" else synth.Q6K
+    layers = [synth.moe_layer_on_device(seed=0, layer=i, zipf=zipf, shared_quant=shared_q) for i in range(n_layers)]
+    stack = MoeStack(MoeGeometry.qwen3_6(block_size, tokens), layers)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(4242)
+    x = torch.randn(tokens, H, device="cuda", generator=gen)
+    hx = x.cpu().pin_memory()
+    hout = torch.empty(tokens, H).pin_memory()
+    stream = torch.cuda.current_stream()
+    distinct = []
+    stack.run(x, on_waypoint=lambda i, h: distinct.append(
+        int(torch.unique(stack.block.buffers().topk_ids[:tokens]).numel())))
+    torch.cuda.synchronize()
+    d_mean = sum(distinct) / len(distinct)
+    stack.capture()
+
+    def step(_i):
+        stack.replay()
+
+    def step_host(_i):  # the step's input from pinned host memory, its result back to the host
+        stack.hidden_in[:tokens].copy_(hx, non_blocking=True)
+        stack.replay()
+        hout.copy_(stack.hidden_out[:tokens], non_blocking=True)
+        stream.synchronize()
+
+    def timed(fn, steps):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(steps):
+            fn(i)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    t0 = time.perf_counter()
+    i = 0
+    while i < max(args.warmup, 3) or time.perf_counter() - t0 < 0.3:
+        step(i)
+        i += 1
+    steps = max(3, min(args.steps, 50))
+    sampler = ClockSampler(0)
+    sampler.start()
+    ms = timed(step, steps)
+    clocks = sampler.stop()
+    for i in range(3):
+        step_host(i)
+    ms_e2e = timed(step_host, steps)
+    status = stack.block.moe.device_status()
+    peak, peak_src = measured_peaks()
+    layer_bytes = layer_algorithmic_bytes(d_mean, tokens, args.shared_quant == "q8_0")
+    achieved = n_layers * layer_bytes / (ms * 1e-3) / 1e9
+    return {
+        "metric": METRIC, "value": tokens * n_layers / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16 activations x exact Q6_K codes, fp32 scales+accumulate",
+        "data": "synthetic",
+        "config": {"workload": args.workload, "tokens_per_rank": tokens, "layers": n_layers, "experts": 256,
+                   "top_k": 8, "hidden": 2048, "intermediate": 512, "quant": "Q6_K",
+                   "shared_expert_quant": args.shared_quant, "bucket": block_size,
+                   "distinct_experts_mean": d_mean, "stack_passes_per_s": 1e3 / ms,
+                   "stack_tokens_per_s": tokens * 1e3 / ms,
+                   "l2": f"every layer has its own weights ({n_layers * layer_bytes / 1e9:.1f} GB per pass, L2 126 MB)",
+                   "parallelism": "one GPU"},
+        "e2e": {"value": tokens * n_layers / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": tokens * H * 4, "d2h_bytes_per_step": tokens * H * 4},
+        "gpu_launches": 7 * n_layers * steps, "cuda_graph": True, "clocks": clocks,
+        "roofline": {"bound": "hbm", "kernel": "whole stack pass (all launches of all layers, one graph)",
+                     "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                     "peak_source": peak_src, "algorithmic_bytes_per_launch": n_layers * layer_bytes,
+                     "ms_per_launch": ms},
+        "device_status": status,
+    }
+
+
 def run_ep(args) -> dict:
     """BASELINE config 3: a stack of MoE layers (Q6_K experts, Q8_0 shared expert), `--ep-tokens` tokens,
     experts sharded over the ranks with NCCL all-to-all dispatch/combine.  Strong scaling: the global
@@ -639,6 +734,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the timed CPU baseline")
     ap.add_argument("--shared-quant", default="q6_k", choices=["q6_k", "q8_0"],
                     help="format of the shared expert in the MoE workloads (the shipped file's is Q8_0)")
+    ap.add_argument("--stack-layers", type=int, default=40, help="layers of the decode64_stack workload")
     ap.add_argument("--ep-tokens", type=int, default=16384)
     ap.add_argument("--ep-layers", type=int, default=40)
     ap.add_argument("--ep-nccl", dest="ep_peer_memory", action="store_false",
@@ -654,6 +750,8 @@ def main():
         out = run_ep(args)
     elif args.workload.startswith("dense"):
         out = run_dense(args)
+    elif args.workload == "decode64_stack":
+        out = run_stack(args)
     else:
         out = run_ours(args)
     if out:

@@ -237,6 +237,23 @@ int xabe_moe_block_forward(xabe_moe* m, void* stream, const xabe_moe_layer_weigh
                            const float* residual, size_t residual_len, int tokens,
                            float* ffn_out, size_t ffn_out_len, float* l_out, size_t l_out_len);
 
+/* The MoE half of Forward::body (crates/xabe-engine/src/forward.rs:3497-3618)
+ * for a stack whose layers are MoE blocks only (the mixers between them are
+ * not part of this library): layer i runs xabe_moe_block_forward with layer
+ * i's weights on the hidden state layer i - 1 left, `hidden_a` holding the
+ * input and the two buffers alternating as residual and l_out, as
+ * `mixer_out` and `hidden_state` do there.  Launches only: nothing reads host
+ * memory, allocates or synchronises, and the live token count is the device
+ * scalar, so the call can be captured once as a CUDA graph and replayed at any
+ * `tokens` published with xabe_moe_set_valid_tokens.  Every layer's tensors
+ * are checked before the first launch (check_stack, moe.rs:6729-6746).
+ * `*final_hidden` (may be NULL) receives the buffer that holds the last
+ * layer's l_out (`hidden_a` for an even layer count); `ffn_out` holds the last
+ * layer's. */
+int xabe_moe_stack_forward(xabe_moe* m, void* stream, const xabe_moe_layer_weights* layers, int n_layers,
+                           float* hidden_a, float* hidden_b, size_t hidden_len, int tokens,
+                           float* ffn_out, size_t ffn_out_len, float** final_hidden);
+
 /* The same call for a caller that holds HOST buffers: copies `tokens` rows of
  * `host_residual` to the device, runs the block and copies `ffn_out`/`l_out`
  * rows back, all on `stream`; returns after enqueueing (synchronise the

@@ -70,6 +70,8 @@ SYMBOLS = {
     "xabe_moe_shared_expert": (_i, [_vp, _vp, QuantTensorC, QuantTensorC, QuantTensorC, _vp, _vp]),
     "xabe_moe_block_forward": (_i, [_vp, _vp, C.POINTER(LayerWeightsC), _vp, _sz, _i, _vp, _sz, _vp, _sz]),
     "xabe_moe_block_forward_host": (_i, [_vp, _vp, C.POINTER(LayerWeightsC), _vp, _i, _vp, _vp]),
+    "xabe_moe_stack_forward": (_i, [_vp, _vp, C.POINTER(LayerWeightsC), _i, _vp, _vp, _sz, _i, _vp, _sz,
+                                    C.POINTER(_vp)]),
     "xabe_dense_ffn_block_forward": (_i, [_vp, _vp, _vp, QuantTensorC, QuantTensorC, QuantTensorC, _vp, _sz,
                                           _i, _vp, _sz, _vp, _sz]),
     "xabe_moe_buffers": (_i, [_vp, C.POINTER(BufferViewC)]),

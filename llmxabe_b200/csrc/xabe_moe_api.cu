@@ -1317,6 +1317,43 @@ int xabe_moe_block_forward(xabe_moe* m, void* stream, const xabe_moe_layer_weigh
     return XABE_OK;
 }
 
+int xabe_moe_stack_forward(xabe_moe* m, void* stream, const xabe_moe_layer_weights* layers, int n_layers,
+                           float* hidden_a, float* hidden_b, size_t hidden_len, int tokens, float* ffn_out,
+                           size_t ffn_out_len, float** final_hidden) {
+    if (!m || !layers || !hidden_a || !hidden_b || !ffn_out || n_layers < 0)
+        return fail(XABE_ERR_INVALID_ARGUMENT, "null argument to stack_forward");
+    if (hidden_a == hidden_b) return fail(XABE_ERR_INVALID_ARGUMENT, "stack_forward needs two distinct hidden-state buffers");
+    int rc = check_routed(m, "stack_forward");
+    if (rc) return rc;
+    const auto& g = m->g;
+    if (tokens < 0 || (uint32_t)tokens > g.max_tokens)
+        return fail(XABE_ERR_TOO_MANY_TOKENS, "%d tokens exceeds the %u this block was sized for", tokens,
+                    g.max_tokens);
+    const size_t n = (size_t)g.max_tokens * g.hidden;
+    if (hidden_len != n)
+        return fail(XABE_ERR_BUFFER_LENGTH, "hidden state must hold %zu floats, holds %zu", n, hidden_len);
+    if (ffn_out_len != n)
+        return fail(XABE_ERR_BUFFER_LENGTH, "ffn_out must hold %zu floats, holds %zu", n, ffn_out_len);
+    // every layer is checked before the first launch (check_stack, moe.rs:6729-6746)
+    for (int i = 0; i < n_layers; ++i) {
+        const xabe_moe_layer_weights* w = layers + i;
+        if (!w->post_norm || !w->router || !w->shared_gate_inp)
+            return fail(XABE_ERR_INVALID_ARGUMENT, "null dense weight in the weights of layer %d", i);
+        if ((rc = check_mlp(m, "routed", w->gate_exps, w->up_exps, w->down_exps, g.num_experts))) return rc;
+        if ((rc = check_mlp(m, "shared", w->shared_gate, w->shared_up, w->shared_down, 1))) return rc;
+    }
+    float* src = hidden_a;
+    float* dst = hidden_b;
+    for (int i = 0; i < n_layers; ++i) {
+        if ((rc = xabe_moe_block_forward(m, stream, layers + i, src, n, tokens, ffn_out, n, dst, n))) return rc;
+        float* t = src;
+        src = dst;
+        dst = t;
+    }
+    if (final_hidden) *final_hidden = src;
+    return XABE_OK;
+}
+
 int xabe_moe_block_forward_host(xabe_moe* m, void* stream, const xabe_moe_layer_weights* w,
                                 const float* host_residual, int tokens, float* host_ffn_out, float* host_l_out) {
     if (!m || !host_residual) return fail(XABE_ERR_INVALID_ARGUMENT, "null argument to block_forward_host");
