@@ -394,6 +394,47 @@ int xabe_moe_block_forward_typed(xabe_moe* m, void* stream, const xabe_moe_layer
  * arithmetic.  `sink` is 4 bytes of device memory (practically never written). */
 int xabe_stream_read(void* stream, const void* dev_bytes, size_t n_bytes, void* sink);
 
+/* ---------------------------------------------------------------------------
+ * LM head (crates/xabe-cuda/src/kernels/lm_head.rs): logits = W x over the
+ * whole vocabulary, W in file layout.  Next to the MoE path because it is the
+ * same streaming machinery on the largest single tensor of the model.
+ * --------------------------------------------------------------------------- */
+
+/* LmHeadGeometry (lm_head.rs:1304-1314) */
+typedef struct xabe_lm_head_geometry {
+    uint32_t hidden;
+    uint32_t vocab;
+    uint32_t max_tokens;
+} xabe_lm_head_geometry;
+
+typedef struct xabe_lm_head xabe_lm_head;
+
+/* LmHeadKernels::new (lm_head.rs:1528-1680): validates the geometry (hidden a
+ * multiple of 256, at most 4096) and allocates the handle's scratch (two f16
+ * copies of the activations).  The only call of this group that allocates. */
+int xabe_lm_head_create(const xabe_lm_head_geometry* geometry, int device, xabe_lm_head** out);
+void xabe_lm_head_destroy(xabe_lm_head* m);
+
+/* LmHeadKernels::forward (lm_head.rs:1695-1937).  `weight` is the head tensor
+ * [vocab][hidden] in file layout, XABE_QUANT_Q8_0 (HeadFormat::Q8_0, the
+ * Qwen3.6 head) or XABE_QUANT_Q6_K (HeadFormat::Q6K); the dense 16-bit and the
+ * community formats return XABE_ERR_UNSUPPORTED_DENSE_TYPE.  `hidden_states`
+ * is [max_tokens][hidden] f32 and `logits` [max_tokens][vocab] f32, both
+ * length-checked; rows at and past `tokens` are neither read nor written.  A
+ * batch costs ceil(tokens / 8) passes over the weights (weight_passes,
+ * lm_head.rs:1380-1383).  Launches only. */
+int xabe_lm_head_forward(xabe_lm_head* m, void* stream, xabe_quant_tensor weight, const float* hidden_states,
+                         size_t hidden_states_len, int tokens, float* logits, size_t logits_len);
+
+/* LmHeadKernels::argmax (lm_head.rs:1950-2015): out[t] = index of the largest
+ * logit of row t, ties to the lower index (gemv.rs:102-111).  `out` holds
+ * max_tokens int32 on the device. */
+int xabe_lm_head_argmax(xabe_lm_head* m, void* stream, const float* logits, size_t logits_len, int tokens,
+                        int32_t* out);
+
+/* As xabe_moe_device_status, for this handle's kernels. */
+int xabe_lm_head_device_status(xabe_lm_head* m, void* stream, int* status_out);
+
 #ifdef __cplusplus
 }
 #endif

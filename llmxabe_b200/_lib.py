@@ -30,6 +30,10 @@ class LayerWeightsC(C.Structure):
                 ("shared_gate", QuantTensorC), ("shared_up", QuantTensorC), ("shared_down", QuantTensorC)]
 
 
+class HeadGeometryC(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("hidden", "vocab", "max_tokens")]
+
+
 class BufferViewC(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in
                 ("valid_tokens", "topk_ids", "topk_weights", "sorted_token_ids", "expert_ids",
@@ -83,6 +87,11 @@ SYMBOLS = {
     "xabe_stream_read": (_i, [_vp, _vp, _sz, _vp]),
     "xabe_moe_block_forward_typed": (_i, [_vp, _vp, _vp, _vp, _i, _sz, _i, _vp, _sz, _vp, _sz]),
     "xabe_shared_expert_noalloc": (_i, [_vp, QuantTensorC, QuantTensorC, QuantTensorC, _i, _i, _vp, _i, _vp]),
+    "xabe_lm_head_create": (_i, [C.POINTER(HeadGeometryC), _i, C.POINTER(_vp)]),
+    "xabe_lm_head_destroy": (None, [_vp]),
+    "xabe_lm_head_forward": (_i, [_vp, _vp, QuantTensorC, _vp, _sz, _i, _vp, _sz]),
+    "xabe_lm_head_argmax": (_i, [_vp, _vp, _vp, _sz, _i, _vp]),
+    "xabe_lm_head_device_status": (_i, [_vp, _vp, C.POINTER(_i)]),
 }
 
 

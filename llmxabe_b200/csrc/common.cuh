@@ -94,6 +94,16 @@ __device__ __forceinline__ void mma_f16_16816(float (&d)[4], const uint32_t (&a)
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f), "f"(0.f), "f"(0.f), "f"(0.f));
 }
 
+// The same product added to `c`.
+__device__ __forceinline__ void mma_f16_16816_acc(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
+                                                  const float (&c)[4]) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%10,%11,%12,%13};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+}
+
 // 32-bit word at a 2-byte-aligned shared-memory address.
 __device__ __forceinline__ uint32_t ld32_al2(const uint8_t* p) {
     uintptr_t a = (uintptr_t)p;

@@ -207,9 +207,24 @@ __device__ __forceinline__ void q6k_codes4(uint32_t ql0, uint32_t ql1, uint32_t 
 // of step `step` of that half.  Each of the four lanes that share a row pair
 // converts the scales of the steps it owns (step % 4 == t); the others fetch
 // them with a shuffle.
-template <int QUANT, bool MIS>
+// With SPLIT the activations come as two f16 parts (value = hi + lo, fragments `bf` and `bl`):
+// the step's product is A * lo added to A * hi inside the tensor core, which keeps about 22 bits
+// of an fp32 activation (the LM head, whose largest logit is the sampled token).
+template <bool SPLIT>
+__device__ __forceinline__ void step_mma(float (&d)[4], const uint32_t (&a)[4], const uint2* bf, const uint2* bl,
+                                         int i) {
+    if (SPLIT) {
+        float lo[4];
+        mma_f16_16816(lo, a, bl[i].x, bl[i].y);
+        mma_f16_16816_acc(d, a, bf[i].x, bf[i].y, lo);
+    } else {
+        mma_f16_16816(d, a, bf[i].x, bf[i].y);
+    }
+}
+
+template <int QUANT, bool MIS, bool SPLIT = false>
 __device__ __forceinline__ void stream_half(const uint8_t* pa, const uint8_t* pb, int h, const uint2* bf, int lane,
-                                            float (&acc)[4]) {
+                                            float (&acc)[4], const uint2* bl = nullptr) {
     const uint32_t bias32 = 0x64206420u;   // half2(1056): 1024 + 32
     const uint32_t bias128 = 0x64806480u;  // half2(1152): 1024 + 128
     const int t = lane & 3;
@@ -241,7 +256,7 @@ __device__ __forceinline__ void stream_half(const uint8_t* pa, const uint8_t* pb
                 a[2] = bytes23_to_h2(ra[j], bias32);
                 a[3] = bytes23_to_h2(rb[j], bias32);
                 float d[4];
-                mma_f16_16816(d, a, bf[c * 4 + j].x, bf[c * 4 + j].y);
+                step_mma<SPLIT>(d, a, bf, bl, c * 4 + j);
                 acc[0] = fmaf(dsa, d[0], acc[0]);
                 acc[1] = fmaf(dsa, d[1], acc[1]);
                 acc[2] = fmaf(dsb, d[2], acc[2]);
@@ -271,7 +286,7 @@ __device__ __forceinline__ void stream_half(const uint8_t* pa, const uint8_t* pb
             a[2] = bytes23_to_h2(wa, bias128);
             a[3] = bytes23_to_h2(wb, bias128);
             float d[4];
-            mma_f16_16816(d, a, bf[step].x, bf[step].y);
+            step_mma<SPLIT>(d, a, bf, bl, step);
             acc[0] = fmaf(dsa, d[0], acc[0]);
             acc[1] = fmaf(dsa, d[1], acc[1]);
             acc[2] = fmaf(dsb, d[2], acc[2]);

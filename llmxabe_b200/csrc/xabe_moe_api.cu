@@ -15,6 +15,7 @@
 #include "glue_kernels.cuh"
 #include "stream_kernels.cuh"
 #include "stream_rows_kernels.cuh"
+#include "head_kernels.cuh"
 #include "ep_kernels.cuh"
 #include "prefill_wide_kernels.cuh"
 
@@ -1660,3 +1661,166 @@ extern "C" int xabe_shared_expert_noalloc(void* stream, xabe_quant_tensor gate, 
     CUDA_TRY(cudaGetLastError());
     return XABE_OK;
 }
+
+
+// ---------------------------------------------------------------------------
+// LM head (LmHeadKernels, crates/xabe-cuda/src/kernels/lm_head.rs:1493-2015)
+// ---------------------------------------------------------------------------
+struct xabe_lm_head {
+    xabe_lm_head_geometry g{};
+    int device = 0;
+    int sm_count = 0;
+    __half* x_hi = nullptr;  // [max_tokens][hidden]
+    __half* x_lo = nullptr;
+    int* status = nullptr;   // device word the bounded waits write
+    int* h_status = nullptr; // pinned
+};
+
+extern "C" {
+
+int xabe_lm_head_create(const xabe_lm_head_geometry* geometry, int device, xabe_lm_head** out) {
+    if (!geometry || !out) return fail(XABE_ERR_INVALID_ARGUMENT, "null geometry or output pointer");
+    *out = nullptr;
+    const xabe_lm_head_geometry g = *geometry;
+    // LmHeadKernels::new validates rather than assumes (lm_head.rs:1542-1680, test :2359)
+    if (g.hidden == 0 || g.vocab == 0 || g.max_tokens == 0)
+        return fail(XABE_ERR_UNSUPPORTED_GEOMETRY, "unsupported LM head geometry {hidden %u, vocab %u, max_tokens %u}: zero dimension",
+                    g.hidden, g.vocab, g.max_tokens);
+    if (g.hidden % 256 != 0 || g.hidden > 4096)
+        return fail(XABE_ERR_UNSUPPORTED_GEOMETRY,
+                    "unsupported LM head geometry: hidden %u must be a multiple of 256 and at most 4096 (the pass keeps "
+                    "eight activation rows in shared memory)", g.hidden);
+    if ((uint64_t)g.vocab * g.hidden > (1ull << 40) || g.max_tokens > (1u << 20))
+        return fail(XABE_ERR_UNSUPPORTED_GEOMETRY, "unsupported LM head geometry: sanity limit exceeded");
+    int n_dev = 0;
+    CUDA_TRY(cudaGetDeviceCount(&n_dev));
+    if (device < 0 || device >= n_dev) return fail(XABE_ERR_DRIVER, "CUDA driver error: no device %d", device);
+    CUDA_TRY(cudaSetDevice(device));
+    cudaDeviceProp prop{};
+    CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+    if (prop.major < 10)
+        return fail(XABE_ERR_DRIVER, "device %d is sm_%d%d; this library is built for sm_100a only", device,
+                    prop.major, prop.minor);
+    xabe_lm_head* m = new (std::nothrow) xabe_lm_head();
+    if (!m) return fail(XABE_ERR_DRIVER, "out of host memory");
+    m->g = g;
+    m->device = device;
+    m->sm_count = prop.multiProcessorCount;
+    const size_t n = (size_t)g.max_tokens * g.hidden;
+    cudaError_t e = cudaMalloc(&m->x_hi, n * sizeof(__half));
+    if (e == cudaSuccess) e = cudaMalloc(&m->x_lo, n * sizeof(__half));
+    if (e == cudaSuccess) e = cudaMalloc(&m->status, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(m->status, 0, sizeof(int));
+    if (e == cudaSuccess) e = cudaMallocHost(&m->h_status, sizeof(int));
+    if (e != cudaSuccess) {
+        xabe_lm_head_destroy(m);
+        return fail(XABE_ERR_DRIVER, "CUDA driver error: %s", cudaGetErrorString(e));
+    }
+    *out = m;
+    return XABE_OK;
+}
+
+void xabe_lm_head_destroy(xabe_lm_head* m) {
+    if (!m) return;
+    cudaSetDevice(m->device);
+    cudaFree(m->x_hi);
+    cudaFree(m->x_lo);
+    cudaFree(m->status);
+    if (m->h_status) cudaFreeHost(m->h_status);
+    delete m;
+}
+
+int xabe_lm_head_forward(xabe_lm_head* m, void* stream, xabe_quant_tensor weight, const float* hidden_states,
+                         size_t hidden_states_len, int tokens, float* logits, size_t logits_len) {
+    if (!m || !weight.dev_bytes || !hidden_states || !logits)
+        return fail(XABE_ERR_INVALID_ARGUMENT, "null argument to lm_head_forward");
+    const auto& g = m->g;
+    if (weight.quant != XABE_QUANT_Q6_K && weight.quant != XABE_QUANT_Q8_0)
+        return fail(XABE_ERR_UNSUPPORTED_DENSE_TYPE, "LM head format %d is not one this kernel reads (Q8_0, Q6_K)",
+                    (int)weight.quant);
+    // lm_head.rs:1703-1800: whole blocks, then exactly vocab x hidden elements
+    const size_t bb = weight.quant == XABE_QUANT_Q6_K ? 210 : 34, be = weight.quant == XABE_QUANT_Q6_K ? 256 : 32;
+    if (weight.n_bytes % bb != 0)
+        return fail(XABE_ERR_RAGGED_WEIGHTS, "LM head weights: %zu bytes is not a whole number of %zu-byte blocks",
+                    weight.n_bytes, bb);
+    const size_t found = weight.n_bytes / bb * be, want = (size_t)g.vocab * g.hidden;
+    if (found != want)
+        return fail(XABE_ERR_WRONG_ELEMENT_COUNT, "LM head weights hold %zu elements, the geometry needs %zu", found,
+                    want);
+    if (tokens < 0 || (uint32_t)tokens > g.max_tokens)
+        return fail(XABE_ERR_TOO_MANY_TOKENS, "%d tokens exceeds the %u this head was sized for", tokens, g.max_tokens);
+    if (hidden_states_len != (size_t)g.max_tokens * g.hidden)
+        return fail(XABE_ERR_BUFFER_LENGTH, "hidden_states must hold %zu floats, holds %zu",
+                    (size_t)g.max_tokens * g.hidden, hidden_states_len);
+    if (logits_len != (size_t)g.max_tokens * g.vocab)
+        return fail(XABE_ERR_BUFFER_LENGTH, "logits must hold %zu floats, holds %zu", (size_t)g.max_tokens * g.vocab,
+                    logits_len);
+    if (tokens == 0) return XABE_OK;
+    const int q = weight.quant == XABE_QUANT_Q6_K ? QUANT_Q6K : QUANT_Q8_0;
+    const int n_spans = (int)g.hidden / 256;
+    const uint64_t row_bytes = (uint64_t)n_spans * span_bytes_of(q);
+    HeadLaunch P{};
+    P.box_w = rows_box_bytes(q);
+    int rc = make_bytes_map(&P.tm_w, weight.dev_bytes, g.vocab, row_bytes, P.box_w);
+    if (rc) return rc;
+    P.x_hi = m->x_hi;
+    P.x_lo = m->x_lo;
+    P.logits = logits;
+    P.status = m->status;
+    P.vocab = (int)g.vocab;
+    P.hidden = (int)g.hidden;
+    P.tokens = tokens;
+    P.stage_bytes = 2u * kRowsGroupRows * P.box_w;
+    P.x_stride = g.hidden * 2u + kXRowPadBytes;
+    uint32_t smem = 0;
+    for (int S = kHeadMaxStages; S >= 2 && !smem; --S) {
+        HeadSmem R = head_smem_layout(S, P.stage_bytes, P.x_stride);
+        if (R.total <= 226u * 1024u) {
+            P.n_stages = S;
+            smem = R.total;
+        }
+    }
+    if (!smem) return fail(XABE_ERR_UNSUPPORTED_GEOMETRY, "LM head pass does not fit shared memory");
+    cudaStream_t st = (cudaStream_t)stream;
+    k_head_split<<<tokens, 256, 0, st>>>(hidden_states, tokens, (int)g.hidden, m->x_hi, m->x_lo);
+    CUDA_TRY(cudaGetLastError());
+    const dim3 grid(m->sm_count, (tokens + 7) / 8), block(32 * (1 + kStreamConsumerWarps));
+    if (q == QUANT_Q6K) {
+        CUDA_TRY(cudaFuncSetAttribute(k_head_rows<QUANT_Q6K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        k_head_rows<QUANT_Q6K><<<grid, block, smem, st>>>(P);
+    } else {
+        CUDA_TRY(cudaFuncSetAttribute(k_head_rows<QUANT_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        k_head_rows<QUANT_Q8_0><<<grid, block, smem, st>>>(P);
+    }
+    CUDA_TRY(cudaGetLastError());
+    return XABE_OK;
+}
+
+int xabe_lm_head_argmax(xabe_lm_head* m, void* stream, const float* logits, size_t logits_len, int tokens,
+                        int32_t* out) {
+    if (!m || !logits || !out) return fail(XABE_ERR_INVALID_ARGUMENT, "null argument to lm_head_argmax");
+    if (tokens < 0 || (uint32_t)tokens > m->g.max_tokens)
+        return fail(XABE_ERR_TOO_MANY_TOKENS, "%d tokens exceeds the %u this head was sized for", tokens,
+                    m->g.max_tokens);
+    if (logits_len != (size_t)m->g.max_tokens * m->g.vocab)
+        return fail(XABE_ERR_BUFFER_LENGTH, "logits must hold %zu floats, holds %zu",
+                    (size_t)m->g.max_tokens * m->g.vocab, logits_len);
+    if (tokens == 0) return XABE_OK;
+    k_head_argmax<<<tokens, 1024, 0, (cudaStream_t)stream>>>(logits, (int)m->g.vocab, tokens, out);
+    CUDA_TRY(cudaGetLastError());
+    return XABE_OK;
+}
+
+int xabe_lm_head_device_status(xabe_lm_head* m, void* stream, int* status_out) {
+    if (!m || !status_out) return fail(XABE_ERR_INVALID_ARGUMENT, "null argument to lm_head_device_status");
+    cudaStream_t st = (cudaStream_t)stream;
+    CUDA_TRY(cudaMemcpyAsync(m->h_status, m->status, sizeof(int), cudaMemcpyDeviceToHost, st));
+    CUDA_TRY(cudaMemsetAsync(m->status, 0, sizeof(int), st));
+    CUDA_TRY(cudaStreamSynchronize(st));
+    *status_out = *m->h_status;
+    if (*status_out != 0)
+        return fail(XABE_ERR_DEVICE_STATUS, "a kernel's bounded wait ran out (device status %d)", *status_out);
+    return XABE_OK;
+}
+
+}  // extern "C"

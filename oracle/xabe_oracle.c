@@ -265,6 +265,48 @@ void xo_gemv(const float* w, size_t out_dim, size_t in_dim, const float* x, floa
     matvec_rows(w, out_dim, in_dim, x, out);
 }
 
+/* gemv.rs:102-111: index of the largest element, ties to the lower index. */
+size_t xo_argmax(const float* v, size_t n) {
+    size_t best = 0;
+    for (size_t i = 1; i < n; ++i)
+        if (v[i] > v[best]) best = i;
+    return best;
+}
+
+/* The LM head's CPU reference as crates/xabe-engine/tests/lm_head_differential.rs:17-19
+ * builds it: `gemv_batch` (gemv.rs:71-88) over rows dequantised from the file
+ * bytes (quant.rs:62-69,171-202), logits [tokens][vocab].  Rows are independent,
+ * so sharing them over threads changes no sum. */
+int xo_lm_head(int quant, const uint8_t* bytes, size_t vocab, size_t hidden, const float* x, size_t tokens,
+               float* logits, int threads) {
+    size_t be = xo_block_elements(quant), bb = xo_block_bytes(quant);
+    if (be == 0 || hidden % be != 0) return -1;
+    size_t row_bytes = hidden / be * bb;
+    int nt = threads > 0 ? threads : omp_get_num_procs();
+    int failed = 0;
+#pragma omp parallel num_threads(nt)
+    {
+        float* row = (float*)malloc(hidden * sizeof(float));
+        if (!row) {
+#pragma omp atomic write
+            failed = 1;
+        }
+#pragma omp for schedule(static)
+        for (long long v = 0; v < (long long)vocab; ++v) {
+            if (!row) continue;
+            xo_dequantize_row(quant, bytes + (size_t)v * row_bytes, row_bytes, row);
+            for (size_t t = 0; t < tokens; ++t) {
+                float acc = -0.0f; /* Rust's f32 sum() starts from -0.0 */
+                const float* xt = x + t * hidden;
+                for (size_t i = 0; i < hidden; ++i) acc = acc + row[i] * xt[i];
+                logits[t * vocab + (size_t)v] = acc;
+            }
+        }
+        free(row);
+    }
+    return failed ? -2 : 0;
+}
+
 /* ===================================================================== */
 /* Orders pinned by the reference's device kernels.                       */
 /* `block_reduce_sum` (crates/xabe-cuda/src/kernels/layer_ops.rs:93-110,   */

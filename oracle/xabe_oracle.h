@@ -65,6 +65,9 @@ float xo_silu(float x);
 float xo_sigmoid(float x);
 void xo_swiglu(const float* gate, const float* up, size_t n, float* out);
 void xo_gemv(const float* w, size_t out_dim, size_t in_dim, const float* x, float* out);
+size_t xo_argmax(const float* v, size_t n);
+int xo_lm_head(int quant, const uint8_t* bytes, size_t vocab, size_t hidden, const float* x, size_t tokens,
+               float* logits, int threads);
 
 /* ---- summation orders pinned by the reference's DEVICE kernels -------- */
 void xo_rms_norm_dev(const float* x, const float* w, float eps, size_t n, float* out);

@@ -103,6 +103,10 @@ def _declare(L):
     L.xo_sigmoid.argtypes = [f32]
     L.xo_sigmoid.restype = f32
     L.xo_gemv.argtypes = [vp, sz, sz, vp, vp]
+    L.xo_argmax.argtypes = [vp, sz]
+    L.xo_argmax.restype = sz
+    L.xo_lm_head.argtypes = [i32, vp, sz, sz, vp, sz, vp, i32]
+    L.xo_lm_head.restype = i32
     L.xo_router_logits_dev.argtypes = [vp, vp, sz, sz, vp]
     L.xo_shared_gate_dot_dev.argtypes = [vp, vp, sz]
     L.xo_shared_gate_dot_dev.restype = f32
@@ -214,6 +218,26 @@ def gemv(w, x) -> np.ndarray:
     w, x = _f32(w), _f32(x)
     out = np.empty(w.shape[0], dtype=np.float32)
     lib().xo_gemv(_p(w), w.shape[0], w.shape[1], _p(x), _p(out))
+    return out
+
+
+def argmax(v) -> int:
+    """gemv.rs:102-111: ties go to the lower index."""
+    v = _f32(v)
+    return int(lib().xo_argmax(_p(v), v.size))
+
+
+def lm_head(quant: int, data, vocab: int, hidden: int, x, threads: int = 0) -> np.ndarray:
+    """Logits [tokens][vocab] of the LM head: gemv_batch over rows dequantised from file bytes
+    (crates/xabe-engine/tests/lm_head_differential.rs:17-19)."""
+    data, x = _u8(data), _f32(x)
+    x = x.reshape(-1, hidden)
+    if data.size != vocab * (hidden // BLOCK_ELEMS[quant]) * BLOCK_BYTES[quant]:
+        raise ValueError("weight bytes do not match vocab x hidden")
+    out = np.empty((x.shape[0], vocab), dtype=np.float32)
+    rc = lib().xo_lm_head(quant, _p(data), vocab, hidden, _p(x), x.shape[0], _p(out), threads)
+    if rc != 0:
+        raise ValueError(f"xo_lm_head failed ({rc})")
     return out
 
 
