@@ -37,6 +37,9 @@ WORKLOADS = {
     "decode32": (32, 16, True),
     # the MoE half of Forward::body: --stack-layers layers chained (l_out -> next residual) in ONE graph
     "decode64_stack": (64, 16, True),
+    # the LM head of the same model (hidden 2048 -> vocab 248,320, Q8_0, 540 MB): run_head() below
+    "lm_head1": (1, 0, False),
+    "lm_head8": (8, 0, False),
     "prefill2048": (2048, 32, True),  # BASELINE config 2
     # BASELINE config 3 (expert-parallel stack, strong scaling): run_ep() below; tokens/layers from --ep-*
     "ep_prefill_stack": (16384, 64, True),
@@ -167,6 +170,29 @@ def run_reference(args) -> dict:
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     from helpers import oracle_layer
     from oracle import xabe_oracle as oracle
+    if args.workload.startswith("lm_head"):
+        # gemv over dequantised rows on a bounded sample of the vocabulary, scaled to all 248,320 rows
+        rows, hidden, vocab = 16384, 2048, 248_320
+        wb = synth.q8_0_bytes(rows * hidden, 0, 0, 3)
+        x = synth.activations(tokens, hidden, seed=0, layer=901)
+        threads = oracle.max_threads()
+        for _ in range(max(args.warmup, 1)):
+            oracle.lm_head(oracle.Q8_0, wb, rows, hidden, x, threads=threads)
+        steps = max(1, min(args.steps, 20))
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            oracle.lm_head(oracle.Q8_0, wb, rows, hidden, x, threads=threads)
+        per_pass = (time.perf_counter() - t0) / steps * (vocab / rows)
+        tps = tokens / per_pass
+        return {
+            "impl": "reference", "metric": "lm_head_tokens_per_s", "value": tps, "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": per_pass * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": args.workload, "tokens": tokens, "hidden": hidden, "vocab": vocab, "quant": "Q8_0"},
+            "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
+                             "sample": f"{rows} of {vocab} vocabulary rows per step, scaled to the whole vocabulary"},
+            "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        }
     L = synth.moe_layer(seed=0, layer=0, zipf=zipf)
     layer = oracle_layer(oracle, L)
     x = synth.activations(tokens, 2048, seed=0, layer=900)
@@ -489,6 +515,115 @@ def run_stack(args) -> dict:
     }
 
 
+def run_head(args) -> dict:
+    """The LM head at the real geometry (crates/xabe-cuda/src/kernels/lm_head.rs:1318-1324): one pass over
+    the 540 MB Q8_0 tensor serves up to eight tokens.  Three resident copies of the head rotate, and
+    one copy alone is four times the L2.  A step = logits for the batch (+ argmax and the 4-byte
+    read-back of each token id in the end-to-end figure, which is what a sampler reads)."""
+    import numpy as np
+    import torch
+
+    from llmxabe_b200 import synth
+    from llmxabe_b200.lm_head import HeadFormat, HeadTensor, LmHeadGeometry, LmHeadKernels
+
+    if int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        raise RuntimeError("the lm_head workloads are one-GPU workloads")
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the LM head has no CPU fallback")
+    torch.cuda.set_device(0)
+    tokens = WORKLOADS[args.workload][0]
+    g = LmHeadGeometry.qwen3_6(tokens)
+    head = LmHeadKernels(g)
+    n_bytes = g.weight_bytes_for(HeadFormat.Q8_0)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(777)
+    copies = []
+    for _ in range(3):
+        raw = torch.randint(0, 256, (n_bytes,), dtype=torch.uint8, device="cuda", generator=gen).view(-1, 34)
+        # the block scale: fp16(|N(0,1)| * 2e-4 * 4.6), as the synthetic Q8_0 tensors of the MoE workloads
+        d = (torch.randn(raw.shape[0], device="cuda", generator=gen).abs() * (2e-4 * 4.6)).to(torch.float16)
+        raw[:, 0:2] = d.view(torch.uint8).view(-1, 2)
+        copies.append(HeadTensor(raw.view(-1), HeadFormat.Q8_0))
+    x = torch.randn(tokens, g.hidden, device="cuda", generator=gen)
+    logits = torch.empty(tokens, g.vocab, device="cuda")
+    ids = torch.zeros(tokens, dtype=torch.int32, device="cuda")
+    hx = x.cpu().pin_memory()
+    hids = torch.zeros(tokens, dtype=torch.int32).pin_memory()
+    stream = torch.cuda.current_stream()
+
+    def step(i):
+        head.forward(copies[i % 3], x, tokens, logits)
+
+    def step_host(i):
+        x.copy_(hx, non_blocking=True)
+        head.forward(copies[i % 3], x, tokens, logits)
+        head.argmax(logits, tokens, ids)
+        hids.copy_(ids, non_blocking=True)
+        stream.synchronize()
+
+    def timed(fn, steps):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(steps):
+            fn(i)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    t0 = time.perf_counter()
+    i = 0
+    while i < max(args.warmup, 3) or time.perf_counter() - t0 < 0.3:
+        step(i)
+        i += 1
+    sampler = ClockSampler(0)
+    sampler.start()
+    ms = timed(step, args.steps)
+    clocks = sampler.stop()
+    for i in range(3):
+        step_host(i)
+    ms_e2e = timed(step_host, args.steps)
+    status = head.device_status()
+    peak, peak_src = measured_peaks()
+    alg_bytes = g.weight_bytes_read(tokens) + tokens * (g.hidden + g.vocab) * 4
+    achieved = alg_bytes / (ms * 1e-3) / 1e9
+    out = {
+        "metric": "lm_head_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None,
+        "dtype": "exact Q8_0 codes x fp32 activations as two f16 parts, fp32 scales+accumulate",
+        "data": "synthetic",
+        "config": {"workload": args.workload, "tokens": tokens, "hidden": g.hidden, "vocab": g.vocab,
+                   "quant": "Q8_0", "weight_bytes": n_bytes,
+                   "l2": "three resident copies of the head rotate; one copy is 540 MB (L2 126 MB)",
+                   "parallelism": "one GPU"},
+        "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": tokens * g.hidden * 4, "d2h_bytes_per_step": tokens * 4},
+        "gpu_launches": 2 * args.steps, "cuda_graph": False, "clocks": clocks,
+        "roofline": {"bound": "hbm", "kernel": "k_head_rows<Q8_0>", "achieved": achieved, "peak": peak,
+                     "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                     "algorithmic_bytes_per_launch": alg_bytes, "ms_per_launch": ms},
+        "device_status": status,
+    }
+    if not args.no_cpu:
+        from oracle import xabe_oracle as oracle
+        rows = 16384  # a bounded sample of the vocabulary, every host thread
+        wb = copies[0].bytes[: rows * 2176].cpu().numpy()
+        xn = x.cpu().numpy()
+        threads = oracle.max_threads()
+        oracle.lm_head(oracle.Q8_0, wb, rows, g.hidden, xn, threads=threads)
+        t0 = time.perf_counter()
+        reps = 0
+        while reps < 3 or time.perf_counter() - t0 < 5.0:
+            oracle.lm_head(oracle.Q8_0, wb, rows, g.hidden, xn, threads=threads)
+            reps += 1
+        per_pass = (time.perf_counter() - t0) / reps * (g.vocab / rows)
+        out["cpu_baseline"] = {"value": tokens / per_pass, "unit": "tokens/s", "cores": threads, "kind": "port",
+                               "sample": f"{rows} of {g.vocab} vocabulary rows x {tokens} tokens, {reps} passes, "
+                                         f"scaled to the whole vocabulary ({per_pass * 1e3:.0f} ms per pass)"}
+    return out
+
+
 def run_ep(args) -> dict:
     """BASELINE config 3: a stack of MoE layers (Q6_K experts, Q8_0 shared expert), `--ep-tokens` tokens,
     experts sharded over the ranks with NCCL all-to-all dispatch/combine.  Strong scaling: the global
@@ -752,6 +887,8 @@ def main():
         out = run_dense(args)
     elif args.workload == "decode64_stack":
         out = run_stack(args)
+    elif args.workload.startswith("lm_head"):
+        out = run_head(args)
     else:
         out = run_ours(args)
     if out:
