@@ -1,4 +1,5 @@
-"""Builds libxabe_moe_sm100.so (the C-ABI library) in-tree with nvcc for sm_100a."""
+"""Builds libxabe_moe_sm100.so (the C-ABI kernel library) in-tree with nvcc for sm_100a, and
+libxabe_gguf.so (the GGUF container reader, host code) with g++."""
 from __future__ import annotations
 
 import os
@@ -12,6 +13,23 @@ LIB = os.path.join(PKG, "libxabe_moe_sm100.so")
 SOURCES = ["xabe_moe_api.cu"]
 HEADERS = sorted(f for f in os.listdir(CSRC) if f.endswith(".cuh")) + [
     os.path.join("..", "..", "include", "xabe_moe.h")]
+
+
+GGUF_LIB = os.path.join(PKG, "libxabe_gguf.so")
+GGUF_DEPS = [os.path.join(CSRC, "xabe_gguf.cpp"), os.path.join(PKG, "..", "include", "xabe_gguf.h")]
+
+
+def build_gguf(force: bool = False) -> str:
+    """The GGUF reader: plain C++17, no CUDA."""
+    if not force and os.path.exists(GGUF_LIB) and all(
+            os.path.getmtime(d) <= os.path.getmtime(GGUF_LIB) for d in GGUF_DEPS):
+        return GGUF_LIB
+    cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++"
+    cmd = [cxx, "-std=c++17", "-O2", "-fPIC", "-shared", "-Wall", "-Wextra", "-o", GGUF_LIB, GGUF_DEPS[0]]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("g++ failed:\n" + r.stdout + r.stderr)
+    return GGUF_LIB
 
 
 def _nvcc() -> str:
@@ -52,3 +70,4 @@ def build(force: bool = False, verbose: bool = False) -> str:
 if __name__ == "__main__":
     build(force=True, verbose="-v" in sys.argv)
     print(LIB)
+    print(build_gguf(force=True))
