@@ -275,6 +275,138 @@ __global__ void __launch_bounds__(256, 1) k_router_logits_wide(const float* __re
 }
 
 // ---------------------------------------------------------------------------
+// Router logits for prefill widths (hundreds of tokens per CTA): the same
+// values and order again, with the sixteen expert rows held in REGISTERS.
+// Thread v owns w[e][v + 256 i] for its CTA's sixteen experts (16 * NI
+// registers, loaded once, coalesced); the CTA's tokens (a contiguous range of
+// rows) arrive four at a time through a ring of bulk TMA copies issued several
+// stages ahead, so neither the weights nor the L2 latency of the activations
+// sit in the inner loop (k_router_logits_wide spends one shared load per four
+// multiply-adds and waits for its prefetched global loads once per tile).  The
+// 32 accumulators of a token pair go through the same transposed tree as in
+// k_router_logits_wide, here with exactly one (output, group) per thread, on a
+// double-buffered scratch so that a pair costs two block barriers.
+// grid: (E / 16, token shares); block 256;
+// dynamic shared memory: router_regw_smem(hidden).
+// ---------------------------------------------------------------------------
+constexpr int kRrTokens = 2;                        // tokens per accumulator set
+constexpr int kRrOutputs = kRwExperts * kRrTokens;  // 32
+constexpr int kRrStageTokens = 4;                   // token rows per ring stage
+constexpr int kRrStages = 4;
+
+__host__ __device__ inline size_t router_regw_smem(int hidden) {
+    return (size_t)kRrStages * kRrStageTokens * hidden * 4 + (size_t)2 * kRrOutputs * kRwPitch * 4 +
+           (size_t)2 * kRrOutputs * 8 * 4;
+}
+
+template <int NI>
+__global__ void __launch_bounds__(256, 1) k_router_logits_regw(const float* __restrict__ w,
+                                                               const float* __restrict__ x,
+                                                               const int* __restrict__ valid_tokens,
+                                                               int num_experts, const float* __restrict__ bias,
+                                                               float* __restrict__ logits,
+                                                               int* __restrict__ status) {
+    pdl_launch_dependents();
+    pdl_wait();
+    constexpr int hidden = NI * 256;
+    extern __shared__ __align__(128) float rr_smem[];
+    float* xs = rr_smem;                                             // [stages][4][hidden]
+    float* red = xs + kRrStages * kRrStageTokens * hidden;           // [2][32][257]: accumulators, transposed
+    float* group_tot = red + 2 * kRrOutputs * kRwPitch;              // [2][32][8]
+    __shared__ __align__(8) uint64_t full[kRrStages];
+    const int tid = threadIdx.x;
+    const int e0 = blockIdx.x * kRwExperts;
+    const int live = *valid_tokens;
+    // this CTA's tokens: a contiguous range, a whole number of stages except at the end of the batch
+    const int stages_total = (live + kRrStageTokens - 1) / kRrStageTokens;
+    const int stages_per = (stages_total + gridDim.y - 1) / gridDim.y;
+    const int stage0 = blockIdx.y * stages_per;
+    const int stage1 = min(stages_total, stage0 + stages_per);
+    if (stage0 >= stage1) return;
+    auto issue = [&](int k) {  // thread 0: fetch the rows of stage k (counted from stage0) into ring slot k % stages
+        const int t = (stage0 + k) * kRrStageTokens;
+        const uint32_t bytes = (uint32_t)min(kRrStageTokens, live - t) * hidden * 4u;
+        mbar_expect_tx(&full[k % kRrStages], bytes);
+        tma_bulk_g2s(xs + (size_t)(k % kRrStages) * kRrStageTokens * hidden, x + (size_t)t * hidden, bytes,
+                     &full[k % kRrStages]);
+    };
+    const int n_stages = stage1 - stage0;
+    if (tid == 0) {
+        for (int i = 0; i < kRrStages; ++i) mbar_init(&full[i], 1);
+        fence_mbar_init();
+        for (int k = 0; k < min(kRrStages, n_stages); ++k) issue(k);
+    }
+    float wr[kRwExperts][NI];
+#pragma unroll
+    for (int e = 0; e < kRwExperts; ++e)
+#pragma unroll
+        for (int i = 0; i < NI; ++i) wr[e][i] = __ldg(w + (size_t)(e0 + e) * hidden + i * 256 + tid);
+    __syncthreads();  // the barriers are initialised
+    int pair_count = 0;
+    for (int k = 0; k < n_stages; ++k) {
+        const int slot = k % kRrStages;
+        if (!__syncthreads_and(mbar_wait_bounded(&full[slot], (uint32_t)(k / kRrStages) & 1u, status))) return;
+        const float* xk = xs + (size_t)slot * kRrStageTokens * hidden;
+        const int t_stage = (stage0 + k) * kRrStageTokens;
+#pragma unroll
+        for (int p = 0; p < kRrStageTokens / kRrTokens; ++p, ++pair_count) {
+            if (t_stage + p * kRrTokens >= live) break;  // uniform: the batch ended inside this stage
+            const int buf = pair_count & 1;
+            float* redb = red + buf * kRrOutputs * kRwPitch;
+            float* totb = group_tot + buf * kRrOutputs * 8;
+            float acc[kRwExperts][kRrTokens];
+#pragma unroll
+            for (int e = 0; e < kRwExperts; ++e)
+#pragma unroll
+                for (int u = 0; u < kRrTokens; ++u) acc[e][u] = 0.0f;
+            // a row past the live tokens was not copied: its sums are formed from stale bytes and never stored
+#pragma unroll
+            for (int i = 0; i < NI; ++i) {
+                float xv[kRrTokens];
+#pragma unroll
+                for (int u = 0; u < kRrTokens; ++u) xv[u] = xk[(p * kRrTokens + u) * hidden + i * 256 + tid];
+#pragma unroll
+                for (int e = 0; e < kRwExperts; ++e)
+#pragma unroll
+                    for (int u = 0; u < kRrTokens; ++u) acc[e][u] = fmaf(wr[e][i], xv[u], acc[e][u]);
+            }
+#pragma unroll
+            for (int e = 0; e < kRwExperts; ++e)
+#pragma unroll
+                for (int u = 0; u < kRrTokens; ++u) redb[(e * kRrTokens + u) * kRwPitch + tid] = acc[e][u];
+            __syncthreads();
+            // every thread has read this stage's last pair once it is past the barrier above: refill the slot
+            if (tid == 0 && (p == kRrStageTokens / kRrTokens - 1 || t_stage + (p + 1) * kRrTokens >= live) &&
+                k + kRrStages < n_stages)
+                issue(k + kRrStages);
+            {
+                // thread -> output o = tid % 32, lane group g = tid / 32: the shuffle-down tree of that group
+                const int o = tid & 31, g = tid >> 5;
+                const float* src = redb + o * kRwPitch + g * 32;
+                float v[32];
+#pragma unroll
+                for (int l = 0; l < 32; ++l) v[l] = src[l];
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+                    for (int l = 0; l < off; ++l) v[l] = v[l] + v[l + off];  // what lane l holds after shuffle-down by off
+                totb[o * 8 + g] = v[0];
+            }
+            __syncthreads();
+            // the other buffer's tree reads ended before the barrier above, so the next pair may overwrite it
+            if (tid < kRrOutputs) {
+                float total = 0.0f;
+#pragma unroll
+                for (int g = 0; g < 8; ++g) total += totb[tid * 8 + g];
+                const int e = e0 + (tid >> 1), t = t_stage + p * kRrTokens + (tid & 1);
+                if (t < live && e < num_experts)
+                    logits[(size_t)t * num_experts + e] = bias ? __fadd_rn(total, bias[e]) : total;
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Routing: stable softmax over all experts, k selection passes by
 // (probability desc, index asc), renormalise over the selected k in selection
 // order (crates/xabe-kernels/src/moe/router.rs:32-76).  One warp per token.

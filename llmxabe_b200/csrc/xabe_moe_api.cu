@@ -670,6 +670,24 @@ int launch_router(xabe_moe* m, cudaStream_t st, const float* router, const float
     const auto& g = m->g;
     if (((uintptr_t)router & 15) != 0)
         return fail(XABE_ERR_INVALID_ARGUMENT, "router weights must be 16-byte aligned");
+    // prefill widths: the expert rows in registers, the tokens streamed two at a time
+    bool regw = g.max_tokens >= 256;
+    if (const char* e = getenv("XABE_MOE_ROUTER_REGW")) regw = e[0] == '1';  // tuning aid
+    if (regw && g.max_tokens >= 2 && g.num_experts % kRwExperts == 0 && (g.hidden == 2048 || g.hidden == 1024)) {
+        const size_t smem_r = router_regw_smem((int)g.hidden);
+        unsigned gx = g.num_experts / kRwExperts;
+        unsigned gy = (unsigned)m->sm_count / gx;
+        unsigned pairs = (g.max_tokens + kRrStageTokens - 1) / kRrStageTokens;
+        if (gy < 1) gy = 1;
+        if (gy > pairs) gy = pairs;
+        auto go_regw = [&](auto kern) -> int {
+            CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_r));
+            CUDA_TRY(launch_pdl(kern, dim3(gx, gy), dim3(256), smem_r, st, router, (const float*)m->normed,
+                                (const int*)m->valid_tokens, (int)g.num_experts, bias, m->logits, m->status));
+            return XABE_OK;
+        };
+        return g.hidden == 2048 ? go_regw(k_router_logits_regw<8>) : go_regw(k_router_logits_regw<4>);
+    }
     // wide passes: sixteen expert rows per CTA, the tokens shared out over the SMs
     if (g.max_tokens >= 32 && g.num_experts % kRwExperts == 0 && (g.hidden == 2048 || g.hidden == 1024)) {
         const size_t smem_w = router_wide_smem((int)g.hidden);
