@@ -876,10 +876,21 @@ def main():
                     help="exchange rows and results with NCCL all-to-alls instead of peer stores over NVLink")
     ap.add_argument("--no-graph", dest="graph", action="store_false", help="time eager launches instead of CUDA-graph replay")
     args = ap.parse_args()
+    # Libraries write to stdout too (NCCL prints its version line there when NCCL_DEBUG asks for it):
+    # while the workload runs, file descriptor 1 points at stderr, and it is put back for the one JSON line.
+    sys.stdout.flush()
+    saved_stdout = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(obj):
+        sys.stdout.flush()
+        os.dup2(saved_stdout, 1)
+        print(json.dumps(obj), flush=True)
+
     if args.impl == "reference":
         if int(os.environ.get("RANK", "0")) != 0:
             return
-        print(json.dumps(run_reference(args)), flush=True)
+        emit(run_reference(args))
         return
     if args.workload == "ep_prefill_stack":
         out = run_ep(args)
@@ -892,7 +903,7 @@ def main():
     else:
         out = run_ours(args)
     if out:
-        print(json.dumps(out), flush=True)
+        emit(out)
 
 
 if __name__ == "__main__":
