@@ -160,6 +160,11 @@ def test_batched_rows_are_bit_identical_to_rows_run_alone(torch_cuda, oracle, re
         one = run_block(alone_blk, real_device_layer, x[t:t + 1], 1)
         for name in ("ffn_out", "l_out", "routed", "shexp", "logits"):
             assert (bits(one[name][0]) == bits(big[name][t])).all(), (name, t)
+    # handles of 16 and 32 tokens (the narrowest that run gate/up through k_gateup_rows) give the same rows
+    for width in (16, 32):
+        mid = run_block(MoeBlock(MoeGeometry.qwen3_6(16, width)), real_device_layer, x[:width], width)
+        for name in ("ffn_out", "l_out", "routed", "shexp"):
+            assert (bits(mid[name]) == bits(big[name][:width])).all(), (name, width)
     # and a different bucket width does not change a row either
     wide = run_block(MoeBlock(MoeGeometry.qwen3_6(32, 64)), real_device_layer, x, 64)
     assert (bits(wide["l_out"]) == bits(big["l_out"])).all()
