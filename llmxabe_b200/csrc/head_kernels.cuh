@@ -121,7 +121,7 @@ __global__ void __launch_bounds__(32 * (1 + kStreamConsumerWarps), 1) k_head_row
         for (int u = blockIdx.x; u < units; u += gridDim.x) {
             const int y0 = u * kHeadUnitRows;
             for (int s = 0; s < n_spans; ++s) {
-                const int x = ((span_b * s) & ~15) >> 2;  // in 32-bit words, at a 16-byte boundary
+                const int x = rows_box_start(span_b * s, span_b * n_spans, (int)P.box_w) >> 2;  // in 32-bit words
 #pragma unroll
                 for (int gi = 0; gi < kStreamGroups; ++gi) {
                     if (use >= 1 && !stream_wait(&empty[st], (use - 1) & 1, abortp, P.status)) return;
@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(32 * (1 + kStreamConsumerWarps), 1) k_head_row
         for (int s = 0; s < n_spans; ++s) {
             if (!stream_wait(&full[st], use & 1, abortp, P.status)) return;
             const uint8_t* pa = smem + lay.stages + (uint32_t)st * P.stage_bytes + (uint32_t)(w * 8 + g) * P.box_w +
-                                (uint32_t)((span_b * s) & 15);
+                                (uint32_t)(span_b * s - rows_box_start(span_b * s, span_b * n_spans, (int)P.box_w));
             const uint8_t* pb = pa + kRowsGroupRows * P.box_w;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {

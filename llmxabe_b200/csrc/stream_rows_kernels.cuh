@@ -36,6 +36,15 @@ struct RowsLaunch {
 
 __host__ __device__ inline uint32_t rows_box_bytes(int quant) { return quant == QUANT_Q6K ? 240u : 272u; }
 
+// Where in its row the box that covers the span at byte `off` starts: the 16-byte boundary below the
+// span, but never so far right that the box would reach past the end of the row.  The bytes of a box
+// past the row's end are the next row's, and for the last row of a tensor they lie beyond the
+// allocation; a copy must not depend on what is mapped there.
+__host__ __device__ inline int rows_box_start(int off, int row_bytes, int box) {
+    const int lo = off & ~15, hi = row_bytes - box;
+    return lo < hi ? lo : hi;
+}
+
 struct RowsSmem {
     uint32_t stages, xbuf, items, bars, total;
 };
@@ -175,7 +184,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) k_gateup_rows(const __grid_
             const int span_b = span_bytes_of(shared ? QS : QR);
             const int y0 = (shared ? 0 : expert * L.rows) + blk * kRowsUnitRows;
             for (int s = 0; s < n_spans; ++s) {
-                const int x = ((span_b * s) & ~15) >> 2;  // in 32-bit words, at a 16-byte boundary
+                const int x = rows_box_start(span_b * s, span_b * n_spans, (int)box) >> 2;  // in 32-bit words
 #pragma unroll
                 for (int gi = 0; gi < kStreamGroups; ++gi) {
                     if (use >= 1 && !stream_wait(&empty[st], (use - 1) & 1, abortp, L.status)) return;
@@ -221,7 +230,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) k_gateup_rows(const __grid_
         for (int s = 0; s < n_spans; ++s) {
             if (!stream_wait(&full[st], use & 1, abortp, L.status)) return;
             const uint8_t* pa = smem + lay.stages + (uint32_t)st * P.stage_bytes + (uint32_t)(w * 8 + g) * box +
-                                (uint32_t)((span_b * s) & 15);
+                                (uint32_t)(span_b * s - rows_box_start(span_b * s, span_b * n_spans, (int)box));
             const uint8_t* pb = pa + kRowsGroupRows * box;
             float acc[4];
             uint2 bf[8];
