@@ -8,7 +8,8 @@
 // one 256-element span of 64 gate rows and 64 up rows, fetched as two boxes of a 2-D tensor map
 // over the weight bytes ([rows][row_bytes], row pitch a multiple of 16 bytes).  A Q6_K span of
 // 210 bytes starts 2 s bytes past a 16-byte boundary, so the box is 240 bytes wide and starts at
-// the boundary below; with a 240-byte (272 for Q8_0) row pitch in shared memory the eight rows a
+// the boundary below (the last span's box starts earlier, so that it ends with the row: see
+// rows_box_start); with a 240-byte (272 for Q8_0) row pitch in shared memory the eight rows a
 // load touches fall in disjoint banks.
 //
 // Unit of work: (column group, block of 128 output rows); group gi of the CTA owns rows
