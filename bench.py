@@ -1,19 +1,30 @@
 """Benchmark of the per-layer MoE FFN block.
 
-    python bench.py --gpus N --steps K --warmup W [--workload decode64] [--impl reference]
+    python bench.py --gpus N --steps K --warmup W [--workload NAME] [--impl reference]
 
-A step is one pass of the block over one batch of synthetic tokens through one
-layer's weights.  Layers rotate every step over `--layers` resident layers so
-that weights come from HBM, not from L2.  `value` is tokens per second per
-layer over all ranks (inputs resident); `e2e` is the same through the
-host-buffer entry point, copies included.  At N > 1 every rank is a replica
-with its own layers and its own batch (weak scaling, no data-path collective),
-the reference's own multi-GPU model.
+A step is one pass of the block over one batch of synthetic tokens through one layer's weights
+(for the stack workloads: one pass over all layers).  Layers rotate every step over `--layers`
+resident layers so that weights come from HBM, not from L2.  `value` is tokens per second per
+layer over all ranks with inputs resident on the device; `e2e` is the same through the host-buffer
+entry point, copies included.
+
+Which workload runs when none is named:
+  * launched as one plain process: `decode64` (64 tokens, Zipf-skewed routing, one layer per step)
+    is the line's `value`; the line's `also` object carries, measured in the same process, the
+    one-token decode step, the 2048-token prefill chunk and the 40-layer 16384-token stack on this
+    one GPU (the base of the expert-parallel curve);
+  * launched by torch.distributed.run (WORLD_SIZE in the environment, any N including 1): the
+    40-layer, 16384-token expert-parallel prefill stack, experts sharded over the N ranks, rows and
+    results exchanged over peer memory (NVLink) -- strong scaling, the same global batch at every N.
+
+The timed region is `--steps` steps, repeated back to back until it is at least 0.5 s long (the
+line's `timed_repeats`); `ms_per_step` is the mean over all of them.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -27,61 +38,96 @@ if ROOT not in sys.path:
 
 METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s/layer"
+MIN_TIMED_SECONDS = 0.5
+BF16_PEAK_TFLOPS_FALLBACK = 1590.0
 
-# name -> (tokens, bucket width, zipf skew).  Geometry 256 experts / top-8 / 2048 / 512, Q6_K everywhere.
+E, K, H, I = 256, 8, 2048, 512
+
+# name -> (tokens, bucket width, zipf skew).  Geometry 256 experts / top-8 / 2048 / 512.
 WORKLOADS = {
-    "decode1": (1, 16, False),      # BASELINE config 0
-    "decode3": (3, 16, True),       # BASELINE config 1, three sequences
-    "decode64": (64, 16, True),     # BASELINE config 1, 64 tokens  (default)
-    "decode16": (16, 16, True),     # widths between the configs, for choosing kernel thresholds
+    "decode1": (1, 16, False),      # one sequence, one token: the latency case
+    "decode3": (3, 16, True),       # three concurrent sequences
+    "decode64": (64, 16, True),     # 64 concurrent sequences (default)
+    "decode16": (16, 16, True),     # widths in between, for choosing kernel thresholds
     "decode32": (32, 16, True),
     # the MoE half of Forward::body: --stack-layers layers chained (l_out -> next residual) in ONE graph
     "decode64_stack": (64, 16, True),
     # the LM head of the same model (hidden 2048 -> vocab 248,320, Q8_0, 540 MB): run_head() below
     "lm_head1": (1, 0, False),
     "lm_head8": (8, 0, False),
-    "prefill2048": (2048, 32, True),  # BASELINE config 2
-    # BASELINE config 3 (expert-parallel stack, strong scaling): run_ep() below; tokens/layers from --ep-*
+    "prefill2048": (2048, 32, True),  # one prefill chunk, bf16 rows in
+    # the 40-layer prefill stack, experts sharded over the ranks (strong scaling): run_ep() below
     "ep_prefill_stack": (16384, 64, True),
-    # BASELINE config 4 (dense 27B block, hidden 5120 / intermediate 17408, Q6_K): run_dense() below;
-    # under torchrun the intermediate dimension is sharded over the ranks (tensor parallel)
+    # the dense 27B block (hidden 5120 / intermediate 17408, Q6_K): run_dense() below; under torchrun
+    # the intermediate dimension is sharded over the ranks (tensor parallel)
     "dense1": (1, 64, False),
     "dense64": (64, 64, False),
     "dense4096": (4096, 64, False),
 }
 
-# DRAM bytes (read + write) of the dominant kernel per launch, from the ncu captures summarised under
-# profiles/ (k_gateup_rows_decode64.md, k_prefill_gemm_prefill2048.md); none taken for the others
-NCU_TRAFFIC_BYTES = {"decode64": 329.3e6 + 4.3e6, "prefill2048": 467.0e6 + 16.5e6}
+# DRAM bytes (read + write) of the dominant kernel per launch from an ncu capture of the same workload
+# (dram__bytes_read.sum + dram__bytes_write.sum); the line says where each figure came from
+NCU_TRAFFIC = {
+    "decode64": (329.3e6 + 4.3e6, "ncu capture of k_gateup_rows at decode64, one launch, constant recorded in bench.py"),
+    "prefill2048": (467.0e6 + 16.5e6, "ncu capture of k_prefill_gemm<GATEUP> at prefill2048, one launch, constant recorded in bench.py"),
+}
 
-Q6K_EXPERT_BYTES = 3 * (512 * 2048 // 256) * 210   # 2,580,480
+Q6K_MATRIX = (512 * 2048 // 256) * 210   # one [512][2048] or [2048][512] matrix, 860,160 B
+Q8_0_MATRIX = (512 * 2048 // 32) * 34    # 1,114,112 B
 ROUTER_BYTES = 256 * 2048 * 4
-VEC_BYTES = 2 * 2048 * 4                           # post-norm weight + shared-gate vector
+VEC_BYTES = 2 * 2048 * 4                 # post-norm weight + shared-gate vector
 
 
 def measured_peaks():
+    """(HBM GB/s, bf16 TFLOP/s burst, source)."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         p = json.load(open(path))
-        return float(p["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
-    return 6650.0, "fallback (no MEASURED_PEAKS.json)"
+        return float(p["hbm_gbs"]), float(p["bf16_tflops"]), "measured (MEASURED_PEAKS.json)"
+    return 6650.0, BF16_PEAK_TFLOPS_FALLBACK, "fallback (no MEASURED_PEAKS.json)"
 
 
-Q8_0_EXPERT_BYTES = 3 * (512 * 2048 // 32) * 34    # 3,342,336
+def matrix_bytes(quant: str) -> int:
+    return Q8_0_MATRIX if quant == "q8_0" else Q6K_MATRIX
 
 
-def layer_algorithmic_bytes(distinct: int, tokens: int, shared_q8: bool = False) -> int:
+def layer_algorithmic_bytes(distinct: float, tokens: int, args) -> float:
     """Weights of the experts actually routed + shared expert + router + vectors + x in, ffn_out, l_out."""
-    shared = Q8_0_EXPERT_BYTES if shared_q8 else Q6K_EXPERT_BYTES
-    return distinct * Q6K_EXPERT_BYTES + shared + ROUTER_BYTES + VEC_BYTES + tokens * 3 * 2048 * 4
+    routed = 2 * matrix_bytes(args.routed_quant) + matrix_bytes(args.routed_down_quant)
+    shared = 3 * matrix_bytes(args.shared_quant)
+    return distinct * routed + shared + ROUTER_BYTES + VEC_BYTES + tokens * 3 * 2048 * 4
 
 
-def gateup_algorithmic_bytes(distinct: int, tokens: int, shared_q8: bool = False) -> int:
+def gateup_algorithmic_bytes(distinct: float, tokens: int, args) -> float:
     """What the gate/up launch must move: gate and up of the routed experts and of the shared one,
     the f16 activations in, the f16 intermediates out."""
-    per = 2 * (512 * 2048 // 256) * 210
-    shared = 2 * (512 * 2048 // 32) * 34 if shared_q8 else per
-    return distinct * per + shared + tokens * 2048 * 2 + tokens * 9 * 512 * 2
+    return (distinct * 2 * matrix_bytes(args.routed_quant) + 2 * matrix_bytes(args.shared_quant)
+            + tokens * 2048 * 2 + tokens * 9 * 512 * 2)
+
+
+def quant_label(args) -> str:
+    r, d = args.routed_quant.upper(), args.routed_down_quant.upper()
+    return f"{r} gate/up/down" if r == d else f"{r} gate/up, {d} down"
+
+
+def moe_config(workload: str, args, world: int) -> dict:
+    """The workload as both arms print it: static facts only, so the two lines' `config` are equal."""
+    tokens, block_size, zipf = WORKLOADS[workload]
+    return {"workload": workload, "tokens": tokens, "experts": E, "top_k": K, "hidden": H, "intermediate": I,
+            "quant": quant_label(args), "shared_expert_quant": args.shared_quant.upper(), "bucket": block_size,
+            "routing": "Zipf(1.1)-skewed" if zipf else "unskewed", "resident_layers": args.layers,
+            "l2": "layers rotate every step; one layer's routed weights (660 MB) exceed the 126 MB L2",
+            "parallelism": f"replicas x{world}"}
+
+
+def ep_config(args, world: int) -> dict:
+    return {"workload": "ep_prefill_stack", "tokens": args.ep_tokens, "layers": args.ep_layers, "experts": E,
+            "top_k": K, "hidden": H, "intermediate": I, "quant": "Q6_K routed experts",
+            "shared_expert_quant": "Q8_0", "bucket": 64, "routing": "Zipf(1.1)-skewed",
+            "l2": "every layer has its own weights; a pass streams all of them (26.6 GB over all ranks)",
+            "parallelism": f"ep{world} ({E // world} experts/rank), " +
+                           ("peer-memory (NVLink) dispatch + combine, device-side counts and flags"
+                            if args.ep_peer_memory else "NCCL all-to-all-v dispatch + combine")}
 
 
 class ClockSampler:
@@ -93,6 +139,7 @@ class ClockSampler:
 
     def __init__(self, index: int):
         self.index, self.rows, self.proc = index, [], None
+        self.mark = 0
 
     def start(self):
         try:
@@ -108,20 +155,73 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
 
+    def begin_region(self):
+        """Samples from here on are the ones reported (the sampler itself starts before warm-up,
+        since nvidia-smi needs a moment to deliver its first line)."""
+        self.mark = len(self.rows)
+
     def stop(self) -> dict:
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"], "samples": 0}
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
-        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        rows = self.rows[self.mark:] or self.rows
+        sm = [float(r[0]) for r in rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i] == "Active" for r in self.rows)]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i] == "Active" for r in rows)]
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": reasons, "samples": len(sm)}
+
+
+class Timer:
+    """CUDA-event timing of a region of steps on the current stream, barrier and synchronise on both
+    sides, the maximum over ranks; regions shorter than MIN_TIMED_SECONDS are repeated back to back."""
+
+    def __init__(self, torch, dist, world):
+        self.torch, self.dist, self.world = torch, dist, world
+        self.stream = torch.cuda.current_stream()
+
+    def barrier(self):
+        self.torch.cuda.synchronize()
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def _max(self, v: float) -> float:
+        if self.world > 1:
+            t = self.torch.tensor([v], device="cuda")
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+            v = float(t.item())
+        return v
+
+    def region(self, fn, steps: int, repeats: int = 1) -> float:
+        """Milliseconds per step over `repeats` x `steps` steps."""
+        torch = self.torch
+        self.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(self.stream)
+        for _ in range(repeats):
+            for i in range(steps):
+                fn(i)
+        e1.record(self.stream)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / (steps * repeats)
+        self.barrier()
+        return self._max(ms)
+
+    def timed(self, fn, steps: int, min_seconds: float = MIN_TIMED_SECONDS):
+        """(ms per step, repeats): first `steps` steps once; if that took under `min_seconds`, the
+        reported figure comes from a second region of as many repeats as fill it."""
+        ms = self.region(fn, steps)
+        total = ms * steps * 1e-3
+        if total >= min_seconds:
+            return ms, 1
+        repeats = max(2, int(math.ceil(min_seconds / max(total, 1e-6))))
+        return self.region(fn, steps, repeats), repeats
 
 
 def host_layer_from_device(w):
@@ -141,7 +241,7 @@ def host_layer_from_device(w):
 
 def time_cpu_oracle(layer, x, steps: int, warmup: int, budget_s: float):
     """Times the CPU oracle (every host thread) on a bounded sample of the batch.  Returns
-    (tokens/s, sample tokens, steps timed, threads)."""
+    (tokens/s, sample tokens, steps timed, threads, ms per step)."""
     from oracle import xabe_oracle as oracle
     threads = oracle.max_threads()
     sample = x.shape[0]
@@ -163,14 +263,20 @@ def time_cpu_oracle(layer, x, steps: int, warmup: int, budget_s: float):
     return sample * steps / dt, sample, steps, threads, dt / steps * 1e3
 
 
-def run_reference(args) -> dict:
-    """`--impl reference`: the CPU oracle (the port of the reference's scalar path) on the host cores."""
-    tokens, block_size, zipf = WORKLOADS[args.workload]
+def _quant_code(name: str) -> int:
+    return 1 if name == "q8_0" else 0
+
+
+def run_reference(args, workload: str) -> dict:
+    """`--impl reference`: the CPU oracle (the port of the reference's scalar path) on the host cores,
+    every host thread, on a bounded sample of the same workload per step."""
     from llmxabe_b200 import synth
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     from helpers import oracle_layer
     from oracle import xabe_oracle as oracle
-    if args.workload.startswith("lm_head"):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if workload.startswith("lm_head"):
+        tokens = WORKLOADS[workload][0]
         # gemv over dequantised rows on a bounded sample of the vocabulary, scaled to all 248,320 rows
         rows, hidden, vocab = 16384, 2048, 248_320
         wb = synth.q8_0_bytes(rows * hidden, 0, 0, 3)
@@ -188,62 +294,92 @@ def run_reference(args) -> dict:
             "impl": "reference", "metric": "lm_head_tokens_per_s", "value": tps, "unit": "tokens/s",
             "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": per_pass * 1e3,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": args.workload, "tokens": tokens, "hidden": hidden, "vocab": vocab, "quant": "Q8_0"},
+            "config": head_config(workload),
             "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
                              "sample": f"{rows} of {vocab} vocabulary rows per step, scaled to the whole vocabulary"},
             "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         }
-    L = synth.moe_layer(seed=0, layer=0, zipf=zipf)
+    if workload == "ep_prefill_stack":
+        # one layer of the stack (Q6_K experts, Q8_0 shared expert) on a sample of the 16384 tokens; the
+        # metric is per layer, so tokens/s over one layer is the stack's figure
+        L = synth.moe_layer(seed=0, layer=0, shared_quant=synth.Q8_0, zipf=True)
+        config, scaling, tokens = ep_config(args, world), "strong", args.ep_tokens
+    elif workload.startswith("dense"):
+        tokens = WORKLOADS[workload][0]
+        hidden, inter = 5120, 17408
+        post_norm, gate, up, down = synth.dense_layer(seed=0, hidden=hidden, inter=inter, quant=0)
+        sample = min(tokens, 16)
+        x = synth.activations(sample, hidden, seed=0, layer=902)
+        threads = oracle.max_threads()
+        oracle.dense_block_forward(post_norm, 1e-6, gate, 0, up, 0, down, 0, hidden, inter, x, dev_order=False,
+                                   threads=threads)
+        steps = max(1, min(args.steps, 3))
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            oracle.dense_block_forward(post_norm, 1e-6, gate, 0, up, 0, down, 0, hidden, inter, x,
+                                       dev_order=False, threads=threads)
+        ms = (time.perf_counter() - t0) / steps * 1e3
+        tps = sample / (ms * 1e-3)
+        return {
+            "impl": "reference", "metric": "dense_layer_tokens_per_s", "value": tps, "unit": UNIT,
+            "n_gpus": args.gpus, "steps": steps, "warmup": 1, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": dense_config(workload, args, world),
+            "cpu_baseline": {"value": tps, "unit": UNIT, "cores": threads, "kind": "port",
+                             "sample": f"{sample} of {tokens} tokens per step, one layer, dequantisation included"},
+            "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        }
+    else:
+        tokens, _, zipf = WORKLOADS[workload]
+        L = synth.moe_layer(seed=0, layer=0, zipf=zipf, routed_quant=_quant_code(args.routed_quant),
+                            down_quant=_quant_code(args.routed_down_quant),
+                            shared_quant=_quant_code(args.shared_quant))
+        config, scaling = moe_config(workload, args, world), "weak"
     layer = oracle_layer(oracle, L)
-    x = synth.activations(tokens, 2048, seed=0, layer=900)
-    tps, sample, steps, threads, ms = time_cpu_oracle(layer, x, args.steps, args.warmup, budget_s=150.0)
+    x = synth.activations(min(tokens, 256), 2048, seed=0, layer=900)
+    tps, sample, steps, threads, ms = time_cpu_oracle(layer, x, max(1, min(args.steps, 20)), min(args.warmup, 2),
+                                                      budget_s=120.0)
     return {
         "impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "tokens": tokens, "experts": 256, "top_k": 8, "hidden": 2048,
-                   "intermediate": 512, "quant": "Q6_K"},
+        "steps": steps, "warmup": min(args.warmup, 2), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
         "cpu_baseline": {"value": tps, "unit": UNIT, "cores": threads, "kind": "port",
                          "sample": f"{sample} of {tokens} tokens per step, one layer, OpenMP over tokens/experts"},
         "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
 
 
-def run_ours(args) -> dict:
+def measure_moe(args, workload: str, *, full: bool, sampler: ClockSampler | None = None) -> dict:
+    """One single-layer MoE workload on this rank's GPU (replicas under torchrun).  `full` adds the
+    eager timing, the repeat distribution and the calibration row (the main line); without it only
+    the graph-replayed step, its stage profile and the host-buffer step are measured."""
     import torch
     import torch.distributed as dist
 
     from llmxabe_b200 import synth
-    from llmxabe_b200.moe import MoeBlock, MoeGeometry
+    from llmxabe_b200.moe import MoeBlock, MoeGeometry, kernel_launch_count
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise RuntimeError("bench.py needs a CUDA device: the MoE path has no CPU fallback")
-    torch.cuda.set_device(local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    tokens, block_size, zipf = WORKLOADS[args.workload]
-    H = 2048
+    tokens, block_size, zipf = WORKLOADS[workload]
     g = MoeGeometry.qwen3_6(block_size, tokens)
     block = MoeBlock(g)
-    shared_q = synth.Q8_0 if args.shared_quant == "q8_0" else synth.Q6K
-    layers = [synth.moe_layer_on_device(seed=rank, layer=i, zipf=zipf, shared_quant=shared_q) for i in range(args.layers)]
+    layers = [synth.moe_layer_on_device(seed=rank, layer=i, zipf=zipf, routed_quant=_quant_code(args.routed_quant),
+                                        down_quant=_quant_code(args.routed_down_quant),
+                                        shared_quant=_quant_code(args.shared_quant)) for i in range(args.layers)]
     gen = torch.Generator(device="cuda")
     gen.manual_seed(4242 + rank)
+    bf16_in = tokens >= 512   # a prefill chunk arrives as bf16 rows from the layers before it
     xs = [torch.randn(tokens, H, device="cuda", generator=gen) for _ in range(args.layers)]
+    if bf16_in:
+        xs = [x.to(torch.bfloat16) for x in xs]
     ffn = torch.empty(tokens, H, device="cuda")
     lout = torch.empty(tokens, H, device="cuda")
-    hx = [x.cpu().pin_memory() for x in xs]
+    hx = [x.float().cpu().pin_memory() for x in xs]
     hout = torch.empty(tokens, H).pin_memory()
     stream = torch.cuda.current_stream()
-
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+    tm = Timer(torch, dist, world)
+    steps = args.steps
 
     def step(i):
         block.forward(layers[i % args.layers], xs[i % args.layers], tokens, ffn, lout)
@@ -251,22 +387,6 @@ def run_ours(args) -> dict:
     def step_host(i):
         block.forward_host(layers[i % args.layers], hx[i % args.layers], tokens, None, hout)
         stream.synchronize()  # the caller reads the result every step
-
-    def timed(fn, steps):
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for i in range(steps):
-            fn(i)
-        e1.record(stream)
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / steps
-        barrier()
-        if world > 1:
-            t = torch.tensor([ms], device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
 
     # warm-up: at least W steps and at least 0.3 s, so clocks are up (the reference warms by duration,
     # crates/xabe-engine/src/bin/bench_dense_ffn.rs:57-65)
@@ -277,76 +397,76 @@ def run_ours(args) -> dict:
         i += 1
     torch.cuda.synchronize()
     # distinct experts each resident layer's batch routes (the "unique" denominator of the byte count)
-    distinct = []
+    distinct, busiest = [], 0
     for li in range(args.layers):
         step(li)
         torch.cuda.synchronize()
-        distinct.append(int(torch.unique(block.buffers().topk_ids[:tokens]).numel()))
+        ids = block.buffers().topk_ids[:tokens]
+        distinct.append(int(torch.unique(ids).numel()))
+        busiest = max(busiest, int(torch.bincount(ids.reshape(-1).long(), minlength=E).max().item()))
     d_mean = sum(distinct) / len(distinct)
 
-    # Decode steps are replayed from a CUDA graph, as the reference's decode bodies are
+    # Steps are replayed from a CUDA graph, as the reference's decode bodies are
     # (crates/xabe-engine/src/forward.rs:2059,3145): one graph holds one step per resident layer.
-    graph = None
+    graph, launches_per_step = None, None
     if args.graph:
         block.publish_tokens(tokens)
         torch.cuda.synchronize()
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            for i in range(args.layers):
-                step(i)
-        torch.cuda.current_stream().wait_stream(side)
-        torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
+        n0 = kernel_launch_count()
         with torch.cuda.graph(graph):
             for i in range(args.layers):
                 step(i)
+        launches_per_step = (kernel_launch_count() - n0) / args.layers
         torch.cuda.synchronize()
+    else:
+        n0 = kernel_launch_count()
+        step(0)
+        launches_per_step = kernel_launch_count() - n0
 
     def replay(i):
         if i % args.layers == 0:
             graph.replay()
 
-    sampler = ClockSampler(local_rank)
-    sampler.start()
-    ms_eager = timed(step, args.steps)
-    if graph is not None:
-        steps_g = (args.steps + args.layers - 1) // args.layers * args.layers
-        for i in range(args.layers * 3):
-            replay(i)
-        ms = timed(replay, steps_g)
-    else:
-        ms = ms_eager
-    clocks = sampler.stop()
-    # distribution over repeats of the timed region (median and best), same method
-    reps = []
-    for _ in range(5):
-        reps.append(timed(replay, steps_g) if graph is not None else timed(step, args.steps))
-    reps.sort()
-    # calibration row: a pure streaming read of one resident layer's expert weights
-    from llmxabe_b200.moe import stream_read
-    sink = torch.zeros(1, dtype=torch.int32, device="cuda")
-    w0 = layers[0]
-    cal_tensors = [w0.gate_exps.bytes, w0.up_exps.bytes, w0.down_exps.bytes]
-    cal_bytes = sum(int(t.numel()) for t in cal_tensors)
+    steps_g = (steps + args.layers - 1) // args.layers * args.layers
+    fn, n = (replay, steps_g) if graph is not None else (step, steps)
+    for i in range(args.layers * 3):
+        fn(i)
+    if sampler is not None:
+        sampler.begin_region()
+    ms, repeats = tm.timed(fn, n)
+    clocks = sampler.stop() if sampler is not None else None
+    out = {"tokens": tokens, "ms": ms, "repeats": repeats, "steps_timed": n, "d_mean": d_mean, "busiest": busiest,
+           "launches_per_step": launches_per_step, "clocks": clocks, "graph": graph is not None,
+           "bf16_in": bf16_in}
+    if full:
+        out["ms_eager"], _ = tm.timed(step, steps, min_seconds=0.1)
+        reps = sorted(tm.region(fn, n, repeats) for _ in range(5))
+        out["reps"] = {"median": reps[len(reps) // 2], "min": reps[0], "max": reps[-1], "n": len(reps)}
+        # calibration row: a pure streaming read of one resident layer's expert weights
+        from llmxabe_b200.moe import stream_read
+        sink = torch.zeros(1, dtype=torch.int32, device="cuda")
+        cal_bytes = sum(int(t.bytes.numel()) for t in (layers[0].gate_exps, layers[0].up_exps, layers[0].down_exps))
 
-    def cal_step(i):
-        w = layers[i % args.layers]
-        for t in (w.gate_exps.bytes, w.up_exps.bytes, w.down_exps.bytes):
-            stream_read(t, sink)
-    for i in range(3):
-        cal_step(i)
-    cal_ms = timed(cal_step, max(8, min(args.steps, 40)))
-    # the same region again with per-stage CUDA events, for the dominant kernel's duration
+        def cal_step(i):
+            w = layers[i % args.layers]
+            for t in (w.gate_exps.bytes, w.up_exps.bytes, w.down_exps.bytes):
+                stream_read(t, sink)
+        for i in range(3):
+            cal_step(i)
+        cal_ms, _ = tm.timed(cal_step, 20, min_seconds=0.1)
+        out["calibration"] = {"what": "pure 128-bit streaming read of one layer's routed expert weights, no arithmetic",
+                              "bytes": cal_bytes, "ms": cal_ms, "gbs": cal_bytes / (cal_ms * 1e-3) / 1e9}
+    # the same step with per-stage CUDA events, for the dominant kernel's duration
     block.moe.stage_profile(True)
-    timed(step, min(args.steps, 256))
+    tm.region(step, min(max(steps, 20), 256))
     stage_ms, calls = block.moe.stage_times()
     block.moe.stage_profile(False)
-    for i in range(3):
-        step_host(i)
+    out["stage_ms"] = {k: v / max(calls, 1) for k, v in stage_ms.items()}
     # The caller replays its host-buffer step from a CUDA graph too (one graph per resident layer:
     # pinned H2D copy, the block's launches, D2H copy) and reads the result after every step.
-    host_graphs = None
+    for i in range(3):
+        step_host(i)
     if args.graph:
         torch.cuda.synchronize()
         host_graphs = []
@@ -362,60 +482,135 @@ def run_ours(args) -> dict:
             stream.synchronize()  # the caller reads the result every step
         for i in range(3):
             step_host_graph(i)
-        ms_e2e = timed(step_host_graph, args.steps)
+        out["ms_e2e"], _ = tm.timed(step_host_graph, steps, min_seconds=0.25)
     else:
-        ms_e2e = timed(step_host, args.steps)
-    status = block.moe.device_status()
+        out["ms_e2e"], _ = tm.timed(step_host, steps, min_seconds=0.25)
+    out["status"] = block.moe.device_status()
+    out["layer0"], out["x0"] = layers[0], xs[0]
+    return out
 
-    launches_per_step = 7 if tokens * 8 <= 2048 and tokens > 8 else (6 if tokens <= 8 else 11)
-    peak, peak_src = measured_peaks()
-    gateup_ms = stage_ms["gate_up"] / max(calls, 1)
-    gu_bytes = gateup_algorithmic_bytes(d_mean, tokens, args.shared_quant == "q8_0")
+
+def moe_rooflines(args, workload: str, m: dict) -> dict:
+    """The roofline objects of one measured MoE workload: `roofline` for its dominant kernel (the
+    gate/up launch), `layer_roofline` for the whole step against HBM, and for prefill widths the
+    step's tensor-pipe figure as well."""
+    hbm, tflops, src = measured_peaks()
+    tokens = m["tokens"]
+    gateup_ms = m["stage_ms"]["gate_up"]
+    gu_bytes = gateup_algorithmic_bytes(m["d_mean"], tokens, args)
     achieved = gu_bytes / (gateup_ms * 1e-3) / 1e9 if gateup_ms > 0 else 0.0
-    layer_bytes = layer_algorithmic_bytes(d_mean, tokens, args.shared_quant == "q8_0")
+    layer_bytes = layer_algorithmic_bytes(m["d_mean"], tokens, args)
+    traffic, traffic_src = NCU_TRAFFIC.get(workload, (None, None))
+    if (args.shared_quant, args.routed_quant, args.routed_down_quant) != ("q6_k", "q6_k", "q6_k"):
+        traffic, traffic_src = None, None
+    kernel = ("k_prefill_gemm<GATEUP>" if tokens >= 512 else "k_gateup_rows" if tokens >= 16
+              else "k_expert_stream<GATEUP>")
+    out = {
+        "roofline": {"bound": "hbm", "kernel": f"gate/up + SwiGLU launch ({kernel})", "achieved": achieved,
+                     "peak": hbm, "unit": "GB/s", "frac": achieved / hbm, "traffic": traffic,
+                     "traffic_source": traffic_src, "peak_source": src,
+                     "algorithmic_bytes_per_launch": gu_bytes, "ms_per_launch": gateup_ms},
+        "layer_roofline": {"bound": "hbm", "algorithmic_bytes": layer_bytes,
+                           "achieved_gbs": layer_bytes / (m["ms"] * 1e-3) / 1e9,
+                           "frac": layer_bytes / (m["ms"] * 1e-3) / 1e9 / hbm},
+    }
+    if tokens >= 512:
+        # routed + shared GEMM flops only, the reference's accounting
+        # (crates/xabe-engine/src/bin/bench_moe_mma.rs:236-244)
+        flops = 2.0 * tokens * (K + 1) * 3 * H * I
+        gu_flops = 2.0 * tokens * (K + 1) * 2 * H * I
+        out["tensor_roofline"] = {
+            "bound": "tensor", "flops_per_step": flops, "achieved": flops / (m["ms"] * 1e-3) / 1e12,
+            "peak": tflops, "unit": "TFLOP/s", "frac": flops / (m["ms"] * 1e-3) / 1e12 / tflops,
+            "gate_up_launch_frac": gu_flops / (gateup_ms * 1e-3) / 1e12 / tflops if gateup_ms > 0 else None,
+            "peak_source": src + ", burst"}
+    return out
+
+
+def moe_entry(args, workload: str, m: dict) -> dict:
+    """The short form of a workload for the main line's `also` object."""
+    tokens = m["tokens"]
+    e = {"config": moe_config(workload, args, 1), "value": tokens / (m["ms"] * 1e-3), "unit": UNIT,
+         "ms_per_step": m["ms"], "timed_repeats": m["repeats"], "steps": m["steps_timed"],
+         "e2e": {"value": tokens / (m["ms_e2e"] * 1e-3), "unit": UNIT, "ms_per_step": m["ms_e2e"],
+                 "h2d_bytes_per_step": tokens * H * 4, "d2h_bytes_per_step": tokens * H * 4},
+         "gpu_launches_per_step": m["launches_per_step"], "stage_ms": m["stage_ms"],
+         "distinct_experts_mean": m["d_mean"], "busiest_expert_tokens": m["busiest"],
+         "device_status": m["status"]}
+    e.update(moe_rooflines(args, workload, m))
+    return e
+
+
+def run_ours(args, workload: str) -> dict:
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the MoE path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    sampler = ClockSampler(local_rank)
+    sampler.start()   # before warm-up: nvidia-smi takes a moment to deliver its first sample
+    m = measure_moe(args, workload, full=True, sampler=sampler)
+    tokens, ms = m["tokens"], m["ms"]
     out = {
         "metric": METRIC, "value": world * tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
-        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f16 activations x exact Q6_K codes, fp32 scales+accumulate",
-        "data": "synthetic",
-        "config": {"workload": args.workload, "tokens_per_rank": tokens, "experts": 256, "top_k": 8,
-                   "hidden": 2048, "intermediate": 512, "quant": "Q6_K", "shared_expert_quant": args.shared_quant,
-                   "bucket": block_size,
-                   "resident_layers": args.layers, "distinct_experts_mean": d_mean,
-                   "l2": f"layers rotate every step; each touches {layer_bytes / 1e6:.0f} MB of weights "
-                         f"(> 126 MB L2) out of {args.layers} resident layers",
-                   "parallelism": f"replicas x{world}"},
-        "e2e": {"value": world * tokens / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "timed_repeats": m["repeats"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": ("f16 activations x Q6_K/Q8_0 weights dequantised to f16 (tcgen05), fp32 accumulate" if tokens >= 512
+                  else "f16 activations x exact Q6_K/Q8_0 codes, fp32 scales+accumulate"),
+        "data": "synthetic", "config": moe_config(workload, args, world),
+        "workload_stats": {"distinct_experts_mean": m["d_mean"], "busiest_expert_tokens": m["busiest"],
+                           "activations_in": "bf16" if m["bf16_in"] else "f32"},
+        "e2e": {"value": world * tokens / (m["ms_e2e"] * 1e-3), "unit": UNIT, "ms_per_step": m["ms_e2e"],
                 "h2d_bytes_per_step": tokens * H * 4, "d2h_bytes_per_step": tokens * H * 4},
-        "gpu_launches": launches_per_step * args.steps, "ms_per_step_eager": ms_eager, "cuda_graph": graph is not None,
-        "clocks": clocks,
-        "roofline": {"bound": "hbm", "kernel": "gate/up + SwiGLU launch (k_expert_stream<GATEUP> below 16 tokens, k_gateup_rows from 16, k_prefill_gemm<GATEUP> from 512)", "achieved": achieved, "peak": peak,
-                     "unit": "GB/s", "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
-                     "peak_source": peak_src,
-                     "algorithmic_bytes_per_launch": gu_bytes, "ms_per_launch": gateup_ms},
-        "layer_roofline": {"algorithmic_bytes": layer_bytes, "achieved_gbs": layer_bytes / (ms * 1e-3) / 1e9,
-                           "frac": layer_bytes / (ms * 1e-3) / 1e9 / peak},
-        "stage_ms": {k: v / max(calls, 1) for k, v in stage_ms.items()},
-        "ms_per_step_repeats": {"median": reps[len(reps) // 2], "min": reps[0], "max": reps[-1], "n": len(reps)},
-        "calibration": {"what": "pure 128-bit streaming read of one layer's routed expert weights, no arithmetic",
-                        "bytes": cal_bytes, "ms": cal_ms, "gbs": cal_bytes / (cal_ms * 1e-3) / 1e9},
-        "device_status": status,
+        "gpu_launches": int(round(m["launches_per_step"] * m["steps_timed"] * m["repeats"])),
+        "gpu_launches_per_step": m["launches_per_step"],
+        "ms_per_step_eager": m["ms_eager"], "cuda_graph": m["graph"], "clocks": m["clocks"],
+        "stage_ms": m["stage_ms"], "ms_per_step_repeats": m["reps"], "calibration": m["calibration"],
+        "device_status": m["status"],
     }
+    out.update(moe_rooflines(args, workload, m))
     if rank == 0 and world == 1 and not args.no_cpu:
-        layer = host_layer_from_device(layers[0])
-        tps, sample, steps, threads, cms = time_cpu_oracle(layer, xs[0].cpu().numpy(), 3, 1, budget_s=30.0)
+        layer = host_layer_from_device(m["layer0"])
+        x_host = m["x0"].float().cpu().numpy()
+        tps, sample, steps, threads, cms = time_cpu_oracle(layer, x_host[:256], 3, 1, budget_s=30.0)
         out["cpu_baseline"] = {"value": tps, "unit": UNIT, "cores": threads, "kind": "port",
                                "sample": f"{sample} of {tokens} tokens x {steps} passes over layer 0 "
                                          f"({cms:.0f} ms per pass)"}
         # the same code on one thread (the reference's scalar path is single-threaded), a smaller sample
         from oracle import xabe_oracle as oracle
         n1 = min(4, tokens)
-        x1 = xs[0][:n1].cpu().numpy()
-        oracle.moe_block_forward(layer, x1, dev_order=False, threads=1)
+        oracle.moe_block_forward(layer, x_host[:n1], dev_order=False, threads=1)
         t0 = time.perf_counter()
-        oracle.moe_block_forward(layer, x1, dev_order=False, threads=1)
+        oracle.moe_block_forward(layer, x_host[:n1], dev_order=False, threads=1)
         out["cpu_baseline"]["single_thread"] = {"value": n1 / (time.perf_counter() - t0), "unit": UNIT,
                                                 "sample": f"{n1} tokens, one pass, dequantisation included"}
+    del m
+    torch.cuda.empty_cache()
+    if args.also and world == 1:
+        also = {}
+        for name in args.also_workloads:
+            if name == workload:
+                continue
+            try:
+                if name == "ep_prefill_stack":
+                    e = run_ep(args, init_dist=False)
+                    also[name] = {k: e[k] for k in ("config", "value", "unit", "ms_per_step", "steps", "scaling",
+                                                    "roofline", "e2e", "phase_ms_per_layer_rank0", "device_status",
+                                                    "gpu_launches_per_step")}
+                else:
+                    mm = measure_moe(args, name, full=False)
+                    also[name] = moe_entry(args, name, mm)
+                    del mm
+            except Exception as exc:  # the main line stands even if a side measurement fails
+                also[name] = {"error": f"{type(exc).__name__}: {exc}"}
+            torch.cuda.empty_cache()
+        out["also"] = also
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -423,14 +618,14 @@ def run_ours(args) -> dict:
 
 
 def run_stack(args) -> dict:
-    """`--stack-layers` MoE layers of config 1's geometry driven as the reference's Forward::body drives
+    """`--stack-layers` MoE layers of the 64-token decode geometry driven as the reference's Forward::body drives
     them (crates/xabe-engine/src/forward.rs:3497-3618): one handle, each layer's l_out the next layer's
     residual, the whole pass one CUDA graph, the token count a device scalar.  A step = one pass over the
     stack; `value` stays per layer (tokens x layers / time) so it compares with the one-layer workloads."""
     import torch
 
     from llmxabe_b200 import synth
-    from llmxabe_b200.moe import MoeGeometry
+    from llmxabe_b200.moe import MoeGeometry, kernel_launch_count
     from llmxabe_b200.stack import MoeStack
 
     if int(os.environ.get("WORLD_SIZE", "1")) != 1:
@@ -438,10 +633,13 @@ def run_stack(args) -> dict:
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py needs a CUDA device: the MoE path has no CPU fallback")
     torch.cuda.set_device(0)
+    sampler = ClockSampler(0)
+    sampler.start()
     tokens, block_size, zipf = WORKLOADS[args.workload]
-    H, n_layers = 2048, args.stack_layers
-    shared_q = synth.Q8_0 if args.shared_quant == "q8_0" else synth.Q6K
-    layers = [synth.moe_layer_on_device(seed=0, layer=i, zipf=zipf, shared_quant=shared_q) for i in range(n_layers)]
+    n_layers = args.stack_layers
+    layers = [synth.moe_layer_on_device(seed=0, layer=i, zipf=zipf, routed_quant=_quant_code(args.routed_quant),
+                                        down_quant=_quant_code(args.routed_down_quant),
+                                        shared_quant=_quant_code(args.shared_quant)) for i in range(n_layers)]
     stack = MoeStack(MoeGeometry.qwen3_6(block_size, tokens), layers)
     gen = torch.Generator(device="cuda")
     gen.manual_seed(4242)
@@ -454,7 +652,9 @@ def run_stack(args) -> dict:
         int(torch.unique(stack.block.buffers().topk_ids[:tokens]).numel())))
     torch.cuda.synchronize()
     d_mean = sum(distinct) / len(distinct)
+    n0 = kernel_launch_count()
     stack.capture()
+    launches_per_pass = (kernel_launch_count() - n0) // 2   # capture() runs the pass twice (warm-up + capture)
 
     def step(_i):
         stack.replay()
@@ -465,54 +665,51 @@ def run_stack(args) -> dict:
         hout.copy_(stack.hidden_out[:tokens], non_blocking=True)
         stream.synchronize()
 
-    def timed(fn, steps):
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for i in range(steps):
-            fn(i)
-        e1.record(stream)
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / steps
-
+    tm = Timer(torch, None, 1)
     t0 = time.perf_counter()
     i = 0
     while i < max(args.warmup, 3) or time.perf_counter() - t0 < 0.3:
         step(i)
         i += 1
     steps = max(3, min(args.steps, 50))
-    sampler = ClockSampler(0)
-    sampler.start()
-    ms = timed(step, steps)
+    sampler.begin_region()
+    ms, repeats = tm.timed(step, steps)
     clocks = sampler.stop()
     for i in range(3):
         step_host(i)
-    ms_e2e = timed(step_host, steps)
+    ms_e2e, _ = tm.timed(step_host, steps, min_seconds=0.25)
     status = stack.block.moe.device_status()
-    peak, peak_src = measured_peaks()
-    layer_bytes = layer_algorithmic_bytes(d_mean, tokens, args.shared_quant == "q8_0")
+    hbm, _, peak_src = measured_peaks()
+    layer_bytes = layer_algorithmic_bytes(d_mean, tokens, args)
     achieved = n_layers * layer_bytes / (ms * 1e-3) / 1e9
+    cfg = moe_config("decode64_stack", args, 1)
+    cfg.update({"layers": n_layers, "resident_layers": n_layers,
+                "l2": f"every layer has its own weights ({n_layers * layer_bytes / 1e9:.1f} GB per pass, L2 126 MB)",
+                "parallelism": "one GPU"})
     return {
         "metric": METRIC, "value": tokens * n_layers / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f16 activations x exact Q6_K codes, fp32 scales+accumulate",
-        "data": "synthetic",
-        "config": {"workload": args.workload, "tokens_per_rank": tokens, "layers": n_layers, "experts": 256,
-                   "top_k": 8, "hidden": 2048, "intermediate": 512, "quant": "Q6_K",
-                   "shared_expert_quant": args.shared_quant, "bucket": block_size,
-                   "distinct_experts_mean": d_mean, "stack_passes_per_s": 1e3 / ms,
-                   "stack_tokens_per_s": tokens * 1e3 / ms,
-                   "l2": f"every layer has its own weights ({n_layers * layer_bytes / 1e9:.1f} GB per pass, L2 126 MB)",
-                   "parallelism": "one GPU"},
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "timed_repeats": repeats, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16 activations x exact Q6_K/Q8_0 codes, fp32 scales+accumulate", "data": "synthetic",
+        "config": cfg,
+        "workload_stats": {"distinct_experts_mean": d_mean, "stack_passes_per_s": 1e3 / ms,
+                           "stack_tokens_per_s": tokens * 1e3 / ms},
         "e2e": {"value": tokens * n_layers / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": tokens * H * 4, "d2h_bytes_per_step": tokens * H * 4},
-        "gpu_launches": 7 * n_layers * steps, "cuda_graph": True, "clocks": clocks,
+        "gpu_launches": launches_per_pass * steps * repeats, "gpu_launches_per_step": launches_per_pass,
+        "cuda_graph": True, "clocks": clocks,
         "roofline": {"bound": "hbm", "kernel": "whole stack pass (all launches of all layers, one graph)",
-                     "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
-                     "peak_source": peak_src, "algorithmic_bytes_per_launch": n_layers * layer_bytes,
-                     "ms_per_launch": ms},
+                     "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm, "traffic": None,
+                     "traffic_source": None, "peak_source": peak_src,
+                     "algorithmic_bytes_per_launch": n_layers * layer_bytes, "ms_per_launch": ms},
         "device_status": status,
     }
+
+
+def head_config(workload: str) -> dict:
+    return {"workload": workload, "tokens": WORKLOADS[workload][0], "hidden": 2048, "vocab": 248_320,
+            "quant": "Q8_0", "l2": "three resident copies of the head rotate; one copy is 540 MB (L2 126 MB)",
+            "parallelism": "one GPU"}
 
 
 def run_head(args) -> dict:
@@ -520,10 +717,8 @@ def run_head(args) -> dict:
     the 540 MB Q8_0 tensor serves up to eight tokens.  Three resident copies of the head rotate, and
     one copy alone is four times the L2.  A step = logits for the batch (+ argmax and the 4-byte
     read-back of each token id in the end-to-end figure, which is what a sampler reads)."""
-    import numpy as np
     import torch
 
-    from llmxabe_b200 import synth
     from llmxabe_b200.lm_head import HeadFormat, HeadTensor, LmHeadGeometry, LmHeadKernels
 
     if int(os.environ.get("WORLD_SIZE", "1")) != 1:
@@ -531,6 +726,8 @@ def run_head(args) -> dict:
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py needs a CUDA device: the LM head has no CPU fallback")
     torch.cuda.set_device(0)
+    sampler = ClockSampler(0)
+    sampler.start()
     tokens = WORKLOADS[args.workload][0]
     g = LmHeadGeometry.qwen3_6(tokens)
     head = LmHeadKernels(g)
@@ -561,48 +758,34 @@ def run_head(args) -> dict:
         hids.copy_(ids, non_blocking=True)
         stream.synchronize()
 
-    def timed(fn, steps):
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for i in range(steps):
-            fn(i)
-        e1.record(stream)
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / steps
-
+    tm = Timer(torch, None, 1)
     t0 = time.perf_counter()
     i = 0
     while i < max(args.warmup, 3) or time.perf_counter() - t0 < 0.3:
         step(i)
         i += 1
-    sampler = ClockSampler(0)
-    sampler.start()
-    ms = timed(step, args.steps)
+    sampler.begin_region()
+    ms, repeats = tm.timed(step, args.steps)
     clocks = sampler.stop()
     for i in range(3):
         step_host(i)
-    ms_e2e = timed(step_host, args.steps)
+    ms_e2e, _ = tm.timed(step_host, args.steps, min_seconds=0.25)
     status = head.device_status()
-    peak, peak_src = measured_peaks()
+    hbm, _, peak_src = measured_peaks()
     alg_bytes = g.weight_bytes_read(tokens) + tokens * (g.hidden + g.vocab) * 4
     achieved = alg_bytes / (ms * 1e-3) / 1e9
     out = {
         "metric": "lm_head_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
-        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "timed_repeats": repeats,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "exact Q8_0 codes x fp32 activations as two f16 parts, fp32 scales+accumulate",
-        "data": "synthetic",
-        "config": {"workload": args.workload, "tokens": tokens, "hidden": g.hidden, "vocab": g.vocab,
-                   "quant": "Q8_0", "weight_bytes": n_bytes,
-                   "l2": "three resident copies of the head rotate; one copy is 540 MB (L2 126 MB)",
-                   "parallelism": "one GPU"},
+        "data": "synthetic", "config": head_config(args.workload),
         "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": tokens * g.hidden * 4, "d2h_bytes_per_step": tokens * 4},
-        "gpu_launches": 2 * args.steps, "cuda_graph": False, "clocks": clocks,
-        "roofline": {"bound": "hbm", "kernel": "k_head_rows<Q8_0>", "achieved": achieved, "peak": peak,
-                     "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
-                     "algorithmic_bytes_per_launch": alg_bytes, "ms_per_launch": ms},
+        "gpu_launches": 2 * args.steps * repeats, "gpu_launches_per_step": 2, "cuda_graph": False, "clocks": clocks,
+        "roofline": {"bound": "hbm", "kernel": "k_head_rows<Q8_0>", "achieved": achieved, "peak": hbm,
+                     "unit": "GB/s", "frac": achieved / hbm, "traffic": None, "traffic_source": None,
+                     "peak_source": peak_src, "algorithmic_bytes_per_launch": alg_bytes, "ms_per_launch": ms},
         "device_status": status,
     }
     if not args.no_cpu:
@@ -624,24 +807,26 @@ def run_head(args) -> dict:
     return out
 
 
-def run_ep(args) -> dict:
-    """BASELINE config 3: a stack of MoE layers (Q6_K experts, Q8_0 shared expert), `--ep-tokens` tokens,
-    experts sharded over the ranks with NCCL all-to-all dispatch/combine.  Strong scaling: the global
-    batch is fixed, each rank owns tokens/N tokens and 256/N experts of every layer."""
+def run_ep(args, init_dist: bool = True) -> dict:
+    """The 40-layer prefill stack (Q6_K experts, Q8_0 shared expert), `--ep-tokens` tokens, experts
+    sharded over the ranks, rows and results exchanged over peer memory (or NCCL all-to-alls with
+    --ep-nccl).  Strong scaling: the global batch is fixed, each rank owns tokens/N tokens and 256/N
+    experts of every layer.  A step = one pass over all layers."""
     import torch
     import torch.distributed as dist
 
     from llmxabe_b200 import synth
     from llmxabe_b200.ep import CudaEpBackend, EpMoeBlock
-    from llmxabe_b200.moe import MoeGeometry, QuantTensor
+    from llmxabe_b200.moe import MoeGeometry, QuantTensor, kernel_launch_count
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
-    if world > 1:
+    if world > 1 and init_dist:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    E, K, H, I = 256, 8, 2048, 512
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     tokens, n_layers = args.ep_tokens, args.ep_layers
     per, epr = tokens // world, E // world
     g = MoeGeometry(E, K, H, I, 64, per)
@@ -669,38 +854,40 @@ def run_ep(args) -> dict:
     gen = torch.Generator(device="cuda")
     gen.manual_seed(31 + rank)
     x0 = torch.randn(per, H, device="cuda", generator=gen)
+    hx = x0.cpu().pin_memory()
+    hout = torch.empty(per, H).pin_memory()
     bufs = [torch.empty(per, H, device="cuda") for _ in range(2)]
     ffn = torch.empty(per, H, device="cuda")
+    stream = torch.cuda.current_stream()
+    xin = torch.empty_like(x0)
 
-    def step(_i):
-        h = x0
+    def step(_i, src=x0):
+        h = src
         for li, (front, local) in enumerate(layers):
             backend.set_layer(front, *local)
             out = bufs[li & 1]
             blk.forward(h, per, ffn, out)
             h = out
+        return h
 
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+    def step_host(i):   # this rank's rows from pinned host memory, its final hidden state back
+        xin.copy_(hx, non_blocking=True)
+        h = step(i, xin)
+        hout.copy_(h, non_blocking=True)
+        stream.synchronize()
 
-    for i in range(max(args.warmup, 1)):
+    tm = Timer(torch, dist, world)
+    for i in range(max(min(args.warmup, 3), 1)):
         step(i)
-    barrier()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
-    stream = torch.cuda.current_stream()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for i in range(args.steps):
-        step(i)
-    e1.record(stream)
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / args.steps
-    barrier()
+    n0 = kernel_launch_count()
+    step(0)
+    launches_per_step = kernel_launch_count() - n0
+    steps = max(1, min(args.steps, 10))
+    sampler.begin_region()
+    ms, repeats = tm.timed(step, steps)
     clocks = sampler.stop()
+    step_host(0)
+    ms_e2e, _ = tm.timed(step_host, max(1, min(steps, 3)), min_seconds=0.0)
     rows = sum(blk.last_plan.recv_counts) if blk.last_plan is not None else 0  # not known on the host with peer memory
     # one more, untimed, pass with per-phase events (per layer, this rank)
     blk.enable_phase_timing()
@@ -708,44 +895,58 @@ def run_ep(args) -> dict:
     phases = {k: v / n_layers for k, v in blk.phase_times_ms().items()}
     blk._events = None
     if world > 1:
-        t = torch.tensor([ms, float(rows)], device="cuda")
+        t = torch.tensor([float(rows)], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, rows = float(t[0].item()), int(t[1].item())
+        rows = int(t[0].item())
     status = backend.front_k.device_status() | backend.back_k.device_status()
+    _, tflops, peak_src = measured_peaks()
     flops = 2.0 * tokens * (K + 1) * 3 * H * I * n_layers
     out = {
         "metric": METRIC, "value": tokens * n_layers / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
-        "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "f16 x f16 -> f32 (tcgen05), weights dequantised to f16",
-        "data": "synthetic",
-        "config": {"workload": "ep_prefill_stack", "tokens_global": tokens, "layers": n_layers, "experts": E,
-                   "top_k": K, "hidden": H, "intermediate": I, "quant": "Q6_K experts, Q8_0 shared",
-                   "parallelism": f"ep{world} ({epr} experts/rank), " +
-                                  ("peer-memory (NVLink) dispatch + combine, device-side counts and flags"
-                                   if args.ep_peer_memory else "NCCL all-to-all-v dispatch + combine"),
-                   "max_rows_received_by_a_rank_last_layer": rows,
-                   "l2": "every layer has its own weights; a pass streams all of them"},
+        "steps": steps, "warmup": max(min(args.warmup, 3), 1), "ms_per_step": ms, "timed_repeats": repeats,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f16 x f16 -> f32 (tcgen05), weights dequantised to f16", "data": "synthetic",
+        "config": ep_config(args, world),
+        "workload_stats": {"max_rows_received_by_a_rank_last_layer": rows},
+        "e2e": {"value": tokens * n_layers / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": per * H * 4, "d2h_bytes_per_step": per * H * 4},
         "clocks": clocks, "device_status": status, "phase_ms_per_layer_rank0": phases,
-        "roofline": {"bound": "tensor", "achieved": flops / (ms * 1e-3) / 1e12 / world, "unit": "TFLOP/s per GPU",
-                     "peak": 1628.8, "frac": flops / (ms * 1e-3) / 1e12 / world / 1628.8, "traffic": None},
-        "gpu_launches": None,
+        "roofline": {"bound": "tensor", "kernel": "whole stack pass per GPU (routed + shared GEMM flops only)",
+                     "achieved": flops / (ms * 1e-3) / 1e12 / world, "unit": "TFLOP/s", "peak": tflops,
+                     "frac": flops / (ms * 1e-3) / 1e12 / world / tflops, "traffic": None, "traffic_source": None,
+                     "peak_source": peak_src + ", burst"},
+        "gpu_launches": launches_per_step * steps * repeats, "gpu_launches_per_step": launches_per_step,
+        "cuda_graph": False,
     }
-    if world > 1:
+    if args.ep_peer_memory:
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        for b in backend._shared.values():
+            b.release()
+    if world > 1 and init_dist:
         dist.barrier()
         dist.destroy_process_group()
     return out if rank == 0 else {}
 
 
+def dense_config(workload: str, args, world: int) -> dict:
+    return {"workload": workload, "tokens": WORKLOADS[workload][0], "hidden": 5120, "intermediate": 17408,
+            "quant": "Q6_K", "resident_layers": max(args.layers, 2),
+            "parallelism": f"tp{world} (intermediate split in whole 256-element units), NCCL all-reduce",
+            "l2": "layers rotate every step; one layer is 219 MB (> 126 MB L2)"}
+
+
 def run_dense(args) -> dict:
-    """BASELINE config 4: the dense SwiGLU block of the 27B sibling, Q6_K.  One rank: DenseFfnBlock.
+    """The dense SwiGLU block of the 27B sibling, Q6_K.  One rank: DenseFfnBlock.
     Several ranks: the intermediate dimension sharded (llmxabe_b200.tp), one all-reduce per layer;
     strong scaling (the token batch is the same on every rank)."""
     import torch
     import torch.distributed as dist
 
     from llmxabe_b200 import synth
-    from llmxabe_b200.moe import QuantTensor
-    from llmxabe_b200.tp import CudaTpBackend, TpDenseFfnBlock, shard_bounds
+    from llmxabe_b200.moe import QuantTensor, kernel_launch_count
+    from llmxabe_b200.tp import CudaTpBackend, TpDenseFfnBlock
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -753,17 +954,18 @@ def run_dense(args) -> dict:
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    H, I = 5120, 17408
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    HD, ID = 5120, 17408
     tokens = WORKLOADS[args.workload][0]
     n_layers = max(args.layers, 2)
-    i0, i1 = shard_bounds(I, rank, world)
     blocks = []
     for li in range(n_layers):
         gen = torch.Generator(device="cuda")
         gen.manual_seed(4000 + li)           # every rank generates the full matrices and keeps its shard
-        full = [QuantTensor(synth._device_quant_bytes(torch, synth.Q6K, H * I, gen, "cuda"), synth.Q6K)
+        full = [QuantTensor(synth._device_quant_bytes(torch, synth.Q6K, HD * ID, gen, "cuda"), synth.Q6K)
                 for _ in range(3)]
-        backend = CudaTpBackend(H, I, tokens, rank, world, torch.ones(H, device="cuda"), *full)
+        backend = CudaTpBackend(HD, ID, tokens, rank, world, torch.ones(HD, device="cuda"), *full)
         if world > 1:
             backend.gate = QuantTensor(backend.gate.bytes.clone(), synth.Q6K)
             backend.up = QuantTensor(backend.up.bytes.clone(), synth.Q6K)
@@ -774,83 +976,61 @@ def run_dense(args) -> dict:
     torch.cuda.empty_cache()
     gen = torch.Generator(device="cuda")
     gen.manual_seed(99)
-    x0 = torch.randn(tokens, H, device="cuda", generator=gen)
-    bufs = [torch.empty(tokens, H, device="cuda") for _ in range(2)]
-    ffn = torch.empty(tokens, H, device="cuda")
+    x0 = torch.randn(tokens, HD, device="cuda", generator=gen)
+    bufs = [torch.empty(tokens, HD, device="cuda") for _ in range(2)]
+    ffn = torch.empty(tokens, HD, device="cuda")
+    stream = torch.cuda.current_stream()
 
     def step(i):
         blocks[i % n_layers].forward(x0, tokens, ffn, bufs[i & 1])
 
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
+    tm = Timer(torch, dist, world)
     for i in range(max(args.warmup, 3)):
         step(i)
-    barrier()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        step(i)
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / args.steps
-    barrier()
+    n0 = kernel_launch_count()
+    step(0)
+    launches_per_step = kernel_launch_count() - n0
+    sampler.begin_region()
+    ms, repeats = tm.timed(step, args.steps)
     clocks = sampler.stop()
-    if world > 1:
-        t = torch.tensor([ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t[0].item())
     status = 0
     for b in blocks:
         status |= b.backend.k.device_status()
     # end to end: host rows in, host rows out
-    hx = torch.randn(tokens, H).pin_memory()
-    hout = torch.empty(tokens, H).pin_memory()
-    dx = torch.empty(tokens, H, device="cuda")
-    barrier()
-    e0.record()
-    e2e_steps = max(3, min(args.steps, 20))
-    for i in range(e2e_steps):
+    hx = torch.randn(tokens, HD).pin_memory()
+    hout = torch.empty(tokens, HD).pin_memory()
+    dx = torch.empty(tokens, HD, device="cuda")
+
+    def step_host(i):
         dx.copy_(hx, non_blocking=True)
         blocks[i % n_layers].forward(dx, tokens, ffn, bufs[0])
         hout.copy_(bufs[0], non_blocking=True)
-    e1.record()
-    torch.cuda.synchronize()
-    e2e_ms = e0.elapsed_time(e1) / e2e_steps
-    if world > 1:
-        t = torch.tensor([e2e_ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t[0].item())
-    peak, peak_src = measured_peaks()
-    weight_bytes = 3 * (H * I // 256) * 210
-    alg_bytes = weight_bytes // world + tokens * H * 4 * 3
-    flops = 2.0 * tokens * 3 * H * I
+        stream.synchronize()
+    step_host(0)
+    e2e_ms, _ = tm.timed(step_host, max(3, min(args.steps, 20)), min_seconds=0.25)
+    hbm, tflops, peak_src = measured_peaks()
+    weight_bytes = 3 * (HD * ID // 256) * 210
+    alg_bytes = weight_bytes // world + tokens * HD * 4 * 3
+    flops = 2.0 * tokens * 3 * HD * ID
     hbm_bound = tokens <= 256
-    roof = ({"bound": "hbm", "achieved": alg_bytes / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
-             "frac": alg_bytes / (ms * 1e-3) / 1e9 / peak, "traffic": None, "peak_source": peak_src,
-             "algorithmic_bytes_per_launch": alg_bytes, "note": "whole layer per rank (norm, gate/up, down, residual)"}
+    roof = ({"bound": "hbm", "kernel": "whole layer per rank (norm, gate/up, down, residual)",
+             "achieved": alg_bytes / (ms * 1e-3) / 1e9, "peak": hbm, "unit": "GB/s",
+             "frac": alg_bytes / (ms * 1e-3) / 1e9 / hbm, "traffic": None, "traffic_source": None,
+             "peak_source": peak_src, "algorithmic_bytes_per_launch": alg_bytes}
             if hbm_bound else
-            {"bound": "tensor", "achieved": flops / world / (ms * 1e-3) / 1e12, "peak": 1628.8, "unit": "TFLOP/s",
-             "frac": flops / world / (ms * 1e-3) / 1e12 / 1628.8, "traffic": None,
-             "peak_source": "measured (MEASURED_PEAKS.json, burst)", "note": "whole layer per rank"})
+            {"bound": "tensor", "kernel": "whole layer per rank", "achieved": flops / world / (ms * 1e-3) / 1e12,
+             "peak": tflops, "unit": "TFLOP/s", "frac": flops / world / (ms * 1e-3) / 1e12 / tflops, "traffic": None,
+             "traffic_source": None, "peak_source": peak_src + ", burst"})
     out = {
         "metric": "dense_layer_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
-        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None,
-        "dtype": "f16 x f16 -> f32 (tcgen05), Q6_K weights dequantised to f16 on the fly", "data": "synthetic",
-        "config": {"workload": args.workload, "tokens": tokens, "hidden": H, "intermediate": I, "quant": "Q6_K",
-                   "resident_layers": n_layers,
-                   "parallelism": f"tp{world} (intermediate {i1 - i0} of {I} per rank), NCCL all-reduce",
-                   "l2": f"layers rotate every step; a layer's shard is {weight_bytes // world >> 20} MiB (> 126 MB L2)"
-                         if weight_bytes // world > 126 << 20 else "layers rotate every step"},
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "timed_repeats": repeats,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f16 activations x Q6_K weights (exact codes at decode widths, f16 weights on tcgen05 at prefill widths), fp32 accumulate",
+        "data": "synthetic", "config": dense_config(args.workload, args, world),
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": tokens * H * 4, "d2h_bytes_per_step": tokens * H * 4},
-        "gpu_launches": args.steps * 5, "clocks": clocks, "roofline": roof, "device_status": status,
+                "h2d_bytes_per_step": tokens * HD * 4, "d2h_bytes_per_step": tokens * HD * 4},
+        "gpu_launches": launches_per_step * args.steps * repeats, "gpu_launches_per_step": launches_per_step,
+        "cuda_graph": False, "clocks": clocks, "roofline": roof, "device_status": status,
     }
     if world > 1:
         dist.barrier()
@@ -864,11 +1044,20 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode64", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
+                    help="default: decode64 as one plain process, ep_prefill_stack under torch.distributed.run")
     ap.add_argument("--layers", type=int, default=4, help="distinct resident layers the steps rotate over")
     ap.add_argument("--no-cpu", action="store_true", help="skip the timed CPU baseline")
+    ap.add_argument("--no-also", dest="also", action="store_false",
+                    help="skip the side measurements the default line carries in `also`")
+    ap.add_argument("--also-workloads", default="decode1,prefill2048,ep_prefill_stack",
+                    type=lambda s: [w for w in s.split(",") if w])
     ap.add_argument("--shared-quant", default="q6_k", choices=["q6_k", "q8_0"],
                     help="format of the shared expert in the MoE workloads (the shipped file's is Q8_0)")
+    ap.add_argument("--routed-quant", default="q6_k", choices=["q6_k", "q8_0"],
+                    help="format of the routed gate/up stacks (Q8_0 in the shipped file's last block)")
+    ap.add_argument("--routed-down-quant", default=None, choices=["q6_k", "q8_0"],
+                    help="format of the routed down stack (the shipped file's is Q8_0); default: as --routed-quant")
     ap.add_argument("--stack-layers", type=int, default=40, help="layers of the decode64_stack workload")
     ap.add_argument("--ep-tokens", type=int, default=16384)
     ap.add_argument("--ep-layers", type=int, default=40)
@@ -876,6 +1065,14 @@ def main():
                     help="exchange rows and results with NCCL all-to-alls instead of peer stores over NVLink")
     ap.add_argument("--no-graph", dest="graph", action="store_false", help="time eager launches instead of CUDA-graph replay")
     args = ap.parse_args()
+    if args.routed_down_quant is None:
+        args.routed_down_quant = args.routed_quant
+    under_torchrun = "WORLD_SIZE" in os.environ and "RANK" in os.environ
+    default_workload = args.workload is None
+    workload = args.workload or ("ep_prefill_stack" if under_torchrun else "decode64")
+    args.workload = workload
+    if not default_workload:
+        args.also = False
     # Libraries write to stdout too (NCCL prints its version line there when NCCL_DEBUG asks for it):
     # while the workload runs, file descriptor 1 points at stderr, and it is put back for the one JSON line.
     sys.stdout.flush()
@@ -890,18 +1087,18 @@ def main():
     if args.impl == "reference":
         if int(os.environ.get("RANK", "0")) != 0:
             return
-        emit(run_reference(args))
+        emit(run_reference(args, workload))
         return
-    if args.workload == "ep_prefill_stack":
+    if workload == "ep_prefill_stack":
         out = run_ep(args)
-    elif args.workload.startswith("dense"):
+    elif workload.startswith("dense"):
         out = run_dense(args)
-    elif args.workload == "decode64_stack":
+    elif workload == "decode64_stack":
         out = run_stack(args)
-    elif args.workload.startswith("lm_head"):
+    elif workload.startswith("lm_head"):
         out = run_head(args)
     else:
-        out = run_ours(args)
+        out = run_ours(args, workload)
     if out:
         emit(out)
 

@@ -122,6 +122,11 @@ const char* xabe_moe_last_error(void);
 /* ABI revision of this header. */
 int xabe_moe_abi_version(void);
 
+/* How many kernels this library has launched in this process so far, counted at the launch sites
+ * (a launch recorded into a CUDA graph during capture counts once, at capture).  No counterpart in
+ * the reference; a benchmark uses the difference around a step to state its launches per step. */
+uint64_t xabe_kernel_launch_count(void);
+
 /* MoeGeometry::{sorted_capacity, expert_block_capacity} (moe.rs:4575-4589). Pure host. */
 uint64_t xabe_moe_sorted_capacity(const xabe_moe_geometry* g);
 uint64_t xabe_moe_expert_block_capacity(const xabe_moe_geometry* g);
@@ -281,6 +286,39 @@ int xabe_moe_buffers(xabe_moe* m, xabe_moe_buffer_view* out);
  * exactly where plain decode's would. */
 int xabe_moe_set_exact_decode_regime(xabe_moe* m, int on);
 
+/* MoeKernels::disable_tensor_cores (moe.rs:5416-5418): from now on this handle never runs the
+ * tcgen05 grouped GEMMs; every width takes the decode-shaped kernels (exact integer codes, fp32
+ * scales), which is the path the tight differential gate is stated on.  Not reversible, as in the
+ * reference.  Contractions the decode kernels cannot hold (the dense 27B block) fall back to the
+ * one-tile-per-CTA kernels.  tensor_cores_enabled mirrors moe.rs:5456-5458. */
+int xabe_moe_disable_tensor_cores(xabe_moe* m);
+int xabe_moe_tensor_cores_enabled(const xabe_moe* m);
+
+/* The opposite switch, for differential tests of the tcgen05 kernels at widths that would not
+ * select them (the reference's tests reach its MMA path the same way, by handle switch rather than
+ * by environment: tests/moe_differential.rs:118-145).  Must be chosen before route_and_dispatch,
+ * which builds the work list of the kernels that will run.  Ignored while the exact-decode regime
+ * or disable_tensor_cores is in force. */
+int xabe_moe_force_prefill_path(xabe_moe* m, int on);
+
+/* Per-handle tuning switches; none changes a result, only which launch shape produces it.  They
+ * replace process-wide environment reads: a host with several handles sets each one's own.
+ * PREFILL_WIDE allocates (set-up time only); the others are plain field writes. */
+#define XABE_TUNE_PDL 0                /* 1: programmatic dependent launch between the block's kernels */
+#define XABE_TUNE_STREAM_STAGES 1      /* ring depth cap of the streaming kernels (0 = as many as fit) */
+#define XABE_TUNE_STREAM_RUNS 2        /* k_expert_stream work split override (0 = the kernel's choice) */
+#define XABE_TUNE_ROWS_MIN_TOKENS 3    /* narrowest handle that runs gate/up through k_gateup_rows (0 = never, -1 = default) */
+#define XABE_TUNE_ROUTER_REGW 4        /* router kernel with expert rows in registers: 0 off, 1 on, -1 by width */
+#define XABE_TUNE_FORCE_TILE_KERNELS 5 /* 1: the one-tile-per-CTA expert kernels everywhere */
+#define XABE_TUNE_PREFILL_WIDE 6       /* 1: k_prefill_gemm_wide (four accumulators per unpacked weight pair), 0: off */
+#define XABE_TUNE_FUSED_DECODE 7       /* 0: the unfused decode front and tail (one kernel per stage), 1: fused (default) */
+int xabe_moe_set_tuning(xabe_moe* m, int key, int value);
+
+/* Iteration limit (x 200 ns) of this handle's waits on other ranks' flags in the peer-memory
+ * exchange; 0 restores the default of several seconds.  A wait that runs out records device
+ * status 3 and the owner-side step that follows it moves nothing (see ep_p2p_receive). */
+int xabe_moe_set_peer_wait_limit(xabe_moe* m, uint32_t iterations);
+
 /* Reads (and clears) the device status word the kernels' bounded waits write:
  * 0 when every wait completed.  Synchronises `stream`. */
 int xabe_moe_device_status(xabe_moe* m, void* stream, int* status_out);
@@ -318,10 +356,22 @@ int xabe_dequantize(void* stream, xabe_quant_tensor t, float* out);
  *   first call before any stream capture.  All calls share the one array, which
  *   keeps the previous call's contents (the call rewrites every word it later
  *   reads): two calls whose kernels overlap on the GPU -- different streams, or
- *   different host threads -- race on it, so keep them on one stream. */
+ *   different host threads -- race on it, so keep them on one stream.  The array
+ *   belongs to the CURRENT device: make the stream's device current before the
+ *   call.  Host threads may make their first calls concurrently (the address
+ *   look-up is an atomic, same-value store). */
 int xabe_shared_expert_noalloc(void* stream, xabe_quant_tensor gate, xabe_quant_tensor up,
                                xabe_quant_tensor down, int hidden, int intermediate,
                                const float* hidden_states, int tokens, float* out);
+
+/* Companion of xabe_shared_expert_noalloc, equally without a counterpart in the
+ * reference and equally allocation-free: the kernels' bounded waits on their
+ * bulk copies record a status word inside the static array, and a caller with
+ * no handle has no other way to learn that one ran out (`out` is then partly
+ * unwritten).  Copies that word into `*status_out` (host memory) and
+ * synchronises `stream`: 0 = every wait of the last call completed; otherwise
+ * XABE_ERR_DEVICE_STATUS is returned as well. */
+int xabe_shared_expert_noalloc_status(void* stream, int* status_out);
 
 /* Expert-parallel exchange over peer memory (NVLink) instead of a library
  * all-to-all; no counterpart in the reference.  Every rank owns six buffers
@@ -339,8 +389,10 @@ int xabe_shared_expert_noalloc(void* stream, xabe_quant_tensor gate, xabe_quant_
  * route_and_dispatch: ep_p2p_send; on the owner-side handle (k = 1, max_tokens
  * = G*C): ep_p2p_receive -> build_dispatch(ids) -> grouped_forward_partial_f16
  * (rows = this rank's `rows` buffer) -> ep_p2p_return; on the tokens' handle:
- * ep_p2p_wait_results -> ep_combine(back).  Waits on other ranks are bounded: a
- * timeout sets device status 3 and the step's output is meaningless. */
+ * ep_p2p_wait_results -> ep_combine(back).  Waits on other ranks are bounded
+ * (xabe_moe_set_peer_wait_limit): a timeout sets device status 3; ep_p2p_receive
+ * then reports every slot empty (ids -1, null destinations), so the experts do
+ * not run and nothing is stored into a peer; the step's output is meaningless. */
 /* Buffers for the peer-memory exchange: device memory of the CURRENT device
  * that another process of this node can map.  ipc_alloc: cudaMalloc, zeroed,
  * plus its 64-byte CUDA IPC handle (send it to the other ranks by any means);

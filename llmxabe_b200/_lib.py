@@ -46,6 +46,7 @@ _vp, _i, _sz, _f = C.c_void_p, C.c_int, C.c_size_t, C.c_float
 SYMBOLS = {
     "xabe_moe_last_error": (C.c_char_p, []),
     "xabe_moe_abi_version": (_i, []),
+    "xabe_kernel_launch_count": (C.c_uint64, []),
     "xabe_moe_sorted_capacity": (C.c_uint64, [C.POINTER(GeometryC)]),
     "xabe_moe_expert_block_capacity": (C.c_uint64, [C.POINTER(GeometryC)]),
     "xabe_moe_create": (_i, [C.POINTER(GeometryC), _i, _i, _f, C.POINTER(_vp)]),
@@ -80,6 +81,11 @@ SYMBOLS = {
                                           _i, _vp, _sz, _vp, _sz]),
     "xabe_moe_buffers": (_i, [_vp, C.POINTER(BufferViewC)]),
     "xabe_moe_set_exact_decode_regime": (_i, [_vp, _i]),
+    "xabe_moe_disable_tensor_cores": (_i, [_vp]),
+    "xabe_moe_tensor_cores_enabled": (_i, [_vp]),
+    "xabe_moe_force_prefill_path": (_i, [_vp, _i]),
+    "xabe_moe_set_tuning": (_i, [_vp, _i, _i]),
+    "xabe_moe_set_peer_wait_limit": (_i, [_vp, C.c_uint32]),
     "xabe_moe_device_status": (_i, [_vp, _vp, C.POINTER(_i)]),
     "xabe_moe_stage_profile": (_i, [_vp, _i]),
     "xabe_moe_stage_times": (_i, [_vp, _vp, C.POINTER(C.c_float), C.POINTER(_i)]),
@@ -87,6 +93,7 @@ SYMBOLS = {
     "xabe_stream_read": (_i, [_vp, _vp, _sz, _vp]),
     "xabe_moe_block_forward_typed": (_i, [_vp, _vp, _vp, _vp, _i, _sz, _i, _vp, _sz, _vp, _sz]),
     "xabe_shared_expert_noalloc": (_i, [_vp, QuantTensorC, QuantTensorC, QuantTensorC, _i, _i, _vp, _i, _vp]),
+    "xabe_shared_expert_noalloc_status": (_i, [_vp, C.POINTER(_i)]),
     "xabe_lm_head_create": (_i, [C.POINTER(HeadGeometryC), _i, C.POINTER(_vp)]),
     "xabe_lm_head_destroy": (None, [_vp]),
     "xabe_lm_head_forward": (_i, [_vp, _vp, QuantTensorC, _vp, _sz, _i, _vp, _sz]),

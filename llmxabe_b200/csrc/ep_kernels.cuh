@@ -11,8 +11,11 @@
 //   back_rows [C][hidden] f32 the owners write the results of this rank's pairs, in its send order
 //   flag_back [G] int32       owner d stores the step number once its results are written
 // Step numbers only grow, so nothing is ever reset.  Every wait is bounded: on a timeout the kernel
-// records STATUS_PEER_TIMEOUT and goes on (the step's output is then meaningless; the host reads
-// the status word).  Plain peer stores and loads only: no multimem, no multicast.
+// records STATUS_PEER_TIMEOUT and returns, and the owner's step that follows is inert: while the
+// status word holds STATUS_PEER_TIMEOUT (until the host reads and clears it) k_ep_fill_slots marks
+// every receive slot empty, so no expert runs and nothing is stored into a peer.  The step's output
+// is then meaningless; the host learns it from the status word.  Plain peer stores and loads only:
+// no multimem, no multicast.
 #pragma once
 
 #include "common.cuh"
@@ -21,7 +24,7 @@ namespace xabe {
 
 constexpr int STATUS_PEER_TIMEOUT = 3;
 constexpr int kEpMaxRanks = 8;
-constexpr uint32_t kPeerWaitLimit = 1u << 24;  // x 200 ns of sleep: several seconds
+constexpr uint32_t kPeerWaitLimit = 1u << 24;  // default iteration limit, x 200 ns of sleep: several seconds
 
 struct EpPeers {
     void* p[kEpMaxRanks];
@@ -112,11 +115,13 @@ __global__ void k_ep_signal_rows(int world, int me, const int* __restrict__ send
     st_release_sys((int*)peer_at(peer_flag_in, d) + me, step);
 }
 
-// One block, `world` threads: wait (bounded) until every flag has reached `step`.
-__global__ void k_ep_wait_flags(int world, const int* __restrict__ flags, int step, int* __restrict__ status) {
+// One block, `world` threads: wait until every flag has reached `step`, for at most `limit`
+// iterations of 200 ns each.
+__global__ void k_ep_wait_flags(int world, const int* __restrict__ flags, int step, uint32_t limit,
+                                int* __restrict__ status) {
     int s = threadIdx.x;
     if (s >= world) return;
-    for (uint32_t it = 0; it < kPeerWaitLimit; ++it) {
+    for (uint32_t it = 0; it < limit; ++it) {
         if (ld_acquire_sys(flags + s) >= step) return;
         __nanosleep(200);
     }
@@ -125,15 +130,22 @@ __global__ void k_ep_wait_flags(int world, const int* __restrict__ flags, int st
 
 // Owner: expert id of every receive slot (-1 where region s holds no row) and where the slot's
 // result goes: the sender's back_rows at (its start for this rank + j).  grid: ceil(G*C/256), block 256.
+// After a wait that ran out the {count, start} words may be half-written by a late sender, so the
+// whole step is made inert (every slot empty); a region whose words do not describe rows inside the
+// sender's buffer of `cap` rows is treated as empty as well.
 __global__ void k_ep_fill_slots(int world, int cap, int hidden, const int* __restrict__ recv_meta,
-                                const int* __restrict__ recv_eid, EpPeers peer_back, int* __restrict__ ids,
+                                const int* __restrict__ recv_eid, int experts_per_rank, EpPeers peer_back,
+                                const int* __restrict__ status, int* __restrict__ ids,
                                 float** __restrict__ result_dst) {
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)world * cap) return;
     int s = (int)(idx / cap), j = (int)(idx % cap);
     int count = recv_meta[2 * s], start = recv_meta[2 * s + 1];
-    bool live = j < count;
-    ids[idx] = live ? recv_eid[idx] : -1;
+    const bool sane = count >= 0 && start >= 0 && count <= cap && start <= cap - count;
+    bool live = sane && j < count && *status != STATUS_PEER_TIMEOUT;
+    int eid = live ? recv_eid[idx] : -1;
+    if (eid < 0 || eid >= experts_per_rank) live = false;
+    ids[idx] = live ? eid : -1;
     result_dst[idx] = live ? (float*)peer_at(peer_back, s) + (size_t)(start + j) * hidden : nullptr;
 }
 

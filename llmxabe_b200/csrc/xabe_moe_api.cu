@@ -2,6 +2,8 @@
 // contract and for the reference method each entry point mirrors.
 #include "../../include/xabe_moe.h"
 
+#include <atomic>
+#include <mutex>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -23,23 +25,64 @@ using namespace xabe;
 
 namespace {
 
+// Kernels this library has launched in this process (xabe_kernel_launch_count): every launch site
+// passes its stream through counted().
+std::atomic<uint64_t> g_kernel_launches{0};
+inline cudaStream_t counted(cudaStream_t st) {
+    g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
+    return st;
+}
+
+// A kernel's dynamic shared-memory ceiling is an attribute of the FUNCTION (per device), shared by
+// every entry point and host thread that launches it.  Every launch site therefore raises it to the
+// same value, the most the device allows beside the kernel's static shared memory, once per function
+// and device: no site ever lowers it, so concurrent callers cannot invalidate one another's launches.
+cudaError_t allow_dynamic_smem(const void* kern, size_t needed) {
+    // a fixed table (function -> bit per device already set): no heap allocation on any call
+    struct Entry { const void* kern; uint64_t devices; };
+    constexpr int kEntries = 128;
+    static std::mutex mu;
+    static Entry table[kEntries] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        for (int i = 0; i < kEntries && table[i].kern; ++i)
+            if (table[i].kern == kern && dev < 64 && (table[i].devices >> dev & 1u)) return cudaSuccess;
+    }
+    cudaFuncAttributes attr{};
+    if ((e = cudaFuncGetAttributes(&attr, kern)) != cudaSuccess) return e;
+    int optin = 0;
+    if ((e = cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev)) != cudaSuccess) return e;
+    const int ceiling = optin - (int)attr.sharedSizeBytes;
+    if ((long long)needed > (long long)ceiling) return cudaErrorInvalidValue;
+    if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ceiling)) != cudaSuccess) return e;
+    if (dev < 64) {
+        std::lock_guard<std::mutex> lock(mu);
+        for (int i = 0; i < kEntries; ++i) {
+            if (!table[i].kern) table[i].kern = kern;
+            if (table[i].kern == kern) {
+                table[i].devices |= 1ull << dev;
+                break;
+            }
+        }  // a full table only means the attribute is written again next time
+    }
+    return cudaSuccess;
+}
+
 // Launch, optionally with programmatic stream serialization (the kernel may then be scheduled while
 // its predecessor on the stream drains; every kernel launched through here waits for the predecessor
-// before it touches its output, see pdl_wait()).  Measured on the decode block: eager launches gain
-// (64 tokens 0.228 -> 0.209 ms, 1 token 54.6 -> 46.3 us) but CUDA-graph replay, which is how the block
-// is meant to be driven, loses a little (0.200 -> 0.207 ms, 42.0 -> 43.9 us), so it is off unless
-// XABE_MOE_PDL=1.
+// before it touches its output, see pdl_wait()).  Per handle, off unless XABE_TUNE_PDL was set.
 template <typename... KArgs, typename... Args>
-cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
-    static const bool off = [] {
-        const char* e = getenv("XABE_MOE_PDL");
-        return !(e && e[0] == '1');
-    }();
+cudaError_t launch_pdl(bool pdl, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                       Args&&... args) {
+    const bool off = !pdl;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
+    cfg.stream = counted(st);
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -121,7 +164,17 @@ struct xabe_moe {
     int* pf_n_items = nullptr;
     uint64_t pf_capacity = 0;
     int pf_item_cols = 128;     // token columns per item: 128 (k_prefill_gemm) or 512 (k_prefill_gemm_wide)
+    // per-handle switches (xabe_moe_set_tuning, xabe_moe_disable_tensor_cores, xabe_moe_force_prefill_path)
     bool force_tile_kernels = false;  // use the one-tile-per-CTA kernels even where the streaming ones apply
+    bool pdl = false;                 // programmatic dependent launch between the block's kernels
+    bool tensor_cores = true;         // false: never the tcgen05 kernels
+    bool force_prefill = false;       // the tcgen05 kernels at every width
+    int stream_stages = 0;            // 0: as many ring stages as fit
+    int stream_runs = 0;              // 0: the kernel's own choice
+    int rows_min_tokens = -1;         // -1: the measured default; 0: k_gateup_rows off
+    int router_regw = -1;             // -1: by width; 0/1: off/on
+    uint32_t peer_wait_limit = 0;     // 0: kPeerWaitLimit
+    bool fused_decode = true;         // decode widths: fused front (norm .. dispatch) and fused tail
     float* normed = nullptr;
     __half* normed_h = nullptr;
     int* ep_compact = nullptr;  // [num_experts + 1] live pairs before each expert (expert parallelism)
@@ -197,18 +250,18 @@ size_t down_smem(int k, int quant) {
 template <int QR, int QS>
 int launch_gateup(xabe_moe* m, cudaStream_t st, const ExpertLaunch& L, int y_blocks, size_t smem) {
     auto kern = k_expert_gateup<QR, QS>;
-    CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CUDA_TRY(allow_dynamic_smem((const void*)kern, smem));
     dim3 grid(L.rows / 8, y_blocks);
-    kern<<<grid, kExpertThreads, smem, st>>>(L);
+    kern<<<grid, kExpertThreads, smem, counted(st)>>>(L);
     CUDA_TRY(cudaGetLastError());
     return XABE_OK;
 }
 template <int QR, int QS>
 int launch_down(xabe_moe* m, cudaStream_t st, const ExpertLaunch& L, int y_blocks, size_t smem) {
     auto kern = k_expert_down<QR, QS>;
-    CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CUDA_TRY(allow_dynamic_smem((const void*)kern, smem));
     dim3 grid(L.rows / 64, y_blocks);
-    kern<<<grid, kExpertThreads, smem, st>>>(L);
+    kern<<<grid, kExpertThreads, smem, counted(st)>>>(L);
     CUDA_TRY(cudaGetLastError());
     return XABE_OK;
 }
@@ -228,7 +281,7 @@ struct StreamShape {
 };
 
 // Whether the streaming kernel serves this projection, and with what ring.
-StreamShape stream_shape(int mode, int rows, int k, int q_routed, int q_shared) {
+StreamShape stream_shape(int mode, int rows, int k, int q_routed, int q_shared, int max_stages = 0) {
     StreamShape sh;
     int n_spans = k / 256;
     int max_spans = mode == MODE_GATEUP ? kStreamGroupWarps : 2;
@@ -245,10 +298,7 @@ StreamShape stream_shape(int mode, int rows, int k, int q_routed, int q_shared) 
     sh.tile_cap = (staged_capacity(rows_per_tile * rb_max) + 15u) & ~15u;
     sh.x_stride = (uint32_t)k * 2u + kXRowPadBytes;
     int s_max = kStreamMaxStages;
-    if (const char* e = getenv("XABE_MOE_STREAM_STAGES")) {  // tuning aid
-        int v = atoi(e);
-        if (v >= 2 && v < s_max) s_max = v;
-    }
+    if (max_stages >= 2 && max_stages < s_max) s_max = max_stages;
     for (int S = s_max; S >= 2; --S) {
         StreamSmem L = stream_smem_layout(mode, S, sh.tile_cap, sh.x_stride);
         if (L.total <= 226u * 1024u) {
@@ -264,8 +314,8 @@ StreamShape stream_shape(int mode, int rows, int k, int q_routed, int q_shared) 
 template <int MODE, int QR, int QS>
 int launch_stream_t(xabe_moe* m, cudaStream_t st, const StreamLaunch& L, uint32_t smem) {
     auto kern = k_expert_stream<MODE, QR, QS>;
-    CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    CUDA_TRY(launch_pdl(kern, dim3(m->sm_count), dim3(kStreamThreads), smem, st, L));
+    CUDA_TRY(allow_dynamic_smem((const void*)kern, smem));
+    CUDA_TRY(launch_pdl(m->pdl, kern, dim3(m->sm_count), dim3(kStreamThreads), smem, st, L));
     return XABE_OK;
 }
 
@@ -347,11 +397,8 @@ RowsShape rows_shape(const xabe_moe* m, int rows, int k, bool has_routed, int qr
                      bool has_shared, int qs, const void* s_a, const void* s_b, uint32_t x_stride) {
     RowsShape sh;
     uint32_t min_tokens = kRowsKernelMinTokens;
-    if (const char* e = getenv("XABE_MOE_ROWS_MIN_TOKENS")) {  // tuning aid; 0 turns the kernel off
-        const int v = atoi(e);
-        if (v <= 0) return sh;
-        min_tokens = (uint32_t)v;
-    }
+    if (m->rows_min_tokens == 0) return sh;
+    if (m->rows_min_tokens > 0) min_tokens = (uint32_t)m->rows_min_tokens;
     if (m->g.max_tokens < min_tokens || m->force_tile_kernels) return sh;
     const int n_spans = k / 256;
     if (n_spans < 2 || rows % kRowsUnitRows != 0) return sh;
@@ -380,14 +427,13 @@ RowsShape rows_shape(const xabe_moe* m, int rows, int k, bool has_routed, int qr
 template <int QR, int QS>
 int launch_rows_t(xabe_moe* m, cudaStream_t st, const RowsLaunch& P, uint32_t smem) {
     auto kern = k_gateup_rows<QR, QS>;
-    CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    CUDA_TRY(launch_pdl(kern, dim3(m->sm_count), dim3(kStreamThreads), smem, st, P));
+    CUDA_TRY(allow_dynamic_smem((const void*)kern, smem));
+    CUDA_TRY(launch_pdl(m->pdl, kern, dim3(m->sm_count), dim3(kStreamThreads), smem, st, P));
     return XABE_OK;
 }
 
 bool prefill_applies(const xabe_moe* m, int gateup_rows, int down_rows, int hidden, int inter) {
-    if (m->force_tile_kernels) return false;
-    if (const char* e = getenv("XABE_MOE_NO_PREFILL_KERNELS")) if (e[0] == '1') return false;
+    if (m->force_tile_kernels || !m->tensor_cores) return false;
     if (!(gateup_rows % 64 == 0 && down_rows % kPfTileM == 0 && hidden % kSpanElems == 0 && inter % kSpanElems == 0))
         return false;
     // Contractions too long for the decode kernels (the dense 27B block: 5120 and 17408) go through
@@ -396,14 +442,15 @@ bool prefill_applies(const xabe_moe* m, int gateup_rows, int down_rows, int hidd
                                       stream_shape(MODE_DOWN, down_rows, inter, XABE_QUANT_Q8_0, XABE_QUANT_Q8_0).ok;
     if (!decode_kernels_serve) return true;
     if (m->exact_decode) return false;
+    if (m->force_prefill) return true;
     return m->g.max_tokens >= kPrefillMinTokens;
 }
 
 template <int MODE, int QR, int QS>
 int launch_prefill_t(cudaStream_t st, const PrefillLaunch& L, dim3 grid, size_t smem, bool wide) {
     auto kern = wide ? k_prefill_gemm_wide<MODE, QR, QS> : k_prefill_gemm<MODE, QR, QS>;
-    CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, wide ? kPfWideThreads : kPfThreads, smem, st>>>(L);
+    CUDA_TRY(allow_dynamic_smem((const void*)kern, smem));
+    kern<<<grid, wide ? kPfWideThreads : kPfThreads, smem, counted(st)>>>(L);
     CUDA_TRY(cudaGetLastError());
     return XABE_OK;
 }
@@ -520,7 +567,7 @@ int run_experts(xabe_moe* m, cudaStream_t st, const MlpWeights& routed, const Ml
             P.tm_routed = m->tm_routed_gu;
             P.tm_shared = m->tm_shared_gu;
             if (routed.present) {  // activation rows in dispatch order, so that an item's columns are consecutive rows
-                k_permute_rows<<<(unsigned)m->sorted_capacity, 256, 0, st>>>(
+                k_permute_rows<<<(unsigned)m->sorted_capacity, 256, 0, counted(st)>>>(
                     m->sorted_token_ids, m->num_tokens_post_pad, m->valid_tokens, (int)g.experts_per_token,
                     (int)g.hidden, x_routed, m->x_sorted);
                 CUDA_TRY(cudaGetLastError());
@@ -561,8 +608,8 @@ int run_experts(xabe_moe* m, cudaStream_t st, const MlpWeights& routed, const Ml
     SL.num_experts = (int)g.num_experts;
     SL.max_tokens = (int)g.max_tokens;
     SL.x_rows_routed = (int)m->sorted_capacity;
-    if (const char* e = getenv("XABE_MOE_STREAM_RUNS")) SL.runs_override = atoi(e);  // tuning aid
-    StreamShape gu = stream_shape(MODE_GATEUP, (int)g.intermediate, (int)g.hidden, qr, qs);
+    SL.runs_override = m->stream_runs;
+    StreamShape gu = stream_shape(MODE_GATEUP, (int)g.intermediate, (int)g.hidden, qr, qs, m->stream_stages);
     if (gu.ok && !m->force_tile_kernels) {
         SL.r_a = L.r_a; SL.r_b = L.r_b; SL.s_a = L.s_a; SL.s_b = L.s_b;
         SL.rows = L.rows; SL.k = L.k;
@@ -619,7 +666,7 @@ int run_experts(xabe_moe* m, cudaStream_t st, const MlpWeights& routed, const Ml
     L.partial = m->partial;
     L.partial_rows = m->partial_rows;
     L.shexp = shexp_out;
-    StreamShape dn = stream_shape(MODE_DOWN, (int)g.hidden, (int)g.intermediate, qr, qs);
+    StreamShape dn = stream_shape(MODE_DOWN, (int)g.hidden, (int)g.intermediate, qr, qs, m->stream_stages);
     if (dn.ok && !m->force_tile_kernels) {
         SL.r_a = L.r_a; SL.r_b = nullptr; SL.s_a = L.s_a; SL.s_b = nullptr;
         SL.rows = L.rows; SL.k = L.k;
@@ -642,6 +689,30 @@ int run_experts(xabe_moe* m, cudaStream_t st, const MlpWeights& routed, const Ml
     return DISPATCH_QQ(launch_down, qr, qs, m, st, L, routed_blocks + shared_tiles, smem);
 }
 
+// What k_prefill_gemm_wide needs beyond the other kernels: the activations in dispatch order and the
+// tensor maps of its four activation sources, all handle-owned, made once.  Set-up time only (allocates).
+int setup_wide_prefill(xabe_moe* m) {
+    const size_t T = m->g.max_tokens, H = m->g.hidden, I = m->g.intermediate;
+    if (H % kSpanElems != 0 || I % kSpanElems != 0) {
+        m->pf_item_cols = kPfTileN;
+        return XABE_OK;
+    }
+    if (m->scope == XABE_SCOPE_ROUTED && !m->x_sorted) {
+        cudaError_t e = dev_alloc(&m->x_sorted, (size_t)m->sorted_capacity * H);
+        if (e != cudaSuccess)
+            return fail(XABE_ERR_DRIVER, "CUDA driver error: %s (allocating the permuted activations)",
+                        cudaGetErrorString(e));
+    }
+    int rc = make_rows_map(&m->tm_shared_gu, m->normed_h, T, H);
+    if (!rc) rc = make_rows_map(&m->tm_shared_dn, m->inter_shared, T, I);
+    if (!rc && m->scope == XABE_SCOPE_ROUTED) {
+        rc = make_rows_map(&m->tm_routed_gu, m->x_sorted, m->sorted_capacity, H);
+        if (!rc) rc = make_rows_map(&m->tm_routed_dn, m->inter_routed, m->sorted_capacity, I);
+    }
+    if (!rc) m->pf_item_cols = kPfWideItemCols;
+    return rc;
+}
+
 int check_routed(xabe_moe* m, const char* entry) {
     if (m->scope != XABE_SCOPE_ROUTED)
         return fail(XABE_ERR_SHARED_ONLY_BUFFERS,
@@ -651,7 +722,7 @@ int check_routed(xabe_moe* m, const char* entry) {
 }
 
 int rows_to_half(xabe_moe* m, cudaStream_t st, const float* hidden_states) {
-    k_rows_to_half<<<m->g.max_tokens, 256, 0, st>>>(hidden_states, m->normed_h, m->valid_tokens, (int)m->g.hidden);
+    k_rows_to_half<<<m->g.max_tokens, 256, 0, counted(st)>>>(hidden_states, m->normed_h, m->valid_tokens, (int)m->g.hidden);
     CUDA_TRY(cudaGetLastError());
     return XABE_OK;
 }
@@ -661,7 +732,7 @@ int launch_rms_norm(xabe_moe* m, cudaStream_t st, const float* x, const float* w
     int block = ((int)m->g.hidden + 31) / 32 * 32;
     if (block > 1024) block = 1024;
     if (block < 32) block = 32;
-    CUDA_TRY(launch_pdl(k_rms_norm, dim3(m->g.max_tokens), dim3(block), 0, st, x, weight, m->normed, m->normed_h,
+    CUDA_TRY(launch_pdl(m->pdl, k_rms_norm, dim3(m->g.max_tokens), dim3(block), 0, st, x, weight, m->normed, m->normed_h,
                         m->valid_tokens, (int)m->g.hidden, m->eps));
     return XABE_OK;
 }
@@ -672,7 +743,7 @@ int launch_router(xabe_moe* m, cudaStream_t st, const float* router, const float
         return fail(XABE_ERR_INVALID_ARGUMENT, "router weights must be 16-byte aligned");
     // prefill widths: the expert rows in registers, the tokens streamed two at a time
     bool regw = g.max_tokens >= 256;
-    if (const char* e = getenv("XABE_MOE_ROUTER_REGW")) regw = e[0] == '1';  // tuning aid
+    if (m->router_regw >= 0) regw = m->router_regw != 0;
     if (regw && g.max_tokens >= 2 && g.num_experts % kRwExperts == 0 && (g.hidden == 2048 || g.hidden == 1024)) {
         const size_t smem_r = router_regw_smem((int)g.hidden);
         unsigned gx = g.num_experts / kRwExperts;
@@ -681,8 +752,8 @@ int launch_router(xabe_moe* m, cudaStream_t st, const float* router, const float
         if (gy < 1) gy = 1;
         if (gy > pairs) gy = pairs;
         auto go_regw = [&](auto kern) -> int {
-            CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_r));
-            CUDA_TRY(launch_pdl(kern, dim3(gx, gy), dim3(256), smem_r, st, router, (const float*)m->normed,
+            CUDA_TRY(allow_dynamic_smem((const void*)kern, smem_r));
+            CUDA_TRY(launch_pdl(m->pdl, kern, dim3(gx, gy), dim3(256), smem_r, st, router, (const float*)m->normed,
                                 (const int*)m->valid_tokens, (int)g.num_experts, bias, m->logits, m->status));
             return XABE_OK;
         };
@@ -697,8 +768,8 @@ int launch_router(xabe_moe* m, cudaStream_t st, const float* router, const float
         if (gy < 1) gy = 1;
         if (gy > tiles) gy = tiles;
         auto go_wide = [&](auto kern) -> int {
-            CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_w));
-            CUDA_TRY(launch_pdl(kern, dim3(gx, gy), dim3(256), smem_w, st, router, (const float*)m->normed,
+            CUDA_TRY(allow_dynamic_smem((const void*)kern, smem_w));
+            CUDA_TRY(launch_pdl(m->pdl, kern, dim3(gx, gy), dim3(256), smem_w, st, router, (const float*)m->normed,
                                 (const int*)m->valid_tokens, (int)g.num_experts, bias, m->logits, m->status));
             return XABE_OK;
         };
@@ -714,8 +785,8 @@ int launch_router(xabe_moe* m, cudaStream_t st, const float* router, const float
         // wide passes share one staged copy of the rows between eight token tiles
         int tiles_per_cta = g.max_tokens > 128 ? 8 : 1;
         unsigned ty = (g.max_tokens + tt * tiles_per_cta - 1) / (tt * tiles_per_cta);
-        CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        CUDA_TRY(launch_pdl(kern, dim3(ex, ty), block, smem, st, router, (const float*)m->normed,
+        CUDA_TRY(allow_dynamic_smem((const void*)kern, smem));
+        CUDA_TRY(launch_pdl(m->pdl, kern, dim3(ex, ty), block, smem, st, router, (const float*)m->normed,
                             (const int*)m->valid_tokens, (int)g.hidden, (int)g.num_experts, bias, m->logits,
                             tiles_per_cta, m->status));
         return XABE_OK;
@@ -736,49 +807,49 @@ int launch_route_and_dispatch(xabe_moe* m, cudaStream_t st, const float* logits)
         size_t smem = (size_t)(3 * kSmallPairs + 11 * g.num_experts + 2) * sizeof(int);
         const float* fused_logits = logits;
         if (logits && g.max_tokens > 8) {  // more than one token per warp: route on many SMs first
-            CUDA_TRY(launch_pdl(k_route, dim3((g.max_tokens + 7) / 8), dim3(256), 0, st, logits,
+            CUDA_TRY(launch_pdl(m->pdl, k_route, dim3((g.max_tokens + 7) / 8), dim3(256), 0, st, logits,
                                 (const int*)m->valid_tokens, (int)g.num_experts, (int)g.experts_per_token,
                                 m->topk_ids, m->topk_weights));
             fused_logits = nullptr;
         }
-        CUDA_TRY(launch_pdl(k_route_dispatch_small, dim3(1), dim3(256), smem, st, fused_logits,
+        CUDA_TRY(launch_pdl(m->pdl, k_route_dispatch_small, dim3(1), dim3(256), smem, st, fused_logits,
                             (const int*)m->valid_tokens, (int)g.num_experts, (int)g.experts_per_token,
                             (int)g.block_size, (int)m->sorted_capacity, (int)m->block_capacity, m->topk_ids,
                             m->topk_weights, m->sorted_token_ids, m->expert_ids, m->num_tokens_post_pad,
                             m->expert_offsets, m->expert_counts, m->work_items, m->n_work));
         if (g.max_tokens >= kPrefillMinTokens) {  // few experts, many tokens: the prefill kernels still apply
             int threads = ((int)g.num_experts + 31) / 32 * 32;
-            k_build_prefill_items<<<1, threads, hist_bytes, st>>>((int)g.num_experts, m->expert_offsets,
+            k_build_prefill_items<<<1, threads, hist_bytes, counted(st)>>>((int)g.num_experts, m->expert_offsets,
                                                                   m->expert_counts, m->pf_items, m->pf_n_items, m->pf_item_cols);
             CUDA_TRY(cudaGetLastError());
         }
         return XABE_OK;
     }
     if (logits) {
-        k_route<<<(g.max_tokens + 7) / 8, 256, 0, st>>>(logits, m->valid_tokens, (int)g.num_experts,
+        k_route<<<(g.max_tokens + 7) / 8, 256, 0, counted(st)>>>(logits, m->valid_tokens, (int)g.num_experts,
                                                        (int)g.experts_per_token, m->topk_ids, m->topk_weights);
         CUDA_TRY(cudaGetLastError());
     }
-    k_align_count<<<m->n_chunks, 32, hist_bytes, st>>>(m->topk_ids, m->valid_tokens, (int)g.experts_per_token,
+    k_align_count<<<m->n_chunks, 32, hist_bytes, counted(st)>>>(m->topk_ids, m->valid_tokens, (int)g.experts_per_token,
                                                       (int)g.num_experts, m->n_chunks, m->align_chunk, (int)m->sorted_capacity,
                                                       (int)m->block_capacity, m->chunk_hist,
                                                       m->sorted_token_ids, m->expert_ids);
     CUDA_TRY(cudaGetLastError());
     int threads = ((int)g.num_experts + 31) / 32 * 32;
-    k_align_scan<<<1, threads, hist_bytes, st>>>((int)g.num_experts, m->n_chunks, (int)g.block_size,
+    k_align_scan<<<1, threads, hist_bytes, counted(st)>>>((int)g.num_experts, m->n_chunks, (int)g.block_size,
                                                  m->chunk_hist, m->expert_offsets, m->expert_counts,
                                                  m->expert_ids, m->num_tokens_post_pad);
     CUDA_TRY(cudaGetLastError());
-    k_align_scatter<<<m->n_chunks, 32, hist_bytes, st>>>(m->topk_ids, m->valid_tokens,
+    k_align_scatter<<<m->n_chunks, 32, hist_bytes, counted(st)>>>(m->topk_ids, m->valid_tokens,
                                                         (int)g.experts_per_token, (int)g.num_experts,
                                                         m->align_chunk, m->chunk_hist, m->sorted_token_ids);
     CUDA_TRY(cudaGetLastError());
     // Only the work list of the kernels that will run: the regime must be chosen before this call.
     if (prefill_applies(m, (int)g.intermediate, (int)g.hidden, (int)g.hidden, (int)g.intermediate)) {
-        k_build_prefill_items<<<1, threads, hist_bytes, st>>>((int)g.num_experts, m->expert_offsets,
+        k_build_prefill_items<<<1, threads, hist_bytes, counted(st)>>>((int)g.num_experts, m->expert_offsets,
                                                               m->expert_counts, m->pf_items, m->pf_n_items, m->pf_item_cols);
     } else {
-        k_build_work<<<1, threads, hist_bytes, st>>>((int)g.num_experts, m->expert_offsets, m->expert_counts,
+        k_build_work<<<1, threads, hist_bytes, counted(st)>>>((int)g.num_experts, m->expert_offsets, m->expert_counts,
                                                      m->sorted_token_ids, m->topk_weights, m->work_items,
                                                      m->n_work);
     }
@@ -805,7 +876,8 @@ int check_mlp(xabe_moe* m, const char* prefix, const xabe_quant_tensor& gate, co
 extern "C" {
 
 const char* xabe_moe_last_error(void) { return g_last_error.c_str(); }
-int xabe_moe_abi_version(void) { return 1; }
+int xabe_moe_abi_version(void) { return 2; }
+uint64_t xabe_kernel_launch_count(void) { return g_kernel_launches.load(std::memory_order_relaxed); }
 
 uint64_t xabe_moe_sorted_capacity(const xabe_moe_geometry* g) { return g ? sorted_capacity_of(*g) : 0; }
 uint64_t xabe_moe_expert_block_capacity(const xabe_moe_geometry* g) {
@@ -863,15 +935,9 @@ int xabe_moe_create(const xabe_moe_geometry* geometry, int device, int scope, fl
     // measured faster only where every item is full and the contraction is long -- the dense block at
     // prefill width (3.40 vs 3.77 ms per layer at 4096 tokens); with the routed experts the extra
     // pass that permutes the activations costs more than the shared unpack work returns.
-    // XABE_MOE_PF_WIDE=0/1 overrides the choice (tuning aid, read when the handle is created).
+    // XABE_TUNE_PREFILL_WIDE overrides the choice after creation.
     m->pf_item_cols = (scope == XABE_SCOPE_SHARED_ONLY && g.max_tokens >= kPrefillWideMinTokens) ? kPfWideItemCols
                                                                                                  : kPfTileN;
-    if (const char* e = getenv("XABE_MOE_PF_WIDE")) {
-        if (e[0] == '1') m->pf_item_cols = kPfWideItemCols;
-        if (e[0] == '0') m->pf_item_cols = kPfTileN;
-    }
-    // debugging aid: XABE_MOE_FORCE_TILE_KERNELS=1 keeps the streaming kernels out of the way
-    if (const char* e = getenv("XABE_MOE_FORCE_TILE_KERNELS")) m->force_tile_kernels = e[0] == '1';
     m->g = g;
     m->device = device;
     m->scope = scope;
@@ -915,7 +981,6 @@ int xabe_moe_create(const xabe_moe_geometry* geometry, int device, int scope, fl
         A(dev_alloc(&m->pf_n_items, 1));
         A(dev_alloc(&m->logits, T * E));
         A(dev_alloc(&m->inter_routed, (size_t)cap * I));
-        if (m->pf_item_cols > kPfTileN) A(dev_alloc(&m->x_sorted, (size_t)cap * H));
         A(dev_alloc(&m->partial, T * K * H));
         A(dev_alloc(&m->routed, T * H));
         A(dev_alloc(&m->gate, T));
@@ -924,14 +989,8 @@ int xabe_moe_create(const xabe_moe_geometry* geometry, int device, int scope, fl
         xabe_moe_destroy(m);
         return fail(XABE_ERR_DRIVER, "CUDA driver error: %s (allocating MoE buffers)", cudaGetErrorString(e));
     }
-    if (m->pf_item_cols > kPfTileN && H % kSpanElems == 0 && I % kSpanElems == 0) {
-        // the four activation sources of k_prefill_gemm_wide, all handle-owned: maps are made once
-        int rc = make_rows_map(&m->tm_shared_gu, m->normed_h, T, H);
-        if (!rc) rc = make_rows_map(&m->tm_shared_dn, m->inter_shared, T, I);
-        if (!rc && scope == XABE_SCOPE_ROUTED) {
-            rc = make_rows_map(&m->tm_routed_gu, m->x_sorted, cap, H);
-            if (!rc) rc = make_rows_map(&m->tm_routed_dn, m->inter_routed, cap, I);
-        }
+    if (m->pf_item_cols > kPfTileN) {
+        int rc = setup_wide_prefill(m);
         if (rc) {
             xabe_moe_destroy(m);
             return rc;
@@ -967,7 +1026,7 @@ int xabe_moe_set_valid_tokens(xabe_moe* m, void* stream, int tokens) {
     if (tokens == m->published_tokens) return XABE_OK;  // moe.rs:5480-5483
     // The value travels as a kernel argument, so no host memory is read later
     // and nothing has to be synchronised.
-    k_set_scalar<<<1, 1, 0, (cudaStream_t)stream>>>(m->valid_tokens, tokens);
+    k_set_scalar<<<1, 1, 0, counted((cudaStream_t)stream)>>>(m->valid_tokens, tokens);
     CUDA_TRY(cudaGetLastError());
     m->published_tokens = tokens;
     return XABE_OK;
@@ -1017,7 +1076,7 @@ int xabe_moe_gate_and_combine(xabe_moe* m, void* stream, const float* shared_gat
     if (residual_len != n || ffn_out_len != n || l_out_len != n)
         return fail(XABE_ERR_BUFFER_LENGTH, "gate_and_combine buffers must hold %zu floats", n);
     dim3 grid(g.max_tokens, g.max_tokens >= 512 ? 1u : (g.hidden + 255) / 256);
-    CUDA_TRY(launch_pdl(k_gate_and_combine, grid, dim3(256), 0, (cudaStream_t)stream, shared_gate_inp,
+    CUDA_TRY(launch_pdl(m->pdl, k_gate_and_combine, grid, dim3(256), 0, (cudaStream_t)stream, shared_gate_inp,
                         (const float*)m->normed, (const float*)m->partial, (const float*)m->shexp, residual,
                         (const int*)m->valid_tokens, (int)g.experts_per_token, (int)g.hidden, m->gate, m->routed,
                         ffn_out, l_out));
@@ -1073,7 +1132,7 @@ int xabe_moe_ep_pack(xabe_moe* m, void* stream, const int64_t* order, size_t n_p
     if (experts_per_rank <= 0 || g.hidden % 8 != 0 || ((uintptr_t)send_rows_f16 & 15) != 0)
         return fail(XABE_ERR_INVALID_ARGUMENT, "ep_pack: bad experts_per_rank, hidden or alignment");
     if (n_pairs == 0) return XABE_OK;
-    k_ep_pack<<<(unsigned)n_pairs, 256, 0, (cudaStream_t)stream>>>(
+    k_ep_pack<<<(unsigned)n_pairs, 256, 0, counted((cudaStream_t)stream)>>>(
         (const long long*)order, m->normed_h, m->topk_ids, (int)g.experts_per_token, (int)g.hidden,
         experts_per_rank, (__half*)send_rows_f16, send_local_expert, inverse);
     CUDA_TRY(cudaGetLastError());
@@ -1092,10 +1151,10 @@ int xabe_moe_ep_plan_pack(xabe_moe* m, void* stream, int experts_per_rank, void*
         return fail(XABE_ERR_INVALID_ARGUMENT, "ep_plan_pack: bad experts_per_rank, hidden or alignment");
     cudaStream_t st = (cudaStream_t)stream;
     int threads = ((int)g.num_experts + 1 + 31) / 32 * 32;
-    k_ep_plan<<<1, threads, (g.num_experts + 1) * sizeof(int), st>>>((int)g.num_experts, experts_per_rank,
+    k_ep_plan<<<1, threads, (g.num_experts + 1) * sizeof(int), counted(st)>>>((int)g.num_experts, experts_per_rank,
                                                                      m->expert_counts, m->ep_compact, send_counts);
     CUDA_TRY(cudaGetLastError());
-    k_ep_pack_sorted<<<(unsigned)m->sorted_capacity, 256, 0, st>>>(
+    k_ep_pack_sorted<<<(unsigned)m->sorted_capacity, 256, 0, counted(st)>>>(
         m->sorted_token_ids, m->expert_ids, m->expert_offsets, m->ep_compact, m->num_tokens_post_pad,
         m->valid_tokens, m->normed_h, (int)g.experts_per_token, (int)g.hidden, (int)g.block_size, experts_per_rank,
         (__half*)send_rows_f16, send_local_expert, inverse);
@@ -1135,16 +1194,16 @@ int xabe_moe_ep_p2p_send(xabe_moe* m, void* stream, int experts_per_rank, int wo
                     g.max_tokens, g.experts_per_token, cap);
     cudaStream_t st = (cudaStream_t)stream;
     int threads = ((int)g.num_experts + 1 + 31) / 32 * 32;
-    k_ep_plan_ranks<<<1, threads, (g.num_experts + 1) * sizeof(int), st>>>(
+    k_ep_plan_ranks<<<1, threads, (g.num_experts + 1) * sizeof(int), counted(st)>>>(
         (int)g.num_experts, experts_per_rank, m->expert_counts, m->ep_compact, m->ep_rank_start, m->ep_send_counts);
     CUDA_TRY(cudaGetLastError());
-    k_ep_push_rows<<<(unsigned)m->sorted_capacity, 256, 0, st>>>(
+    k_ep_push_rows<<<(unsigned)m->sorted_capacity, 256, 0, counted(st)>>>(
         m->sorted_token_ids, m->expert_ids, m->expert_offsets, m->ep_compact, m->ep_rank_start,
         m->num_tokens_post_pad, m->valid_tokens, m->normed_h, (int)g.experts_per_token, (int)g.hidden,
         (int)g.block_size, experts_per_rank, rank, cap, peers_of(peers->rows, world), peers_of(peers->eid, world),
         inverse);
     CUDA_TRY(cudaGetLastError());
-    k_ep_signal_rows<<<1, 32, 0, st>>>(world, rank, m->ep_send_counts, m->ep_rank_start,
+    k_ep_signal_rows<<<1, 32, 0, counted(st)>>>(world, rank, m->ep_send_counts, m->ep_rank_start,
                                        peers_of(peers->meta, world), peers_of(peers->flag_in, world), step);
     CUDA_TRY(cudaGetLastError());
     return XABE_OK;
@@ -1159,12 +1218,13 @@ int xabe_moe_ep_p2p_receive(xabe_moe* m, void* stream, int world, int rank, int 
         return fail(XABE_ERR_TOO_MANY_TOKENS, "ep_p2p_receive: %d x %d slots exceed max_tokens %u", world, cap,
                     m->g.max_tokens);
     cudaStream_t st = (cudaStream_t)stream;
-    k_ep_wait_flags<<<1, 32, 0, st>>>(world, (const int*)peers->flag_in[rank], step, m->status);
+    k_ep_wait_flags<<<1, 32, 0, counted(st)>>>(world, (const int*)peers->flag_in[rank], step,
+                                      m->peer_wait_limit ? m->peer_wait_limit : kPeerWaitLimit, m->status);
     CUDA_TRY(cudaGetLastError());
     size_t slots = (size_t)world * cap;
-    k_ep_fill_slots<<<(unsigned)((slots + 255) / 256), 256, 0, st>>>(
+    k_ep_fill_slots<<<(unsigned)((slots + 255) / 256), 256, 0, counted(st)>>>(
         world, cap, (int)m->g.hidden, (const int*)peers->meta[rank], (const int*)peers->eid[rank],
-        peers_of(peers->back, world), ids_out, (float**)result_dst);
+        (int)m->g.num_experts, peers_of(peers->back, world), (const int*)m->status, ids_out, (float**)result_dst);
     CUDA_TRY(cudaGetLastError());
     return XABE_OK;
 }
@@ -1220,11 +1280,11 @@ int xabe_moe_ep_p2p_return(xabe_moe* m, void* stream, int world, int rank, int c
         return fail(XABE_ERR_INVALID_ARGUMENT, "ep_p2p_return: needs the owner-side handle (k = 1) and its slot table");
     cudaStream_t st = (cudaStream_t)stream;
     if (m->partial_rows != (float* const*)result_dst) {  // the down projection did not store through this table itself
-        k_ep_push_results<<<(unsigned)((size_t)world * cap), 256, 0, st>>>(m->partial, (float* const*)result_dst,
+        k_ep_push_results<<<(unsigned)((size_t)world * cap), 256, 0, counted(st)>>>(m->partial, (float* const*)result_dst,
                                                                            (int)m->g.hidden);
         CUDA_TRY(cudaGetLastError());
     }
-    k_ep_signal_results<<<1, 32, 0, st>>>(world, rank, peers_of(peers->flag_back, world), step);
+    k_ep_signal_results<<<1, 32, 0, counted(st)>>>(world, rank, peers_of(peers->flag_back, world), step);
     CUDA_TRY(cudaGetLastError());
     return XABE_OK;
 }
@@ -1233,7 +1293,9 @@ int xabe_moe_ep_p2p_wait_results(xabe_moe* m, void* stream, int world, int rank,
                                  int step) {
     int rc = check_p2p(m, peers, world, rank, 1, "ep_p2p_wait_results");
     if (rc) return rc;
-    k_ep_wait_flags<<<1, 32, 0, (cudaStream_t)stream>>>(world, (const int*)peers->flag_back[rank], step, m->status);
+    k_ep_wait_flags<<<1, 32, 0, counted((cudaStream_t)stream)>>>(world, (const int*)peers->flag_back[rank], step,
+                                                        m->peer_wait_limit ? m->peer_wait_limit : kPeerWaitLimit,
+                                                        m->status);
     CUDA_TRY(cudaGetLastError());
     return XABE_OK;
 }
@@ -1252,7 +1314,7 @@ int xabe_moe_ep_combine(xabe_moe* m, void* stream, const float* back_rows, size_
     if (n_rows > (size_t)g.max_tokens * g.experts_per_token)
         return fail(XABE_ERR_TOO_MANY_TOKENS, "%zu rows exceed max_tokens * k", n_rows);
     dim3 grid(g.max_tokens, g.max_tokens >= 512 ? 1u : (g.hidden + 255) / 256);
-    k_ep_combine<<<grid, 256, 0, (cudaStream_t)stream>>>(
+    k_ep_combine<<<grid, 256, 0, counted((cudaStream_t)stream)>>>(
         shared_gate_inp, m->normed, back_rows, inverse, m->topk_weights, m->shexp, residual, m->valid_tokens,
         (int)g.experts_per_token, (int)g.hidden, m->gate, m->routed, ffn_out, l_out);
     CUDA_TRY(cudaGetLastError());
@@ -1265,7 +1327,7 @@ int xabe_moe_grouped_forward(xabe_moe* m, void* stream, xabe_quant_tensor gate, 
     int rc = xabe_moe_grouped_forward_partial(m, stream, gate, up, down, hidden_states);
     if (rc) return rc;
     dim3 grid(m->g.max_tokens, (m->g.hidden + 255) / 256);
-    k_reduce<<<grid, 256, 0, (cudaStream_t)stream>>>(m->partial, m->valid_tokens, (int)m->g.experts_per_token,
+    k_reduce<<<grid, 256, 0, counted((cudaStream_t)stream)>>>(m->partial, m->valid_tokens, (int)m->g.experts_per_token,
                                                      (int)m->g.hidden, out);
     CUDA_TRY(cudaGetLastError());
     return XABE_OK;
@@ -1328,7 +1390,7 @@ int xabe_moe_block_forward(xabe_moe* m, void* stream, const xabe_moe_layer_weigh
     if ((rc = run_experts(m, st, r, s, m->shexp, 4))) return rc;
     prof_mark(m, st, 5);
     dim3 grid(g.max_tokens, g.max_tokens >= 512 ? 1u : (g.hidden + 255) / 256);
-    CUDA_TRY(launch_pdl(k_gate_and_combine, grid, dim3(256), 0, st, w->shared_gate_inp, (const float*)m->normed,
+    CUDA_TRY(launch_pdl(m->pdl, k_gate_and_combine, grid, dim3(256), 0, st, w->shared_gate_inp, (const float*)m->normed,
                         (const float*)m->partial, (const float*)m->shexp, residual, (const int*)m->valid_tokens,
                         (int)g.experts_per_token, (int)g.hidden, m->gate, m->routed, ffn_out, l_out));
     prof_mark(m, st, 6);
@@ -1410,7 +1472,7 @@ int xabe_moe_block_forward_typed(xabe_moe* m, void* stream, const xabe_moe_layer
                     g.max_tokens);
     int rc = xabe_moe_set_valid_tokens(m, stream, tokens);
     if (rc) return rc;
-    k_rows_bf16_to_f32<<<g.max_tokens, 256, 0, (cudaStream_t)stream>>>((const unsigned short*)residual, m->stage_in,
+    k_rows_bf16_to_f32<<<g.max_tokens, 256, 0, counted((cudaStream_t)stream)>>>((const unsigned short*)residual, m->stage_in,
                                                                       m->valid_tokens, (int)g.hidden);
     CUDA_TRY(cudaGetLastError());
     return xabe_moe_block_forward(m, stream, w, m->stage_in, n, tokens, ffn_out, ffn_out_len, l_out, l_out_len);
@@ -1440,7 +1502,7 @@ int xabe_dense_ffn_block_forward(xabe_moe* m, void* stream, const float* post_no
     s.up = up;
     s.down = down;
     if ((rc = run_experts(m, st, MlpWeights{}, s, ffn_out))) return rc;
-    k_add_residual<<<g.max_tokens, 256, 0, st>>>(ffn_out, residual, m->valid_tokens, (int)g.hidden, l_out);
+    k_add_residual<<<g.max_tokens, 256, 0, counted(st)>>>(ffn_out, residual, m->valid_tokens, (int)g.hidden, l_out);
     CUDA_TRY(cudaGetLastError());
     return XABE_OK;
 }
@@ -1470,6 +1532,46 @@ int xabe_moe_set_exact_decode_regime(xabe_moe* m, int on) {
     return XABE_OK;
 }
 
+int xabe_moe_disable_tensor_cores(xabe_moe* m) {
+    if (!m) return fail(XABE_ERR_INVALID_ARGUMENT, "null handle");
+    m->tensor_cores = false;
+    return XABE_OK;
+}
+
+int xabe_moe_tensor_cores_enabled(const xabe_moe* m) { return m && m->tensor_cores ? 1 : 0; }
+
+int xabe_moe_force_prefill_path(xabe_moe* m, int on) {
+    if (!m) return fail(XABE_ERR_INVALID_ARGUMENT, "null handle");
+    m->force_prefill = on != 0;
+    return XABE_OK;
+}
+
+int xabe_moe_set_peer_wait_limit(xabe_moe* m, uint32_t iterations) {
+    if (!m) return fail(XABE_ERR_INVALID_ARGUMENT, "null handle");
+    m->peer_wait_limit = iterations;
+    return XABE_OK;
+}
+
+int xabe_moe_set_tuning(xabe_moe* m, int key, int value) {
+    if (!m) return fail(XABE_ERR_INVALID_ARGUMENT, "null handle");
+    switch (key) {
+        case XABE_TUNE_PDL: m->pdl = value != 0; return XABE_OK;
+        case XABE_TUNE_STREAM_STAGES: m->stream_stages = value; return XABE_OK;
+        case XABE_TUNE_STREAM_RUNS: m->stream_runs = value; return XABE_OK;
+        case XABE_TUNE_ROWS_MIN_TOKENS: m->rows_min_tokens = value; return XABE_OK;
+        case XABE_TUNE_ROUTER_REGW: m->router_regw = value; return XABE_OK;
+        case XABE_TUNE_FORCE_TILE_KERNELS: m->force_tile_kernels = value != 0; return XABE_OK;
+        case XABE_TUNE_FUSED_DECODE: m->fused_decode = value != 0; return XABE_OK;
+        case XABE_TUNE_PREFILL_WIDE:
+            if (value == 0) {
+                m->pf_item_cols = kPfTileN;
+                return XABE_OK;
+            }
+            return setup_wide_prefill(m);
+        default: return fail(XABE_ERR_INVALID_ARGUMENT, "unknown tuning key %d", key);
+    }
+}
+
 int xabe_moe_device_status(xabe_moe* m, void* stream, int* status_out) {
     if (!m || !status_out) return fail(XABE_ERR_INVALID_ARGUMENT, "null argument to device_status");
     cudaStream_t st = (cudaStream_t)stream;
@@ -1488,7 +1590,7 @@ int xabe_stream_read(void* stream, const void* dev_bytes, size_t n_bytes, void* 
     int dev = 0, sms = 0;
     CUDA_TRY(cudaGetDevice(&dev));
     CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    k_stream_read<<<sms * 8, 256, 0, (cudaStream_t)stream>>>((const uint4*)dev_bytes, n_bytes / 16, (unsigned*)sink);
+    k_stream_read<<<sms * 8, 256, 0, counted((cudaStream_t)stream)>>>((const uint4*)dev_bytes, n_bytes / 16, (unsigned*)sink);
     CUDA_TRY(cudaGetLastError());
     return XABE_OK;
 }
@@ -1535,9 +1637,9 @@ int xabe_dequantize(void* stream, xabe_quant_tensor t, float* out) {
     if (n == 0) return XABE_OK;
     unsigned blocks = (unsigned)((n + 255) / 256);
     if (t.quant == XABE_QUANT_Q6_K)
-        k_dequant_q6k<<<blocks, 256, 0, (cudaStream_t)stream>>>((const uint8_t*)t.dev_bytes, n, out);
+        k_dequant_q6k<<<blocks, 256, 0, counted((cudaStream_t)stream)>>>((const uint8_t*)t.dev_bytes, n, out);
     else
-        k_dequant_q8_0<<<blocks, 256, 0, (cudaStream_t)stream>>>((const uint8_t*)t.dev_bytes, n, out);
+        k_dequant_q8_0<<<blocks, 256, 0, counted((cudaStream_t)stream)>>>((const uint8_t*)t.dev_bytes, n, out);
     CUDA_TRY(cudaGetLastError());
     return XABE_OK;
 }
@@ -1570,7 +1672,9 @@ constexpr size_t kNoAllocBytes = kNoAllocHeader + kNoAllocXBytes + kNoAllocInter
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
 
 constexpr int kNoAllocMaxDevices = 64;
-unsigned char* g_noalloc_ptr[kNoAllocMaxDevices] = {};  // device address of the array, per device
+// Device address of the array, per device.  Host threads may race to fill an entry; every one of them
+// stores the same value, and the atomic makes the store and the later loads well defined.
+std::atomic<unsigned char*> g_noalloc_ptr[kNoAllocMaxDevices] = {};
 
 // In host code `g_noalloc_scratch` is only a handle for the runtime, not an
 // address a kernel may use: the device address comes from the runtime, once
@@ -1581,13 +1685,13 @@ int noalloc_scratch_for_current_device(unsigned char** out) {
     if (dev < 0 || dev >= kNoAllocMaxDevices)
         return fail(XABE_ERR_DRIVER, "device index %d is outside the %d this entry point tracks", dev,
                     kNoAllocMaxDevices);
-    if (!g_noalloc_ptr[dev]) {
-        unsigned char* p = nullptr;
+    unsigned char* p = g_noalloc_ptr[dev].load(std::memory_order_acquire);
+    if (!p) {
         CUDA_TRY(cudaGetSymbolAddress((void**)&p, g_noalloc_scratch));
         if (!p) return fail(XABE_ERR_DRIVER, "the runtime returned a null address for the static scratch");
-        g_noalloc_ptr[dev] = p;
+        g_noalloc_ptr[dev].store(p, std::memory_order_release);
     }
-    *out = g_noalloc_ptr[dev];
+    *out = p;
     return XABE_OK;
 }
 
@@ -1631,9 +1735,9 @@ extern "C" int xabe_shared_expert_noalloc(void* stream, xabe_quant_tensor gate, 
     __half* inter = (__half*)(base + kNoAllocHeader + kNoAllocXBytes);
     // the array keeps the previous call's contents: the two words that must start clean are rewritten,
     // the activation and intermediate rows this call reads are all rewritten by it
-    k_set_scalar<<<1, 1, 0, st>>>(live, tokens);
-    k_set_scalar<<<1, 1, 0, st>>>(status, 0);
-    k_rows_to_half<<<tokens, 256, 0, st>>>(hidden_states, x_h, live, hidden);
+    k_set_scalar<<<1, 1, 0, counted(st)>>>(live, tokens);
+    k_set_scalar<<<1, 1, 0, counted(st)>>>(status, 0);
+    k_rows_to_half<<<tokens, 256, 0, counted(st)>>>(hidden_states, x_h, live, hidden);
     CUDA_TRY(cudaGetLastError());
     ExpertLaunch L{};
     L.routed_blocks = 0;
@@ -1649,17 +1753,15 @@ extern "C" int xabe_shared_expert_noalloc(void* stream, xabe_quant_tensor gate, 
     L.x_shared = x_h;
     L.inter_shared = inter;
     unsigned tiles = (unsigned)((tokens + bucket - 1) / bucket);
-    // The dynamic shared-memory ceiling of a kernel is a per-function attribute that other entry points
-    // of this library also set; state it again here (an attribute write, not an allocation).
-    if (gate.quant == XABE_QUANT_Q6_K) {
-        CUDA_TRY(cudaFuncSetAttribute(k_expert_gateup<QUANT_Q6K, QUANT_Q6K>,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_gu));
-        k_expert_gateup<QUANT_Q6K, QUANT_Q6K><<<dim3(intermediate / 8, tiles), kExpertThreads, smem_gu, st>>>(L);
-    } else {
-        CUDA_TRY(cudaFuncSetAttribute(k_expert_gateup<QUANT_Q8_0, QUANT_Q8_0>,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_gu));
-        k_expert_gateup<QUANT_Q8_0, QUANT_Q8_0><<<dim3(intermediate / 8, tiles), kExpertThreads, smem_gu, st>>>(L);
-    }
+    // (the kernels' shared-memory ceiling: an attribute write through the runtime, not an allocation)
+    if (gate.quant == XABE_QUANT_Q6_K) CUDA_TRY(allow_dynamic_smem((const void*)k_expert_gateup<QUANT_Q6K, QUANT_Q6K>, smem_gu));
+    else CUDA_TRY(allow_dynamic_smem((const void*)k_expert_gateup<QUANT_Q8_0, QUANT_Q8_0>, smem_gu));
+    if (down.quant == XABE_QUANT_Q6_K) CUDA_TRY(allow_dynamic_smem((const void*)k_expert_down<QUANT_Q6K, QUANT_Q6K>, smem_dn));
+    else CUDA_TRY(allow_dynamic_smem((const void*)k_expert_down<QUANT_Q8_0, QUANT_Q8_0>, smem_dn));
+    if (gate.quant == XABE_QUANT_Q6_K)
+        k_expert_gateup<QUANT_Q6K, QUANT_Q6K><<<dim3(intermediate / 8, tiles), kExpertThreads, smem_gu, counted(st)>>>(L);
+    else
+        k_expert_gateup<QUANT_Q8_0, QUANT_Q8_0><<<dim3(intermediate / 8, tiles), kExpertThreads, smem_gu, counted(st)>>>(L);
     CUDA_TRY(cudaGetLastError());
     L.s_a = (const uint8_t*)down.dev_bytes;
     L.s_b = nullptr;
@@ -1667,16 +1769,28 @@ extern "C" int xabe_shared_expert_noalloc(void* stream, xabe_quant_tensor gate, 
     L.k = intermediate;
     L.x_shared = inter;
     L.shexp = out;
-    if (down.quant == XABE_QUANT_Q6_K) {
-        CUDA_TRY(cudaFuncSetAttribute(k_expert_down<QUANT_Q6K, QUANT_Q6K>,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dn));
-        k_expert_down<QUANT_Q6K, QUANT_Q6K><<<dim3(hidden / 64, tiles), kExpertThreads, smem_dn, st>>>(L);
-    } else {
-        CUDA_TRY(cudaFuncSetAttribute(k_expert_down<QUANT_Q8_0, QUANT_Q8_0>,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dn));
-        k_expert_down<QUANT_Q8_0, QUANT_Q8_0><<<dim3(hidden / 64, tiles), kExpertThreads, smem_dn, st>>>(L);
-    }
+    if (down.quant == XABE_QUANT_Q6_K)
+        k_expert_down<QUANT_Q6K, QUANT_Q6K><<<dim3(hidden / 64, tiles), kExpertThreads, smem_dn, counted(st)>>>(L);
+    else
+        k_expert_down<QUANT_Q8_0, QUANT_Q8_0><<<dim3(hidden / 64, tiles), kExpertThreads, smem_dn, counted(st)>>>(L);
     CUDA_TRY(cudaGetLastError());
+    return XABE_OK;
+}
+
+// The status word of the static array as the last xabe_shared_expert_noalloc call on `stream` left it:
+// 0 when every bounded wait of its kernels completed.  Copies four bytes to `status_out` (host memory)
+// and synchronises `stream`; allocates nothing.
+extern "C" int xabe_shared_expert_noalloc_status(void* stream, int* status_out) {
+    if (!status_out) return fail(XABE_ERR_INVALID_ARGUMENT, "null status pointer");
+    unsigned char* base = nullptr;
+    int rc = noalloc_scratch_for_current_device(&base);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    int v = -1;
+    CUDA_TRY(cudaMemcpyAsync(&v, base + sizeof(int), sizeof(int), cudaMemcpyDeviceToHost, st));
+    CUDA_TRY(cudaStreamSynchronize(st));
+    *status_out = v;
+    if (v != 0) return fail(XABE_ERR_DEVICE_STATUS, "a kernel's bounded wait ran out (device status %d)", v);
     return XABE_OK;
 }
 
@@ -1800,15 +1914,15 @@ int xabe_lm_head_forward(xabe_lm_head* m, void* stream, xabe_quant_tensor weight
     }
     if (!smem) return fail(XABE_ERR_UNSUPPORTED_GEOMETRY, "LM head pass does not fit shared memory");
     cudaStream_t st = (cudaStream_t)stream;
-    k_head_split<<<tokens, 256, 0, st>>>(hidden_states, tokens, (int)g.hidden, m->x_hi, m->x_lo);
+    k_head_split<<<tokens, 256, 0, counted(st)>>>(hidden_states, tokens, (int)g.hidden, m->x_hi, m->x_lo);
     CUDA_TRY(cudaGetLastError());
     const dim3 grid(m->sm_count, (tokens + 7) / 8), block(32 * (1 + kStreamConsumerWarps));
     if (q == QUANT_Q6K) {
-        CUDA_TRY(cudaFuncSetAttribute(k_head_rows<QUANT_Q6K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        k_head_rows<QUANT_Q6K><<<grid, block, smem, st>>>(P);
+        CUDA_TRY(allow_dynamic_smem((const void*)k_head_rows<QUANT_Q6K>, smem));
+        k_head_rows<QUANT_Q6K><<<grid, block, smem, counted(st)>>>(P);
     } else {
-        CUDA_TRY(cudaFuncSetAttribute(k_head_rows<QUANT_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        k_head_rows<QUANT_Q8_0><<<grid, block, smem, st>>>(P);
+        CUDA_TRY(allow_dynamic_smem((const void*)k_head_rows<QUANT_Q8_0>, smem));
+        k_head_rows<QUANT_Q8_0><<<grid, block, smem, counted(st)>>>(P);
     }
     CUDA_TRY(cudaGetLastError());
     return XABE_OK;
@@ -1824,7 +1938,7 @@ int xabe_lm_head_argmax(xabe_lm_head* m, void* stream, const float* logits, size
         return fail(XABE_ERR_BUFFER_LENGTH, "logits must hold %zu floats, holds %zu",
                     (size_t)m->g.max_tokens * m->g.vocab, logits_len);
     if (tokens == 0) return XABE_OK;
-    k_head_argmax<<<tokens, 1024, 0, (cudaStream_t)stream>>>(logits, (int)m->g.vocab, tokens, out);
+    k_head_argmax<<<tokens, 1024, 0, counted((cudaStream_t)stream)>>>(logits, (int)m->g.vocab, tokens, out);
     CUDA_TRY(cudaGetLastError());
     return XABE_OK;
 }

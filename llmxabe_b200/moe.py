@@ -233,7 +233,29 @@ class MoeKernels:
     def set_exact_decode_regime(self, on: bool) -> None:
         _check(_lib.lib().xabe_moe_set_exact_decode_regime(self._h, int(on)))
 
+    # -- MoeKernels::disable_tensor_cores / tensor_cores_enabled, moe.rs:5416-5458
+    def disable_tensor_cores(self) -> None:
+        _check(_lib.lib().xabe_moe_disable_tensor_cores(self._h))
+
+    def tensor_cores_enabled(self) -> bool:
+        return bool(_lib.lib().xabe_moe_tensor_cores_enabled(self._h))
+
+    def force_prefill_path(self, on: bool) -> None:
+        """The tcgen05 kernels at every width (differential tests); choose before route_and_dispatch."""
+        _check(_lib.lib().xabe_moe_force_prefill_path(self._h, int(on)))
+
+    TUNE = {"pdl": 0, "stream_stages": 1, "stream_runs": 2, "rows_min_tokens": 3, "router_regw": 4,
+            "force_tile_kernels": 5, "prefill_wide": 6, "fused_decode": 7}
+
+    def set_tuning(self, key: str, value: int) -> None:
+        """Per-handle launch-shape switches (XABE_TUNE_* of include/xabe_moe.h); results do not change."""
+        _check(_lib.lib().xabe_moe_set_tuning(self._h, self.TUNE[key], int(value)))
+
+    def set_peer_wait_limit(self, iterations: int) -> None:
+        _check(_lib.lib().xabe_moe_set_peer_wait_limit(self._h, iterations))
+
     def device_status(self, stream=None) -> int:
+        """The status word the kernels' bounded waits write (read and cleared); raises DeviceStatus when non-zero."""
         st = C.c_int(0)
         _check(_lib.lib().xabe_moe_device_status(self._h, _stream_ptr(stream), C.byref(st)))
         return st.value
@@ -297,6 +319,11 @@ class MoeBuffers:
         self.gate = mk(v.gate, (T,), torch.float32)
 
 
+def kernel_launch_count() -> int:
+    """Kernels this library has launched in this process so far (see include/xabe_moe.h)."""
+    return int(_lib.lib().xabe_kernel_launch_count())
+
+
 def dequantize(t: QuantTensor, stream=None) -> torch.Tensor:
     """Standalone dequantisation (crates/xabe-cuda/src/kernels/dequant.rs), bit-identical to the scalar reference."""
     n = t.bytes.numel() // t.quant.file_block_bytes * t.quant.block_elements
@@ -322,6 +349,14 @@ def shared_expert_noalloc(gate: QuantTensor, up: QuantTensor, down: QuantTensor,
     """
     _check(_lib.lib().xabe_shared_expert_noalloc(_stream_ptr(stream), gate._c(), up._c(), down._c(), hidden,
                                                  intermediate, hidden_states.data_ptr(), tokens, out.data_ptr()))
+
+
+def shared_expert_noalloc_status(stream=None) -> int:
+    """The status word of the static scratch after the last `shared_expert_noalloc` call on `stream`
+    (0 = every bounded wait completed); synchronises the stream, allocates nothing."""
+    st = C.c_int(-1)
+    _check(_lib.lib().xabe_shared_expert_noalloc_status(_stream_ptr(stream), C.byref(st)))
+    return st.value
 
 
 class MoeLayerWeights:

@@ -83,6 +83,49 @@ def test_one_rank_peer_memory_exchange_equals_the_plain_block(tokens, live, mode
     assert (bits(lo) == bits(plain["l_out"])).all() and (bits(ffn) == bits(plain["ffn_out"])).all()
 
 
+def test_a_peer_wait_that_runs_out_reports_status_and_moves_nothing():
+    """The failure path of the peer-memory exchange without harming the GPU: the owner waits for a step
+    number no sender has announced, with a limit of a few thousand 200 ns iterations.  The wait gives up
+    and returns, the status word reads 3, every receive slot is reported empty (so no expert runs and
+    nothing is stored into a peer), and the next normal layer is still bit-identical to the plain block."""
+    import torch
+    from llmxabe_b200 import errors, synth
+    from llmxabe_b200.ep import EpMoeBlock, PeerMemoryEpBackend
+    from llmxabe_b200.moe import MoeBlock, MoeGeometry
+    tokens = 24
+    L = synth.moe_layer(seed=24, num_experts=8, top_k=2, hidden=512, inter=256, zipf=True)
+    x = synth.activations(tokens, 512, seed=24)
+    w = device_layer(L)
+    g = MoeGeometry(8, 2, 512, 256, 16, tokens)
+    backend = PeerMemoryEpBackend(g, 8, 0, 1, w, w.gate_exps, w.up_exps, w.down_exps)
+    blk = EpMoeBlock(backend, 8, 2, 0, 1)
+    res = torch.from_numpy(x).cuda()
+    ffn = torch.zeros(tokens, 512, device="cuda")
+    lo = torch.zeros(tokens, 512, device="cuda")
+    blk.forward(res, tokens, ffn, lo)           # a normal layer first: the regions now hold live rows
+    torch.cuda.synchronize()
+    assert backend.back_k.device_status() == 0
+    backend.back_k.set_peer_wait_limit(4000)    # under a millisecond
+    backend.slot_ids.fill_(7)
+    backend.result_dst.fill_(1)
+    backend.back_k.ep_p2p_receive(1, 0, backend.cap, backend.peers, backend.step + 1, backend.slot_ids,
+                                  backend.result_dst)
+    torch.cuda.synchronize()
+    assert bool((backend.slot_ids == -1).all().item()), "a timed-out step must report every slot empty"
+    assert bool((backend.result_dst == 0).all().item()), "and no destination pointers"
+    with pytest.raises(errors.DeviceStatus, match="status 3"):
+        backend.back_k.device_status()
+    assert backend.back_k.device_status() == 0  # reading cleared it
+    backend.back_k.set_peer_wait_limit(0)
+    plain = run_block(MoeBlock(g), w, x, tokens)
+    blk.forward(res, tokens, ffn, lo)
+    torch.cuda.synchronize()
+    assert backend.front_k.device_status() == 0 and backend.back_k.device_status() == 0
+    assert (bits(lo.cpu().numpy()) == bits(plain["l_out"])).all()
+    for b in backend._shared.values():
+        b.release()
+
+
 def _rank_main(rank, world, port, out_dir, peer_memory=False):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))

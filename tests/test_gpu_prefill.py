@@ -69,17 +69,18 @@ def test_real_geometry_prefill_512(torch_cuda, oracle):
     _check(oracle, got, want, "prefill real T=512")
 
 
-def test_four_accumulator_kernel_matches_the_oracle(oracle, monkeypatch):
+def test_four_accumulator_kernel_matches_the_oracle(oracle):
     """k_prefill_gemm_wide (items of up to 512 columns, TMA-loaded activation tiles) is chosen by default only
-    for the dense block at prefill width; the switch forces it here for a routed block and a dense block."""
+    for the dense block at prefill width; the per-handle switch selects it here for a routed block and a dense block."""
     import torch
     from llmxabe_b200 import synth
     from llmxabe_b200.moe import DenseFfnBlock, MoeBlock, MoeGeometry, QuantTensor
-    monkeypatch.setenv("XABE_MOE_PF_WIDE", "1")
     T = 700
     L = synth.moe_layer(seed=61, num_experts=4, top_k=2, hidden=512, inter=256, zipf=True)
     x = synth.activations(T, 512, seed=61)
-    got = run_block(MoeBlock(MoeGeometry(4, 2, 512, 256, 32, T)), device_layer(L), x, T)
+    routed_blk = MoeBlock(MoeGeometry(4, 2, 512, 256, 32, T))
+    routed_blk.moe.set_tuning("prefill_wide", 1)
+    got = run_block(routed_blk, device_layer(L), x, T)
     want = oracle.moe_block_forward(oracle_layer(oracle, L), x, dev_order=True)
     assert (got["topk_ids"] == want["topk_ids"]).all() and got["untouched"]
     rel = np.linalg.norm(got["l_out"].astype(np.float64) - want["l_out"]) / np.linalg.norm(want["l_out"].astype(np.float64))
@@ -90,6 +91,7 @@ def test_four_accumulator_kernel_matches_the_oracle(oracle, monkeypatch):
     xd = synth.activations(tokens, hidden, seed=62)
     want_ffn, _ = oracle.dense_block_forward(post_norm, 1e-6, gate, 0, up, 0, down, 0, hidden, inter, xd, dev_order=True)
     blk = DenseFfnBlock(MoeGeometry(1, 1, hidden, inter, 64, tokens))
+    blk.moe.set_tuning("prefill_wide", 1)
     qt = [QuantTensor(torch.from_numpy(a).cuda(), 0) for a in (gate, up, down)]
     res = torch.from_numpy(xd).cuda()
     ffn = torch.zeros(tokens, hidden, device="cuda")

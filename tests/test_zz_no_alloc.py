@@ -19,7 +19,8 @@ def test_no_alloc_shared_expert_matches_the_handle_based_entry_point_twice_in_a_
     if not torch.cuda.is_available():
         pytest.fail("gpu-marked test collected without a CUDA device")
     from llmxabe_b200 import errors, synth
-    from llmxabe_b200.moe import (ExpertQuant, MoeGeometry, MoeKernels, QuantTensor, shared_expert_noalloc)
+    from llmxabe_b200.moe import (ExpertQuant, MoeGeometry, MoeKernels, QuantTensor, shared_expert_noalloc,
+                                  shared_expert_noalloc_status)
     from oracle import xabe_oracle as oracle
     H, I = 2048, 512
     for call, (quant, tokens) in enumerate([(0, 37), (1, 5)]):
@@ -36,6 +37,8 @@ def test_no_alloc_shared_expert_matches_the_handle_based_entry_point_twice_in_a_
         # the allocation-free one: no handle; outputs past `tokens` must stay untouched
         got = torch.full((64, H), 777.0, device="cuda")
         shared_expert_noalloc(gate, up, down, H, I, x, tokens, got)
+        # a caller without a handle learns from this word whether a bounded wait of the kernels ran out
+        assert shared_expert_noalloc_status() == 0
         torch.cuda.synchronize()
         r = oracle.compare(got[:tokens].cpu().numpy(), want[:tokens].cpu().numpy())
         print(f"call {call} (quant {quant}, {tokens} tokens): {r}")
