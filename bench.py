@@ -364,6 +364,8 @@ def measure_moe(args, workload: str, *, full: bool, sampler: ClockSampler | None
     tokens, block_size, zipf = WORKLOADS[workload]
     g = MoeGeometry.qwen3_6(block_size, tokens)
     block = MoeBlock(g)
+    for key, value in args.tune:
+        block.moe.set_tuning(key, value)
     layers = [synth.moe_layer_on_device(seed=rank, layer=i, zipf=zipf, routed_quant=_quant_code(args.routed_quant),
                                         down_quant=_quant_code(args.routed_down_quant),
                                         shared_quant=_quant_code(args.shared_quant)) for i in range(args.layers)]
@@ -459,7 +461,9 @@ def measure_moe(args, workload: str, *, full: bool, sampler: ClockSampler | None
                               "bytes": cal_bytes, "ms": cal_ms, "gbs": cal_bytes / (cal_ms * 1e-3) / 1e9}
     # the same step with per-stage CUDA events, for the dominant kernel's duration
     block.moe.stage_profile(True)
-    tm.region(step, min(max(steps, 20), 256))
+    tm.region(step, 8)
+    block.moe.stage_times()   # the first calls after the graph replays run at eager-launch pace: not recorded
+    tm.region(step, min(max(steps, 100), 256))
     stage_ms, calls = block.moe.stage_times()
     block.moe.stage_profile(False)
     out["stage_ms"] = {k: v / max(calls, 1) for k, v in stage_ms.items()}
@@ -1064,6 +1068,8 @@ def main():
     ap.add_argument("--ep-nccl", dest="ep_peer_memory", action="store_false",
                     help="exchange rows and results with NCCL all-to-alls instead of peer stores over NVLink")
     ap.add_argument("--no-graph", dest="graph", action="store_false", help="time eager launches instead of CUDA-graph replay")
+    ap.add_argument("--tune", default=[], type=lambda s: [(kv.split("=")[0], int(kv.split("=")[1])) for kv in s.split(",") if kv],
+                    help="per-handle launch-shape switches of the single-layer MoE workloads, e.g. fused_decode=0,pdl=1")
     args = ap.parse_args()
     if args.routed_down_quant is None:
         args.routed_down_quant = args.routed_quant

@@ -18,13 +18,19 @@ namespace xabe {
 // tid sums x[j]^2 for j = tid, tid+blockDim, ... with fused multiply-add,
 // then block_reduce_sum; 1/sqrtf (not rsqrtf); x * inv_rms * w in that order.
 // Also writes a half-precision copy, the B operand of the expert kernels.
+// With `gate_w` (and `width` floats of dynamic shared memory) it also leaves the shared expert's
+// gate of the row in gate[row]: sigmoid(dot(gate_w, normed row)) in the order of
+// moe_block_gate_and_combine (256 lanes at stride 256, block_reduce_sum), for a block whose last
+// stage is folded into the down projection and so has no kernel of its own to compute it.
 // grid: (max_tokens); rows at and beyond *valid_tokens are skipped.
 // ---------------------------------------------------------------------------
 __global__ void k_rms_norm(const float* __restrict__ x, const float* __restrict__ weight,
                            float* __restrict__ out, __half* __restrict__ out_h,
-                           const int* __restrict__ valid_tokens, int width, float eps) {
+                           const int* __restrict__ valid_tokens, int width, float eps,
+                           const float* __restrict__ gate_w, float* __restrict__ gate) {
     pdl_launch_dependents();
     pdl_wait();
+    extern __shared__ float norm_row[];
     __shared__ float scratch[32];
     int row = blockIdx.x;
     if (row >= *valid_tokens) return;
@@ -40,6 +46,16 @@ __global__ void k_rms_norm(const float* __restrict__ x, const float* __restrict_
         float y = __fmul_rn(__fmul_rn(x[base + j], inv_rms), weight[j]);
         out[base + j] = y;
         if (out_h) out_h[base + j] = __float2half_rn(y);
+        if (gate_w) norm_row[j] = y;
+    }
+    if (gate_w) {
+        __syncthreads();
+        float s = 0.0f;
+        if (threadIdx.x < 256)
+            for (int j = threadIdx.x; j < width; j += 256) s = fmaf(gate_w[j], norm_row[j], s);
+        // warps past the eighth add +0 after the eight totals: the sum is the eight-warp sum
+        s = block_reduce_sum_pinned(s, scratch);
+        if (threadIdx.x == 0) gate[row] = __fdiv_rn(1.0f, 1.0f + expf(-s));
     }
 }
 
@@ -421,12 +437,13 @@ template <int kRouteLaneExperts>
 __device__ __forceinline__ void route_one_token(const float* __restrict__ row, int num_experts, int top_k,
                                                 int lane, int* __restrict__ ids_out,
                                                 float* __restrict__ w_out) {
+    // the row may have been written by other CTAs of the same launch: read it through L2
     float lg[kRouteLaneExperts];
-    float mx = row[0];
+    float mx = __ldcg(row);
 #pragma unroll
     for (int i = 0; i < kRouteLaneExperts; ++i) {
         int e = lane + 32 * i;
-        lg[i] = e < num_experts ? row[e] : 0.0f;
+        lg[i] = e < num_experts ? __ldcg(row + e) : 0.0f;
         if (e < num_experts) mx = fmaxf(mx, lg[i]);
     }
 #pragma unroll
@@ -449,30 +466,33 @@ __device__ __forceinline__ void route_one_token(const float* __restrict__ row, i
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) s += __shfl_down_sync(0xffffffffu, s, off);
     float sum_exp = __shfl_sync(0xffffffffu, s, 0);
+    // Selection keys: a probability is a non-negative float, so its bit pattern orders like the value;
+    // key 0 marks "not selectable" (already taken, past the last expert, or not a number).
+    unsigned key[kRouteLaneExperts];
 #pragma unroll
     for (int i = 0; i < kRouteLaneExperts; ++i) {
         int e = lane + 32 * i;
-        p[i] = e < num_experts ? __fdiv_rn(p[i], sum_exp) : -1.0f;
+        float pv = e < num_experts ? __fdiv_rn(p[i], sum_exp) : -1.0f;
+        key[i] = pv >= 0.0f ? __float_as_uint(pv) + 1u : 0u;
     }
     float sel_sum = 0.0f;
     float sel[16];
     for (int j = 0; j < top_k; ++j) {
-        float bv = -1.0f;
-        int bi = -1;
-#pragma unroll
-        for (int i = 0; i < kRouteLaneExperts; ++i) {
-            int e = lane + 32 * i;
-            if (p[i] > bv || (p[i] == bv && p[i] >= 0.0f && (bi < 0 || e < bi))) { bv = p[i]; bi = e; }
-        }
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) {
-            float cv = __shfl_xor_sync(0xffffffffu, bv, off);
-            int ci = __shfl_xor_sync(0xffffffffu, bi, off);
-            if (cv > bv || (cv == bv && ci >= 0 && (bi < 0 || ci < bi))) { bv = cv; bi = ci; }
-        }
+        // this lane's best (largest key, lowest expert on a tie), then two warp reductions: the
+        // largest key, and the lowest expert index among the lanes that hold it
+        unsigned bk = 0u;
+        int be = 0x7fffffff;
 #pragma unroll
         for (int i = 0; i < kRouteLaneExperts; ++i)
-            if (bi >= 0 && lane + 32 * i == bi) p[i] = -1.0f;
+            if (key[i] > bk) { bk = key[i]; be = lane + 32 * i; }
+        const unsigned mk = __reduce_max_sync(0xffffffffu, bk);
+        const int cand = (bk == mk && mk != 0u) ? be : 0x7fffffff;
+        const int bi_raw = (int)__reduce_min_sync(0xffffffffu, (unsigned)cand);
+        const int bi = mk != 0u ? bi_raw : -1;
+        const float bv = mk != 0u ? __uint_as_float(mk - 1u) : -1.0f;
+#pragma unroll
+        for (int i = 0; i < kRouteLaneExperts; ++i)
+            if (bi >= 0 && lane + 32 * i == bi) key[i] = 0u;
         if (lane == 0) ids_out[j] = bi;
         if (j < 16) sel[j] = bv;
         sel_sum += bv;  // selection order, as router.rs:62
@@ -674,55 +694,44 @@ __global__ void k_build_work(int num_experts, const int* __restrict__ expert_off
 // ---------------------------------------------------------------------------
 constexpr int kSmallPairs = 2048;
 
-__global__ void __launch_bounds__(256) k_route_dispatch_small(
-    const float* __restrict__ logits, const int* __restrict__ valid_tokens, int num_experts, int top_k,
-    int block_size, int sorted_capacity, int block_capacity, int* __restrict__ topk_ids,
-    float* __restrict__ topk_weights, int* __restrict__ sorted_token_ids, int* __restrict__ expert_ids,
-    int* __restrict__ num_tokens_post_pad, int* __restrict__ expert_offsets, int* __restrict__ expert_counts,
-    int* __restrict__ work_items, int* __restrict__ n_work) {
-    pdl_launch_dependents();
-    pdl_wait();
-    extern __shared__ int sm[];
+// The tables and the column groups from a routing decision that is already in topk_ids /
+// topk_weights (global memory, written by this block or made visible to it), by a block of NT
+// threads.  `sm` is the block's scratch: (3 * kSmallPairs + (NT / 32 + 3) * E + 2) ints.
+template <int NT>
+__device__ __forceinline__ void dispatch_small_body(
+    int* sm, int live, int num_experts, int top_k, int block_size, int sorted_capacity, int block_capacity,
+    const int* __restrict__ topk_ids, const float* __restrict__ topk_weights, int* __restrict__ sorted_token_ids,
+    int* __restrict__ expert_ids, int* __restrict__ num_tokens_post_pad, int* __restrict__ expert_offsets,
+    int* __restrict__ expert_counts, int* __restrict__ work_items, int* __restrict__ n_work) {
+    constexpr int NW = NT / 32;
     int* ids_s = sm;                          // [kSmallPairs]
-    int* hist = ids_s + kSmallPairs;          // [8][E] per-warp chunk histograms -> cursors
-    int* start_s = hist + 8 * num_experts;    // [E + 1] padded exclusive offsets
+    int* hist = ids_s + kSmallPairs;          // [NW][E] per-warp chunk histograms -> cursors
+    int* start_s = hist + NW * num_experts;   // [E + 1] padded exclusive offsets
     int* count_s = start_s + num_experts + 1; // [E] live counts
     int* cstart_s = count_s + num_experts;    // [E] unpadded exclusive offsets
     int* sorted_s = cstart_s + num_experts;   // [kSmallPairs] live flat ids in dispatch order
     float* wts_s = (float*)(sorted_s + kSmallPairs);  // [kSmallPairs] routing weights by flat id
-    int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    int live = *valid_tokens;
-    int numel = live * top_k;
-    if (logits) {  // at most one token per warp is routed here; wider steps route in k_route first
-        for (int t = warp; t < live; t += 8) {
-            if (num_experts <= 256)
-                route_one_token<8>(logits + (size_t)t * num_experts, num_experts, top_k, lane,
-                                   topk_ids + (size_t)t * top_k, topk_weights + (size_t)t * top_k);
-            else
-                route_one_token<16>(logits + (size_t)t * num_experts, num_experts, top_k, lane,
-                                    topk_ids + (size_t)t * top_k, topk_weights + (size_t)t * top_k);
-        }
-    }
-    for (int i = tid; i < 8 * num_experts; i += 256) hist[i] = 0;
-    for (int i = tid; i < sorted_capacity; i += 256) sorted_token_ids[i] = numel;
-    for (int i = tid; i < block_capacity; i += 256) expert_ids[i] = -1;
-    __syncthreads();  // ids are in global memory, written by this block
-    for (int i = tid; i < numel; i += 256) {
-        ids_s[i] = topk_ids[i];
-        wts_s[i] = topk_weights[i];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int numel = live * top_k;
+    for (int i = tid; i < NW * num_experts; i += NT) hist[i] = 0;
+    for (int i = tid; i < sorted_capacity; i += NT) sorted_token_ids[i] = numel;
+    for (int i = tid; i < block_capacity; i += NT) expert_ids[i] = -1;
+    for (int i = tid; i < numel; i += NT) {
+        ids_s[i] = __ldcg(topk_ids + i);
+        wts_s[i] = __ldcg(topk_weights + i);
     }
     __syncthreads();
     // warp w owns flat pairs [w * chunk, (w + 1) * chunk), chunk a multiple of 32
-    int chunk = ((numel + 7) / 8 + 31) / 32 * 32;
+    int chunk = ((numel + NW - 1) / NW + 31) / 32 * 32;
     int begin = warp * chunk, end = min(numel, begin + chunk);
     for (int i = begin + lane; i < end; i += 32) {
         int e = ids_s[i];
         if (e >= 0) atomicAdd(&hist[warp * num_experts + e], 1);  // negative: a row that holds nothing
     }
     __syncthreads();
-    for (int e = tid; e < num_experts; e += 256) {
+    for (int e = tid; e < num_experts; e += NT) {
         int total = 0;
-        for (int w = 0; w < 8; ++w) {
+        for (int w = 0; w < NW; ++w) {
             int h = hist[w * num_experts + e];
             hist[w * num_experts + e] = total;
             total += h;
@@ -763,12 +772,12 @@ __global__ void __launch_bounds__(256) k_route_dispatch_small(
         }
     }
     __syncthreads();
-    for (int e = tid; e < num_experts; e += 256) {
+    for (int e = tid; e < num_experts; e += NT) {
         int s0 = start_s[e], s1 = start_s[e + 1];
         expert_offsets[e] = s0;
         expert_counts[e] = count_s[e];
         for (int b = s0 / block_size; b < s1 / block_size; ++b) expert_ids[b] = e;
-        for (int w = 0; w < 8; ++w) hist[w * num_experts + e] += s0;
+        for (int w = 0; w < NW; ++w) hist[w * num_experts + e] += s0;
     }
     if (tid == 0) expert_offsets[num_experts] = start_s[num_experts];
     __syncthreads();
@@ -791,7 +800,7 @@ __global__ void __launch_bounds__(256) k_route_dispatch_small(
     }
     __syncthreads();
     // column groups: reuse hist[0..E) as the group base
-    for (int e = tid; e < num_experts; e += 256) hist[e] = (count_s[e] + 7) >> 3;
+    for (int e = tid; e < num_experts; e += NT) hist[e] = (count_s[e] + 7) >> 3;
     __syncthreads();
     if (warp == 0) {
         int per = (num_experts + 31) / 32;
@@ -813,7 +822,7 @@ __global__ void __launch_bounds__(256) k_route_dispatch_small(
         if (lane == 31) *n_work = incl;
     }
     __syncthreads();
-    for (int e = tid; e < num_experts; e += 256) {
+    for (int e = tid; e < num_experts; e += NT) {
         int count = count_s[e], groups = (count + 7) >> 3;
         for (int i = 0; i < groups; ++i) {
             int* it = work_items + (size_t)(hist[e] + i) * kWorkItemInts;
@@ -829,6 +838,38 @@ __global__ void __launch_bounds__(256) k_route_dispatch_small(
             }
         }
     }
+}
+
+__host__ __device__ inline size_t dispatch_small_smem(int num_experts, int threads) {
+    return (size_t)(3 * kSmallPairs + (threads / 32 + 3) * num_experts + 2) * sizeof(int);
+}
+
+__global__ void __launch_bounds__(256) k_route_dispatch_small(
+    const float* __restrict__ logits, const int* __restrict__ valid_tokens, int num_experts, int top_k,
+    int block_size, int sorted_capacity, int block_capacity, int* __restrict__ topk_ids,
+    float* __restrict__ topk_weights, int* __restrict__ sorted_token_ids, int* __restrict__ expert_ids,
+    int* __restrict__ num_tokens_post_pad, int* __restrict__ expert_offsets, int* __restrict__ expert_counts,
+    int* __restrict__ work_items, int* __restrict__ n_work) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ int sm[];
+    int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int live = *valid_tokens;
+    if (logits) {  // at most one token per warp is routed here; wider steps route in k_route first
+        for (int t = warp; t < live; t += 8) {
+            if (num_experts <= 256)
+                route_one_token<8>(logits + (size_t)t * num_experts, num_experts, top_k, lane,
+                                   topk_ids + (size_t)t * top_k, topk_weights + (size_t)t * top_k);
+            else
+                route_one_token<16>(logits + (size_t)t * num_experts, num_experts, top_k, lane,
+                                    topk_ids + (size_t)t * top_k, topk_weights + (size_t)t * top_k);
+        }
+    }
+    __threadfence();  // the ids were written by this block; the body reads them back through L2
+    __syncthreads();
+    dispatch_small_body<256>(sm, live, num_experts, top_k, block_size, sorted_capacity, block_capacity, topk_ids,
+                             topk_weights, sorted_token_ids, expert_ids, num_tokens_post_pad, expert_offsets,
+                             expert_counts, work_items, n_work);
 }
 
 // ---------------------------------------------------------------------------

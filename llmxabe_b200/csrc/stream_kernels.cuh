@@ -68,7 +68,54 @@ struct StreamLaunch {
     int max_tokens;
     int down_row_step;    // MODE_DOWN: rows of one fragment half are this far apart (bank-conflict free reads)
     int runs_override;    // tuning aid: > 0 fixes the runs per column group
+    // MODE_DOWN, optional: the block's last stage folded into this launch (see combine_tile).  A null
+    // tail_done means a separate kernel combines.
+    int* tail_done;             // [max_tokens][rows / 128] arrivals per (token, row tile), zero between launches
+    int tail_target;            // arrivals that complete a (token, row tile): (top_k + 1) groups x 8 warps
+    const float* tail_gate;     // [max_tokens] sigmoid gate of the shared expert
+    const float* tail_residual; // [max_tokens][rows]
+    float* tail_routed;         // [max_tokens][rows]
+    float* tail_ffn;            // [max_tokens][rows]
+    float* tail_lout;           // [max_tokens][rows]
 };
+
+// The last stage of the block (moe_block_gate_and_combine, crates/xabe-engine/src/block/moe.rs:424-483)
+// for 128 output columns of one token, by one warp: routed = ascending-k sum of the weighted expert
+// rows, ffn_out = routed + shexp * gate, l_out = ffn_out + residual.  Called by the warp whose
+// arrival completed the token's row tile (every expert row and the shared expert's row of these 128
+// columns is then in memory; they were written by other CTAs, so they are read through L2).
+__device__ __forceinline__ void combine_tile(const StreamLaunch& L, int token, int tile, int lane) {
+    const int rows = L.rows;
+    const size_t col = (size_t)tile * 128 + (size_t)lane * 4;
+    float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float* pbase = L.partial + (size_t)token * L.top_k * rows + col;
+    for (int k0 = 0; k0 < L.top_k; k0 += 4) {  // four rows in flight, then the same ascending-k sum
+        float4 pv[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            if (k0 + k < L.top_k) pv[k] = __ldcg((const float4*)(pbase + (size_t)(k0 + k) * rows));
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            if (k0 + k < L.top_k) {
+                r.x += pv[k].x;
+                r.y += pv[k].y;
+                r.z += pv[k].z;
+                r.w += pv[k].w;
+            }
+    }
+    const size_t o = (size_t)token * rows + col;
+    const float4 sh = __ldcg((const float4*)(L.shexp + o));
+    const float4 res = *(const float4*)(L.tail_residual + o);
+    const float g = L.tail_gate[token];
+    float4 v;
+    v.x = fmaf(sh.x, g, r.x);
+    v.y = fmaf(sh.y, g, r.y);
+    v.z = fmaf(sh.z, g, r.z);
+    v.w = fmaf(sh.w, g, r.w);
+    *(float4*)(L.tail_routed + o) = r;
+    *(float4*)(L.tail_ffn + o) = v;
+    *(float4*)(L.tail_lout + o) = make_float4(v.x + res.x, v.y + res.y, v.z + res.z, v.w + res.w);
+}
 
 // Buffers for the activation rows of a unit.  The producer stages a unit's rows while the consumers
 // still work on the unit before it, into the buffer of the unit before that one.  gate/up gives
@@ -351,9 +398,10 @@ __device__ __forceinline__ int gateup_span_of(int w, int h, int n_spans) {
 // rows 0-7 / 8-15), eight warps split the spans, SwiGLU epilogue, f16 out.
 // MODE_DOWN: tile = 128 rows, one m16 tile per warp over the whole contraction
 // (at most two spans), weight * value (routed) or value (shared) out, fp32.
+// TAIL (MODE_DOWN only): the launch also performs the block's last stage, see combine_tile.
 // grid: number of SMs; block: kStreamThreads.
 // ---------------------------------------------------------------------------
-template <int MODE, int QR, int QS>
+template <int MODE, int QR, int QS, bool TAIL = false>
 __global__ void __launch_bounds__(kStreamThreads, 1) k_expert_stream(StreamLaunch L) {
     pdl_launch_dependents();
     pdl_wait();
@@ -672,6 +720,27 @@ __global__ void __launch_bounds__(kStreamThreads, 1) k_expert_stream(StreamLaunc
                         float* dst = result_row(L.partial, L.partial_rows, flat1, L.rows);
                         dst[row_lo] = wgt1 * acc[1];
                         dst[row_hi] = wgt1 * acc[3];
+                    }
+                }
+                if (TAIL) {
+                    // This warp's 16 rows of the tile are stored.  Count the arrival for every token of
+                    // the group; the arrival that completes a (token, row tile) combines its 128 columns.
+                    __threadfence();
+                    __syncwarp();
+                    int tok = -1;
+                    if (lane < ncols) tok = shared ? first + lane : desc[4 + lane] / L.top_k;
+                    bool fin = false;
+                    if (tok >= 0) {
+                        int* cnt = L.tail_done + (size_t)tok * plan.row_tiles + tile;
+                        fin = atomicAdd(cnt, 1) == L.tail_target - 1;
+                        if (fin) *cnt = 0;  // the last arrival: ready for the next launch
+                    }
+                    unsigned todo = __ballot_sync(0xffffffffu, fin);
+                    if (todo) __threadfence();
+                    while (todo) {
+                        const int src = __ffs(todo) - 1;
+                        todo &= todo - 1;
+                        combine_tile(L, __shfl_sync(0xffffffffu, tok, src), tile, lane);
                     }
                 }
             }

@@ -15,6 +15,7 @@
 #include "common.cuh"
 #include "expert_kernels.cuh"
 #include "glue_kernels.cuh"
+#include "front_kernels.cuh"
 #include "stream_kernels.cuh"
 #include "stream_rows_kernels.cuh"
 #include "head_kernels.cuh"
@@ -97,6 +98,9 @@ constexpr uint32_t kPrefillWideMinTokens = 1024;
 // Wide passes only take the tcgen05 prefill kernels; the launch shape comes from max_tokens.
 constexpr uint32_t kPrefillMinTokens = 512;
 
+// Handles narrower than this fold the block's last stage into the down projection's launch.
+constexpr uint32_t kTailMaxTokens = 16;
+
 thread_local std::string g_last_error;
 
 int fail(int code, const char* fmt, ...) {
@@ -174,9 +178,16 @@ struct xabe_moe {
     int rows_min_tokens = -1;         // -1: the measured default; 0: k_gateup_rows off
     int router_regw = -1;             // -1: by width; 0/1: off/on
     uint32_t peer_wait_limit = 0;     // 0: kPeerWaitLimit
-    bool fused_decode = true;         // decode widths: fused front (norm .. dispatch) and fused tail
+    // Both fusions are off by default.  Measured under CUDA-graph replay at 1 / 3 / 64 tokens (us per
+    // layer): one kernel per stage 34.8 / 49.5 / 154.7; last stage folded in 36.9 / 54.4 / -; front
+    // fused as well 34.3 / 54.8 / 182.6.  A launch boundary inside a replayed graph costs about 2 us,
+    // less than the fences, arrival counts and one-CTA phases that replace it.
+    bool fused_tail = false;          // handles under 16 tokens: gate-and-combine folded into the down launch
+    bool fused_front = false;         // handles up to 256 tokens: norm .. dispatch in one launch (k_decode_front)
     float* normed = nullptr;
     __half* normed_h = nullptr;
+    int* tail_done = nullptr;      // [kTailMaxTokens][hidden / 128] arrivals of the fused combine, zero between launches
+    int* front_tickets = nullptr;  // [1 + max_tokens] arrival counters of k_decode_front, zero between launches
     int* ep_compact = nullptr;  // [num_experts + 1] live pairs before each expert (expert parallelism)
     int* ep_rank_start = nullptr;   // [kEpMaxRanks] where each rank's pairs start in the send order
     int* ep_send_counts = nullptr;  // [kEpMaxRanks]
@@ -313,7 +324,8 @@ StreamShape stream_shape(int mode, int rows, int k, int q_routed, int q_shared, 
 
 template <int MODE, int QR, int QS>
 int launch_stream_t(xabe_moe* m, cudaStream_t st, const StreamLaunch& L, uint32_t smem) {
-    auto kern = k_expert_stream<MODE, QR, QS>;
+    auto kern = (MODE == MODE_DOWN && L.tail_done) ? k_expert_stream<MODE, QR, QS, MODE == MODE_DOWN>
+                                                   : k_expert_stream<MODE, QR, QS, false>;
     CUDA_TRY(allow_dynamic_smem((const void*)kern, smem));
     CUDA_TRY(launch_pdl(m->pdl, kern, dim3(m->sm_count), dim3(kStreamThreads), smem, st, L));
     return XABE_OK;
@@ -468,10 +480,31 @@ struct MlpWeights {
     xabe_quant_tensor gate{}, up{}, down{};
 };
 
+// The block's last stage, when the down projection is to perform it itself (k_expert_stream<DOWN>'s
+// combine_tile) instead of a launch of k_gate_and_combine.
+struct TailFusion {
+    const float* gate;      // [max_tokens], already computed (k_decode_front)
+    const float* residual;
+    float* routed;
+    float* ffn_out;
+    float* l_out;
+};
+
+bool tail_applies(const xabe_moe* m, const xabe_moe_layer_weights* w) {
+    const auto& g = m->g;
+    // Handles of fewer than 16 tokens: the routed and the shared experts always share one launch there
+    // (see run_experts), and the per-tile fence the arrival count needs costs less than a launch.
+    if (!m->fused_tail || g.max_tokens >= kTailMaxTokens || m->force_tile_kernels || m->partial_rows) return false;
+    if (g.hidden > 8192) return false;  // k_rms_norm keeps the row in shared memory for the gate
+    if (g.hidden % 128 != 0) return false;
+    return stream_shape(MODE_DOWN, (int)g.hidden, (int)g.intermediate, w->down_exps.quant, w->shared_down.quant,
+                        m->stream_stages).ok;
+}
+
 // Both projections of the routed experts and/or the shared expert, each in one
 // launch.  `routed`/`shared` say which halves ride the launch.
 int run_experts(xabe_moe* m, cudaStream_t st, const MlpWeights& routed, const MlpWeights& shared,
-                float* shexp_out, int mark_between = -1) {
+                float* shexp_out, int mark_between = -1, const TailFusion* tail = nullptr) {
     const auto& g = m->g;
     if (!routed.present && !shared.present) return XABE_OK;
     // Different formats for the routed experts and the shared expert (the shipped file: Q6_K and Q8_0):
@@ -679,6 +712,15 @@ int run_experts(xabe_moe* m, cudaStream_t st, const MlpWeights& routed, const Ml
             bool four = ((words * 4u) % 32u) % 8u == 4u && ((words_s * 4u) % 32u) % 8u == 4u;
             SL.down_row_step = four ? 4 : 1;
         }
+        if (tail && routed.present && shared.present) {
+            SL.tail_done = m->tail_done;
+            SL.tail_target = ((int)g.experts_per_token + 1) * kStreamGroupWarps;
+            SL.tail_gate = tail->gate;
+            SL.tail_residual = tail->residual;
+            SL.tail_routed = tail->routed;
+            SL.tail_ffn = tail->ffn_out;
+            SL.tail_lout = tail->l_out;
+        }
         return launch_stream<MODE_DOWN>(m, st, SL, dn.smem, qr, qs);
     }
     size_t smem = down_smem(L.k, qr);
@@ -727,13 +769,16 @@ int rows_to_half(xabe_moe* m, cudaStream_t st, const float* hidden_states) {
     return XABE_OK;
 }
 
-int launch_rms_norm(xabe_moe* m, cudaStream_t st, const float* x, const float* weight) {
+int launch_rms_norm(xabe_moe* m, cudaStream_t st, const float* x, const float* weight,
+                    const float* gate_w = nullptr) {
     // block_for_width, crates/xabe-cuda/src/kernels/layer_ops.rs:1219-1221
     int block = ((int)m->g.hidden + 31) / 32 * 32;
     if (block > 1024) block = 1024;
     if (block < 32) block = 32;
-    CUDA_TRY(launch_pdl(m->pdl, k_rms_norm, dim3(m->g.max_tokens), dim3(block), 0, st, x, weight, m->normed, m->normed_h,
-                        m->valid_tokens, (int)m->g.hidden, m->eps));
+    if (gate_w && block < 256) gate_w = nullptr;  // (hidden is a multiple of 256, so this does not happen)
+    const size_t smem = gate_w ? (size_t)m->g.hidden * sizeof(float) : 0;
+    CUDA_TRY(launch_pdl(m->pdl, k_rms_norm, dim3(m->g.max_tokens), dim3(block), smem, st, x, weight, m->normed,
+                        m->normed_h, m->valid_tokens, (int)m->g.hidden, m->eps, gate_w, m->gate));
     return XABE_OK;
 }
 
@@ -804,7 +849,7 @@ int launch_route_and_dispatch(xabe_moe* m, cudaStream_t st, const float* logits)
     size_t hist_bytes = (size_t)(g.num_experts + 1) * sizeof(int);
     if ((uint64_t)g.max_tokens * g.experts_per_token <= (uint64_t)kSmallPairs) {
         // decode widths: one single-CTA launch
-        size_t smem = (size_t)(3 * kSmallPairs + 11 * g.num_experts + 2) * sizeof(int);
+        size_t smem = dispatch_small_smem((int)g.num_experts, 256);
         const float* fused_logits = logits;
         if (logits && g.max_tokens > 8) {  // more than one token per warp: route on many SMs first
             CUDA_TRY(launch_pdl(m->pdl, k_route, dim3((g.max_tokens + 7) / 8), dim3(256), 0, st, logits,
@@ -817,7 +862,7 @@ int launch_route_and_dispatch(xabe_moe* m, cudaStream_t st, const float* logits)
                             (int)g.block_size, (int)m->sorted_capacity, (int)m->block_capacity, m->topk_ids,
                             m->topk_weights, m->sorted_token_ids, m->expert_ids, m->num_tokens_post_pad,
                             m->expert_offsets, m->expert_counts, m->work_items, m->n_work));
-        if (g.max_tokens >= kPrefillMinTokens) {  // few experts, many tokens: the prefill kernels still apply
+        if (prefill_applies(m, (int)g.intermediate, (int)g.hidden, (int)g.hidden, (int)g.intermediate)) {  // few experts, many tokens
             int threads = ((int)g.num_experts + 31) / 32 * 32;
             k_build_prefill_items<<<1, threads, hist_bytes, counted(st)>>>((int)g.num_experts, m->expert_offsets,
                                                                   m->expert_counts, m->pf_items, m->pf_n_items, m->pf_item_cols);
@@ -854,6 +899,72 @@ int launch_route_and_dispatch(xabe_moe* m, cudaStream_t st, const float* logits)
                                                      m->n_work);
     }
     CUDA_TRY(cudaGetLastError());
+    return XABE_OK;
+}
+
+// Whether k_decode_front serves this handle and these pointers: decode widths (the single-block
+// dispatch holds every flat pair), rows that a bulk copy can fetch, and the streaming expert kernels
+// downstream (it builds their column groups, not the tensor-core kernels' items).
+int front_tile_tokens(const xabe_moe* m) { return m->g.max_tokens > 4 ? 8 : m->g.max_tokens > 1 ? 4 : 1; }
+bool front_applies(const xabe_moe* m, const float* x, const float* router) {
+    const auto& g = m->g;
+    if (!m->fused_front || m->scope != XABE_SCOPE_ROUTED) return false;
+    if ((uint64_t)g.max_tokens * g.experts_per_token > (uint64_t)kSmallPairs) return false;
+    if (((uintptr_t)x & 15) != 0 || ((uintptr_t)router & 15) != 0) return false;
+    if (front_smem((int)g.hidden, front_tile_tokens(m)) > 200 * 1024) return false;
+    return !prefill_applies(m, (int)g.intermediate, (int)g.hidden, (int)g.hidden, (int)g.intermediate);
+}
+
+int launch_front(xabe_moe* m, cudaStream_t st, const float* x, const xabe_moe_layer_weights* w) {
+    const auto& g = m->g;
+    FrontLaunch P{};
+    P.x = x;
+    P.norm_w = w->post_norm;
+    P.router = w->router;
+    P.bias = w->router_bias;
+    P.gate_w = w->shared_gate_inp;
+    P.valid_tokens = m->valid_tokens;
+    P.normed = m->normed;
+    P.normed_h = m->normed_h;
+    P.logits = m->logits;
+    P.gate = m->gate;
+    P.topk_ids = m->topk_ids;
+    P.topk_weights = m->topk_weights;
+    P.sorted_token_ids = m->sorted_token_ids;
+    P.expert_ids = m->expert_ids;
+    P.num_tokens_post_pad = m->num_tokens_post_pad;
+    P.expert_offsets = m->expert_offsets;
+    P.expert_counts = m->expert_counts;
+    P.work_items = m->work_items;
+    P.n_work = m->n_work;
+    P.tickets = m->front_tickets;
+    P.zero_buf = m->tail_done;
+    P.zero_count = (int)(kTailMaxTokens * (g.hidden / 128 + 1));
+    P.status = m->status;
+    P.hidden = (int)g.hidden;
+    P.num_experts = (int)g.num_experts;
+    P.top_k = (int)g.experts_per_token;
+    P.block_size = (int)g.block_size;
+    P.sorted_capacity = (int)m->sorted_capacity;
+    P.block_capacity = (int)m->block_capacity;
+    P.eps = m->eps;
+    const int tt = front_tile_tokens(m);
+    const size_t smem = front_smem((int)g.hidden, tt);
+    P.fused_dispatch = (uint64_t)g.max_tokens * g.experts_per_token <= (uint64_t)kTinyPairs ? 1 : 0;
+    const dim3 grid((g.num_experts + 3) / 4, (g.max_tokens + tt - 1) / tt);
+    auto go = [&](auto kern) -> int {
+        CUDA_TRY(allow_dynamic_smem((const void*)kern, smem));
+        CUDA_TRY(launch_pdl(m->pdl, kern, grid, dim3(kFrontThreads), smem, st, P));
+        return XABE_OK;
+    };
+    int rc = tt == 8 ? go(k_decode_front<8>) : tt == 4 ? go(k_decode_front<4>) : go(k_decode_front<1>);
+    if (rc || P.fused_dispatch) return rc;
+    // wider handles: the tables from the routing the launch above stored (256 threads, one CTA)
+    CUDA_TRY(launch_pdl(m->pdl, k_route_dispatch_small, dim3(1), dim3(256), dispatch_small_smem((int)g.num_experts, 256),
+                        st, (const float*)nullptr, (const int*)m->valid_tokens, (int)g.num_experts,
+                        (int)g.experts_per_token, (int)g.block_size, (int)m->sorted_capacity, (int)m->block_capacity,
+                        m->topk_ids, m->topk_weights, m->sorted_token_ids, m->expert_ids, m->num_tokens_post_pad,
+                        m->expert_offsets, m->expert_counts, m->work_items, m->n_work));
     return XABE_OK;
 }
 
@@ -970,6 +1081,8 @@ int xabe_moe_create(const xabe_moe_geometry* geometry, int device, int scope, fl
         A(dev_alloc(&m->chunk_hist, (size_t)m->n_chunks * E));
         A(dev_alloc(&m->expert_offsets, E + 1));
         A(dev_alloc(&m->expert_counts, E + 1));
+        A(dev_alloc(&m->front_tickets, T + 1));
+        A(dev_alloc(&m->tail_done, (size_t)kTailMaxTokens * (H / 128 + 1)));
         A(dev_alloc(&m->ep_compact, E + 1));
         A(dev_alloc(&m->ep_rank_start, kEpMaxRanks));
         A(dev_alloc(&m->ep_send_counts, kEpMaxRanks));
@@ -1004,7 +1117,7 @@ void xabe_moe_destroy(xabe_moe* m) {
     if (!m) return;
     cudaSetDevice(m->device);
     void* dev[] = {m->valid_tokens, m->status, m->topk_ids, m->topk_weights, m->sorted_token_ids, m->expert_ids,
-                   m->num_tokens_post_pad, m->chunk_hist, m->expert_offsets, m->expert_counts, m->ep_compact, m->ep_rank_start, m->ep_send_counts, m->work_items, m->n_work, m->pf_items,
+                   m->num_tokens_post_pad, m->chunk_hist, m->expert_offsets, m->expert_counts, m->front_tickets, m->tail_done, m->ep_compact, m->ep_rank_start, m->ep_send_counts, m->work_items, m->n_work, m->pf_items,
                    m->pf_n_items, m->normed, m->normed_h, m->logits,
                    m->inter_routed, m->inter_shared, m->x_sorted, m->partial, m->routed, m->shexp, m->gate, m->stage_in,
                    m->stage_ffn, m->stage_out};
@@ -1373,11 +1486,22 @@ int xabe_moe_block_forward(xabe_moe* m, void* stream, const xabe_moe_layer_weigh
     cudaStream_t st = (cudaStream_t)stream;
     if ((rc = xabe_moe_set_valid_tokens(m, stream, tokens))) return rc;
     prof_mark(m, st, 0);
-    if ((rc = launch_rms_norm(m, st, residual, w->post_norm))) return rc;
-    prof_mark(m, st, 1);
-    if ((rc = launch_router(m, st, w->router, w->router_bias))) return rc;
-    prof_mark(m, st, 2);
-    if ((rc = launch_route_and_dispatch(m, st, m->logits))) return rc;
+    const bool fused_front = front_applies(m, residual, w->router);
+    const bool fused_tail = tail_applies(m, w) && ((uintptr_t)residual & 15) == 0 && ((uintptr_t)ffn_out & 15) == 0 &&
+                            ((uintptr_t)l_out & 15) == 0;
+    if (fused_front) {
+        // one launch for norm, router, routing and dispatch: the stage profile books it under stage 0
+        if ((rc = launch_front(m, st, residual, w))) return rc;
+        prof_mark(m, st, 1);
+        prof_mark(m, st, 2);
+    } else {
+        // with the last stage folded into the down launch, the gate it needs is formed here
+        if ((rc = launch_rms_norm(m, st, residual, w->post_norm, fused_tail ? w->shared_gate_inp : nullptr))) return rc;
+        prof_mark(m, st, 1);
+        if ((rc = launch_router(m, st, w->router, w->router_bias))) return rc;
+        prof_mark(m, st, 2);
+        if ((rc = launch_route_and_dispatch(m, st, m->logits))) return rc;
+    }
     prof_mark(m, st, 3);
     MlpWeights r, s;
     r.present = s.present = true;
@@ -1387,12 +1511,20 @@ int xabe_moe_block_forward(xabe_moe* m, void* stream, const xabe_moe_layer_weigh
     s.gate = w->shared_gate;
     s.up = w->shared_up;
     s.down = w->shared_down;
-    if ((rc = run_experts(m, st, r, s, m->shexp, 4))) return rc;
-    prof_mark(m, st, 5);
-    dim3 grid(g.max_tokens, g.max_tokens >= 512 ? 1u : (g.hidden + 255) / 256);
-    CUDA_TRY(launch_pdl(m->pdl, k_gate_and_combine, grid, dim3(256), 0, st, w->shared_gate_inp, (const float*)m->normed,
-                        (const float*)m->partial, (const float*)m->shexp, residual, (const int*)m->valid_tokens,
-                        (int)g.experts_per_token, (int)g.hidden, m->gate, m->routed, ffn_out, l_out));
+    if (fused_tail) {
+        // the down launch combines: routed, ffn_out and l_out are complete when it is
+        const TailFusion tail{m->gate, residual, m->routed, ffn_out, l_out};
+        if ((rc = run_experts(m, st, r, s, m->shexp, 4, &tail))) return rc;
+        prof_mark(m, st, 5);
+    } else {
+        if ((rc = run_experts(m, st, r, s, m->shexp, 4))) return rc;
+        prof_mark(m, st, 5);
+        dim3 grid(g.max_tokens, g.max_tokens >= 512 ? 1u : (g.hidden + 255) / 256);
+        CUDA_TRY(launch_pdl(m->pdl, k_gate_and_combine, grid, dim3(256), 0, st, w->shared_gate_inp,
+                            (const float*)m->normed, (const float*)m->partial, (const float*)m->shexp, residual,
+                            (const int*)m->valid_tokens, (int)g.experts_per_token, (int)g.hidden, m->gate, m->routed,
+                            ffn_out, l_out));
+    }
     prof_mark(m, st, 6);
     if (m->prof_on && m->prof_calls < kProfCalls) m->prof_calls++;
     return XABE_OK;
@@ -1561,7 +1693,10 @@ int xabe_moe_set_tuning(xabe_moe* m, int key, int value) {
         case XABE_TUNE_ROWS_MIN_TOKENS: m->rows_min_tokens = value; return XABE_OK;
         case XABE_TUNE_ROUTER_REGW: m->router_regw = value; return XABE_OK;
         case XABE_TUNE_FORCE_TILE_KERNELS: m->force_tile_kernels = value != 0; return XABE_OK;
-        case XABE_TUNE_FUSED_DECODE: m->fused_decode = value != 0; return XABE_OK;
+        case XABE_TUNE_FUSED_DECODE:
+            m->fused_tail = (value & 1) != 0;
+            m->fused_front = (value & 2) != 0;
+            return XABE_OK;
         case XABE_TUNE_PREFILL_WIDE:
             if (value == 0) {
                 m->pf_item_cols = kPfTileN;

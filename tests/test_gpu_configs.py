@@ -162,6 +162,50 @@ def test_rows_are_bit_identical_across_the_kernel_switches(torch_cuda, oracle, l
                 assert (bits(one[name][0]) == bits(got[name][t])).all(), (name, t, width)
 
 
+# (tokens, max_tokens, launches with the last stage folded in, launches with the front fused as well)
+FUSION_WIDTHS = [(1, 1, 5, 3), (3, 4, 5, 3), (8, 8, 5, 3), (12, 15, 6, 3), (16, 16, 7, 4), (64, 64, 7, 5),
+                 (200, 256, 7, 5)]
+
+
+@pytest.mark.parametrize("tokens,max_tokens,launches_tail,launches_both", FUSION_WIDTHS)
+def test_fused_decode_launches_equal_the_unfused_ones(torch_cuda, oracle, layers, tokens, max_tokens,
+                                                      launches_tail, launches_both):
+    """Per-handle switches fold the gate-and-combine stage of handles under 16 tokens into the down
+    projection's launch, and run norm, router, routing and dispatch as ONE launch: with both, three
+    launches per layer instead of six.  Every waypoint and table must be bit-identical to the
+    one-kernel-per-stage path (the default), whichever combination runs."""
+    from llmxabe_b200 import synth
+    from llmxabe_b200.moe import MoeBlock, MoeGeometry, kernel_launch_count
+    torch = torch_cuda
+    _, _, w = layers("q6k")
+    g = MoeGeometry.qwen3_6(16, max_tokens)
+    x = synth.activations(tokens, 2048, seed=0, layer=8000 + tokens)
+    plain_blk = MoeBlock(g)
+    plain_blk.moe.set_tuning("fused_decode", 0)
+    plain = run_block(plain_blk, w, x, max_tokens)
+    plain2 = run_block(plain_blk, w, x[: max(1, tokens - 1)], max_tokens)
+    for mode, launches in ((1, launches_tail), (3, launches_both)):
+        blk = MoeBlock(g)
+        blk.moe.set_tuning("fused_decode", mode)
+        fused = run_block(blk, w, x, max_tokens)
+        assert blk.moe.device_status() == 0
+        for name in ("normed", "logits", "topk_weights", "gate", "routed", "shexp", "ffn_out", "l_out"):
+            assert (bits(fused[name]) == bits(plain[name])).all(), (mode, name)
+        for name in ("topk_ids", "sorted_token_ids", "expert_ids", "num_tokens_post_pad"):
+            assert (fused[name] == plain[name]).all(), (mode, name)
+        assert fused["untouched"]
+        # a second step on the same handle (the arrival counters must have returned to zero), fewer live rows
+        again = run_block(blk, w, x[: max(1, tokens - 1)], max_tokens)
+        assert (bits(again["l_out"]) == bits(plain2["l_out"])).all() and again["untouched"], mode
+        # launches per step, counted at the launch sites (the token count is already published)
+        res = torch.zeros(max_tokens, 2048, device="cuda")
+        out = torch.zeros(max_tokens, 2048, device="cuda")
+        n0 = kernel_launch_count()
+        blk.forward(w, res, max(1, tokens - 1), out, out.clone())
+        assert kernel_launch_count() - n0 == launches, mode
+        torch.cuda.synchronize()
+
+
 def test_exact_decode_regime_holds_rows_across_the_tensor_core_switch(torch_cuda, oracle, layers):
     """With the exact-decode switch (moe.rs:5450) a 512-token handle keeps the decode kernels, so its
     rows equal the rows run alone; without it the tensor-core kernels differ by the weight rounding only."""
