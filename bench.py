@@ -854,6 +854,9 @@ def run_ep(args, init_dist: bool = True) -> dict:
         backend = PeerMemoryEpBackend(g, epr, rank, world, layers[0][0], *layers[0][1])
     else:
         backend = CudaEpBackend(g, epr, max_rows, layers[0][0], *layers[0][1])
+    for key, value in args.tune:
+        backend.front_k.set_tuning(key, value)
+        backend.back_k.set_tuning(key, value)
     blk = EpMoeBlock(backend, E, K, rank, world)
     gen = torch.Generator(device="cuda")
     gen.manual_seed(31 + rank)

@@ -313,8 +313,10 @@ int xabe_moe_force_prefill_path(xabe_moe* m, int on);
 #define XABE_TUNE_PREFILL_WIDE 6       /* 1: k_prefill_gemm_wide (four accumulators per unpacked weight pair), 0: off */
 #define XABE_TUNE_FUSED_DECODE 7       /* bit 0: handles under 16 tokens fold gate-and-combine into the down launch;
                                           bit 1: handles up to 256 tokens run norm, router, routing and dispatch as one
-                                          launch.  3 = a three-launch layer at up to 15 tokens.  Default 0: under
-                                          CUDA-graph replay the separate launches measured as fast or faster. */
+                                          launch.  3 = a three-launch layer at up to 15 tokens; both measured no
+                                          faster than the separate launches under CUDA-graph replay, so they are off;
+                                          bit 2: handles of one or two tokens let the router normalise its input rows
+                                          itself (no RMSNorm launch).  Default 4. */
 int xabe_moe_set_tuning(xabe_moe* m, int key, int value);
 
 /* Iteration limit (x 200 ns) of this handle's waits on other ranks' flags in the peer-memory

@@ -51,6 +51,7 @@ struct FrontLaunch {
     int* status;
     int hidden, num_experts, top_k, block_size, sorted_capacity, block_capacity;
     int fused_dispatch;  // 1: at most kTinyPairs flat pairs, the tables are built here; 0: by the launch that follows
+    int route;           // 0: the launch ends with the logits (norm fused into the router, nothing else)
     float eps;
 };
 
@@ -360,6 +361,10 @@ __global__ void __launch_bounds__(kFrontThreads) k_decode_front(FrontLaunch P) {
         }
     };
 
+    if (!P.route) {  // norm + router only: the routing is the next launch's
+        gate_of_this_cta();
+        return;
+    }
     // ---- ticket 1: the last CTA of the tile routes the tile's tokens
     __syncthreads();
     if (tid == 0) {

@@ -184,6 +184,7 @@ struct xabe_moe {
     // less than the fences, arrival counts and one-CTA phases that replace it.
     bool fused_tail = false;          // handles under 16 tokens: gate-and-combine folded into the down launch
     bool fused_front = false;         // handles up to 256 tokens: norm .. dispatch in one launch (k_decode_front)
+    bool fused_norm = true;           // handles up to 8 tokens: the router normalises its input rows itself
     float* normed = nullptr;
     __half* normed_h = nullptr;
     int* tail_done = nullptr;      // [kTailMaxTokens][hidden / 128] arrivals of the fused combine, zero between launches
@@ -906,16 +907,25 @@ int launch_route_and_dispatch(xabe_moe* m, cudaStream_t st, const float* logits)
 // dispatch holds every flat pair), rows that a bulk copy can fetch, and the streaming expert kernels
 // downstream (it builds their column groups, not the tensor-core kernels' items).
 int front_tile_tokens(const xabe_moe* m) { return m->g.max_tokens > 4 ? 8 : m->g.max_tokens > 1 ? 4 : 1; }
-bool front_applies(const xabe_moe* m, const float* x, const float* router) {
+// Handles of one or two tokens: the router's CTAs normalise the rows themselves (the consumer-side
+// fold of the norm; crates/xabe-engine/src/forward.rs:3534-3585 is the seam), which removes the
+// RMSNorm launch.  Wider handles keep k_rms_norm: every CTA repeats its tile's normalisation row by
+// row, and measured under graph replay that already costs what the launch saves at three tokens
+// (1 token 33.7 -> 32.8 us per layer, 3 tokens 49.5 -> 50.3).
+constexpr uint32_t kNormInRouterMaxTokens = 2;
+
+bool front_applies(const xabe_moe* m, const float* x, const float* router, bool* with_routing) {
     const auto& g = m->g;
-    if (!m->fused_front || m->scope != XABE_SCOPE_ROUTED) return false;
+    *with_routing = m->fused_front;
+    if (m->scope != XABE_SCOPE_ROUTED) return false;
+    if (!m->fused_front && !(m->fused_norm && g.max_tokens <= kNormInRouterMaxTokens)) return false;
     if ((uint64_t)g.max_tokens * g.experts_per_token > (uint64_t)kSmallPairs) return false;
     if (((uintptr_t)x & 15) != 0 || ((uintptr_t)router & 15) != 0) return false;
     if (front_smem((int)g.hidden, front_tile_tokens(m)) > 200 * 1024) return false;
     return !prefill_applies(m, (int)g.intermediate, (int)g.hidden, (int)g.hidden, (int)g.intermediate);
 }
 
-int launch_front(xabe_moe* m, cudaStream_t st, const float* x, const xabe_moe_layer_weights* w) {
+int launch_front(xabe_moe* m, cudaStream_t st, const float* x, const xabe_moe_layer_weights* w, bool with_routing) {
     const auto& g = m->g;
     FrontLaunch P{};
     P.x = x;
@@ -951,6 +961,7 @@ int launch_front(xabe_moe* m, cudaStream_t st, const float* x, const xabe_moe_la
     const int tt = front_tile_tokens(m);
     const size_t smem = front_smem((int)g.hidden, tt);
     P.fused_dispatch = (uint64_t)g.max_tokens * g.experts_per_token <= (uint64_t)kTinyPairs ? 1 : 0;
+    P.route = with_routing ? 1 : 0;
     const dim3 grid((g.num_experts + 3) / 4, (g.max_tokens + tt - 1) / tt);
     auto go = [&](auto kern) -> int {
         CUDA_TRY(allow_dynamic_smem((const void*)kern, smem));
@@ -958,7 +969,9 @@ int launch_front(xabe_moe* m, cudaStream_t st, const float* x, const xabe_moe_la
         return XABE_OK;
     };
     int rc = tt == 8 ? go(k_decode_front<8>) : tt == 4 ? go(k_decode_front<4>) : go(k_decode_front<1>);
-    if (rc || P.fused_dispatch) return rc;
+    if (rc) return rc;
+    if (!with_routing) return launch_route_and_dispatch(m, st, m->logits);
+    if (P.fused_dispatch) return rc;
     // wider handles: the tables from the routing the launch above stored (256 threads, one CTA)
     CUDA_TRY(launch_pdl(m->pdl, k_route_dispatch_small, dim3(1), dim3(256), dispatch_small_smem((int)g.num_experts, 256),
                         st, (const float*)nullptr, (const int*)m->valid_tokens, (int)g.num_experts,
@@ -1486,12 +1499,13 @@ int xabe_moe_block_forward(xabe_moe* m, void* stream, const xabe_moe_layer_weigh
     cudaStream_t st = (cudaStream_t)stream;
     if ((rc = xabe_moe_set_valid_tokens(m, stream, tokens))) return rc;
     prof_mark(m, st, 0);
-    const bool fused_front = front_applies(m, residual, w->router);
+    bool front_routes = false;
+    const bool fused_front = front_applies(m, residual, w->router, &front_routes);
     const bool fused_tail = tail_applies(m, w) && ((uintptr_t)residual & 15) == 0 && ((uintptr_t)ffn_out & 15) == 0 &&
                             ((uintptr_t)l_out & 15) == 0;
     if (fused_front) {
         // one launch for norm, router, routing and dispatch: the stage profile books it under stage 0
-        if ((rc = launch_front(m, st, residual, w))) return rc;
+        if ((rc = launch_front(m, st, residual, w, front_routes))) return rc;
         prof_mark(m, st, 1);
         prof_mark(m, st, 2);
     } else {
@@ -1696,6 +1710,7 @@ int xabe_moe_set_tuning(xabe_moe* m, int key, int value) {
         case XABE_TUNE_FUSED_DECODE:
             m->fused_tail = (value & 1) != 0;
             m->fused_front = (value & 2) != 0;
+            m->fused_norm = (value & 4) != 0;
             return XABE_OK;
         case XABE_TUNE_PREFILL_WIDE:
             if (value == 0) {

@@ -162,18 +162,20 @@ def test_rows_are_bit_identical_across_the_kernel_switches(torch_cuda, oracle, l
                 assert (bits(one[name][0]) == bits(got[name][t])).all(), (name, t, width)
 
 
-# (tokens, max_tokens, launches with the last stage folded in, launches with the front fused as well)
-FUSION_WIDTHS = [(1, 1, 5, 3), (3, 4, 5, 3), (8, 8, 5, 3), (12, 15, 6, 3), (16, 16, 7, 4), (64, 64, 7, 5),
-                 (200, 256, 7, 5)]
+# (tokens, max_tokens, launches per layer: default [the router normalises its rows at one or two tokens],
+#  last stage folded into the down launch, front fused as well)
+FUSION_WIDTHS = [(1, 1, 5, 5, 3), (2, 2, 5, 5, 3), (3, 4, 6, 5, 3), (8, 8, 6, 5, 3), (12, 15, 7, 6, 3), (16, 16, 7, 7, 4),
+                 (64, 64, 7, 7, 5), (200, 256, 7, 7, 5)]
 
 
-@pytest.mark.parametrize("tokens,max_tokens,launches_tail,launches_both", FUSION_WIDTHS)
+@pytest.mark.parametrize("tokens,max_tokens,launches_default,launches_tail,launches_both", FUSION_WIDTHS)
 def test_fused_decode_launches_equal_the_unfused_ones(torch_cuda, oracle, layers, tokens, max_tokens,
-                                                      launches_tail, launches_both):
-    """Per-handle switches fold the gate-and-combine stage of handles under 16 tokens into the down
-    projection's launch, and run norm, router, routing and dispatch as ONE launch: with both, three
-    launches per layer instead of six.  Every waypoint and table must be bit-identical to the
-    one-kernel-per-stage path (the default), whichever combination runs."""
+                                                      launches_default, launches_tail, launches_both):
+    """By default the router of a handle of one or two tokens normalises its input rows itself (no RMSNorm
+    launch: five launches per layer instead of six).  Per-handle switches also fold the gate-and-combine
+    stage of handles under 16 tokens into the down projection's launch, and run norm, router, routing
+    and dispatch as ONE launch: with both, three launches per layer.  Every waypoint and table must be
+    bit-identical to the one-kernel-per-stage path, whichever combination runs."""
     from llmxabe_b200 import synth
     from llmxabe_b200.moe import MoeBlock, MoeGeometry, kernel_launch_count
     torch = torch_cuda
@@ -184,7 +186,7 @@ def test_fused_decode_launches_equal_the_unfused_ones(torch_cuda, oracle, layers
     plain_blk.moe.set_tuning("fused_decode", 0)
     plain = run_block(plain_blk, w, x, max_tokens)
     plain2 = run_block(plain_blk, w, x[: max(1, tokens - 1)], max_tokens)
-    for mode, launches in ((1, launches_tail), (3, launches_both)):
+    for mode, launches in ((4, launches_default), (1, launches_tail), (3, launches_both)):
         blk = MoeBlock(g)
         blk.moe.set_tuning("fused_decode", mode)
         fused = run_block(blk, w, x, max_tokens)
