@@ -317,6 +317,8 @@ int xabe_moe_force_prefill_path(xabe_moe* m, int on);
                                           faster than the separate launches under CUDA-graph replay, so they are off;
                                           bit 2: handles of one or two tokens let the router normalise its input rows
                                           itself (no RMSNorm launch).  Default 4. */
+#define XABE_TUNE_DENSE_ROWS 8         /* 0: the dense block of up to 64 tokens through the tcgen05 kernels instead of
+                                          k_dense_rows (default 1) */
 int xabe_moe_set_tuning(xabe_moe* m, int key, int value);
 
 /* Iteration limit (x 200 ns) of this handle's waits on other ranks' flags in the peer-memory

@@ -21,6 +21,7 @@
 #include "head_kernels.cuh"
 #include "ep_kernels.cuh"
 #include "prefill_wide_kernels.cuh"
+#include "dense_rows_kernels.cuh"
 
 using namespace xabe;
 
@@ -187,6 +188,9 @@ struct xabe_moe {
     bool fused_norm = true;           // handles up to 8 tokens: the router normalises its input rows itself
     float* normed = nullptr;
     __half* normed_h = nullptr;
+    float* dense_partial = nullptr;  // [dense_k_splits][max_tokens][hidden]: k_dense_rows<DOWN>'s shares of the contraction
+    int dense_k_splits = 1;
+    bool dense_rows = true;          // decode-width dense block through k_dense_rows (XABE_TUNE_DENSE_ROWS)
     int* tail_done = nullptr;      // [kTailMaxTokens][hidden / 128] arrivals of the fused combine, zero between launches
     int* front_tickets = nullptr;  // [1 + max_tokens] arrival counters of k_decode_front, zero between launches
     int* ep_compact = nullptr;  // [num_experts + 1] live pairs before each expert (expert parallelism)
@@ -476,6 +480,28 @@ int launch_prefill(cudaStream_t st, const PrefillLaunch& L, dim3 grid, size_t sm
                                  : launch_prefill_t<MODE, QUANT_Q8_0, QUANT_Q8_0>(st, L, grid, smem, wide);
 }
 
+// ---- decode-width dense block (k_dense_rows) -------------------------------------------
+template <int MODE, int QUANT>
+int launch_dense_rows_q(xabe_moe* m, cudaStream_t st, const DenseRowsLaunch& P, int ng, uint32_t smem) {
+    auto go = [&](auto kern) -> int {
+        CUDA_TRY(allow_dynamic_smem((const void*)kern, smem));
+        kern<<<dim3(m->sm_count), dim3(kDrThreads), smem, counted(st)>>>(P);
+        CUDA_TRY(cudaGetLastError());
+        return XABE_OK;
+    };
+    switch (ng) {
+        case 1: return go(k_dense_rows<MODE, QUANT, 1>);
+        case 2: return go(k_dense_rows<MODE, QUANT, 2>);
+        case 4: return go(k_dense_rows<MODE, QUANT, 4>);
+        default: return go(k_dense_rows<MODE, QUANT, 8>);
+    }
+}
+template <int MODE>
+int launch_dense_rows(xabe_moe* m, cudaStream_t st, const DenseRowsLaunch& P, int quant, int ng, uint32_t smem) {
+    return quant == XABE_QUANT_Q6_K ? launch_dense_rows_q<MODE, QUANT_Q6K>(m, st, P, ng, smem)
+                                    : launch_dense_rows_q<MODE, QUANT_Q8_0>(m, st, P, ng, smem);
+}
+
 struct MlpWeights {
     bool present = false;
     xabe_quant_tensor gate{}, up{}, down{};
@@ -554,6 +580,63 @@ int run_experts(xabe_moe* m, cudaStream_t st, const MlpWeights& routed, const Ml
     L.x_shared = m->normed_h;
     L.inter_routed = m->inter_routed;
     L.inter_shared = m->inter_shared;
+    // One expert, decode width, contraction too long for the streaming kernels to hold a token's row
+    // (the dense 27B block): k_dense_rows streams slices of the contraction.
+    if (!routed.present && shared.present && m->dense_rows && !m->force_tile_kernels && !m->force_prefill &&
+        g.max_tokens <= (uint32_t)kDrMaxTokens && g.intermediate % 128 == 0 && g.hidden % 256 == 0 &&
+        !(stream_shape(MODE_GATEUP, (int)g.intermediate, (int)g.hidden, qs, qs).ok &&
+          stream_shape(MODE_DOWN, (int)g.hidden, (int)g.intermediate, shared.down.quant, shared.down.quant).ok)) {
+        const int qd = shared.down.quant;
+        const size_t rb_gu = (size_t)(g.hidden / 256) * span_bytes_of(qs), rb_dn = (size_t)(g.intermediate / 256) * span_bytes_of(qd);
+        const bool ok = rb_gu % 4 == 0 && rb_dn % 4 == 0 && shared.gate.n_bytes % 16 == 0 && shared.up.n_bytes % 16 == 0 &&
+                        shared.down.n_bytes % 16 == 0 && (m->dense_k_splits == 1 || m->dense_partial);
+        if (ok) {
+            int ng = 1;
+            while (ng * 8 < (int)g.max_tokens) ng *= 2;
+            DenseRowsLaunch P{};
+            P.valid_tokens = m->valid_tokens;
+            P.status = m->status;
+            P.max_tokens = (int)g.max_tokens;
+            P.x_rows = 8 * ng;
+            auto shape = [&](int quant) {
+                P.raw_pitch = dense_rows_pitch(quant == XABE_QUANT_Q6_K ? QUANT_Q6K : QUANT_Q8_0);
+                P.n_stages = 2;
+                for (int S = kDrMaxStages; S >= 2; --S)
+                    if (dense_rows_smem(S, P.raw_pitch, P.x_rows) <= 200u * 1024u) {
+                        P.n_stages = S;
+                        break;
+                    }
+                return dense_rows_smem(P.n_stages, P.raw_pitch, P.x_rows);
+            };
+            P.w_a = (const uint8_t*)shared.gate.dev_bytes;
+            P.w_b = (const uint8_t*)shared.up.dev_bytes;
+            P.rows = (int)g.intermediate;
+            P.k = (int)g.hidden;
+            P.x = m->normed_h;
+            P.inter = m->inter_shared;
+            P.k_splits = 1;
+            uint32_t smem = shape(qs);
+            int rc = launch_dense_rows<MODE_GATEUP>(m, st, P, qs, ng, smem);
+            if (rc) return rc;
+            if (mark_between >= 0) prof_mark(m, st, mark_between);
+            P.w_a = (const uint8_t*)shared.down.dev_bytes;
+            P.w_b = nullptr;
+            P.rows = (int)g.hidden;
+            P.k = (int)g.intermediate;
+            P.x = m->inter_shared;
+            P.inter = nullptr;
+            P.k_splits = m->dense_k_splits;
+            P.out = P.k_splits > 1 ? m->dense_partial : shexp_out;
+            smem = shape(qd);
+            if ((rc = launch_dense_rows<MODE_DOWN>(m, st, P, qd, ng, smem))) return rc;
+            if (P.k_splits > 1) {
+                k_sum_k_splits<<<dim3(g.max_tokens, (g.hidden + 255) / 256), 256, 0, counted(st)>>>(
+                    m->dense_partial, P.k_splits, (int)g.max_tokens, (int)g.hidden, m->valid_tokens, shexp_out);
+                CUDA_TRY(cudaGetLastError());
+            }
+            return XABE_OK;
+        }
+    }
     if (prefill_applies(m, (int)g.intermediate, (int)g.hidden, (int)g.hidden, (int)g.intermediate)) {
         PrefillLaunch P{};
         P.top_k = L.top_k;
@@ -1111,6 +1194,16 @@ int xabe_moe_create(const xabe_moe_geometry* geometry, int device, int scope, fl
         A(dev_alloc(&m->routed, T * H));
         A(dev_alloc(&m->gate, T));
     }
+    if (g.max_tokens <= (uint32_t)kDrMaxTokens && H % 256 == 0) {
+        // k_dense_rows<DOWN>: about as many units as SMs, by splitting the contraction as well
+        const int row_blocks = (int)(H / 256), n_spans = (int)(I / 256);
+        int ks = row_blocks > 0 ? m->sm_count / row_blocks : 1;
+        if (ks < 1) ks = 1;
+        if (ks > n_spans) ks = n_spans;
+        if (ks > 16) ks = 16;
+        m->dense_k_splits = ks;
+        if (ks > 1) A(dev_alloc(&m->dense_partial, (size_t)ks * T * H));
+    }
     if (e != cudaSuccess) {
         xabe_moe_destroy(m);
         return fail(XABE_ERR_DRIVER, "CUDA driver error: %s (allocating MoE buffers)", cudaGetErrorString(e));
@@ -1132,7 +1225,7 @@ void xabe_moe_destroy(xabe_moe* m) {
     void* dev[] = {m->valid_tokens, m->status, m->topk_ids, m->topk_weights, m->sorted_token_ids, m->expert_ids,
                    m->num_tokens_post_pad, m->chunk_hist, m->expert_offsets, m->expert_counts, m->front_tickets, m->tail_done, m->ep_compact, m->ep_rank_start, m->ep_send_counts, m->work_items, m->n_work, m->pf_items,
                    m->pf_n_items, m->normed, m->normed_h, m->logits,
-                   m->inter_routed, m->inter_shared, m->x_sorted, m->partial, m->routed, m->shexp, m->gate, m->stage_in,
+                   m->inter_routed, m->inter_shared, m->x_sorted, m->dense_partial, m->partial, m->routed, m->shexp, m->gate, m->stage_in,
                    m->stage_ffn, m->stage_out};
     for (void* p : dev)
         if (p) cudaFree(p);
@@ -1707,6 +1800,7 @@ int xabe_moe_set_tuning(xabe_moe* m, int key, int value) {
         case XABE_TUNE_ROWS_MIN_TOKENS: m->rows_min_tokens = value; return XABE_OK;
         case XABE_TUNE_ROUTER_REGW: m->router_regw = value; return XABE_OK;
         case XABE_TUNE_FORCE_TILE_KERNELS: m->force_tile_kernels = value != 0; return XABE_OK;
+        case XABE_TUNE_DENSE_ROWS: m->dense_rows = value != 0; return XABE_OK;
         case XABE_TUNE_FUSED_DECODE:
             m->fused_tail = (value & 1) != 0;
             m->fused_front = (value & 2) != 0;

@@ -245,7 +245,7 @@ class MoeKernels:
         _check(_lib.lib().xabe_moe_force_prefill_path(self._h, int(on)))
 
     TUNE = {"pdl": 0, "stream_stages": 1, "stream_runs": 2, "rows_min_tokens": 3, "router_regw": 4,
-            "force_tile_kernels": 5, "prefill_wide": 6, "fused_decode": 7}
+            "force_tile_kernels": 5, "prefill_wide": 6, "fused_decode": 7, "dense_rows": 8}
 
     def set_tuning(self, key: str, value: int) -> None:
         """Per-handle launch-shape switches (XABE_TUNE_* of include/xabe_moe.h); results do not change."""

@@ -325,6 +325,34 @@ def test_dense_27b_block_at_decode_widths(torch_cuda, oracle, dense_27b, tokens,
         assert r.non_finite_count == 0 and r.rel_l2 <= REL_L2, f"{name}: {r}"
 
 
+def test_dense_27b_rows_are_batch_invariant_and_agree_with_the_tensor_core_path(torch_cuda, oracle, dense_27b):
+    """Decode widths of the dense block run k_dense_rows (slices of the contraction streamed with the
+    activations, one accumulator tile per eight tokens).  A token's row must not depend on its batch:
+    the 64-token handle's rows equal the rows run alone bit for bit; and the tcgen05 kernels, which the
+    per-handle switch brings back, agree to the weight rounding."""
+    torch = torch_cuda
+    from llmxabe_b200 import synth
+    from llmxabe_b200.moe import DenseFfnBlock, MoeGeometry
+    hidden, inter, post_norm, _, dev = dense_27b
+    x = synth.activations(64, hidden, seed=78, layer=64)
+    ffn64, lo64 = _dense_forward(torch, dense_27b, x, 64)
+    for tk in (0, 7, 8, 33, 63):
+        ffn1, lo1 = _dense_forward(torch, dense_27b, x[tk:tk + 1], 1)
+        assert (bits(ffn1[0]) == bits(ffn64[tk])).all() and (bits(lo1[0]) == bits(lo64[tk])).all(), tk
+    ffn20, _ = _dense_forward(torch, dense_27b, x[:20], 24)
+    assert (bits(ffn20) == bits(ffn64[:20])).all()
+    blk = DenseFfnBlock(MoeGeometry(1, 1, hidden, inter, 64, 64))
+    blk.moe.set_tuning("dense_rows", 0)
+    res = torch.from_numpy(x).cuda()
+    ffn = torch.zeros(64, hidden, device="cuda")
+    lo = torch.zeros(64, hidden, device="cuda")
+    blk.forward(torch.from_numpy(post_norm).cuda(), dev[0], dev[1], dev[2], res, 64, ffn, lo)
+    torch.cuda.synchronize()
+    r = oracle.compare(ffn.cpu().numpy(), ffn64)
+    print(f"dense 27B, 64 tokens, tensor-core kernels vs k_dense_rows: {r}")
+    assert r.rel_l2 <= REL_L2
+
+
 def test_dense_27b_block_at_4096_tokens_by_sampled_rows(torch_cuda, oracle, dense_27b):
     """The prefill width of the dense block: all 4096 rows computed on the device, 48 seeded rows
     compared with the oracle (a row depends on its own input only)."""
