@@ -857,7 +857,7 @@ def run_ep(args, init_dist: bool = True) -> dict:
     for key, value in args.tune:
         backend.front_k.set_tuning(key, value)
         backend.back_k.set_tuning(key, value)
-    blk = EpMoeBlock(backend, E, K, rank, world)
+    blk = EpMoeBlock(backend, E, K, rank, world, overlap_shared=args.ep_overlap)
     gen = torch.Generator(device="cuda")
     gen.manual_seed(31 + rank)
     x0 = torch.randn(per, H, device="cuda", generator=gen)
@@ -1070,6 +1070,8 @@ def main():
     ap.add_argument("--ep-layers", type=int, default=40)
     ap.add_argument("--ep-nccl", dest="ep_peer_memory", action="store_false",
                     help="exchange rows and results with NCCL all-to-alls instead of peer stores over NVLink")
+    ap.add_argument("--ep-no-overlap", dest="ep_overlap", action="store_false",
+                    help="run the shared expert on the main stream instead of beside the exchange")
     ap.add_argument("--no-graph", dest="graph", action="store_false", help="time eager launches instead of CUDA-graph replay")
     ap.add_argument("--tune", default=[], type=lambda s: [(kv.split("=")[0], int(kv.split("=")[1])) for kv in s.split(",") if kv],
                     help="per-handle launch-shape switches of the single-layer MoE workloads, e.g. fused_decode=0,pdl=1")

@@ -76,7 +76,8 @@ def all_to_all_rows(send: torch.Tensor, send_counts: list[int], recv_counts: lis
 class EpMoeBlock:
     """`MoeBlock` with the routed experts sharded over `world` ranks."""
 
-    def __init__(self, backend, num_experts: int, experts_per_token: int, rank: int, world: int, group=None):
+    def __init__(self, backend, num_experts: int, experts_per_token: int, rank: int, world: int, group=None,
+                 overlap_shared: bool = True):
         if num_experts % world != 0:
             raise ValueError(f"{num_experts} experts do not split over {world} ranks")
         self.backend = backend
@@ -85,6 +86,13 @@ class EpMoeBlock:
         self.experts_per_rank = num_experts // world
         self.last_plan: EpPlan | None = None
         self._events = None
+        # The shared expert needs only this rank's own tokens and its result is read by the last kernel of
+        # the layer, so it runs on a stream of its own beside the exchange (CUDA backends only).
+        self._side = None
+        self._ev_fork = self._ev_join = None
+        if overlap_shared and torch.cuda.is_available() and getattr(backend, "supports_streams", False):
+            self._side = torch.cuda.Stream()
+            self._ev_fork, self._ev_join = torch.cuda.Event(), torch.cuda.Event()
 
     def forward(self, residual: torch.Tensor, tokens: int, ffn_out: torch.Tensor, l_out: torch.Tensor) -> None:
         b = self.backend
@@ -95,17 +103,22 @@ class EpMoeBlock:
         if getattr(b, "peer_memory", False):
             # rows, counts and completion flags travel by peer stores over NVLink: no library
             # collective, no host read-back; the three calls below only enqueue kernels
+            self._shared_fork()
             b.p2p_send()
-            b.shared()
+            if self._side is None:
+                b.shared()
             mark("plan_pack")
             b.p2p_experts()
             mark("experts")
+            self._shared_join()
             b.p2p_finish(residual, tokens, ffn_out, l_out)
             mark("finish")
             return
         # rows grouped by owner rank (by expert inside a rank), and how many go to each rank
         send_rows, send_eid, inverse, send_counts = b.plan_pack(self.experts_per_rank, self.world)
-        b.shared()   # needs only this rank's tokens: keeps the GPU busy while the host reads the counts back
+        self._shared_fork()
+        if self._side is None:
+            b.shared()   # needs only this rank's tokens: keeps the GPU busy while the host reads the counts back
         plan = exchange_counts(send_counts, tokens * self.k, self.world, self.group)
         self.last_plan = plan
         mark("plan_pack")
@@ -117,8 +130,23 @@ class EpMoeBlock:
         mark("experts")
         back = all_to_all_rows(out, plan.recv_counts, plan.send_counts, self.world, self.group)
         mark("combine_exchange")
+        self._shared_join()
         b.finish(back, inverse, residual, tokens, ffn_out, l_out)  # weight, sum ascending k, shared expert, residual
         mark("finish")
+
+    def _shared_fork(self) -> None:
+        """Starts the shared expert on the side stream, after everything enqueued so far (the front)."""
+        if self._side is None:
+            return
+        main = torch.cuda.current_stream()
+        self._ev_fork.record(main)
+        self._side.wait_event(self._ev_fork)
+        self.backend.shared(stream=self._side)
+        self._ev_join.record(self._side)
+
+    def _shared_join(self) -> None:
+        if self._side is not None:
+            torch.cuda.current_stream().wait_event(self._ev_join)
 
     # -- optional per-phase device timing (CUDA events on the current stream), for the benchmark
     def enable_phase_timing(self) -> None:
@@ -204,8 +232,10 @@ class CudaEpBackend:
         k.grouped_forward_partial_f16(self.local[0], self.local[1], self.local[2], rows)
         return self.bb.partial[:R]
 
-    def shared(self):
-        self.front_k.shared_expert(self.w.shared_gate, self.w.shared_up, self.w.shared_down)
+    supports_streams = True
+
+    def shared(self, stream=None):
+        self.front_k.shared_expert(self.w.shared_gate, self.w.shared_up, self.w.shared_down, stream=stream)
 
     def finish(self, back, inverse, residual, tokens, ffn_out, l_out):
         k = self.front_k
