@@ -130,7 +130,7 @@ def real_device_layer(torch_cuda, real_layer):
 
 @pytest.mark.parametrize("max_tokens,tokens,block_size", [(1, 1, 16), (3, 3, 16), (64, 64, 16), (64, 37, 32)])
 def test_real_geometry_block(torch_cuda, oracle, real_layer, real_device_layer, max_tokens, tokens, block_size):
-    """BASELINE configs 0 and 1: 256 experts, top-8, hidden 2048, intermediate 512, Q6_K, seed 0."""
+    """The one-token and the 3- / 64-token decode shapes: 256 experts, top-8, hidden 2048, intermediate 512, Q6_K, seed 0."""
     from llmxabe_b200 import synth
     from llmxabe_b200.moe import MoeBlock, MoeGeometry
     L, ol = real_layer
@@ -147,7 +147,7 @@ def test_real_geometry_block(torch_cuda, oracle, real_layer, real_device_layer, 
 
 
 def test_batched_rows_are_bit_identical_to_rows_run_alone(torch_cuda, oracle, real_layer, real_device_layer):
-    """The serving contract: a sequence's output does not depend on its batch (config 1)."""
+    """The serving contract: a sequence's output does not depend on its batch (1, 3 and 64 concurrent sequences)."""
     from llmxabe_b200 import synth
     from llmxabe_b200.moe import MoeBlock, MoeGeometry
     x = synth.activations(64, 2048, seed=0, layer=164)

@@ -56,7 +56,7 @@ def test_small_geometry_prefill(torch_cuda, oracle, routed_quant, shared_quant, 
 
 
 def test_real_geometry_prefill_512(torch_cuda, oracle):
-    """256 experts / top-8 / 2048 / 512, Q6_K, 512 bf16-rounded tokens, Zipf routing (BASELINE config 2 shape)."""
+    """256 experts / top-8 / 2048 / 512, Q6_K, 512 bf16-rounded tokens, Zipf routing (the prefill shape at a quarter of its width)."""
     from llmxabe_b200 import synth
     from llmxabe_b200.moe import MoeBlock, MoeGeometry
     L = synth.moe_layer(seed=0, layer=0, zipf=True)
