@@ -403,8 +403,18 @@ struct PfCtl {
     uint64_t raw_empty[kPfMaxRaw];      // unpack warps -> loader
     uint64_t acc_full[kPfAccums];       // MMA (tcgen05.commit) -> epilogue
     uint64_t acc_empty[kPfAccums];      // epilogue -> MMA
+    uint64_t tab_full[2];               // the four epilogue warps -> one another (MODE_DOWN's column table)
     uint32_t tmem_base;
     int abort_flag;
+};
+
+// MODE_DOWN: what the epilogue needs to know about a token column of its tile, fetched once per tile
+// by the lane that owns the column and read back by every lane as ONE 16-byte broadcast load.
+struct __align__(16) PfColumn {
+    float* dst;     // the column's result row (routed: row `flat` of the partial buffer or the caller's pointer;
+                    // shared: the token's row of the shared expert's output); nullptr: nothing to store
+    float factor;   // routing weight / kPfWeightScale (shared expert: 1 / kPfWeightScale)
+    uint32_t live;  // 0: skip the column
 };
 
 // MODE_GATEUP (0): TMEM lane m = 32q + i holds gate row r0 + 16q + i for i < 16 and up row
@@ -415,6 +425,7 @@ template <int MODE, int QR, int QS>
 __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) PfCtl ctl;
+    __shared__ PfColumn col_tab[MODE == MODE_DOWN ? 2 : 1][MODE == MODE_DOWN ? kPfTileN : 1];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int valid = *L.valid_tokens;
@@ -442,6 +453,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L)
             mbar_init(&ctl.acc_full[i], 1);
             mbar_init(&ctl.acc_empty[i], 4);
         }
+        for (int i = 0; i < 2; ++i) mbar_init(&ctl.tab_full[i], 4);
         fence_mbar_init();
     }
     if (warp == kPfWarpMma) {
@@ -667,24 +679,37 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L)
         for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++n) {
             const PfTile T = pf_tile(L, t, n_routed, valid);
             const uint32_t acc = n % kPfAccums;
-            // Down, routed: lane c fetches the flat (token, k) id, the routing weight and the result row of
-            // columns c, c + 32, c + 64, c + 96 now -- three dependent loads each -- so that they are
-            // in flight while the accumulator is still being computed, not after it is ready.
-            float col_wgt[4] = {0.f, 0.f, 0.f, 0.f};
-            float* col_row[4] = {nullptr, nullptr, nullptr, nullptr};
-            if (MODE == MODE_DOWN && !T.shared) {
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const int mycol = q * 32 + lane;
-                    if (mycol < T.ncols) {
+            // Down: lane c of epilogue warp q describes column 32 q + c of the tile in the table (routed:
+            // three dependent loads -- flat (token, k) id, routing weight, result row) before it waits for
+            // the accumulator, so the loads are in flight while the tile is still being computed.  The
+            // table alternates between two copies by tile: a warp can be at most one tile ahead of the
+            // slowest, because it has to wait for that warp's entries of the tile in between.
+            const PfColumn* tab = col_tab[MODE == MODE_DOWN ? (n & 1) : 0];
+            if (MODE == MODE_DOWN) {
+                const int mycol = quad * 32 + lane;
+                PfColumn e{nullptr, 0.f, 0u};
+                if (mycol < T.ncols) {
+                    if (T.shared) {
+                        e.dst = L.shexp + (size_t)(T.first + mycol) * L.rows;
+                        e.factor = inv;
+                    } else {
                         const int flat = __ldg(L.sorted_token_ids + T.first + mycol);
-                        col_wgt[q] = __ldg(L.topk_weights + flat);
-                        col_row[q] = result_row(L.partial, L.partial_rows, flat, L.rows);
+                        // the weight scale is a power of two: folded into the routing weight exactly
+                        e.factor = __ldg(L.topk_weights + flat) * inv;
+                        e.dst = result_row(L.partial, L.partial_rows, flat, L.rows);
                     }
+                    e.live = e.dst != nullptr;
                 }
+                col_tab[n & 1][mycol] = e;
+                __syncwarp();
+                if (lane == 0) mbar_arrive_pf(&ctl.tab_full[n & 1]);
             }
             ok = stream_wait_pf<true>(&ctl.acc_full[acc], (n / kPfAccums) & 1, abortp, L.status);
             if (!ok) break;
+            if (MODE == MODE_DOWN) {
+                ok = stream_wait_pf(&ctl.tab_full[n & 1], (n >> 1) & 1, abortp, L.status);
+                if (!ok) break;
+            }
             tc_fence_after();
             const uint32_t taddr = tmem_base + acc * kPfTileN + ((uint32_t)(quad * 32) << 16);
             for (int cb = 0; cb * 32 < T.ncols; ++cb) {
@@ -699,36 +724,28 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L)
                 if (MODE == MODE_GATEUP) {
                     const int out_row = T.bx * 64 + quad * 16 + (lane & 15);
                     __half* dst_base = T.shared ? L.inter_shared : L.inter_routed;
+                    // Lanes 0-15 hold the gate rows and finish column jj, lanes 16-31 hold the same rows of up
+                    // and finish column jj + 16: each sends the value its partner needs, so all 32 lanes
+                    // are in the exponential and the division of every pass.
+                    const bool lower = lane < 16;
 #pragma unroll
-                    for (int jj = 0; jj < 32; ++jj) {
-                        float mine = __uint_as_float(r[jj]) * inv;
-                        float other = __shfl_xor_sync(0xffffffffu, mine, 16);
-                        bool do_it = (lane < 16) == (jj < 16);  // lanes 0-15 finish columns 0-15, lanes 16-31 the rest
-                        int col = cb * 32 + jj;
-                        if (do_it && col < T.ncols) {
-                            float gv = lane < 16 ? mine : other;
-                            float uv = lane < 16 ? other : mine;
+                    for (int jj = 0; jj < 16; ++jj) {
+                        const float lo = __uint_as_float(r[jj]) * inv, hi = __uint_as_float(r[jj + 16]) * inv;
+                        const float recv = __shfl_xor_sync(0xffffffffu, lower ? hi : lo, 16);
+                        const float gv = lower ? lo : recv;
+                        const float uv = lower ? recv : hi;
+                        const int col = cb * 32 + jj + (lower ? 0 : 16);
+                        if (col < T.ncols) {
                             float v = __fdiv_rn(gv, 1.0f + expf(-gv)) * uv;
                             dst_base[(size_t)(T.first + col) * L.rows + out_row] = __float2half_rn(v);
                         }
                     }
                 } else {
                     const int out_row = T.bx * kPfTileM + quad * 32 + lane;
-                    float my_wgt = col_wgt[0];
-                    float* my_row = col_row[0];
-                    if (cb == 1) { my_wgt = col_wgt[1]; my_row = col_row[1]; }
-                    if (cb == 2) { my_wgt = col_wgt[2]; my_row = col_row[2]; }
-                    if (cb == 3) { my_wgt = col_wgt[3]; my_row = col_row[3]; }
 #pragma unroll
                     for (int jj = 0; jj < 32; ++jj) {
-                        const int col = cb * 32 + jj;
-                        const float wgt = __shfl_sync(0xffffffffu, my_wgt, jj);
-                        float* row = (float*)__shfl_sync(0xffffffffu, (unsigned long long)my_row, jj);
-                        if (col < T.ncols) {
-                            float v = __uint_as_float(r[jj]) * inv;
-                            if (T.shared) L.shexp[(size_t)(T.first + col) * L.rows + out_row] = v;
-                            else if (row) row[out_row] = wgt * v;
-                        }
+                        const PfColumn e = tab[cb * 32 + jj];  // every lane the same address: one broadcast load
+                        if (e.live) e.dst[out_row] = e.factor * __uint_as_float(r[jj]);
                     }
                 }
             }

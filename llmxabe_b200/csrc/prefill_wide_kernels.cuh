@@ -354,7 +354,7 @@ __global__ void __launch_bounds__(kPfWideThreads, 1) k_prefill_gemm_wide(const _
                         const int mycol = q * 32 + lane;
                         if (mycol < ncols) {
                             const int flat = __ldg(L.sorted_token_ids + first + mycol);
-                            col_wgt[q] = __ldg(L.topk_weights + flat);
+                            col_wgt[q] = __ldg(L.topk_weights + flat) * inv;  // the weight scale is a power of two: folded in exactly
                             col_row[q] = result_row(L.partial, L.partial_rows, flat, L.rows);
                         }
                     }
@@ -376,15 +376,15 @@ __global__ void __launch_bounds__(kPfWideThreads, 1) k_prefill_gemm_wide(const _
                     if (MODE == MODE_GATEUP) {
                         const int out_row = T.bx * 64 + quad * 16 + (lane & 15);
                         __half* dst_base = T.shared ? L.inter_shared : L.inter_routed;
+                        const bool lower = lane < 16;  // as in k_prefill_gemm: columns jj and jj + 16 in one pass
 #pragma unroll
-                        for (int jj = 0; jj < 32; ++jj) {
-                            float mine = __uint_as_float(r[jj]) * inv;
-                            float other = __shfl_xor_sync(0xffffffffu, mine, 16);
-                            bool do_it = (lane < 16) == (jj < 16);
-                            int col = cb * 32 + jj;
-                            if (do_it && col < ncols) {
-                                float gv = lane < 16 ? mine : other;
-                                float uv = lane < 16 ? other : mine;
+                        for (int jj = 0; jj < 16; ++jj) {
+                            const float lo = __uint_as_float(r[jj]) * inv, hi = __uint_as_float(r[jj + 16]) * inv;
+                            const float recv = __shfl_xor_sync(0xffffffffu, lower ? hi : lo, 16);
+                            const float gv = lower ? lo : recv;
+                            const float uv = lower ? recv : hi;
+                            const int col = cb * 32 + jj + (lower ? 0 : 16);
+                            if (col < ncols) {
                                 float v = __fdiv_rn(gv, 1.0f + expf(-gv)) * uv;
                                 dst_base[(size_t)(first + col) * L.rows + out_row] = __float2half_rn(v);
                             }
@@ -402,8 +402,8 @@ __global__ void __launch_bounds__(kPfWideThreads, 1) k_prefill_gemm_wide(const _
                             const float wgt = __shfl_sync(0xffffffffu, my_wgt, jj);
                             float* row = (float*)__shfl_sync(0xffffffffu, (unsigned long long)my_row, jj);
                             if (col < ncols) {
-                                float v = __uint_as_float(r[jj]) * inv;
-                                if (T.shared) L.shexp[(size_t)(first + col) * L.rows + out_row] = v;
+                                const float v = __uint_as_float(r[jj]);
+                                if (T.shared) L.shexp[(size_t)(first + col) * L.rows + out_row] = v * inv;
                                 else if (row) row[out_row] = wgt * v;
                             }
                         }
