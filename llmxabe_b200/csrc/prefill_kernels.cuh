@@ -16,10 +16,12 @@
 //     asynchronous 16-byte copies that gather the 128 token rows (B tile);
 //   * one thread issues four tcgen05.mma (M128 N128 K16, f16 x f16 -> f32) per
 //     stage and commits them to the stage's "empty" barrier; two accumulators
-//     in TMEM alternate between tiles;
-//   * four epilogue warps read a finished accumulator with tcgen05.ld and
-//     apply SwiGLU (gate/up) or the routing weight (down) while the other
-//     roles are already on the next tile.
+//     in TMEM alternate between tiles.  The token tile is the M operand, the
+//     weight tile the N operand: D[token][weight row];
+//   * four epilogue warps read a finished accumulator with tcgen05.ld (a thread
+//     = one token, 32 consecutive weight rows per read) and apply SwiGLU
+//     (gate/up) or the routing weight (down), storing 16 bytes at a time, while
+//     the other roles are already on the next tile.
 //
 // Numerics: weights are rounded to f16 after the fp32-exact code is multiplied
 // by the f16-rounded group scale (times 256, undone in the epilogue, which
@@ -403,29 +405,19 @@ struct PfCtl {
     uint64_t raw_empty[kPfMaxRaw];      // unpack warps -> loader
     uint64_t acc_full[kPfAccums];       // MMA (tcgen05.commit) -> epilogue
     uint64_t acc_empty[kPfAccums];      // epilogue -> MMA
-    uint64_t tab_full[2];               // the four epilogue warps -> one another (MODE_DOWN's column table)
     uint32_t tmem_base;
     int abort_flag;
 };
 
-// MODE_DOWN: what the epilogue needs to know about a token column of its tile, fetched once per tile
-// by the lane that owns the column and read back by every lane as ONE 16-byte broadcast load.
-struct __align__(16) PfColumn {
-    float* dst;     // the column's result row (routed: row `flat` of the partial buffer or the caller's pointer;
-                    // shared: the token's row of the shared expert's output); nullptr: nothing to store
-    float factor;   // routing weight / kPfWeightScale (shared expert: 1 / kPfWeightScale)
-    uint32_t live;  // 0: skip the column
-};
-
-// MODE_GATEUP (0): TMEM lane m = 32q + i holds gate row r0 + 16q + i for i < 16 and up row
-// r0 + 16q + (i - 16) otherwise (r0 = 64 * bx), so SwiGLU pairs two lanes of one warp.
-// MODE_DOWN (1): lane m holds row 128 * bx + m.
+// The accumulator is D[token][tile row]: TMEM lane = token column of the tile, TMEM column = tile row.
+// MODE_GATEUP (0): tile row m = 32q + i is gate row r0 + 16q + i for i < 16 and up row
+// r0 + 16q + (i - 16) otherwise (r0 = 64 * bx), so SwiGLU pairs two columns of one lane.
+// MODE_DOWN (1): tile row m is row 128 * bx + m.
 // grid: one CTA per SM (or fewer); block kPfThreads.
 template <int MODE, int QR, int QS>
 __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) PfCtl ctl;
-    __shared__ PfColumn col_tab[MODE == MODE_DOWN ? 2 : 1][MODE == MODE_DOWN ? kPfTileN : 1];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int valid = *L.valid_tokens;
@@ -453,7 +445,6 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L)
             mbar_init(&ctl.acc_full[i], 1);
             mbar_init(&ctl.acc_empty[i], 4);
         }
-        for (int i = 0; i < 2; ++i) mbar_init(&ctl.tab_full[i], 4);
         fence_mbar_init();
     }
     if (warp == kPfWarpMma) {
@@ -470,7 +461,8 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L)
         // ------------------------------ unpack warps ------------------------------
         // Per pair of chunks: this warp unpacks tile rows 8w..8w+7 (32 weights per lane) and every
         // thread starts up to four 16-byte copies of the B tiles (token columns tid/8 and tid/8 + 64
-        // of both stages; columns the tile does not have are skipped, the tensor core never reads them).
+        // of both stages; columns the tile does not have are skipped: the tensor core reads stale rows
+        // there, whose sums land in TMEM lanes nobody stores).
         // Lanes 4q..4q+3 serve one row; eight consecutive lanes (the unit a 128-bit shared store is
         // processed in) serve rows r and r + 4, whose chunks fall into different halves of the
         // swizzled 128-byte line, so the A-tile stores are free of bank conflicts.
@@ -586,11 +578,12 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L)
             const int G = gridDim.x;
             uint32_t kc = 0, n = 0;
             bool ok = true;
-            int ncols = (int)blockIdx.x < n_tiles ? pf_tile(L, blockIdx.x, n_routed, valid).ncols : 0;
+            // D[token][weight row]: the TOKEN tile is the M operand, so a TMEM lane (= an epilogue thread)
+            // holds one token's outputs for consecutive weight rows and stores them 16 bytes at a time.
+            // Token rows past the tile's count hold whatever the stage held before; each lane's sums
+            // depend on its own row only, and those lanes are never stored.
+            constexpr uint32_t idesc = umma_idesc_f16(kPfTileN, kPfTileM);
             for (int t = blockIdx.x; t < n_tiles && ok; t += G, ++n) {
-                // the tensor core computes only as many token columns as the tile has (in steps of 16)
-                const uint32_t idesc = umma_idesc_f16(kPfTileM, max(16, (ncols + 15) & ~15));
-                if (t + G < n_tiles) ncols = pf_tile(L, t + G, n_routed, valid).ncols;  // in flight during this tile
                 const uint32_t acc = n % kPfAccums;
                 if (n >= (uint32_t)kPfAccums) {
                     ok = stream_wait_pf(&ctl.acc_empty[acc], (n / kPfAccums - 1) & 1, abortp, L.status);
@@ -607,11 +600,11 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L)
                     const uint32_t a_addr = smem_u32(stages + (size_t)st * kPfStageBytes);
 #pragma unroll
                     for (int half = 0; half < 2; ++half) {
-                        const uint64_t adesc = umma_smem_desc(a_addr + half * kPfStageBytes);
-                        const uint64_t bdesc = umma_smem_desc(a_addr + half * kPfStageBytes + kPfTileM * kPfChunkK * 2);
+                        const uint64_t wdesc = umma_smem_desc(a_addr + half * kPfStageBytes);  // weight rows
+                        const uint64_t xdesc = umma_smem_desc(a_addr + half * kPfStageBytes + kPfTileM * kPfChunkK * 2);
 #pragma unroll
                         for (int k4 = 0; k4 < kPfChunkK / 16; ++k4)  // 32 bytes per K16 step inside the swizzle row
-                            umma_f16(tmem_d, adesc + 2 * k4, bdesc + 2 * k4, idesc,
+                            umma_f16(tmem_d, xdesc + 2 * k4, wdesc + 2 * k4, idesc,
                                      (c > 0 || half > 0 || k4 > 0) ? 1u : 0u);
                     }
                     umma_commit(&ctl.empty_bar[st >> 1]);  // the pair is free once these MMAs have read it
@@ -672,80 +665,74 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L)
         asm volatile("cp.async.wait_all;" ::: "memory");
     } else {
         // ------------------------------- epilogue -------------------------------
-        const int quad = warp & 3;  // TMEM lanes 32 * quad .. 32 * quad + 31
+        // Thread (quad, lane) owns token column 32 quad + lane of every tile: TMEM lane = token, TMEM
+        // column = tile row.  Gate/up: columns 32 c .. 32 c + 15 are gate rows 16 c .. 16 c + 15 of the tile's
+        // 64, columns 32 c + 16 .. 32 c + 31 the same rows of up, so SwiGLU stays inside the thread.
+        const int quad = warp & 3;
         const float inv = 1.0f / kPfWeightScale;
         uint32_t n = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++n) {
             const PfTile T = pf_tile(L, t, n_routed, valid);
             const uint32_t acc = n % kPfAccums;
-            // Down: lane c of epilogue warp q describes column 32 q + c of the tile in the table (routed:
-            // three dependent loads -- flat (token, k) id, routing weight, result row) before it waits for
-            // the accumulator, so the loads are in flight while the tile is still being computed.  The
-            // table alternates between two copies by tile: a warp can be at most one tile ahead of the
-            // slowest, because it has to wait for that warp's entries of the tile in between.
-            const PfColumn* tab = col_tab[MODE == MODE_DOWN ? (n & 1) : 0];
-            if (MODE == MODE_DOWN) {
-                const int mycol = quad * 32 + lane;
-                PfColumn e{nullptr, 0.f, 0u};
-                if (mycol < T.ncols) {
-                    if (T.shared) {
-                        e.dst = L.shexp + (size_t)(T.first + mycol) * L.rows;
-                        e.factor = inv;
-                    } else {
-                        const int flat = __ldg(L.sorted_token_ids + T.first + mycol);
-                        // the weight scale is a power of two: folded into the routing weight exactly
-                        e.factor = __ldg(L.topk_weights + flat) * inv;
-                        e.dst = result_row(L.partial, L.partial_rows, flat, L.rows);
-                    }
-                    e.live = e.dst != nullptr;
+            const int tok = quad * 32 + lane;
+            const bool live = tok < T.ncols;
+            // Down, routed: the flat (token, k) id, the routing weight and the result row -- three dependent
+            // loads -- are fetched before the wait, so they are in flight while the tile is computed.
+            float factor = inv;  // the weight scale is a power of two: folded into the routing weight exactly
+            float* dst = nullptr;
+            __half* hdst = nullptr;
+            if (live) {
+                if (MODE == MODE_GATEUP) {
+                    hdst = (T.shared ? L.inter_shared : L.inter_routed) + (size_t)(T.first + tok) * L.rows + T.bx * 64;
+                } else if (T.shared) {
+                    dst = L.shexp + (size_t)(T.first + tok) * L.rows;
+                } else {
+                    const int flat = __ldg(L.sorted_token_ids + T.first + tok);
+                    factor = __ldg(L.topk_weights + flat) * inv;
+                    dst = result_row(L.partial, L.partial_rows, flat, L.rows);
                 }
-                col_tab[n & 1][mycol] = e;
-                __syncwarp();
-                if (lane == 0) mbar_arrive_pf(&ctl.tab_full[n & 1]);
+                if (MODE == MODE_DOWN && dst) dst += T.bx * kPfTileM;
             }
             ok = stream_wait_pf<true>(&ctl.acc_full[acc], (n / kPfAccums) & 1, abortp, L.status);
             if (!ok) break;
-            if (MODE == MODE_DOWN) {
-                ok = stream_wait_pf(&ctl.tab_full[n & 1], (n >> 1) & 1, abortp, L.status);
-                if (!ok) break;
-            }
             tc_fence_after();
             const uint32_t taddr = tmem_base + acc * kPfTileN + ((uint32_t)(quad * 32) << 16);
-            for (int cb = 0; cb * 32 < T.ncols; ++cb) {
+            const bool any_live = quad * 32 < T.ncols;  // the same for the whole warp
+            for (int cb = 0; cb < kPfTileM / 32; ++cb) {
                 uint32_t r[32];
-                tmem_ld32(taddr + (uint32_t)(cb * 32), r);
-                tmem_ld_wait();
-                if ((cb + 1) * 32 >= T.ncols) {  // last read of this accumulator: hand it back before the stores
+                if (any_live) {
+                    tmem_ld32(taddr + (uint32_t)(cb * 32), r);
+                    tmem_ld_wait();
+                }
+                if (cb == kPfTileM / 32 - 1 || !any_live) {  // last read of this accumulator: hand it back before the stores
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive_pf(&ctl.acc_empty[acc]);
+                    if (!any_live) break;
                 }
                 if (MODE == MODE_GATEUP) {
-                    const int out_row = T.bx * 64 + quad * 16 + (lane & 15);
-                    __half* dst_base = T.shared ? L.inter_shared : L.inter_routed;
-                    // Lanes 0-15 hold the gate rows and finish column jj, lanes 16-31 hold the same rows of up
-                    // and finish column jj + 16: each sends the value its partner needs, so all 32 lanes
-                    // are in the exponential and the division of every pass.
-                    const bool lower = lane < 16;
+                    if (hdst) {
+                        uint32_t h[8];
 #pragma unroll
-                    for (int jj = 0; jj < 16; ++jj) {
-                        const float lo = __uint_as_float(r[jj]) * inv, hi = __uint_as_float(r[jj + 16]) * inv;
-                        const float recv = __shfl_xor_sync(0xffffffffu, lower ? hi : lo, 16);
-                        const float gv = lower ? lo : recv;
-                        const float uv = lower ? recv : hi;
-                        const int col = cb * 32 + jj + (lower ? 0 : 16);
-                        if (col < T.ncols) {
-                            float v = __fdiv_rn(gv, 1.0f + expf(-gv)) * uv;
-                            dst_base[(size_t)(T.first + col) * L.rows + out_row] = __float2half_rn(v);
+                        for (int i = 0; i < 8; ++i) {
+                            const float g0 = __uint_as_float(r[2 * i]) * inv, g1 = __uint_as_float(r[2 * i + 1]) * inv;
+                            const float u0 = __uint_as_float(r[16 + 2 * i]) * inv, u1 = __uint_as_float(r[17 + 2 * i]) * inv;
+                            const __half2 v = __floats2half2_rn(__fdiv_rn(g0, 1.0f + expf(-g0)) * u0,
+                                                                __fdiv_rn(g1, 1.0f + expf(-g1)) * u1);
+                            h[i] = *(const uint32_t*)&v;
                         }
+                        uint4* o = (uint4*)(hdst + cb * 16);
+                        o[0] = make_uint4(h[0], h[1], h[2], h[3]);
+                        o[1] = make_uint4(h[4], h[5], h[6], h[7]);
                     }
                 } else {
-                    const int out_row = T.bx * kPfTileM + quad * 32 + lane;
+                    if (dst) {
+                        float4* o = (float4*)(dst + cb * 32);
 #pragma unroll
-                    for (int jj = 0; jj < 32; ++jj) {
-                        const PfColumn e = tab[cb * 32 + jj];  // every lane the same address: one broadcast load
-                        if (e.live) e.dst[out_row] = e.factor * __uint_as_float(r[jj]);
+                        for (int i = 0; i < 8; ++i)
+                            o[i] = make_float4(factor * __uint_as_float(r[4 * i]), factor * __uint_as_float(r[4 * i + 1]),
+                                               factor * __uint_as_float(r[4 * i + 2]), factor * __uint_as_float(r[4 * i + 3]));
                     }
                 }
             }
