@@ -68,8 +68,8 @@ WORKLOADS = {
 # DRAM bytes (read + write) of the dominant kernel per launch from an ncu capture of the same workload
 # (dram__bytes_read.sum + dram__bytes_write.sum); the line says where each figure came from
 NCU_TRAFFIC = {
-    "decode64": (329.3e6 + 4.3e6, "ncu capture of k_gateup_rows at decode64, one launch, constant recorded in bench.py"),
-    "prefill2048": (467.0e6 + 16.5e6, "ncu capture of k_prefill_gemm<GATEUP> at prefill2048, one launch, constant recorded in bench.py"),
+    "decode64": (332.9e6 + 5.9e6, "ncu capture of k_gateup_rows at decode64, one launch, constant recorded in bench.py"),
+    "prefill2048": (468.3e6 + 18.1e6, "ncu capture of k_prefill_gemm<GATEUP> at prefill2048, one launch, constant recorded in bench.py"),
 }
 
 Q6K_MATRIX = (512 * 2048 // 256) * 210   # one [512][2048] or [2048][512] matrix, 860,160 B
