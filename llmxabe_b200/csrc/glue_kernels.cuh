@@ -895,8 +895,14 @@ __global__ void k_reduce(const float* __restrict__ partial, const int* __restric
 // lanes at stride 256 and block_reduce_sum; routed = ascending-k sum of
 // partial; ffn_out = routed + shexp * g (routed on the left); l_out =
 // ffn_out + residual (the pre-norm input).
-// grid: (max_tokens, 1 or hidden / 256), block 256.
+// grid: (max_tokens, 1 or hidden / 256), block 256.  VEC (grid.y == 1, hidden a multiple of 4, every
+// row pointer 16-byte aligned): a thread owns four neighbouring columns and moves them 16 bytes at a
+// time; each column's sums are the same operations in the same order.
 // ---------------------------------------------------------------------------
+__device__ __forceinline__ float4 f4_add(float4 a, float4 b) {
+    return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+}
+template <bool VEC>
 __global__ void __launch_bounds__(256) k_gate_and_combine(
     const float* __restrict__ w, const float* __restrict__ normed, const float* __restrict__ partial,
     const float* __restrict__ shexp, const float* __restrict__ residual, const int* __restrict__ valid_tokens,
@@ -915,6 +921,26 @@ __global__ void __launch_bounds__(256) k_gate_and_combine(
     float g = __fdiv_rn(1.0f, 1.0f + expf(-s));
     if (threadIdx.x == 0 && blockIdx.y == 0) gate[t] = g;
     size_t pbase = (size_t)t * top_k * hidden;
+    if (VEC && top_k == 8) {
+        const float4* p4 = (const float4*)(partial + pbase);
+        const float4* sh4 = (const float4*)(shexp + base);
+        const float4* res4 = (const float4*)(residual + base);
+        const int h4 = hidden >> 2;
+        for (int j = threadIdx.x; j < h4; j += 256) {
+            float4 pv[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) pv[k] = p4[(size_t)k * h4 + j];
+            const float4 sh = sh4[j], res = res4[j];
+            float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) r = f4_add(r, pv[k]);
+            const float4 v = make_float4(fmaf(sh.x, g, r.x), fmaf(sh.y, g, r.y), fmaf(sh.z, g, r.z), fmaf(sh.w, g, r.w));
+            ((float4*)(routed + base))[j] = r;
+            ((float4*)(ffn_out + base))[j] = v;
+            ((float4*)(l_out + base))[j] = f4_add(v, res);
+        }
+        return;
+    }
     // gridDim.y blocks share a token's columns: 1 at prefill widths (the gate, a block-wide reduction,
     // is then computed once per token), hidden / 256 at decode widths (more blocks than SMs)
     for (int j = blockIdx.y * 256 + threadIdx.x; j < hidden; j += 256 * gridDim.y) {
@@ -1010,6 +1036,7 @@ __global__ void __launch_bounds__(256) k_ep_pack_sorted(
 // routed = sum over ascending k of weight[t][k] * back[inverse[t*K + k]], each
 // product rounded to fp32 before it is added -- the value the one-GPU path
 // stores in `partial` and sums, so the result is bit-identical to it.
+template <bool VEC>
 __global__ void __launch_bounds__(256) k_ep_combine(
     const float* __restrict__ w, const float* __restrict__ normed, const float* __restrict__ back,
     const int* __restrict__ inverse, const float* __restrict__ topk_weights, const float* __restrict__ shexp,
@@ -1032,6 +1059,28 @@ __global__ void __launch_bounds__(256) k_ep_combine(
         for (int k = 0; k < 8; ++k) {
             src[k] = inverse[t * 8 + k];
             pw[k] = topk_weights[t * 8 + k];
+        }
+        if (VEC) {  // as in k_gate_and_combine: four neighbouring columns per thread
+            const float4* sh4 = (const float4*)(shexp + base);
+            const float4* res4 = (const float4*)(residual + base);
+            const int h4 = hidden >> 2;
+            for (int j = threadIdx.x; j < h4; j += 256) {
+                float4 pv[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) pv[k] = ((const float4*)(back + (size_t)src[k] * hidden))[j];
+                const float4 sh = sh4[j], res = res4[j];
+                float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    r = make_float4(__fadd_rn(r.x, __fmul_rn(pw[k], pv[k].x)), __fadd_rn(r.y, __fmul_rn(pw[k], pv[k].y)),
+                                    __fadd_rn(r.z, __fmul_rn(pw[k], pv[k].z)), __fadd_rn(r.w, __fmul_rn(pw[k], pv[k].w)));
+                const float4 v =
+                    make_float4(fmaf(sh.x, g, r.x), fmaf(sh.y, g, r.y), fmaf(sh.z, g, r.z), fmaf(sh.w, g, r.w));
+                ((float4*)(routed + base))[j] = r;
+                ((float4*)(ffn_out + base))[j] = v;
+                ((float4*)(l_out + base))[j] = f4_add(v, res);
+            }
+            return;
         }
         for (int j = blockIdx.y * 256 + threadIdx.x; j < hidden; j += 256 * gridDim.y) {
             float pv[8];

@@ -1283,6 +1283,14 @@ int xabe_moe_build_dispatch(xabe_moe* m, void* stream, const int32_t* topk_ids, 
     return launch_route_and_dispatch(m, st, nullptr);
 }
 
+// The combine kernels move 16 bytes per thread when one block owns a token's whole row and every row
+// they touch starts on a 16-byte boundary.
+static bool combine_vec(const xabe_moe* m, dim3 grid, const void* a, const void* b, const void* c,
+                        const void* d = nullptr) {
+    auto al = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+    return grid.y == 1 && m->g.hidden % 4 == 0 && m->g.experts_per_token == 8 && al(a) && al(b) && al(c) && al(d);
+}
+
 int xabe_moe_gate_and_combine(xabe_moe* m, void* stream, const float* shared_gate_inp, const float* residual,
                               size_t residual_len, float* ffn_out, size_t ffn_out_len, float* l_out,
                               size_t l_out_len) {
@@ -1295,7 +1303,9 @@ int xabe_moe_gate_and_combine(xabe_moe* m, void* stream, const float* shared_gat
     if (residual_len != n || ffn_out_len != n || l_out_len != n)
         return fail(XABE_ERR_BUFFER_LENGTH, "gate_and_combine buffers must hold %zu floats", n);
     dim3 grid(g.max_tokens, g.max_tokens >= 512 ? 1u : (g.hidden + 255) / 256);
-    CUDA_TRY(launch_pdl(m->pdl, k_gate_and_combine, grid, dim3(256), 0, (cudaStream_t)stream, shared_gate_inp,
+    CUDA_TRY(launch_pdl(m->pdl,
+                        combine_vec(m, grid, residual, ffn_out, l_out) ? k_gate_and_combine<true> : k_gate_and_combine<false>,
+                        grid, dim3(256), 0, (cudaStream_t)stream, shared_gate_inp,
                         (const float*)m->normed, (const float*)m->partial, (const float*)m->shexp, residual,
                         (const int*)m->valid_tokens, (int)g.experts_per_token, (int)g.hidden, m->gate, m->routed,
                         ffn_out, l_out));
@@ -1533,7 +1543,8 @@ int xabe_moe_ep_combine(xabe_moe* m, void* stream, const float* back_rows, size_
     if (n_rows > (size_t)g.max_tokens * g.experts_per_token)
         return fail(XABE_ERR_TOO_MANY_TOKENS, "%zu rows exceed max_tokens * k", n_rows);
     dim3 grid(g.max_tokens, g.max_tokens >= 512 ? 1u : (g.hidden + 255) / 256);
-    k_ep_combine<<<grid, 256, 0, counted((cudaStream_t)stream)>>>(
+    auto kern = combine_vec(m, grid, residual, ffn_out, l_out, back_rows) ? k_ep_combine<true> : k_ep_combine<false>;
+    kern<<<grid, 256, 0, counted((cudaStream_t)stream)>>>(
         shared_gate_inp, m->normed, back_rows, inverse, m->topk_weights, m->shexp, residual, m->valid_tokens,
         (int)g.experts_per_token, (int)g.hidden, m->gate, m->routed, ffn_out, l_out);
     CUDA_TRY(cudaGetLastError());
@@ -1627,7 +1638,10 @@ int xabe_moe_block_forward(xabe_moe* m, void* stream, const xabe_moe_layer_weigh
         if ((rc = run_experts(m, st, r, s, m->shexp, 4))) return rc;
         prof_mark(m, st, 5);
         dim3 grid(g.max_tokens, g.max_tokens >= 512 ? 1u : (g.hidden + 255) / 256);
-        CUDA_TRY(launch_pdl(m->pdl, k_gate_and_combine, grid, dim3(256), 0, st, w->shared_gate_inp,
+        CUDA_TRY(launch_pdl(m->pdl,
+                            combine_vec(m, grid, residual, ffn_out, l_out) ? k_gate_and_combine<true>
+                                                                           : k_gate_and_combine<false>,
+                            grid, dim3(256), 0, st, w->shared_gate_inp,
                             (const float*)m->normed, (const float*)m->partial, (const float*)m->shexp, residual,
                             (const int*)m->valid_tokens, (int)g.experts_per_token, (int)g.hidden, m->gate, m->routed,
                             ffn_out, l_out));
