@@ -75,14 +75,17 @@ __global__ void k_ep_plan_ranks(int num_experts, int experts_per_rank, const int
 }
 
 // Sender: every live slot of the dispatch tables -> the owner's receive region of this rank.
-// grid: sorted_capacity, block 256.
+// One WARP per slot (eight slots per block): the chain of dependent table reads that tells a slot
+// where its row goes is then in flight for 64 slots per SM instead of 8, and a lane keeps eight
+// 16-byte loads in flight.  grid: ceil(sorted_capacity / 8), block 256.
+constexpr int kEpPushSlotsPerBlock = 8;
 __global__ void __launch_bounds__(256) k_ep_push_rows(
     const int* __restrict__ sorted_token_ids, const int* __restrict__ expert_ids,
     const int* __restrict__ expert_offsets, const int* __restrict__ compact, const int* __restrict__ rank_start,
     const int* __restrict__ num_tokens_post_pad, const int* __restrict__ valid_tokens,
     const __half* __restrict__ normed_h, int top_k, int hidden, int block_size, int experts_per_rank, int me,
     int cap, EpPeers peer_rows, EpPeers peer_eid, int* __restrict__ inverse) {
-    const int s = blockIdx.x;
+    const int s = blockIdx.x * kEpPushSlotsPerBlock + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (s >= *num_tokens_post_pad) return;
     const int flat = sorted_token_ids[s];
     if (flat >= *valid_tokens * top_k) return;  // padding slot
@@ -92,8 +95,17 @@ __global__ void __launch_bounds__(256) k_ep_push_rows(
     const int j = i - rank_start[d];                     // position among the rows bound for rank d
     const uint4* src = (const uint4*)(normed_h + (size_t)(flat / top_k) * hidden);
     uint4* dst = (uint4*)((__half*)peer_at(peer_rows, d) + ((size_t)me * cap + j) * hidden);
-    for (int u = threadIdx.x; u < hidden / 8; u += 256) dst[u] = __ldg(src + u);
-    if (threadIdx.x == 0) {
+    const int units = hidden / 8;
+    for (int u0 = 0; u0 < units; u0 += 256) {
+        uint4 v[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+            if (u0 + q * 32 + lane < units) v[q] = __ldg(src + u0 + q * 32 + lane);
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+            if (u0 + q * 32 + lane < units) dst[u0 + q * 32 + lane] = v[q];
+    }
+    if (lane == 0) {
         ((int*)peer_at(peer_eid, d))[(size_t)me * cap + j] = e % experts_per_rank;
         inverse[flat] = i;
     }

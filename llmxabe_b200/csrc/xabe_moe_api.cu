@@ -1426,7 +1426,8 @@ int xabe_moe_ep_p2p_send(xabe_moe* m, void* stream, int experts_per_rank, int wo
     k_ep_plan_ranks<<<1, threads, (g.num_experts + 1) * sizeof(int), counted(st)>>>(
         (int)g.num_experts, experts_per_rank, m->expert_counts, m->ep_compact, m->ep_rank_start, m->ep_send_counts);
     CUDA_TRY(cudaGetLastError());
-    k_ep_push_rows<<<(unsigned)m->sorted_capacity, 256, 0, counted(st)>>>(
+    k_ep_push_rows<<<(unsigned)((m->sorted_capacity + kEpPushSlotsPerBlock - 1) / kEpPushSlotsPerBlock), 256, 0,
+                     counted(st)>>>(
         m->sorted_token_ids, m->expert_ids, m->expert_offsets, m->ep_compact, m->ep_rank_start,
         m->num_tokens_post_pad, m->valid_tokens, m->normed_h, (int)g.experts_per_token, (int)g.hidden,
         (int)g.block_size, experts_per_rank, rank, cap, peers_of(peers->rows, world), peers_of(peers->eid, world),
