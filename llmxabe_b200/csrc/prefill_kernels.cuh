@@ -418,6 +418,12 @@ template <int MODE, int QR, int QS>
 __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) PfCtl ctl;
+    // MODE_DOWN: an epilogue warp turns 32 tokens x 16 outputs around in shared memory, so that four
+    // lanes store 64 neighbouring bytes of one result row instead of every lane 16 bytes of a row of its
+    // own (32 rows per store instruction: slow through L1, and slower still when the rows are in
+    // another GPU's memory, as with a caller's table of result rows).
+    __shared__ __align__(16) float epi_stage[MODE == MODE_DOWN ? 4 : 1][MODE == MODE_DOWN ? 32 * 16 : 4];
+    __shared__ float* epi_dst[MODE == MODE_DOWN ? 4 : 1][32];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int valid = *L.valid_tokens;
@@ -669,6 +675,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L)
         // column = tile row.  Gate/up: columns 32 c .. 32 c + 15 are gate rows 16 c .. 16 c + 15 of the tile's
         // 64, columns 32 c + 16 .. 32 c + 31 the same rows of up, so SwiGLU stays inside the thread.
         const int quad = warp & 3;
+        const int ew = MODE == MODE_DOWN ? warp - kPfWarpEpi0 : 0;
         const float inv = 1.0f / kPfWeightScale;
         uint32_t n = 0;
         bool ok = true;
@@ -693,6 +700,10 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L)
                     dst = result_row(L.partial, L.partial_rows, flat, L.rows);
                 }
                 if (MODE == MODE_DOWN && dst) dst += T.bx * kPfTileM;
+            }
+            if (MODE == MODE_DOWN) {  // the warp's 32 row addresses (nullptr: nothing to store), read back by other lanes
+                epi_dst[ew][lane] = dst;
+                __syncwarp();
             }
             ok = stream_wait_pf<true>(&ctl.acc_full[acc], (n / kPfAccums) & 1, abortp, L.status);
             if (!ok) break;
@@ -727,12 +738,28 @@ __global__ void __launch_bounds__(kPfThreads, 1) k_prefill_gemm(PrefillLaunch L)
                         o[1] = make_uint4(h[4], h[5], h[6], h[7]);
                     }
                 } else {
-                    if (dst) {
-                        float4* o = (float4*)(dst + cb * 32);
 #pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            o[i] = make_float4(factor * __uint_as_float(r[4 * i]), factor * __uint_as_float(r[4 * i + 1]),
-                                               factor * __uint_as_float(r[4 * i + 2]), factor * __uint_as_float(r[4 * i + 3]));
+                    for (int half = 0; half < 2; ++half) {
+                        // lane = token: its 16 outputs as four 16-byte chunks, chunk c at position
+                        // c ^ ((lane / 2) % 4) of the 64-byte row, which keeps both the stores here and the
+                        // loads below free of bank conflicts
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            const int q = half * 16 + 4 * c;
+                            *(float4*)(epi_stage[ew] + lane * 16 + ((c ^ ((lane >> 1) & 3)) << 2)) =
+                                make_float4(factor * __uint_as_float(r[q]), factor * __uint_as_float(r[q + 1]),
+                                            factor * __uint_as_float(r[q + 2]), factor * __uint_as_float(r[q + 3]));
+                        }
+                        __syncwarp();
+                        // lanes 4R' .. 4R' + 3 of a pass: the four chunks of token row R, 64 bytes side by side
+#pragma unroll
+                        for (int it = 0; it < 4; ++it) {
+                            const int R = it * 8 + (lane >> 2), c = lane & 3;
+                            const float4 v = *(const float4*)(epi_stage[ew] + R * 16 + ((c ^ ((R >> 1) & 3)) << 2));
+                            float* p = epi_dst[ew][R];
+                            if (p) *(float4*)(p + cb * 32 + half * 16 + c * 4) = v;
+                        }
+                        __syncwarp();
                     }
                 }
             }
