@@ -108,7 +108,7 @@ class EpMoeBlock:
             if self._side is None:
                 b.shared()
             mark("plan_pack")
-            b.p2p_experts()
+            b.p2p_experts(mark if self._events is not None else None)
             mark("experts")
             self._shared_join()
             b.p2p_finish(residual, tokens, ffn_out, l_out)
@@ -166,7 +166,11 @@ class EpMoeBlock:
         ev = self._events or []
         for (_, e0), (name, e1) in zip(ev, ev[1:]):
             if name != "start":
-                out[name] = out.get(name, 0.0) + e0.elapsed_time(e1)
+                ms = e0.elapsed_time(e1)
+                out[name] = out.get(name, 0.0) + ms
+                if ":" in name:     # a part of a phase ("experts:tables"): counted in the phase as well
+                    phase = name.split(":")[0]
+                    out[phase] = out.get(phase, 0.0) + ms
         self._events = []
         return out
 
@@ -321,13 +325,19 @@ class PeerMemoryEpBackend(CudaEpBackend):
         self.step += 1
         self.front_k.ep_p2p_send(self.epr, self.world, self.rank, self.cap, self.peers, self.step, self.inverse)
 
-    def p2p_experts(self):
+    def p2p_experts(self, mark=None):
+        """The owner's step.  `mark(name)` (optional) records a device event after each part, for the
+        benchmark's per-phase timing."""
+        mark = mark or (lambda name: None)
         k = self.back_k
         k.ep_p2p_receive(self.world, self.rank, self.cap, self.peers, self.step, self.slot_ids, self.result_dst)
+        mark("experts:wait_rows+slots")
         k.build_dispatch(self.slot_ids, None)
+        mark("experts:tables")
         if self.fused_return:   # the down projection's epilogue stores each result row at its sender
             k.set_result_destinations(self.result_dst)
         k.grouped_forward_partial_f16(self.local[0], self.local[1], self.local[2], self._own["rows"])
+        mark("experts:gemms")
         k.ep_p2p_return(self.world, self.rank, self.cap, self.peers, self.step, self.result_dst)
         k.set_result_destinations(None)
 
