@@ -979,6 +979,8 @@ def run_dense(args) -> dict:
         else:
             backend.down = full[2]
         del full
+        for key, value in args.tune:
+            backend.k.set_tuning(key, value)
         blocks.append(TpDenseFfnBlock(backend, rank, world))
     torch.cuda.empty_cache()
     gen = torch.Generator(device="cuda")
@@ -997,8 +999,27 @@ def run_dense(args) -> dict:
     n0 = kernel_launch_count()
     step(0)
     launches_per_step = kernel_launch_count() - n0
+    # Decode widths on one GPU: the steps are replayed from a CUDA graph (one step per resident layer), as
+    # the MoE decode steps are and as the reference's decode bodies are (crates/xabe-engine/src/forward.rs:2059)
+    graph = None
+    if args.graph and world == 1 and tokens <= 64:
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(n_layers):
+                step(i)
+        torch.cuda.synchronize()
+
+    def replay(i):
+        if i % n_layers == 0:
+            graph.replay()
+
+    steps_g = (args.steps + n_layers - 1) // n_layers * n_layers
+    fn, n_timed = (replay, steps_g) if graph is not None else (step, args.steps)
+    for i in range(n_layers * 3):
+        fn(i)
     sampler.begin_region()
-    ms, repeats = tm.timed(step, args.steps)
+    ms, repeats = tm.timed(fn, n_timed)
     clocks = sampler.stop()
     status = 0
     for b in blocks:
@@ -1036,8 +1057,9 @@ def run_dense(args) -> dict:
         "data": "synthetic", "config": dense_config(args.workload, args, world),
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": tokens * HD * 4, "d2h_bytes_per_step": tokens * HD * 4},
-        "gpu_launches": launches_per_step * args.steps * repeats, "gpu_launches_per_step": launches_per_step,
-        "cuda_graph": False, "clocks": clocks, "roofline": roof, "device_status": status,
+        "gpu_launches": launches_per_step * n_timed * repeats, "gpu_launches_per_step": launches_per_step,
+        "cuda_graph": graph is not None, "steps_timed": n_timed, "clocks": clocks, "roofline": roof,
+        "device_status": status,
     }
     if world > 1:
         dist.barrier()
