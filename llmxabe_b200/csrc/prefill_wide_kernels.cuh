@@ -74,6 +74,9 @@ template <int MODE, int QR, int QS>
 __global__ void __launch_bounds__(kPfWideThreads, 1) k_prefill_gemm_wide(const __grid_constant__ PrefillLaunch L) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) PfWideCtl ctl;
+    // MODE_DOWN: the epilogue warps' turn-around buffers and row addresses, as in k_prefill_gemm
+    __shared__ __align__(16) float epi_stage[MODE == MODE_DOWN ? 4 : 1][MODE == MODE_DOWN ? 32 * 16 : 4];
+    __shared__ float* epi_dst[MODE == MODE_DOWN ? 4 : 1][32];
     constexpr int kTile = kPfTileM * kPfChunkK * 2;  // one 16 KB A or B chunk tile
     constexpr int kUnit = 2 * kTile;                 // a pair of chunk tiles
 
@@ -184,7 +187,7 @@ __global__ void __launch_bounds__(kPfWideThreads, 1) k_prefill_gemm_wide(const _
         // One thread: for every pair of chunks and every column tile of the item, two TMA copies
         // (chunk k0 and k0 + 64, token rows first + 128 ct .. + 127) into the next unit of the B ring.
         // Rows past the item's last column belong to a neighbour or are out of bounds (zero-filled);
-        // the tensor core is told the tile's width and their columns are never stored.
+        // their sums land in TMEM lanes that are never stored.
         if (lane == 0) {
             const int n_pairs = L.k / (2 * kPfChunkK);
             const uint32_t b32 = smem_u32(b_ring), bfull32 = smem_u32(&ctl.b_full[0]);
@@ -231,14 +234,10 @@ __global__ void __launch_bounds__(kPfWideThreads, 1) k_prefill_gemm_wide(const _
             uint32_t acc_base = 0, acc_used = 0, acc_par = 0;  // per-slot: used before / parity of the next wait
             bool ok = true;
             int ncols = (int)blockIdx.x < n_tiles ? pf_tile(L, blockIdx.x, n_routed, valid).ncols : 0;
+            // D[token][weight row], as in k_prefill_gemm: the token tile is the M operand
+            constexpr uint32_t idesc = umma_idesc_f16(kPfTileN, kPfTileM);
             for (int t = blockIdx.x; t < n_tiles && ok; t += G) {
                 const int nct = (ncols + kPfTileN - 1) / kPfTileN;
-                uint32_t idesc[kPfWideMaxCt];
-#pragma unroll
-                for (int ct = 0; ct < kPfWideMaxCt; ++ct) {
-                    int c = min(kPfTileN, ncols - ct * kPfTileN);
-                    idesc[ct] = umma_idesc_f16(kPfTileM, max(16, (c + 15) & ~15));
-                }
                 if (t + G < n_tiles) ncols = pf_tile(L, t + G, n_routed, valid).ncols;  // in flight during this tile
                 for (int p = 0; p < n_pairs && ok; ++p, ++pc) {
                     const uint32_t aslot = pc & 1;
@@ -262,11 +261,11 @@ __global__ void __launch_bounds__(kPfWideThreads, 1) k_prefill_gemm_wide(const _
                         const uint32_t tmem_d = tmem_base + as * kPfTileN;
 #pragma unroll
                         for (int half = 0; half < 2; ++half) {
-                            const uint64_t adesc = umma_smem_desc(a_addr + half * kTile);
-                            const uint64_t bdesc = umma_smem_desc(b_addr + half * kTile);
+                            const uint64_t wdesc = umma_smem_desc(a_addr + half * kTile);  // weight rows
+                            const uint64_t xdesc = umma_smem_desc(b_addr + half * kTile);  // token rows
 #pragma unroll
                             for (int k4 = 0; k4 < kPfChunkK / 16; ++k4)
-                                umma_f16(tmem_d, adesc + 2 * k4, bdesc + 2 * k4, idesc[ct],
+                                umma_f16(tmem_d, xdesc + 2 * k4, wdesc + 2 * k4, idesc,
                                          (p > 0 || half > 0 || k4 > 0) ? 1u : 0u);
                         }
                         umma_commit(&ctl.b_empty[bslot]);  // the unit is free once these MMAs have read it
@@ -334,7 +333,10 @@ __global__ void __launch_bounds__(kPfWideThreads, 1) k_prefill_gemm_wide(const _
         asm volatile("cp.async.wait_all;" ::: "memory");
     } else {
         // ------------------------------- epilogue -------------------------------
+        // As in k_prefill_gemm: thread (quad, lane) owns token column 32 quad + lane of a column tile;
+        // a TMEM read is 32 consecutive tile rows of that token.
         const int quad = warp & 3;
+        const int ew = MODE == MODE_DOWN ? warp - kPfWarpEpi0 : 0;
         const float inv = 1.0f / kPfWeightScale;
         uint32_t acc_base = 0, acc_par = 0;
         bool ok = true;
@@ -345,67 +347,81 @@ __global__ void __launch_bounds__(kPfWideThreads, 1) k_prefill_gemm_wide(const _
                 const uint32_t as = (acc_base + ct) & 3u;
                 const int first = T.first + ct * kPfTileN;
                 const int ncols = min(kPfTileN, T.ncols - ct * kPfTileN);
-                // down, routed: the three dependent loads per column are issued before the wait
-                float col_wgt[4] = {0.f, 0.f, 0.f, 0.f};
-                float* col_row[4] = {nullptr, nullptr, nullptr, nullptr};
-                if (MODE == MODE_DOWN && !T.shared) {
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const int mycol = q * 32 + lane;
-                        if (mycol < ncols) {
-                            const int flat = __ldg(L.sorted_token_ids + first + mycol);
-                            col_wgt[q] = __ldg(L.topk_weights + flat) * inv;  // the weight scale is a power of two: folded in exactly
-                            col_row[q] = result_row(L.partial, L.partial_rows, flat, L.rows);
-                        }
+                const int tok = quad * 32 + lane;
+                const bool live = tok < ncols;
+                // down, routed: the three dependent loads of the thread's token are issued before the wait
+                float factor = inv;  // the weight scale is a power of two: folded into the routing weight exactly
+                float* dst = nullptr;
+                __half* hdst = nullptr;
+                if (live) {
+                    if (MODE == MODE_GATEUP) {
+                        hdst = (T.shared ? L.inter_shared : L.inter_routed) + (size_t)(first + tok) * L.rows + T.bx * 64;
+                    } else if (T.shared) {
+                        dst = L.shexp + (size_t)(first + tok) * L.rows;
+                    } else {
+                        const int flat = __ldg(L.sorted_token_ids + first + tok);
+                        factor = __ldg(L.topk_weights + flat) * inv;
+                        dst = result_row(L.partial, L.partial_rows, flat, L.rows);
                     }
+                    if (MODE == MODE_DOWN && dst) dst += T.bx * kPfTileM;
+                }
+                if (MODE == MODE_DOWN) {  // the warp's 32 row addresses (nullptr: nothing to store)
+                    epi_dst[ew][lane] = dst;
+                    __syncwarp();
                 }
                 ok = stream_wait_pf<true>(&ctl.acc_full[as], acc_par >> as & 1u, abortp, L.status);
                 if (!ok) break;
                 acc_par ^= 1u << as;
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + as * kPfTileN + ((uint32_t)(quad * 32) << 16);
-                for (int cb = 0; cb * 32 < ncols; ++cb) {
+                const bool any_live = quad * 32 < ncols;  // the same for the whole warp
+                for (int cb = 0; cb < kPfTileM / 32; ++cb) {
                     uint32_t r[32];
-                    tmem_ld32(taddr + (uint32_t)(cb * 32), r);
-                    tmem_ld_wait();
-                    if ((cb + 1) * 32 >= ncols) {  // last read of this accumulator: hand it back before the stores
+                    if (any_live) {
+                        tmem_ld32(taddr + (uint32_t)(cb * 32), r);
+                        tmem_ld_wait();
+                    }
+                    if (cb == kPfTileM / 32 - 1 || !any_live) {  // last read of this accumulator: hand it back
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive_pf(&ctl.acc_empty[as]);
+                        if (!any_live) break;
                     }
                     if (MODE == MODE_GATEUP) {
-                        const int out_row = T.bx * 64 + quad * 16 + (lane & 15);
-                        __half* dst_base = T.shared ? L.inter_shared : L.inter_routed;
-                        const bool lower = lane < 16;  // as in k_prefill_gemm: columns jj and jj + 16 in one pass
+                        if (hdst) {
+                            uint32_t h[8];
 #pragma unroll
-                        for (int jj = 0; jj < 16; ++jj) {
-                            const float lo = __uint_as_float(r[jj]) * inv, hi = __uint_as_float(r[jj + 16]) * inv;
-                            const float recv = __shfl_xor_sync(0xffffffffu, lower ? hi : lo, 16);
-                            const float gv = lower ? lo : recv;
-                            const float uv = lower ? recv : hi;
-                            const int col = cb * 32 + jj + (lower ? 0 : 16);
-                            if (col < ncols) {
-                                float v = __fdiv_rn(gv, 1.0f + expf(-gv)) * uv;
-                                dst_base[(size_t)(first + col) * L.rows + out_row] = __float2half_rn(v);
+                            for (int i = 0; i < 8; ++i) {
+                                const float g0 = __uint_as_float(r[2 * i]) * inv, g1 = __uint_as_float(r[2 * i + 1]) * inv;
+                                const float u0 = __uint_as_float(r[16 + 2 * i]) * inv,
+                                            u1 = __uint_as_float(r[17 + 2 * i]) * inv;
+                                const __half2 v = __floats2half2_rn(__fdiv_rn(g0, 1.0f + expf(-g0)) * u0,
+                                                                    __fdiv_rn(g1, 1.0f + expf(-g1)) * u1);
+                                h[i] = *(const uint32_t*)&v;
                             }
+                            uint4* o = (uint4*)(hdst + cb * 16);
+                            o[0] = make_uint4(h[0], h[1], h[2], h[3]);
+                            o[1] = make_uint4(h[4], h[5], h[6], h[7]);
                         }
                     } else {
-                        const int out_row = T.bx * kPfTileM + quad * 32 + lane;
-                        float my_wgt = col_wgt[0];
-                        float* my_row = col_row[0];
-                        if (cb == 1) { my_wgt = col_wgt[1]; my_row = col_row[1]; }
-                        if (cb == 2) { my_wgt = col_wgt[2]; my_row = col_row[2]; }
-                        if (cb == 3) { my_wgt = col_wgt[3]; my_row = col_row[3]; }
 #pragma unroll
-                        for (int jj = 0; jj < 32; ++jj) {
-                            const int col = cb * 32 + jj;
-                            const float wgt = __shfl_sync(0xffffffffu, my_wgt, jj);
-                            float* row = (float*)__shfl_sync(0xffffffffu, (unsigned long long)my_row, jj);
-                            if (col < ncols) {
-                                const float v = __uint_as_float(r[jj]);
-                                if (T.shared) L.shexp[(size_t)(first + col) * L.rows + out_row] = v * inv;
-                                else if (row) row[out_row] = wgt * v;
+                        for (int half = 0; half < 2; ++half) {
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) {
+                                const int q = half * 16 + 4 * c;
+                                *(float4*)(epi_stage[ew] + lane * 16 + ((c ^ ((lane >> 1) & 3)) << 2)) =
+                                    make_float4(factor * __uint_as_float(r[q]), factor * __uint_as_float(r[q + 1]),
+                                                factor * __uint_as_float(r[q + 2]), factor * __uint_as_float(r[q + 3]));
                             }
+                            __syncwarp();
+#pragma unroll
+                            for (int it = 0; it < 4; ++it) {
+                                const int R = it * 8 + (lane >> 2), c = lane & 3;
+                                const float4 v = *(const float4*)(epi_stage[ew] + R * 16 + ((c ^ ((R >> 1) & 3)) << 2));
+                                float* p = epi_dst[ew][R];
+                                if (p) *(float4*)(p + cb * 32 + half * 16 + c * 4) = v;
+                            }
+                            __syncwarp();
                         }
                     }
                 }
