@@ -1826,7 +1826,13 @@ int xabe_moe_set_tuning(xabe_moe* m, int key, int value) {
                 m->pf_item_cols = kPfTileN;
                 return XABE_OK;
             }
-            return setup_wide_prefill(m);
+            {
+                const int rc = setup_wide_prefill(m);
+                // 2, 3: items of two or three 128-column tiles (the B ring then runs further ahead of the MMAs)
+                if (!rc && m->pf_item_cols > kPfTileN && value >= 2 && value < kPfWideMaxCt)
+                    m->pf_item_cols = value * kPfTileN;
+                return rc;
+            }
         default: return fail(XABE_ERR_INVALID_ARGUMENT, "unknown tuning key %d", key);
     }
 }
