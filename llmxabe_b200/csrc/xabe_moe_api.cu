@@ -861,6 +861,26 @@ int launch_rms_norm(xabe_moe* m, cudaStream_t st, const float* x, const float* w
     if (block < 32) block = 32;
     if (gate_w && block < 256) gate_w = nullptr;  // (hidden is a multiple of 256, so this does not happen)
     const size_t smem = gate_w ? (size_t)m->g.hidden * sizeof(float) : 0;
+    // many rows: blocks that walk rows with the next row's loads in flight (same sums, same order)
+    const int ept = ((int)m->g.hidden + block - 1) / block;
+    if (!gate_w && m->g.max_tokens >= 256 && ept <= 8) {
+        const dim3 grid((unsigned)std::min<uint32_t>(m->g.max_tokens, 2u * (uint32_t)m->sm_count));
+        auto go = [&](auto kern) -> int {
+            CUDA_TRY(launch_pdl(m->pdl, kern, grid, dim3(block), 0, st, x, weight, m->normed, m->normed_h,
+                                (const int*)m->valid_tokens, (int)m->g.hidden, m->eps));
+            return XABE_OK;
+        };
+        switch (ept) {
+            case 1: return go(k_rms_norm_stream<1>);
+            case 2: return go(k_rms_norm_stream<2>);
+            case 3: return go(k_rms_norm_stream<3>);
+            case 4: return go(k_rms_norm_stream<4>);
+            case 5: return go(k_rms_norm_stream<5>);
+            case 6: return go(k_rms_norm_stream<6>);
+            case 7: return go(k_rms_norm_stream<7>);
+            default: return go(k_rms_norm_stream<8>);
+        }
+    }
     CUDA_TRY(launch_pdl(m->pdl, k_rms_norm, dim3(m->g.max_tokens), dim3(block), smem, st, x, weight, m->normed,
                         m->normed_h, m->valid_tokens, (int)m->g.hidden, m->eps, gate_w, m->gate));
     return XABE_OK;
