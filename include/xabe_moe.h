@@ -310,7 +310,8 @@ int xabe_moe_force_prefill_path(xabe_moe* m, int on);
 #define XABE_TUNE_ROWS_MIN_TOKENS 3    /* narrowest handle that runs gate/up through k_gateup_rows (0 = never, -1 = default) */
 #define XABE_TUNE_ROUTER_REGW 4        /* router kernel with expert rows in registers: 0 off, 1 on, -1 by width */
 #define XABE_TUNE_FORCE_TILE_KERNELS 5 /* 1: the one-tile-per-CTA expert kernels everywhere */
-#define XABE_TUNE_PREFILL_WIDE 6       /* 1: k_prefill_gemm_wide (four accumulators per unpacked weight pair), 0: off */
+#define XABE_TUNE_PREFILL_WIDE 6       /* 1 or 4: k_prefill_gemm_wide with up to four 128-column accumulators per unpacked
+                                          weight pair; 2, 3: up to two or three; 0: k_prefill_gemm (one) */
 #define XABE_TUNE_FUSED_DECODE 7       /* bit 0: handles under 16 tokens fold gate-and-combine into the down launch;
                                           bit 1: handles up to 256 tokens run norm, router, routing and dispatch as one
                                           launch.  3 = a three-launch layer at up to 15 tokens; both measured no
