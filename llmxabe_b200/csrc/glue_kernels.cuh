@@ -357,10 +357,10 @@ __global__ void __launch_bounds__(256, 1) k_router_logits_wide(const float* __re
 // rows) arrive four at a time through a ring of bulk TMA copies issued several
 // stages ahead, so neither the weights nor the L2 latency of the activations
 // sit in the inner loop (k_router_logits_wide spends one shared load per four
-// multiply-adds and waits for its prefetched global loads once per tile).  The
-// 32 accumulators of a token pair go through the same transposed tree as in
-// k_router_logits_wide, here with exactly one (output, group) per thread, on a
-// double-buffered scratch so that a pair costs two block barriers.
+// multiply-adds and waits for its prefetched global loads once per tile).  A warp
+// is one lane group of every output, so the 32 trees of a token pair run inside the
+// warp (warp_trees32: no shared memory, no barrier); only the eight group totals
+// per output cross warps, through 1 KB of shared memory and one block barrier.
 // grid: (E / 16, token shares); block 256;
 // dynamic shared memory: router_regw_smem(hidden).
 // ---------------------------------------------------------------------------
@@ -370,8 +370,35 @@ constexpr int kRrStageTokens = 4;                   // token rows per ring stage
 constexpr int kRrStages = 4;
 
 __host__ __device__ inline size_t router_regw_smem(int hidden) {
-    return (size_t)kRrStages * kRrStageTokens * hidden * 4 + (size_t)2 * kRrOutputs * kRwPitch * 4 +
-           (size_t)2 * kRrOutputs * 8 * 4;
+    return (size_t)kRrStages * kRrStageTokens * hidden * 4 + (size_t)2 * kRrOutputs * 8 * 4;
+}
+
+// The shuffle-down trees of 32 outputs over the 32 lanes of a warp, all at once: `a[o]` is this lane's
+// addend of output o.  At the level with offset 16 lanes l and l ^ 16 swap halves -- the lower lane keeps
+// outputs 0-15 and gets the partner's addends of those, the upper lane keeps 16-31 -- and each adds what
+// it received to what it kept; then offset 8 within each half, and so on.  Every sum formed is
+// v[l] + v[l + off] of the shuffle-down tree of its output (the left operand is the lower lane's), so
+// after five levels lane o holds in a[0] exactly what lane 0 of `for (off = 16; off; off >>= 1)
+// v += shfl_down(v, off)` would hold for output o.  31 shuffles per lane instead of 160, and no shared
+// memory.
+template <int HALF>
+__device__ __forceinline__ void warp_trees_level(float (&a)[32], int lane) {
+    const bool upper = (lane & HALF) != 0;
+#pragma unroll
+    for (int i = 0; i < HALF; ++i) {
+        const float send = upper ? a[i] : a[HALF + i];
+        const float keep = upper ? a[HALF + i] : a[i];
+        const float recv = __shfl_xor_sync(0xffffffffu, send, HALF);
+        a[i] = upper ? __fadd_rn(recv, keep) : __fadd_rn(keep, recv);
+    }
+}
+__device__ __forceinline__ float warp_trees32(float (&a)[32], int lane) {
+    warp_trees_level<16>(a, lane);
+    warp_trees_level<8>(a, lane);
+    warp_trees_level<4>(a, lane);
+    warp_trees_level<2>(a, lane);
+    warp_trees_level<1>(a, lane);
+    return a[0];
 }
 
 template <int NI>
@@ -386,8 +413,7 @@ __global__ void __launch_bounds__(256, 1) k_router_logits_regw(const float* __re
     constexpr int hidden = NI * 256;
     extern __shared__ __align__(128) float rr_smem[];
     float* xs = rr_smem;                                             // [stages][4][hidden]
-    float* red = xs + kRrStages * kRrStageTokens * hidden;           // [2][32][257]: accumulators, transposed
-    float* group_tot = red + 2 * kRrOutputs * kRwPitch;              // [2][32][8]
+    float* group_tot = xs + kRrStages * kRrStageTokens * hidden;     // [2][32][8]
     __shared__ __align__(8) uint64_t full[kRrStages];
     const int tid = threadIdx.x;
     const int e0 = blockIdx.x * kRwExperts;
@@ -427,13 +453,10 @@ __global__ void __launch_bounds__(256, 1) k_router_logits_regw(const float* __re
         for (int p = 0; p < kRrStageTokens / kRrTokens; ++p, ++pair_count) {
             if (t_stage + p * kRrTokens >= live) break;  // uniform: the batch ended inside this stage
             const int buf = pair_count & 1;
-            float* redb = red + buf * kRrOutputs * kRwPitch;
             float* totb = group_tot + buf * kRrOutputs * 8;
-            float acc[kRwExperts][kRrTokens];
+            float acc[kRrOutputs];  // output o = 2 e + u
 #pragma unroll
-            for (int e = 0; e < kRwExperts; ++e)
-#pragma unroll
-                for (int u = 0; u < kRrTokens; ++u) acc[e][u] = 0.0f;
+            for (int o = 0; o < kRrOutputs; ++o) acc[o] = 0.0f;
             // a row past the live tokens was not copied: its sums are formed from stale bytes and never stored
 #pragma unroll
             for (int i = 0; i < NI; ++i) {
@@ -443,32 +466,19 @@ __global__ void __launch_bounds__(256, 1) k_router_logits_regw(const float* __re
 #pragma unroll
                 for (int e = 0; e < kRwExperts; ++e)
 #pragma unroll
-                    for (int u = 0; u < kRrTokens; ++u) acc[e][u] = fmaf(wr[e][i], xv[u], acc[e][u]);
+                    for (int u = 0; u < kRrTokens; ++u)
+                        acc[e * kRrTokens + u] = fmaf(wr[e][i], xv[u], acc[e * kRrTokens + u]);
             }
-#pragma unroll
-            for (int e = 0; e < kRwExperts; ++e)
-#pragma unroll
-                for (int u = 0; u < kRrTokens; ++u) redb[(e * kRrTokens + u) * kRwPitch + tid] = acc[e][u];
+            // this warp is lane group tid / 32 of every output: its 32 trees, then lane o's total of output o
+            const float tot = warp_trees32(acc, tid & 31);
+            totb[(tid & 31) * 8 + (tid >> 5)] = tot;
             __syncthreads();
             // every thread has read this stage's last pair once it is past the barrier above: refill the slot
             if (tid == 0 && (p == kRrStageTokens / kRrTokens - 1 || t_stage + (p + 1) * kRrTokens >= live) &&
                 k + kRrStages < n_stages)
                 issue(k + kRrStages);
-            {
-                // thread -> output o = tid % 32, lane group g = tid / 32: the shuffle-down tree of that group
-                const int o = tid & 31, g = tid >> 5;
-                const float* src = redb + o * kRwPitch + g * 32;
-                float v[32];
-#pragma unroll
-                for (int l = 0; l < 32; ++l) v[l] = src[l];
-#pragma unroll
-                for (int off = 16; off > 0; off >>= 1)
-#pragma unroll
-                    for (int l = 0; l < off; ++l) v[l] = v[l] + v[l + off];  // what lane l holds after shuffle-down by off
-                totb[o * 8 + g] = v[0];
-            }
-            __syncthreads();
-            // the other buffer's tree reads ended before the barrier above, so the next pair may overwrite it
+            // `group_tot` alternates between two copies by pair: the copy written two pairs on is read here
+            // by warp 0 before that warp reaches the barrier in between
             if (tid < kRrOutputs) {
                 float total = 0.0f;
 #pragma unroll
