@@ -360,7 +360,7 @@ __global__ void __launch_bounds__(256, 1) k_router_logits_wide(const float* __re
 // multiply-adds and waits for its prefetched global loads once per tile).  A warp
 // is one lane group of every output, so the 32 trees of a token pair run inside the
 // warp (warp_trees32: no shared memory, no barrier); only the eight group totals
-// per output cross warps, through 1 KB of shared memory and one block barrier.
+// per output cross warps, through shared memory and one block barrier per ring stage.
 // grid: (E / 16, token shares); block 256;
 // dynamic shared memory: router_regw_smem(hidden).
 // ---------------------------------------------------------------------------
@@ -370,7 +370,7 @@ constexpr int kRrStageTokens = 4;                   // token rows per ring stage
 constexpr int kRrStages = 4;
 
 __host__ __device__ inline size_t router_regw_smem(int hidden) {
-    return (size_t)kRrStages * kRrStageTokens * hidden * 4 + (size_t)2 * kRrOutputs * 8 * 4;
+    return (size_t)kRrStages * kRrStageTokens * hidden * 4 + (size_t)2 * (kRrStageTokens / kRrTokens) * kRrOutputs * 8 * 4;
 }
 
 // The shuffle-down trees of 32 outputs over the 32 lanes of a warp, all at once: `a[o]` is this lane's
@@ -413,7 +413,7 @@ __global__ void __launch_bounds__(256, 1) k_router_logits_regw(const float* __re
     constexpr int hidden = NI * 256;
     extern __shared__ __align__(128) float rr_smem[];
     float* xs = rr_smem;                                             // [stages][4][hidden]
-    float* group_tot = xs + kRrStages * kRrStageTokens * hidden;     // [2][32][8]
+    float* group_tot = xs + kRrStages * kRrStageTokens * hidden;     // [2 stages][2 pairs][32][8]
     __shared__ __align__(8) uint64_t full[kRrStages];
     const int tid = threadIdx.x;
     const int e0 = blockIdx.x * kRwExperts;
@@ -443,17 +443,18 @@ __global__ void __launch_bounds__(256, 1) k_router_logits_regw(const float* __re
 #pragma unroll
         for (int i = 0; i < NI; ++i) wr[e][i] = __ldg(w + (size_t)(e0 + e) * hidden + i * 256 + tid);
     __syncthreads();  // the barriers are initialised
-    int pair_count = 0;
+    if (!__syncthreads_and(mbar_wait_bounded(&full[0], 0u, status))) return;
+    constexpr int kPairs = kRrStageTokens / kRrTokens;  // token pairs per ring stage
     for (int k = 0; k < n_stages; ++k) {
         const int slot = k % kRrStages;
-        if (!__syncthreads_and(mbar_wait_bounded(&full[slot], (uint32_t)(k / kRrStages) & 1u, status))) return;
         const float* xk = xs + (size_t)slot * kRrStageTokens * hidden;
         const int t_stage = (stage0 + k) * kRrStageTokens;
+        // `group_tot` holds the totals of two stages (four pairs): a copy is rewritten two stages after it
+        // was written, one block barrier after the warp that reads it has done so
+        float* tot_stage = group_tot + (k & 1) * kPairs * kRrOutputs * 8;
 #pragma unroll
-        for (int p = 0; p < kRrStageTokens / kRrTokens; ++p, ++pair_count) {
+        for (int p = 0; p < kPairs; ++p) {
             if (t_stage + p * kRrTokens >= live) break;  // uniform: the batch ended inside this stage
-            const int buf = pair_count & 1;
-            float* totb = group_tot + buf * kRrOutputs * 8;
             float acc[kRrOutputs];  // output o = 2 e + u
 #pragma unroll
             for (int o = 0; o < kRrOutputs; ++o) acc[o] = 0.0f;
@@ -471,19 +472,27 @@ __global__ void __launch_bounds__(256, 1) k_router_logits_regw(const float* __re
             }
             // this warp is lane group tid / 32 of every output: its 32 trees, then lane o's total of output o
             const float tot = warp_trees32(acc, tid & 31);
-            totb[(tid & 31) * 8 + (tid >> 5)] = tot;
-            __syncthreads();
-            // every thread has read this stage's last pair once it is past the barrier above: refill the slot
-            if (tid == 0 && (p == kRrStageTokens / kRrTokens - 1 || t_stage + (p + 1) * kRrTokens >= live) &&
-                k + kRrStages < n_stages)
-                issue(k + kRrStages);
-            // `group_tot` alternates between two copies by pair: the copy written two pairs on is read here
-            // by warp 0 before that warp reaches the barrier in between
-            if (tid < kRrOutputs) {
+            tot_stage[p * kRrOutputs * 8 + (tid & 31) * 8 + (tid >> 5)] = tot;
+        }
+        // One block barrier per stage: it publishes the group totals, tells thread 0 that every thread has
+        // read the stage's rows, and agrees on whether the next stage's rows (requested kRrStages stages
+        // ago) have landed.
+        bool ok = true;
+        if (k + 1 < n_stages)
+            ok = mbar_wait_bounded(&full[(k + 1) % kRrStages], (uint32_t)((k + 1) / kRrStages) & 1u, status);
+        if (!__syncthreads_and(ok)) return;
+        if (tid == 0 && k + kRrStages < n_stages) issue(k + kRrStages);
+        // the eight group totals of an output, ascending, from +0; the pairs of a stage go to different warps
+#pragma unroll
+        for (int p = 0; p < kPairs; ++p) {
+            if (t_stage + p * kRrTokens >= live) break;
+            if ((tid >> 5) == ((k * kPairs + p) & 7)) {
+                const int o = tid & 31;
+                const float* totb = tot_stage + p * kRrOutputs * 8;
                 float total = 0.0f;
 #pragma unroll
-                for (int g = 0; g < 8; ++g) total += totb[tid * 8 + g];
-                const int e = e0 + (tid >> 1), t = t_stage + p * kRrTokens + (tid & 1);
+                for (int g = 0; g < 8; ++g) total += totb[o * 8 + g];
+                const int e = e0 + (o >> 1), t = t_stage + p * kRrTokens + (o & 1);
                 if (t < live && e < num_experts)
                     logits[(size_t)t * num_experts + e] = bias ? __fadd_rn(total, bias[e]) : total;
             }
