@@ -308,7 +308,8 @@ int xabe_moe_force_prefill_path(xabe_moe* m, int on);
 #define XABE_TUNE_STREAM_STAGES 1      /* ring depth cap of the streaming kernels (0 = as many as fit) */
 #define XABE_TUNE_STREAM_RUNS 2        /* k_expert_stream work split override (0 = the kernel's choice) */
 #define XABE_TUNE_ROWS_MIN_TOKENS 3    /* narrowest handle that runs gate/up through k_gateup_rows (0 = never, -1 = default) */
-#define XABE_TUNE_ROUTER_REGW 4        /* router kernel with expert rows in registers: 0 off, 1 on, -1 by width */
+#define XABE_TUNE_ROUTER_REGW 4        /* router kernel with expert rows in registers: 0 off, 1 sixteen rows per CTA
+                                          (one CTA per SM), 2 eight rows (two CTAs per SM), -1 by width (from 256 tokens: 2) */
 #define XABE_TUNE_FORCE_TILE_KERNELS 5 /* 1: the one-tile-per-CTA expert kernels everywhere */
 #define XABE_TUNE_PREFILL_WIDE 6       /* 1 or 4: k_prefill_gemm_wide with up to four 128-column accumulators per unpacked
                                           weight pair; 2, 3: up to two or three; 0: k_prefill_gemm (one) */

@@ -364,13 +364,12 @@ __global__ void __launch_bounds__(256, 1) k_router_logits_wide(const float* __re
 // grid: (E / 16, token shares); block 256;
 // dynamic shared memory: router_regw_smem(hidden).
 // ---------------------------------------------------------------------------
-constexpr int kRrTokens = 2;                        // tokens per accumulator set
-constexpr int kRrOutputs = kRwExperts * kRrTokens;  // 32
+constexpr int kRrOutputs = 32;                      // outputs per accumulator set: NE experts x 32 / NE tokens
 constexpr int kRrStageTokens = 4;                   // token rows per ring stage
-constexpr int kRrStages = 4;
+__host__ __device__ constexpr int rr_stages(int ne) { return ne == 16 ? 4 : 3; }
 
-__host__ __device__ inline size_t router_regw_smem(int hidden) {
-    return (size_t)kRrStages * kRrStageTokens * hidden * 4 + (size_t)2 * (kRrStageTokens / kRrTokens) * kRrOutputs * 8 * 4;
+__host__ __device__ inline size_t router_regw_smem(int hidden, int ne) {
+    return (size_t)rr_stages(ne) * kRrStageTokens * hidden * 4 + (size_t)2 * (kRrStageTokens * ne / 32) * kRrOutputs * 8 * 4;
 }
 
 // The shuffle-down trees of 32 outputs over the 32 lanes of a warp, all at once: `a[o]` is this lane's
@@ -401,8 +400,11 @@ __device__ __forceinline__ float warp_trees32(float (&a)[32], int lane) {
     return a[0];
 }
 
-template <int NI>
-__global__ void __launch_bounds__(256, 1) k_router_logits_regw(const float* __restrict__ w,
+// NE: expert rows per CTA held in registers.  16: one CTA per SM, two tokens per accumulator set.
+// 8: two CTAs per SM (half the weight registers), four tokens per set, a three-stage ring; twice as
+// many CTAs read each token row.
+template <int NI, int NE>
+__global__ void __launch_bounds__(256, NE == 16 ? 1 : 2) k_router_logits_regw(const float* __restrict__ w,
                                                                const float* __restrict__ x,
                                                                const int* __restrict__ valid_tokens,
                                                                int num_experts, const float* __restrict__ bias,
@@ -411,12 +413,14 @@ __global__ void __launch_bounds__(256, 1) k_router_logits_regw(const float* __re
     pdl_launch_dependents();
     pdl_wait();
     constexpr int hidden = NI * 256;
+    constexpr int kRrTokens = kRrOutputs / NE;  // tokens per accumulator set
+    constexpr int kRrStages = rr_stages(NE);
     extern __shared__ __align__(128) float rr_smem[];
     float* xs = rr_smem;                                             // [stages][4][hidden]
-    float* group_tot = xs + kRrStages * kRrStageTokens * hidden;     // [2 stages][2 pairs][32][8]
+    float* group_tot = xs + kRrStages * kRrStageTokens * hidden;     // [2 stages][sets per stage][32][8]
     __shared__ __align__(8) uint64_t full[kRrStages];
     const int tid = threadIdx.x;
-    const int e0 = blockIdx.x * kRwExperts;
+    const int e0 = blockIdx.x * NE;
     const int live = *valid_tokens;
     // this CTA's tokens: a contiguous range, a whole number of stages except at the end of the batch
     const int stages_total = (live + kRrStageTokens - 1) / kRrStageTokens;
@@ -437,9 +441,9 @@ __global__ void __launch_bounds__(256, 1) k_router_logits_regw(const float* __re
         fence_mbar_init();
         for (int k = 0; k < min(kRrStages, n_stages); ++k) issue(k);
     }
-    float wr[kRwExperts][NI];
+    float wr[NE][NI];
 #pragma unroll
-    for (int e = 0; e < kRwExperts; ++e)
+    for (int e = 0; e < NE; ++e)
 #pragma unroll
         for (int i = 0; i < NI; ++i) wr[e][i] = __ldg(w + (size_t)(e0 + e) * hidden + i * 256 + tid);
     __syncthreads();  // the barriers are initialised
@@ -455,7 +459,7 @@ __global__ void __launch_bounds__(256, 1) k_router_logits_regw(const float* __re
 #pragma unroll
         for (int p = 0; p < kPairs; ++p) {
             if (t_stage + p * kRrTokens >= live) break;  // uniform: the batch ended inside this stage
-            float acc[kRrOutputs];  // output o = 2 e + u
+            float acc[kRrOutputs];  // output o = e * tokens + u
 #pragma unroll
             for (int o = 0; o < kRrOutputs; ++o) acc[o] = 0.0f;
             // a row past the live tokens was not copied: its sums are formed from stale bytes and never stored
@@ -465,7 +469,7 @@ __global__ void __launch_bounds__(256, 1) k_router_logits_regw(const float* __re
 #pragma unroll
                 for (int u = 0; u < kRrTokens; ++u) xv[u] = xk[(p * kRrTokens + u) * hidden + i * 256 + tid];
 #pragma unroll
-                for (int e = 0; e < kRwExperts; ++e)
+                for (int e = 0; e < NE; ++e)
 #pragma unroll
                     for (int u = 0; u < kRrTokens; ++u)
                         acc[e * kRrTokens + u] = fmaf(wr[e][i], xv[u], acc[e * kRrTokens + u]);
@@ -492,7 +496,7 @@ __global__ void __launch_bounds__(256, 1) k_router_logits_regw(const float* __re
                 float total = 0.0f;
 #pragma unroll
                 for (int g = 0; g < 8; ++g) total += totb[o * 8 + g];
-                const int e = e0 + (o >> 1), t = t_stage + p * kRrTokens + (o & 1);
+                const int e = e0 + o / kRrTokens, t = t_stage + p * kRrTokens + o % kRrTokens;
                 if (t < live && e < num_experts)
                     logits[(size_t)t * num_experts + e] = bias ? __fadd_rn(total, bias[e]) : total;
             }

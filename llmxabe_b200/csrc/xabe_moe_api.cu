@@ -894,9 +894,12 @@ int launch_router(xabe_moe* m, cudaStream_t st, const float* router, const float
     bool regw = g.max_tokens >= 256;
     if (m->router_regw >= 0) regw = m->router_regw != 0;
     if (regw && g.max_tokens >= 2 && g.num_experts % kRwExperts == 0 && (g.hidden == 2048 || g.hidden == 1024)) {
-        const size_t smem_r = router_regw_smem((int)g.hidden);
-        unsigned gx = g.num_experts / kRwExperts;
-        unsigned gy = (unsigned)m->sm_count / gx;
+        // eight expert rows per CTA and two CTAs per SM (measured 0.085 against 0.091 ms at 2048 tokens);
+        // router_regw 1 selects sixteen rows and one CTA per SM
+        const int ne = m->router_regw == 1 ? 16 : 8;
+        const size_t smem_r = router_regw_smem((int)g.hidden, ne);
+        unsigned gx = g.num_experts / ne;
+        unsigned gy = (unsigned)m->sm_count * (ne == 16 ? 1u : 2u) / gx;
         unsigned pairs = (g.max_tokens + kRrStageTokens - 1) / kRrStageTokens;
         if (gy < 1) gy = 1;
         if (gy > pairs) gy = pairs;
@@ -906,7 +909,8 @@ int launch_router(xabe_moe* m, cudaStream_t st, const float* router, const float
                                 (const int*)m->valid_tokens, (int)g.num_experts, bias, m->logits, m->status));
             return XABE_OK;
         };
-        return g.hidden == 2048 ? go_regw(k_router_logits_regw<8>) : go_regw(k_router_logits_regw<4>);
+        if (ne == 8) return g.hidden == 2048 ? go_regw(k_router_logits_regw<8, 8>) : go_regw(k_router_logits_regw<4, 8>);
+        return g.hidden == 2048 ? go_regw(k_router_logits_regw<8, 16>) : go_regw(k_router_logits_regw<4, 16>);
     }
     // wide passes: sixteen expert rows per CTA, the tokens shared out over the SMs
     if (g.max_tokens >= 32 && g.num_experts % kRwExperts == 0 && (g.hidden == 2048 || g.hidden == 1024)) {

@@ -164,14 +164,15 @@ def test_rows_are_bit_identical_across_the_kernel_switches(torch_cuda, oracle, l
 
 @pytest.mark.parametrize("tokens,max_tokens", [(257, 257), (301, 512), (2, 256), (1030, 1030)])
 def test_router_kernels_agree_bit_for_bit(torch_cuda, oracle, layers, tokens, max_tokens):
-    """Two router kernels serve the prefill widths (token rows broadcast from shared memory; expert rows
-    held in registers, the default from 256 tokens): identical logits, equal to the oracle's."""
+    """Three router launches serve the prefill widths (token rows broadcast from shared memory; expert rows
+    held in registers, sixteen per CTA with one CTA per SM or eight with two): identical logits, equal to
+    the oracle's."""
     from llmxabe_b200 import synth
     from llmxabe_b200.moe import MoeBlock, MoeGeometry
     _, ol, w = layers("q6k")
     x = synth.activations(tokens, 2048, seed=0, layer=7700 + tokens)
     want = oracle.moe_block_forward(ol, x, dev_order=True)["logits"]
-    for mode in (1, 0):
+    for mode in (2, 1, 0):
         blk = MoeBlock(MoeGeometry.qwen3_6(32, max_tokens))
         blk.moe.set_tuning("router_regw", mode)
         got = run_block(blk, w, x, max_tokens)
