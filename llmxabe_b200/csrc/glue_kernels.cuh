@@ -238,21 +238,47 @@ __global__ void __launch_bounds__(128) k_router_logits(const float* __restrict__
 // j = v, v + 256, ... ascending.  It keeps sixteen expert rows in shared memory
 // (one bulk TMA copy) and walks its share of the tokens four at a time, so a
 // thread holds 64 accumulators and does 64 multiply-adds per 16 shared-memory
-// and 4 (prefetched) global loads.  The shuffle-down tree of each group of 32
-// lanes is then evaluated by ONE thread per (output, group) on a transposed
-// copy in shared memory, in the tree's exact pairing, and the eight group
-// totals are added in ascending order starting from +0: five shuffles and five
-// adds per accumulator per lane become 31 adds per output per group.
+// and 4 (prefetched) global loads.  A warp is one group of 32 lanes of every
+// output, so the shuffle-down trees run inside the warp, 32 outputs at a time
+// (warp_trees32 below), and the eight group totals are added in ascending order
+// starting from +0.
 // grid: (E / 16, token shares); block 256;
-// dynamic shared memory: 16 * hidden * 4 + 64 * 257 * 4 + 512 * 4 bytes.
+// dynamic shared memory: 16 * hidden * 4 + 512 * 4 bytes.
 // ---------------------------------------------------------------------------
+// The shuffle-down trees of 32 outputs over the 32 lanes of a warp, all at once: `a[o]` is this lane's
+// addend of output o.  At the level with offset 16 lanes l and l ^ 16 swap halves -- the lower lane keeps
+// outputs 0-15 and gets the partner's addends of those, the upper lane keeps 16-31 -- and each adds what
+// it received to what it kept; then offset 8 within each half, and so on.  Every sum formed is
+// v[l] + v[l + off] of the shuffle-down tree of its output (the left operand is the lower lane's), so
+// after five levels lane o holds in a[0] exactly what lane 0 of `for (off = 16; off; off >>= 1)
+// v += shfl_down(v, off)` would hold for output o.  31 shuffles per lane instead of 160, and no shared
+// memory.
+template <int HALF>
+__device__ __forceinline__ void warp_trees_level(float (&a)[32], int lane) {
+    const bool upper = (lane & HALF) != 0;
+#pragma unroll
+    for (int i = 0; i < HALF; ++i) {
+        const float send = upper ? a[i] : a[HALF + i];
+        const float keep = upper ? a[HALF + i] : a[i];
+        const float recv = __shfl_xor_sync(0xffffffffu, send, HALF);
+        a[i] = upper ? __fadd_rn(recv, keep) : __fadd_rn(keep, recv);
+    }
+}
+__device__ __forceinline__ float warp_trees32(float (&a)[32], int lane) {
+    warp_trees_level<16>(a, lane);
+    warp_trees_level<8>(a, lane);
+    warp_trees_level<4>(a, lane);
+    warp_trees_level<2>(a, lane);
+    warp_trees_level<1>(a, lane);
+    return a[0];
+}
+
 constexpr int kRwExperts = 16;
 constexpr int kRwTokens = 4;
 constexpr int kRwOutputs = kRwExperts * kRwTokens;
-constexpr int kRwPitch = 257;  // odd: the tree threads read 32 rows at one column without bank conflicts
 
 __host__ __device__ inline size_t router_wide_smem(int hidden) {
-    return (size_t)kRwExperts * hidden * 4 + (size_t)kRwOutputs * kRwPitch * 4 + 512 * 4;
+    return (size_t)kRwExperts * hidden * 4 + 512 * 4;
 }
 
 template <int NI>
@@ -267,8 +293,7 @@ __global__ void __launch_bounds__(256, 1) k_router_logits_wide(const float* __re
     constexpr int hidden = NI * 256;
     extern __shared__ __align__(128) float rw_smem[];
     float* w_s = rw_smem;                                 // [16][hidden]
-    float* red = rw_smem + kRwExperts * hidden;           // [64][257]: accumulators, transposed
-    float* group_tot = red + kRwOutputs * kRwPitch;       // [64][8]
+    float* group_tot = rw_smem + kRwExperts * hidden;     // [64][8]
     __shared__ __align__(8) uint64_t bar;
     const int tid = threadIdx.x;
     const int e0 = blockIdx.x * kRwExperts;
@@ -305,38 +330,28 @@ __global__ void __launch_bounds__(256, 1) k_router_logits_wide(const float* __re
 #pragma unroll
             for (int i = 0; i < NI; ++i) xc[u][i] = xn[u][i];
         if (tile + 1 < tile1) load_tile(tile + 1);  // in flight during this tile's arithmetic
-        float acc[kRwExperts][kRwTokens];
+        // outputs o = 4 e + u, in two halves of 32 (experts 0-7 and 8-15 of the CTA)
+        float acc[2][32];
 #pragma unroll
-        for (int e = 0; e < kRwExperts; ++e)
+        for (int h = 0; h < 2; ++h)
 #pragma unroll
-            for (int u = 0; u < kRwTokens; ++u) acc[e][u] = 0.0f;
+            for (int o = 0; o < 32; ++o) acc[h][o] = 0.0f;
 #pragma unroll
         for (int i = 0; i < NI; ++i) {
 #pragma unroll
             for (int e = 0; e < kRwExperts; ++e) {
                 const float wv = w_s[e * hidden + i * 256 + tid];
 #pragma unroll
-                for (int u = 0; u < kRwTokens; ++u) acc[e][u] = fmaf(wv, xc[u][i], acc[e][u]);
+                for (int u = 0; u < kRwTokens; ++u)
+                    acc[e >> 3][(e & 7) * kRwTokens + u] = fmaf(wv, xc[u][i], acc[e >> 3][(e & 7) * kRwTokens + u]);
             }
         }
+        // this warp is lane group tid / 32 of every output: lane o ends with the totals of outputs o and 32 + o
+        __syncthreads();  // the previous tile's totals have been read
 #pragma unroll
-        for (int e = 0; e < kRwExperts; ++e)
-#pragma unroll
-            for (int u = 0; u < kRwTokens; ++u) red[(e * kRwTokens + u) * kRwPitch + tid] = acc[e][u];
-        __syncthreads();
-        // thread -> output o = tid % 64, lane groups g = tid / 64 and g + 4
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-            const int o = tid & 63, g = (tid >> 6) + 4 * k;
-            const float* src = red + o * kRwPitch + g * 32;
-            float v[32];
-#pragma unroll
-            for (int l = 0; l < 32; ++l) v[l] = src[l];
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1)
-#pragma unroll
-                for (int l = 0; l < off; ++l) v[l] = v[l] + v[l + off];  // what lane l holds after shuffle-down by off
-            group_tot[o * 8 + g] = v[0];
+        for (int h = 0; h < 2; ++h) {
+            const float tot = warp_trees32(acc[h], tid & 31);
+            group_tot[(h * 32 + (tid & 31)) * 8 + (tid >> 5)] = tot;
         }
         __syncthreads();
         if (tid < kRwOutputs) {
@@ -370,34 +385,6 @@ __host__ __device__ constexpr int rr_stages(int ne) { return ne == 16 ? 4 : 3; }
 
 __host__ __device__ inline size_t router_regw_smem(int hidden, int ne) {
     return (size_t)rr_stages(ne) * kRrStageTokens * hidden * 4 + (size_t)2 * (kRrStageTokens * ne / 32) * kRrOutputs * 8 * 4;
-}
-
-// The shuffle-down trees of 32 outputs over the 32 lanes of a warp, all at once: `a[o]` is this lane's
-// addend of output o.  At the level with offset 16 lanes l and l ^ 16 swap halves -- the lower lane keeps
-// outputs 0-15 and gets the partner's addends of those, the upper lane keeps 16-31 -- and each adds what
-// it received to what it kept; then offset 8 within each half, and so on.  Every sum formed is
-// v[l] + v[l + off] of the shuffle-down tree of its output (the left operand is the lower lane's), so
-// after five levels lane o holds in a[0] exactly what lane 0 of `for (off = 16; off; off >>= 1)
-// v += shfl_down(v, off)` would hold for output o.  31 shuffles per lane instead of 160, and no shared
-// memory.
-template <int HALF>
-__device__ __forceinline__ void warp_trees_level(float (&a)[32], int lane) {
-    const bool upper = (lane & HALF) != 0;
-#pragma unroll
-    for (int i = 0; i < HALF; ++i) {
-        const float send = upper ? a[i] : a[HALF + i];
-        const float keep = upper ? a[HALF + i] : a[i];
-        const float recv = __shfl_xor_sync(0xffffffffu, send, HALF);
-        a[i] = upper ? __fadd_rn(recv, keep) : __fadd_rn(keep, recv);
-    }
-}
-__device__ __forceinline__ float warp_trees32(float (&a)[32], int lane) {
-    warp_trees_level<16>(a, lane);
-    warp_trees_level<8>(a, lane);
-    warp_trees_level<4>(a, lane);
-    warp_trees_level<2>(a, lane);
-    warp_trees_level<1>(a, lane);
-    return a[0];
 }
 
 // NE: expert rows per CTA held in registers.  16: one CTA per SM, two tokens per accumulator set.
