@@ -168,4 +168,35 @@ __device__ __forceinline__ float block_reduce_sum_pinned(float v, float* scratch
     return r;
 }
 
+// Exclusive prefix sum of one int per thread over the block (blockDim.x a multiple of 32, at most 1024):
+// shuffle scans inside the warps, then the warp totals.  `warp_sums` holds 33 ints; *total gets the
+// sum over the block.  Integers: any order gives the same result.
+__device__ __forceinline__ int block_exclusive_scan(int v, int* warp_sums, int* total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = (blockDim.x + 31) >> 5;
+    int incl = v;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += up;
+    }
+    if (lane == 31) warp_sums[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        const int w = lane < n_warps ? warp_sums[lane] : 0;
+        int wi = w;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, wi, off);
+            if (lane >= off) wi += up;
+        }
+        warp_sums[lane] = wi - w;  // exclusive prefix of the warp totals
+        if (lane == 31) warp_sums[32] = wi;
+    }
+    __syncthreads();
+    const int r = warp_sums[warp] + incl - v;
+    *total = warp_sums[32];
+    __syncthreads();  // warp_sums may be reused
+    return r;
+}
+
 }  // namespace xabe

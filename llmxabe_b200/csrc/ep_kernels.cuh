@@ -53,20 +53,15 @@ __global__ void k_ep_plan_ranks(int num_experts, int experts_per_rank, const int
                                 int* __restrict__ compact, int* __restrict__ rank_start,
                                 int* __restrict__ send_counts) {
     extern __shared__ int cnt_s[];  // [num_experts + 1]
+    __shared__ int warp_sums[33];
     int e = threadIdx.x;
-    if (e < num_experts) cnt_s[e] = expert_counts[e];
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int run = 0;
-        for (int i = 0; i < num_experts; ++i) {
-            int c = cnt_s[i];
-            cnt_s[i] = run;
-            run += c;
-        }
-        cnt_s[num_experts] = run;
+    int total = 0;
+    const int before = block_exclusive_scan(e < num_experts ? expert_counts[e] : 0, warp_sums, &total);
+    if (e <= num_experts) {
+        cnt_s[e] = before;  // e == num_experts: the total
+        compact[e] = before;
     }
     __syncthreads();
-    if (e <= num_experts) compact[e] = cnt_s[e];
     int world = num_experts / experts_per_rank;
     if (e < world) {
         rank_start[e] = cnt_s[e * experts_per_rank];

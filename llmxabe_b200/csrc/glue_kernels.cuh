@@ -627,11 +627,12 @@ __global__ void __launch_bounds__(32) k_align_count(const int* __restrict__ topk
     for (int i = c * perb + lane; i < (c + 1) * perb && i < block_capacity; i += 32) expert_ids[i] = -1;
 }
 
-// One block, one thread per expert (num_experts <= 1024).
+// One block, one thread per expert (num_experts <= 1024).  chunk_hist[c][e] becomes the number of expert
+// e's pairs in the chunks before c; the scatter adds the expert's padded offset itself.
 __global__ void k_align_scan(int num_experts, int n_chunks, int block_size, int* __restrict__ chunk_hist,
                              int* __restrict__ expert_offsets, int* __restrict__ expert_counts,
                              int* __restrict__ expert_ids, int* __restrict__ num_tokens_post_pad) {
-    extern __shared__ int padded[];  // [num_experts + 1]
+    __shared__ int warp_sums[33];
     int e = threadIdx.x;
     int total = 0;
     if (e < num_experts) {
@@ -645,27 +646,18 @@ __global__ void k_align_scan(int num_experts, int n_chunks, int block_size, int*
                 total += h[u];
             }
         }
-        padded[e] = (total + block_size - 1) / block_size * block_size;
         expert_counts[e] = total;
     }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int run = 0;
-        for (int i = 0; i < num_experts; ++i) {
-            int p = padded[i];
-            padded[i] = run;
-            run += p;
-        }
-        padded[num_experts] = run;
-        *num_tokens_post_pad = run;
-    }
-    __syncthreads();
+    const int padded = e < num_experts ? (total + block_size - 1) / block_size * block_size : 0;
+    int all = 0;
+    const int start = block_exclusive_scan(padded, warp_sums, &all);
     if (e < num_experts) {
-        int start = padded[e], end = padded[e + 1];
         expert_offsets[e] = start;
-        if (e == 0) expert_offsets[num_experts] = padded[num_experts];
-        for (int b = start / block_size; b < end / block_size; ++b) expert_ids[b] = e;
-        for (int c = 0; c < n_chunks; ++c) chunk_hist[(size_t)c * num_experts + e] += start;
+        if (e == 0) {
+            expert_offsets[num_experts] = all;
+            *num_tokens_post_pad = all;
+        }
+        for (int b = start / block_size; b < (start + padded) / block_size; ++b) expert_ids[b] = e;
     }
 }
 
@@ -673,13 +665,15 @@ __global__ void __launch_bounds__(32) k_align_scatter(const int* __restrict__ to
                                                       const int* __restrict__ valid_tokens, int top_k,
                                                       int num_experts, int chunk,
                                                       const int* __restrict__ chunk_hist,
+                                                      const int* __restrict__ expert_offsets,
                                                       int* __restrict__ sorted_token_ids) {
     extern __shared__ int cursor[];
     int c = blockIdx.x, lane = threadIdx.x;
     int numel = *valid_tokens * top_k;
     int begin = c * chunk;
     if (begin >= numel) return;
-    for (int e = lane; e < num_experts; e += 32) cursor[e] = chunk_hist[(size_t)c * num_experts + e];
+    for (int e = lane; e < num_experts; e += 32)
+        cursor[e] = expert_offsets[e] + chunk_hist[(size_t)c * num_experts + e];
     __syncwarp();
     for (int i0 = begin; i0 < begin + chunk && i0 < numel; i0 += 32) {
         int i = i0 + lane;

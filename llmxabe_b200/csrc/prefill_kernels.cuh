@@ -331,24 +331,16 @@ __device__ __forceinline__ bool stream_wait_pf(uint64_t* bar, uint32_t parity, v
 __global__ void k_build_prefill_items(int num_experts, const int* __restrict__ expert_offsets,
                                       const int* __restrict__ expert_counts, int* __restrict__ items,
                                       int* __restrict__ n_items, int item_cols) {
-    extern __shared__ int base_s[];
+    __shared__ int warp_sums[33];
     int e = threadIdx.x;
-    if (e < num_experts) base_s[e] = (expert_counts[e] + item_cols - 1) / item_cols;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int run = 0;
-        for (int i = 0; i < num_experts; ++i) {
-            int g = base_s[i];
-            base_s[i] = run;
-            run += g;
-        }
-        *n_items = run;
-    }
-    __syncthreads();
+    const int mine = e < num_experts ? (expert_counts[e] + item_cols - 1) / item_cols : 0;
+    int total = 0;
+    const int base = block_exclusive_scan(mine, warp_sums, &total);
+    if (e == 0) *n_items = total;
     if (e < num_experts) {
         int count = expert_counts[e], start = expert_offsets[e];
         for (int i = 0; i * item_cols < count; ++i) {
-            int* it = items + (size_t)(base_s[e] + i) * kPfItemInts;
+            int* it = items + (size_t)(base + i) * kPfItemInts;
             it[0] = e;
             it[1] = start + i * item_cols;
             it[2] = min(item_cols, count - i * item_cols);

@@ -989,13 +989,14 @@ int launch_route_and_dispatch(xabe_moe* m, cudaStream_t st, const float* logits)
                                                       m->sorted_token_ids, m->expert_ids);
     CUDA_TRY(cudaGetLastError());
     int threads = ((int)g.num_experts + 31) / 32 * 32;
-    k_align_scan<<<1, threads, hist_bytes, counted(st)>>>((int)g.num_experts, m->n_chunks, (int)g.block_size,
+    k_align_scan<<<1, threads, 0, counted(st)>>>((int)g.num_experts, m->n_chunks, (int)g.block_size,
                                                  m->chunk_hist, m->expert_offsets, m->expert_counts,
                                                  m->expert_ids, m->num_tokens_post_pad);
     CUDA_TRY(cudaGetLastError());
     k_align_scatter<<<m->n_chunks, 32, hist_bytes, counted(st)>>>(m->topk_ids, m->valid_tokens,
                                                         (int)g.experts_per_token, (int)g.num_experts,
-                                                        m->align_chunk, m->chunk_hist, m->sorted_token_ids);
+                                                        m->align_chunk, m->chunk_hist, m->expert_offsets,
+                                                        m->sorted_token_ids);
     CUDA_TRY(cudaGetLastError());
     // Only the work list of the kernels that will run: the regime must be chosen before this call.
     if (prefill_applies(m, (int)g.intermediate, (int)g.hidden, (int)g.hidden, (int)g.intermediate)) {
