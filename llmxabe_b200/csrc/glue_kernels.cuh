@@ -1189,6 +1189,18 @@ __global__ void k_rows_bf16_to_f32(const unsigned short* __restrict__ x, float* 
     int row = blockIdx.x;
     if (row >= *valid_tokens) return;
     size_t base = (size_t)row * width;
+    if ((width & 7) == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0) {  // eight elements per thread and pass
+        const uint4* src = (const uint4*)(x + base);
+        float4* dst = (float4*)(out + base);
+        for (int u = threadIdx.x; u < width / 8; u += blockDim.x) {
+            const uint4 v = __ldg(src + u);
+            dst[2 * u] = make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xFFFF0000u),
+                                     __uint_as_float(v.y << 16), __uint_as_float(v.y & 0xFFFF0000u));
+            dst[2 * u + 1] = make_float4(__uint_as_float(v.z << 16), __uint_as_float(v.z & 0xFFFF0000u),
+                                         __uint_as_float(v.w << 16), __uint_as_float(v.w & 0xFFFF0000u));
+        }
+        return;
+    }
     for (int j = threadIdx.x; j < width; j += blockDim.x)
         out[base + j] = __uint_as_float((unsigned)x[base + j] << 16);
 }
