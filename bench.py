@@ -851,7 +851,8 @@ def run_ep(args, init_dist: bool = True) -> dict:
         layers.append((front, local))
     if args.ep_peer_memory:
         from llmxabe_b200.ep import PeerMemoryEpBackend
-        backend = PeerMemoryEpBackend(g, epr, rank, world, layers[0][0], *layers[0][1])
+        backend = PeerMemoryEpBackend(g, epr, rank, world, layers[0][0], *layers[0][1],
+                                      fused_return=not args.ep_separate_return)
     else:
         backend = CudaEpBackend(g, epr, max_rows, layers[0][0], *layers[0][1])
     for key, value in args.tune:
@@ -1090,6 +1091,9 @@ def main():
     ap.add_argument("--stack-layers", type=int, default=40, help="layers of the decode64_stack workload")
     ap.add_argument("--ep-tokens", type=int, default=16384)
     ap.add_argument("--ep-layers", type=int, default=40)
+    ap.add_argument("--ep-separate-return", action="store_true",
+                    help="peer-memory exchange with the result rows pushed by a kernel of their own after the "
+                         "down projection instead of by its epilogue (for comparison)")
     ap.add_argument("--ep-nccl", dest="ep_peer_memory", action="store_false",
                     help="exchange rows and results with NCCL all-to-alls instead of peer stores over NVLink")
     ap.add_argument("--ep-no-overlap", dest="ep_overlap", action="store_false",
