@@ -71,8 +71,12 @@ __global__ void __launch_bounds__(1024) k_rms_norm_stream(const float* __restric
                                                           const int* __restrict__ valid_tokens, int width, float eps) {
     pdl_launch_dependents();
     pdl_wait();
-    __shared__ float scratch[32];
+    // block_reduce_sum_pinned's sums on a scratch that alternates by row: a row's total is read before
+    // the next row's first barrier and its copy is rewritten only after that row's second, so the third
+    // barrier of the one-row form is not needed
+    __shared__ float scratch[2][33];
     const int rows = *valid_tokens;
+    int parity = 0;
     float wv[EPT], v[EPT], vn[EPT];
 #pragma unroll
     for (int i = 0; i < EPT; ++i) {
@@ -103,7 +107,19 @@ __global__ void __launch_bounds__(1024) k_rms_norm_stream(const float* __restric
 #pragma unroll
         for (int i = 0; i < EPT; ++i)
             if (threadIdx.x + i * blockDim.x < width) partial = fmaf(v[i], v[i], partial);
-        const float sum_sq = block_reduce_sum_pinned(partial, scratch);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) partial += __shfl_down_sync(0xffffffffu, partial, off);
+        if ((threadIdx.x & 31) == 0) scratch[parity][threadIdx.x >> 5] = partial;
+        __syncthreads();
+        if (threadIdx.x == 0) {  // the warp totals in ascending order, by one thread
+            const int n_warps = (blockDim.x + 31) >> 5;
+            float total = 0.0f;
+            for (int w = 0; w < n_warps; ++w) total += scratch[parity][w];
+            scratch[parity][32] = total;
+        }
+        __syncthreads();
+        const float sum_sq = scratch[parity][32];
+        parity ^= 1;
         const float inv_rms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum_sq, (float)width), eps)));
         const size_t base = (size_t)row * width;
 #pragma unroll
