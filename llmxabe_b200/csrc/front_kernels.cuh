@@ -23,7 +23,6 @@
 namespace xabe {
 
 constexpr int kFrontThreads = 128;
-constexpr int kTinyPairs = 128;  // flat pairs dispatch_tiny_warp holds: handles of up to 16 tokens at top-8
 
 struct FrontLaunch {
     const float* x;        // residual [max_tokens][hidden]
@@ -59,101 +58,6 @@ struct FrontLaunch {
 // CTAs of the widest tile still share an SM)
 __host__ __device__ inline size_t front_smem(int hidden, int tt) {
     return (size_t)(4 + tt + 1) * hidden * sizeof(float);
-}
-
-// The dispatch tables and column groups for at most 128 flat (token, k) pairs, by ONE warp (lane i
-// holds pairs i, i + 32, i + 64, i + 96): no block barrier on the way.  Same tables as dispatch_small_body.  The
-// caller has filled sorted_token_ids with the sentinel and expert_ids with -1, zeroed cnt_s, and
-// synchronised the block.  cnt_s / start_s / gbase_s: shared scratch of num_experts ints each.
-__device__ __forceinline__ void dispatch_tiny_warp(
-    int lane, int numel, int num_experts, int block_size, int* cnt_s, int* start_s, int* gbase_s,
-    const int* __restrict__ topk_ids, const float* __restrict__ topk_weights, int* __restrict__ sorted_token_ids,
-    int* __restrict__ expert_ids, int* __restrict__ num_tokens_post_pad, int* __restrict__ expert_offsets,
-    int* __restrict__ expert_counts, int* __restrict__ work_items, int* __restrict__ n_work) {
-    const unsigned lt = (1u << lane) - 1u;
-    constexpr int NB = kTinyPairs / 32;
-    int e[NB], rank[NB];
-    float wt[NB];
-#pragma unroll
-    for (int b = 0; b < NB; ++b) {
-        const int i = lane + 32 * b;
-        e[b] = i < numel ? __ldcg(topk_ids + i) : -1;
-        wt[b] = i < numel ? __ldcg(topk_weights + i) : 0.0f;
-        rank[b] = 0;
-    }
-#pragma unroll
-    for (int b = 0; b < NB; ++b) {  // pairs in ascending flat order: batch 0 first, lanes ascending inside a batch
-        if (32 * b >= numel) break;  // uniform over the warp
-        const bool on = e[b] >= 0;  // a negative id marks a row that holds nothing
-        const int base = on ? cnt_s[e[b]] : 0;
-        const unsigned active = __ballot_sync(0xffffffffu, on);
-        unsigned same = 0u;
-        if (on) {
-            same = __match_any_sync(active, e[b]);
-            rank[b] = base + __popc(same & lt);
-        }
-        __syncwarp();
-        if (on && (same & lt) == 0u) cnt_s[e[b]] = base + __popc(same);
-        __syncwarp();
-    }
-    // padded offsets, live counts and column-group bases: each lane owns a contiguous run of experts
-    const int per = (num_experts + 31) / 32;
-    const int lo = lane * per, hi = min(num_experts, lo + per);
-    int sum_pad = 0, sum_grp = 0;
-    for (int x = lo; x < hi; ++x) {
-        const int c = cnt_s[x];
-        sum_pad += (c + block_size - 1) / block_size * block_size;
-        sum_grp += (c + 7) >> 3;
-    }
-    int incl_pad = sum_pad, incl_grp = sum_grp;
-#pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-        const int a = __shfl_up_sync(0xffffffffu, incl_pad, off);
-        const int g = __shfl_up_sync(0xffffffffu, incl_grp, off);
-        if (lane >= off) {
-            incl_pad += a;
-            incl_grp += g;
-        }
-    }
-    int run_pad = incl_pad - sum_pad, run_grp = incl_grp - sum_grp;
-    for (int x = lo; x < hi; ++x) {
-        const int c = cnt_s[x];
-        const int pad = (c + block_size - 1) / block_size * block_size;
-        start_s[x] = run_pad;
-        gbase_s[x] = run_grp;
-        expert_offsets[x] = run_pad;
-        expert_counts[x] = c;
-        for (int blk = run_pad / block_size; blk < (run_pad + pad) / block_size; ++blk) expert_ids[blk] = x;
-        run_pad += pad;
-        run_grp += (c + 7) >> 3;
-    }
-    if (lane == 31) {
-        expert_offsets[num_experts] = incl_pad;
-        *num_tokens_post_pad = incl_pad;
-        *n_work = incl_grp;
-    }
-    __syncwarp();
-#pragma unroll
-    for (int b = 0; b < NB; ++b) {
-        if (e[b] < 0) continue;
-        const int flat = lane + 32 * b;
-        const int first = start_s[e[b]], gi = rank[b] >> 3, c = rank[b] & 7;
-        sorted_token_ids[first + rank[b]] = flat;
-        int* it = work_items + (size_t)(gbase_s[e[b]] + gi) * kWorkItemInts;
-        it[4 + c] = flat;
-        it[12 + c] = __float_as_int(wt[b]);
-        if (c == 0) {  // the group's first column also writes its header and clears the unused columns
-            const int ncols = min(8, cnt_s[e[b]] - 8 * gi);
-            it[0] = e[b];
-            it[1] = first + 8 * gi;
-            it[2] = ncols;
-            it[3] = 0;
-            for (int c2 = ncols; c2 < 8; ++c2) {
-                it[4 + c2] = 0;
-                it[12 + c2] = 0;
-            }
-        }
-    }
 }
 
 template <int TT>
